@@ -1,0 +1,88 @@
+"""Host-side work list for the paged attention kernels.
+
+One step's queries are cut into tiles of whole tokens (a tile holds the ``group`` query
+heads of one KV head for ``tokens_per_tile`` consecutive tokens of one segment).  A tile
+whose visible key range is long and that would leave SMs idle is split along the keys;
+each split writes a partial result (running max, sum, unnormalised output) that a merge
+kernel combines in split order.  The reference fixes 8 splits for decode
+(python/freetoken/attention/triton.py:90, python/freetoken/kernel/triton/attention.py:352-466)
+and never splits prefill; here the count follows the work so that a single long request
+still fills the GPU.
+
+A work item is 8 int32: segment, first token of the tile (within the segment), tokens in
+the tile, first key, one past the last key, number of splits of the tile, index of this
+split, and the tile's first partial slot.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+
+ITEM_INTS = 8
+SPLIT_QUANTUM = 64  # split boundaries are multiples of this many keys
+
+
+@dataclass
+class AttentionPlan:
+    items: np.ndarray  # [W, 8] int32
+    n_items: int
+    n_slots: int  # partial slots used (0 when nothing is split)
+    tokens_per_tile: int
+    max_splits: int
+
+
+def tokens_per_tile(tile_rows: int, group: int) -> int:
+    return max(1, tile_rows // group)
+
+
+def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
+               window: Optional[int], n_kv_heads: int, sm_count: int = 148,
+               max_splits: int = 32, min_split_keys: int = 256,
+               fixed_splits: Optional[int] = None) -> AttentionPlan:
+    """``segments`` holds (q_len, kv_len) per segment, in step order.
+
+    ``fixed_splits`` forces every tile to be planned with exactly that many item rows
+    (unused ones get an empty key range); CUDA-graph replay uses it so that the item
+    count of a step never changes."""
+    tpt = tokens_per_tile(tile_rows, group)
+    tiles: List[Tuple[int, int, int, int, int]] = []  # seg, tok0, ntok, lo, hi
+    for s, (q_len, kv_len) in enumerate(segments):
+        pos0 = kv_len - q_len
+        for tok0 in range(0, q_len, tpt):
+            ntok = min(tpt, q_len - tok0)
+            hi = pos0 + tok0 + ntok  # last query's position + 1
+            lo = 0
+            if window is not None:
+                lo = max(0, pos0 + tok0 - window + 1)
+            tiles.append((s, tok0, ntok, lo, hi))
+    n_tiles = len(tiles)
+    target = 2 * sm_count
+    rows: List[List[int]] = []
+    n_slots = 0
+    for (s, tok0, ntok, lo, hi) in tiles:
+        span = hi - lo
+        if fixed_splits is not None:
+            want = fixed_splits
+        elif n_tiles * n_kv_heads >= target:
+            want = 1
+        else:
+            want = min(max_splits, -(-target // max(1, n_tiles * n_kv_heads)),
+                       max(1, span // min_split_keys))
+        quanta = -(-span // SPLIT_QUANTUM)
+        n_real = max(1, min(want, quanta))
+        per = -(-quanta // n_real) * SPLIT_QUANTUM
+        n_real = max(1, -(-span // per)) if span > 0 else 1
+        n_rows = fixed_splits if fixed_splits is not None else n_real
+        base = n_slots if n_rows > 1 else 0
+        for i in range(n_rows):
+            b = min(hi, lo + i * per)
+            e = min(hi, lo + (i + 1) * per)
+            rows.append([s, tok0, ntok, b, e, n_rows, i, base])
+        if n_rows > 1:
+            n_slots += n_rows
+    items = np.asarray(rows, dtype=np.int32).reshape(-1, ITEM_INTS)
+    return AttentionPlan(items=items, n_items=items.shape[0], n_slots=n_slots,
+                         tokens_per_tile=tpt, max_splits=max_splits)

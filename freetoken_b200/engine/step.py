@@ -1,0 +1,130 @@
+"""Packing one step's metadata into a single host-to-device copy.
+
+Everything the kernels need to know about a step is int32: token ids, positions, cache
+slots of the new tokens per paged group, per-segment (q_start, q_len, kv_len, block-table
+row), state slots, the rows whose logits are wanted, block-table changes, and the attention
+work lists.  The sections are laid out back to back (16-byte aligned) in one pinned host
+buffer and copied once; kernels read them through views of the device buffer.  The
+reference stages the same quantities as several pinned tensors
+(python/freetoken/scheduler/scheduler.py:874-905, python/freetoken/attention/triton.py:229-240).
+
+A step whose layout is *fixed* (decode-only steps replayed from a CUDA graph) pads its
+variable sections to a size that depends only on the batch size, so that every replay
+finds each section at the same address.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .attention_plan import AttentionPlan, build_plan
+
+ALIGN = 4  # int32 elements = 16 bytes
+
+
+@dataclass
+class DevicePlan:
+    """An attention work list on the device, with its scratch for split tiles."""
+
+    items_dev: torch.Tensor
+    n_items: int
+    part_o: Optional[torch.Tensor]
+    part_ml: Optional[torch.Tensor]
+    host: AttentionPlan
+
+
+class StepBuffers:
+    """Pinned staging (double-buffered) and the device copy of the packed metadata."""
+
+    def __init__(self, device: torch.device, capacity_ints: int):
+        self.device = device
+        self.capacity = capacity_ints
+        pin = device.type == "cuda"
+        self.host = [torch.empty(capacity_ints, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+        self.host_np = [h.numpy() for h in self.host]
+        self.dev = torch.zeros(capacity_ints, dtype=torch.int32, device=device)
+        self.events: List[Optional[Any]] = [None, None]
+        self.turn = 0
+
+    def grow(self, need: int) -> None:
+        if need <= self.capacity:
+            return
+        raise RuntimeError(
+            f"step metadata needs {need} int32, the buffer holds {self.capacity}; "
+            f"raise max_step_tokens / max_running_req")
+
+    def upload(self, sections: List[Tuple[str, np.ndarray]]) -> Dict[str, torch.Tensor]:
+        offsets = []
+        n = 0
+        for _, arr in sections:
+            offsets.append(n)
+            n += -(-max(arr.size, 1) // ALIGN) * ALIGN
+        self.grow(n)
+        i = self.turn
+        self.turn ^= 1
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        buf = self.host_np[i]
+        for (name, arr), off in zip(sections, offsets):
+            buf[off:off + arr.size] = arr.reshape(-1)
+        if n:
+            self.dev[:n].copy_(self.host[i][:n], non_blocking=True)
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record()
+            self.events[i] = ev
+        out = {}
+        for (name, arr), off in zip(sections, offsets):
+            out[name] = self.dev[off:off + arr.size].view(arr.shape)
+        return out
+
+
+class StepBuilder:
+    """Collects the sections of one step; mixers add what their kernels need."""
+
+    def __init__(self, engine, seg_lens: Sequence[Tuple[int, int]], fixed: bool, sm_count: int):
+        self.engine = engine
+        self.seg_lens = list(seg_lens)  # (q_len, kv_len) per segment
+        self.fixed = fixed
+        self.sm_count = sm_count
+        self.sections: List[Tuple[str, np.ndarray]] = []
+        self.plans: Dict[Any, AttentionPlan] = {}
+        self.plan_dims: Dict[Any, Tuple[int, int, int]] = {}
+
+    def add(self, name: str, arr: np.ndarray) -> None:
+        self.sections.append((name, np.ascontiguousarray(arr, dtype=np.int32)))
+
+    def fixed_splits(self, n_kv_heads: int) -> int:
+        """Splits per tile of a graph-replayed decode step: enough CTAs to fill the GPU at
+        this batch size, independent of the requests' lengths."""
+        b = max(1, len(self.seg_lens))
+        return int(min(16, max(1, -(-2 * self.sm_count // (b * n_kv_heads)))))
+
+    def attention_plan(self, group: int, tile_rows: int, window: Optional[int], n_kv_heads: int,
+                       head_dim: int) -> Any:
+        key = ("attention", group, tile_rows, window, n_kv_heads, head_dim)
+        if key not in self.plans:
+            plan = build_plan(self.seg_lens, group, tile_rows, window, n_kv_heads,
+                              sm_count=self.sm_count,
+                              fixed_splits=self.fixed_splits(n_kv_heads) if self.fixed else None)
+            self.plans[key] = plan
+            self.plan_dims[key] = (n_kv_heads, tile_rows, head_dim)
+            self.add(f"plan.{len(self.plans) - 1}", plan.items)
+        return key
+
+    def finish(self, buffers: StepBuffers, workspace) -> Tuple[Dict[str, torch.Tensor], Dict[Any, DevicePlan]]:
+        tensors = buffers.upload(self.sections)
+        plans: Dict[Any, DevicePlan] = {}
+        for i, (key, plan) in enumerate(self.plans.items()):
+            n_kv, rows, dim = self.plan_dims[key]
+            part_o = part_ml = None
+            if plan.n_slots:
+                tag = f"attn.part.{i}.fixed{len(self.seg_lens)}" if self.fixed else f"attn.part.{i}"
+                part_o = workspace.get(tag + ".o", (plan.n_slots, n_kv, rows, dim), torch.float32)
+                part_ml = workspace.get(tag + ".ml", (plan.n_slots, n_kv, rows, 2), torch.float32)
+            plans[key] = DevicePlan(tensors[f"plan.{i}"], plan.n_items, part_o, part_ml, plan)
+        return tensors, plans

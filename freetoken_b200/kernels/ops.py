@@ -1,0 +1,397 @@
+"""Python face of the CUDA kernels: argument checks, then one C call per op.
+
+Every function takes device tensors, writes into caller-provided outputs, launches on the
+current CUDA stream and allocates nothing.  A tensor that is not on a CUDA device, has the
+wrong dtype or is not contiguous raises :class:`KernelError` before anything is launched;
+the native side checks sizes again and reports through ``ftk_last_error``.
+
+Kernel inventory (reference kernel each one stands for):
+
+=====================  ==========================================================
+embedding_gather       python/freetoken/kernel/csrc/jit/index.cu:31-59
+add_rmsnorm            python/freetoken/kernel/triton/norm.py:42-112
+norm_rope_store        norm.py:42-75 + python/freetoken/kernel/triton/rope.py:28-91 +
+                       python/freetoken/kernel/csrc/jit/store.cu:27-53, in one pass
+paged_attention        python/freetoken/kernel/triton/attention.py:147-466,469-880
+router_topk            python/freetoken/models/minimax_m3/moe.py:71-81
+moe_permute            python/freetoken/kernel/triton/fused_moe.py:5-108
+moe_gemm1_act          fused_moe.py:156-302 + python/freetoken/kernel/triton/activation.py:67-112
+moe_gemm2              fused_moe.py:156-302 (route weight on the accumulator, :292-296)
+moe_combine            fused_moe.py:111-153
+act_and_mul            activation.py:67-112
+sample                 python/freetoken/engine/sample.py:24-80, python/freetoken/kernel/triton/sampling.py
+=====================  ==========================================================
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence
+
+import torch
+
+from ..errors import KernelError
+from . import library
+
+F32, BF16 = 0, 1
+ACT_SILU, ACT_SWIGLUOAI = 0, 1
+SCORE_SIGMOID, SCORE_SOFTMAX = 0, 1
+ACT_CODES = {"silu": ACT_SILU, "swigluoai": ACT_SWIGLUOAI}
+SCORE_CODES = {"sigmoid": SCORE_SIGMOID, "softmax": SCORE_SOFTMAX}
+
+_vp = ctypes.c_void_p
+_i = ctypes.c_int
+_f = ctypes.c_float
+
+
+class _Section(ctypes.Structure):
+    _fields_ = [
+        ("first_head", _i), ("n_heads", _i), ("norm_weight", _vp), ("rotate", _i),
+        ("dense_out", _vp), ("slab", _vp), ("slot_map", _vp), ("page_size", _i), ("num_pages", _i),
+    ]
+
+
+_SIGNATURES = {
+    "ftk_embedding_gather": [_vp, _i, _vp, _i, _i, _i, _vp, _vp],
+    "ftk_add_rmsnorm": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _f, _i, _vp],
+    "ftk_norm_rope_store": [_vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _f, _i, _i,
+                            ctypes.POINTER(_Section), _vp],
+    "ftk_paged_attention": [_vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
+                            _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "ftk_router_topk": [_vp, _vp, _i, _i, _i, _i, _f, _vp, _vp, _vp],
+    "ftk_moe_permute": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp],
+    "ftk_moe_gather": [_vp, _i, _vp, _i, _i, _i, _vp, _vp],
+    "ftk_moe_gemm1_act": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _f, _f, _vp, _vp],
+    "ftk_moe_gemm2": [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
+    "ftk_moe_combine": [_vp, _i, _vp, _i, _i, _i, _vp, _vp, _vp],
+    "ftk_act_and_mul": [_vp, _i, _i, _i, _i, _f, _f, _vp, _vp],
+    "ftk_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
+    "ftk_cast": [_vp, _i, _vp, _i, ctypes.c_longlong, _vp],
+    "ftk_table_update": [_vp, ctypes.c_longlong, _vp, _i, _vp],
+}
+_bound = False
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels launched through this module so far (graph replays add their recorded count)."""
+    return _launches
+
+
+def count_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
+def _lib():
+    global _bound
+    lib = library.load()
+    if not _bound:
+        for name, args in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = _i
+        _bound = True
+    return lib
+
+
+def _check(status: int, name: str, launches: int = 1) -> None:
+    global _launches
+    _launches += launches
+    if status != 0:
+        msg = library.load().ftk_last_error()
+        raise KernelError(f"{name}: {msg.decode() if msg else 'error ' + str(status)}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _code(t: torch.Tensor, what: str) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"{what}: dtype {t.dtype} is not supported (float32 or bfloat16)")
+
+
+def _dev(t: Optional[torch.Tensor], what: str, dtype: Optional[torch.dtype] = None) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError(f"{what}: tensor is on '{t.device}', the kernels run on a CUDA device only")
+    if not t.is_contiguous():
+        raise KernelError(f"{what}: tensor must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{what}: expected {dtype}, got {t.dtype}")
+    return t.data_ptr()
+
+
+# --------------------------------------------------------------------------- elementwise
+def embedding_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[t, :] = float32(table[ids[t], :])``; ``out`` is the 32-bit residual stream."""
+    V, H = table.shape
+    T = ids.shape[0]
+    if out.shape != (T, H):
+        raise KernelError(f"embedding_gather: out shape {tuple(out.shape)} != {(T, H)}")
+    _check(_lib().ftk_embedding_gather(_dev(table, "table"), _code(table, "table"),
+                                       _dev(ids, "ids", torch.int32), T, H, V,
+                                       _dev(out, "out", torch.float32), _stream()),
+           "embedding_gather")
+
+
+def add_rmsnorm(x: Optional[torch.Tensor], residual: Optional[torch.Tensor], weight: torch.Tensor,
+                eps: float, gemma: bool, out: torch.Tensor, out_f32: Optional[torch.Tensor] = None,
+                rows: Optional[torch.Tensor] = None) -> None:
+    """RMSNorm with the residual sum fused in.
+
+    ``z = x + residual`` in 32-bit (either may be None); without ``rows`` the sum is stored
+    back to ``residual``; ``out = z * rsqrt(mean(z^2) + eps) * (1 + w)`` (``w`` when not
+    ``gemma``).  With ``rows`` only those rows are read and ``out[i]`` belongs to
+    ``rows[i]``; the residual stays as it is.  ``out_f32`` receives ``float32(out)``.
+    """
+    src = x if x is not None else residual
+    if src is None:
+        raise KernelError("add_rmsnorm: x and residual are both None")
+    H = src.shape[-1]
+    n_rows = rows.shape[0] if rows is not None else src.numel() // H
+    if weight.shape != (H,):
+        raise KernelError(f"add_rmsnorm: weight shape {tuple(weight.shape)} != {(H,)}")
+    if out.numel() != n_rows * H:
+        raise KernelError(f"add_rmsnorm: out has {out.numel()} elements, expected {n_rows * H}")
+    if out_f32 is not None and out_f32.numel() != n_rows * H:
+        raise KernelError("add_rmsnorm: out_f32 has the wrong size")
+    _check(_lib().ftk_add_rmsnorm(_dev(x, "x"), _code(x, "x") if x is not None else F32,
+                                  _dev(residual, "residual", torch.float32),
+                                  _dev(weight, "weight", torch.float32),
+                                  _dev(out, "out"), _code(out, "out"),
+                                  _dev(out_f32, "out_f32", torch.float32),
+                                  _dev(rows, "rows", torch.int32), n_rows, H, float(eps),
+                                  1 if gemma else 0, _stream()), "add_rmsnorm")
+
+
+def act_and_mul(gate_up: torch.Tensor, out: torch.Tensor, act: str, alpha: float, limit: float) -> None:
+    """``out = act(gate_up[:, :I], gate_up[:, I:])`` with ``act`` silu or swigluoai."""
+    n, two_i = gate_up.shape
+    if two_i % 2 or out.shape != (n, two_i // 2) or out.dtype != gate_up.dtype:
+        raise KernelError("act_and_mul: out must be [rows, I] of the input's dtype")
+    _check(_lib().ftk_act_and_mul(_dev(gate_up, "gate_up"), _code(gate_up, "gate_up"), n, two_i // 2,
+                                  ACT_CODES[act], float(alpha), float(limit), _dev(out, "out"),
+                                  _stream()), "act_and_mul")
+
+
+def table_update(table: torch.Tensor, updates: torch.Tensor, n_updates: int) -> None:
+    """``table.flat[updates[i, 0]] = updates[i, 1]`` for ``i < n_updates``; negative indices are skipped."""
+    if updates.numel() < 2 * n_updates:
+        raise KernelError("table_update: updates shorter than n_updates")
+    _check(_lib().ftk_table_update(_dev(table, "table", torch.int32), table.numel(),
+                                   _dev(updates, "updates", torch.int32), n_updates, _stream()),
+           "table_update")
+
+
+def cast(src: torch.Tensor, dst: torch.Tensor) -> None:
+    """``dst = src`` converted between float32 and bfloat16 (round to nearest even)."""
+    if src.numel() != dst.numel():
+        raise KernelError("cast: sizes differ")
+    _check(_lib().ftk_cast(_dev(src, "src"), _code(src, "src"), _dev(dst, "dst"), _code(dst, "dst"),
+                           src.numel(), _stream()), "cast")
+
+
+# --------------------------------------------------------------------------- attention
+def norm_rope_store(x: torch.Tensor, head_dim: int, rotary_dim: int, positions: torch.Tensor,
+                    rope_table: Optional[torch.Tensor], eps: float, gemma: bool,
+                    sections: Sequence[dict]) -> None:
+    """Per-head RMSNorm, partial NeoX rotation and scatter of projected heads, in one pass.
+
+    ``x [T, n_heads_total * head_dim]`` is cut into sections of whole heads.  A section is a
+    dict: ``first_head``, ``n_heads``, ``norm_weight`` (float32 ``[head_dim]`` or None),
+    ``rotate`` (bool), and one destination: ``dense_out [T, n_heads, head_dim]`` or
+    ``slab [pages, n_heads, page_size, head_dim]`` with ``slot_map [T]`` (slot = page *
+    page_size + offset, negative = skip).  ``rope_table [max_pos, rotary_dim]`` holds
+    cos then sin of ``position * inv_freq`` in float32.
+    """
+    T = x.shape[0]
+    n_total = x.shape[1] // head_dim
+    arr = (_Section * len(sections))()
+    keep = []
+    for i, s in enumerate(sections):
+        if s["first_head"] + s["n_heads"] > n_total:
+            raise KernelError("norm_rope_store: section exceeds the heads of x")
+        arr[i].first_head = s["first_head"]
+        arr[i].n_heads = s["n_heads"]
+        arr[i].norm_weight = _dev(s.get("norm_weight"), "norm_weight", torch.float32)
+        arr[i].rotate = 1 if s.get("rotate") else 0
+        dense, slab = s.get("dense_out"), s.get("slab")
+        if (dense is None) == (slab is None):
+            raise KernelError("norm_rope_store: a section needs exactly one of dense_out and slab")
+        if dense is not None:
+            if dense.dtype != x.dtype or dense.numel() != T * s["n_heads"] * head_dim:
+                raise KernelError("norm_rope_store: dense_out has the wrong dtype or size")
+            arr[i].dense_out = _dev(dense, "dense_out")
+        else:
+            if slab.dtype != x.dtype or slab.dim() != 4 or slab.shape[1] != s["n_heads"] \
+                    or slab.shape[3] != head_dim:
+                raise KernelError("norm_rope_store: slab must be [pages, n_heads, page_size, head_dim]")
+            arr[i].slab = _dev(slab, "slab")
+            arr[i].slot_map = _dev(s["slot_map"], "slot_map", torch.int32)
+            if s["slot_map"].shape[0] < T:
+                raise KernelError("norm_rope_store: slot_map shorter than the tokens")
+            arr[i].num_pages = slab.shape[0]
+            arr[i].page_size = slab.shape[2]
+        keep.append(s)
+    if rotary_dim:
+        if rope_table is None or rope_table.shape[1] != rotary_dim:
+            raise KernelError("norm_rope_store: rope_table must be [max_pos, rotary_dim]")
+    max_pos = rope_table.shape[0] if rope_table is not None else 0
+    _check(_lib().ftk_norm_rope_store(_dev(x, "x"), _code(x, "x"), T, x.shape[1], head_dim, rotary_dim,
+                                      _dev(positions, "positions", torch.int32),
+                                      _dev(rope_table, "rope_table", torch.float32), max_pos,
+                                      float(eps), 1 if gemma else 0, len(sections), arr, _stream()),
+           "norm_rope_store")
+
+
+def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
+                    block_table: torch.Tensor, seg_info: torch.Tensor, n_segs: int,
+                    items: torch.Tensor, n_items: int, part_o: Optional[torch.Tensor],
+                    part_ml: Optional[torch.Tensor], out: torch.Tensor, tile_rows: int, scale: float,
+                    window: Optional[int]) -> None:
+    """Causal softmax attention of the step's queries over the paged keys and values.
+
+    ``q, out [T, Hq, D]``; slabs ``[pages, Hkv, page_size, D]``; ``block_table [rows, width]``
+    page ids; ``seg_info [S, 4]`` = q_start, q_len, kv_len, block-table row; ``items [W, 8]``
+    from :func:`freetoken_b200.engine.attention_plan.build_plan`; ``part_o [slots, Hkv,
+    tile_rows, D]`` and ``part_ml [slots, Hkv, tile_rows, 2]`` float32 scratch for split
+    tiles.  Query ``t`` of a segment sits at position ``kv_len - q_len + t`` and reads keys at
+    positions ``<=`` its own (and ``>`` its own minus ``window`` when a window is given).
+    """
+    T, Hq, D = q.shape
+    pages, Hkv, P, D2 = k_slab.shape
+    if D2 != D or v_slab.shape != k_slab.shape or Hq % Hkv:
+        raise KernelError("paged_attention: q / slab shapes do not agree")
+    if out.shape != q.shape or out.dtype != q.dtype or k_slab.dtype != q.dtype:
+        raise KernelError("paged_attention: dtypes or out shape do not agree")
+    n_slots = part_o.shape[0] if part_o is not None else 0
+    if part_o is not None and (part_o.shape[1:] != (Hkv, tile_rows, D) or part_ml is None
+                               or part_ml.shape != (n_slots, Hkv, tile_rows, 2)):
+        raise KernelError("paged_attention: scratch shapes do not match tile_rows / heads")
+    _check(_lib().ftk_paged_attention(
+        _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"), _code(q, "q"),
+        _dev(block_table, "block_table", torch.int32), block_table.shape[1],
+        _dev(seg_info, "seg_info", torch.int32), n_segs,
+        _dev(items, "items", torch.int32), n_items,
+        _dev(part_o, "part_o", torch.float32), _dev(part_ml, "part_ml", torch.float32), n_slots,
+        _dev(out, "out"), Hq, Hkv, D, P, pages, tile_rows, float(scale),
+        int(window) if window else 0, _stream()), "paged_attention", 2 if n_slots else 1)
+
+
+# --------------------------------------------------------------------------- experts
+def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, scoring: str,
+                scale: float, ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """Expert choice from float32 router logits ``[T, E]``.
+
+    sigmoid: ``s = sigmoid(l)``; choice by ``s + bias``; ``w = s[ids] / (sum + 1e-20) * scale``.
+    softmax: ``s = softmax(l)``; choice by ``s (+ bias)``; ``w = s[ids] / sum * scale``.
+    The largest goes first; the lower expert index wins a tie.
+    """
+    T, E = logits.shape
+    if ids.shape != (T, top_k) or weights.shape != (T, top_k):
+        raise KernelError("router_topk: ids / weights must be [T, top_k]")
+    if bias is not None and bias.shape != (E,):
+        raise KernelError("router_topk: bias must be [E]")
+    _check(_lib().ftk_router_topk(_dev(logits, "logits", torch.float32), _dev(bias, "bias", torch.float32),
+                                  T, E, top_k, SCORE_CODES[scoring], float(scale),
+                                  _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32),
+                                  _stream()), "router_topk")
+
+
+def moe_permute(topk_ids: torch.Tensor, n_experts: int, expert_offsets: torch.Tensor,
+                sorted_routes: torch.Tensor, route_pos: torch.Tensor) -> None:
+    """Sort the routes ``(t, j)`` by expert, keeping their order within an expert.
+
+    ``expert_offsets [E + 1]``: rows of expert ``e`` are ``[offsets[e], offsets[e+1])``;
+    ``sorted_routes [T*k]``: route index ``t*k + j`` at each sorted row;
+    ``route_pos [T*k]``: sorted row of each route."""
+    T, k = topk_ids.shape
+    if expert_offsets.shape != (n_experts + 1,) or sorted_routes.numel() != T * k \
+            or route_pos.numel() != T * k:
+        raise KernelError("moe_permute: output shapes are wrong")
+    _check(_lib().ftk_moe_permute(_dev(topk_ids, "topk_ids", torch.int32), T, k, n_experts,
+                                  _dev(expert_offsets, "expert_offsets", torch.int32),
+                                  _dev(sorted_routes, "sorted_routes", torch.int32),
+                                  _dev(route_pos, "route_pos", torch.int32), _stream()), "moe_permute", 2)
+
+
+def moe_gather(h: torch.Tensor, sorted_routes: torch.Tensor, top_k: int, out: torch.Tensor) -> None:
+    """``out[r, :] = h[sorted_routes[r] // top_k, :]``."""
+    T, H = h.shape
+    R = sorted_routes.numel()
+    if out.shape != (R, H) or out.dtype != h.dtype:
+        raise KernelError("moe_gather: out must be [routes, hidden] of h's dtype")
+    _check(_lib().ftk_moe_gather(_dev(h, "h"), _code(h, "h"), _dev(sorted_routes, "sorted_routes", torch.int32),
+                                 R, top_k, H, _dev(out, "out"), _stream()), "moe_gather")
+
+
+def moe_gemm1_act(x_sorted: torch.Tensor, w1: torch.Tensor, expert_offsets: torch.Tensor,
+                  act: str, alpha: float, limit: float, out: torch.Tensor) -> None:
+    """``out[r] = act(x[r] W1[e]^T)`` for the rows of each expert; ``w1 [E, 2I, H]`` rows gate then up."""
+    R, H = x_sorted.shape
+    E, two_i, H2 = w1.shape
+    if H2 != H or two_i % 2 or out.shape != (R, two_i // 2) or w1.dtype != x_sorted.dtype \
+            or out.dtype != x_sorted.dtype:
+        raise KernelError("moe_gemm1_act: shapes or dtypes do not agree")
+    _check(_lib().ftk_moe_gemm1_act(_dev(x_sorted, "x_sorted"), _dev(w1, "w1"), _code(w1, "w1"),
+                                    _dev(expert_offsets, "expert_offsets", torch.int32), E, R, H,
+                                    two_i // 2, ACT_CODES[act], float(alpha), float(limit),
+                                    _dev(out, "out"), _stream()), "moe_gemm1_act")
+
+
+def moe_gemm2(a: torch.Tensor, w2: torch.Tensor, expert_offsets: torch.Tensor,
+              sorted_routes: torch.Tensor, topk_weights: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[r] = (a[r] W2[e]^T) * topk_weights[sorted_routes[r]]``; ``w2 [E, H, I]``."""
+    R, I = a.shape
+    E, H, I2 = w2.shape
+    if I2 != I or out.shape != (R, H) or w2.dtype != a.dtype or out.dtype != a.dtype:
+        raise KernelError("moe_gemm2: shapes or dtypes do not agree")
+    if topk_weights.numel() != R or sorted_routes.numel() != R:
+        raise KernelError("moe_gemm2: one weight and one route per row expected")
+    _check(_lib().ftk_moe_gemm2(_dev(a, "a"), _dev(w2, "w2"), _code(w2, "w2"),
+                                _dev(expert_offsets, "expert_offsets", torch.int32),
+                                _dev(sorted_routes, "sorted_routes", torch.int32),
+                                _dev(topk_weights, "topk_weights", torch.float32), E, R, H, I,
+                                _dev(out, "out"), _stream()), "moe_gemm2")
+
+
+def moe_combine(y: torch.Tensor, route_pos: torch.Tensor, n_tokens: int, top_k: int,
+                shared: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """``out[t] = sum_j y[route_pos[t*k + j]]`` in route order, 32-bit sum, ``+ shared[t]``."""
+    R, H = y.shape
+    if R != n_tokens * top_k or out.shape != (n_tokens, H) or out.dtype != y.dtype:
+        raise KernelError("moe_combine: shapes or dtypes do not agree")
+    if shared is not None and (shared.shape != out.shape or shared.dtype != y.dtype):
+        raise KernelError("moe_combine: shared must match out")
+    _check(_lib().ftk_moe_combine(_dev(y, "y"), _code(y, "y"), _dev(route_pos, "route_pos", torch.int32),
+                                  n_tokens, top_k, H, _dev(shared, "shared"), _dev(out, "out"),
+                                  _stream()), "moe_combine")
+
+
+# --------------------------------------------------------------------------- sampling
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           u: torch.Tensor, out: torch.Tensor) -> None:
+    """One token per row of float32 ``logits [R, V]``.
+
+    ``temperature[r] <= 0``: argmax, lowest index on a tie.  Else ``p = softmax(logits / T)``;
+    top-k keeps ``p >=`` the k-th largest value (``top_k <= 0`` keeps all); top-p then keeps
+    ``p >= th`` for the largest ``th`` whose kept mass reaches ``top_p`` of the remaining mass;
+    the token is the first index whose running kept mass exceeds ``u[r]`` times the kept mass.
+    """
+    R, V = logits.shape
+    for name, t, dt in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
+                        ("top_p", top_p, torch.float32), ("u", u, torch.float32),
+                        ("out", out, torch.int32)):
+        if t.numel() < R:
+            raise KernelError(f"sample: {name} has fewer than {R} entries")
+    _check(_lib().ftk_sample(_dev(logits, "logits", torch.float32), R, V,
+                             _dev(temperature, "temperature", torch.float32),
+                             _dev(top_k, "top_k", torch.int32), _dev(top_p, "top_p", torch.float32),
+                             _dev(u, "u", torch.float32), _dev(out, "out", torch.int32), _stream()),
+           "sample")

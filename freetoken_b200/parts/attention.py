@@ -1,0 +1,119 @@
+"""Grouped-query softmax attention over a paged cache.
+
+Order of operations (python/freetoken/models/minimax_m3/attention.py:79-119): fused qkv
+projection (rows q, k, v), per-head RMSNorm of q and k heads with one ``[head_dim]`` weight
+each (:54-56,90-91), partial NeoX rotation of q and k (:92), keys and values of the new
+tokens stored in the cache before it is read (python/freetoken/attention/triton.py:150),
+causal softmax attention with scale ``head_dim^-0.5`` where query head ``h`` reads KV head
+``h // group`` (python/freetoken/kernel/triton/attention.py:74,102,118-137), output
+projection.  Norm, rotation and the page write are one kernel here; the projections are
+library matrix products, as in the reference (python/freetoken/layers/linear.py:31-32).
+"""
+
+from __future__ import annotations
+
+from typing import Any, Dict, Optional
+
+import torch
+
+from ..config.spec import PagedKVNeed, ParamSpec, PartSpec
+from ..errors import ConfigError
+from ..kernels import ops
+from .base import MIXERS, BuildEnv, Mixer, StepState
+from .rope import shared_position
+
+
+def attention_tile_rows(dtype: torch.dtype) -> int:
+    """Query rows (tokens x group heads) one attention CTA handles."""
+    return 64 if dtype == torch.bfloat16 else 16
+
+
+@MIXERS.register("gqa_attention")
+class GQAttention(Mixer):
+    """params: ``hidden``, ``n_heads``, ``n_kv_heads``, ``head_dim``, ``qk_norm`` (bool),
+    ``eps``, ``gemma`` (bool), ``position`` (PartSpec of a position encoding), ``window``
+    (None or tokens), ``scale`` (None = head_dim^-0.5)."""
+
+    graph_safe = True  # running a step twice writes the same keys and values again
+
+    def __init__(self, spec: PartSpec, env: BuildEnv):
+        super().__init__(spec, env)
+        self.hidden = int(spec["hidden"])
+        self.n_heads = int(spec["n_heads"])
+        self.n_kv_heads = int(spec["n_kv_heads"])
+        self.head_dim = int(spec["head_dim"])
+        if self.n_heads % self.n_kv_heads:
+            raise ConfigError("gqa_attention: n_heads must be a multiple of n_kv_heads")
+        if self.head_dim % 16 or not 16 <= self.head_dim <= 256:
+            raise ConfigError(
+                f"gqa_attention: head_dim={self.head_dim} must be a multiple of 16 in [16, 256]")
+        self.group = self.n_heads // self.n_kv_heads
+        self.qk_norm = bool(spec.get("qk_norm", True))
+        self.eps = float(spec.get("eps", 1e-6))
+        self.gemma = bool(spec.get("gemma", True))
+        self.window: Optional[int] = spec.get("window")
+        self.scale = float(spec.get("scale") or self.head_dim ** -0.5)
+        self.position = shared_position(spec.get("position") or PartSpec("none"), env)
+        self.rotary_dim = int(getattr(self.position, "rotary_dim", 0))
+        if self.rotary_dim > self.head_dim:
+            raise ConfigError("gqa_attention: rotary_dim exceeds head_dim")
+        self.tile_rows = attention_tile_rows(env.dtype)
+        if self.group > self.tile_rows:
+            raise ConfigError(
+                f"gqa_attention: {self.group} query heads per KV head exceed the kernel's "
+                f"{self.tile_rows}-row tile")
+        self.q_dim = self.n_heads * self.head_dim
+        self.kv_dim = self.n_kv_heads * self.head_dim
+
+    # ------------------------------------------------------------------ tensors
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        out = {
+            "qkv_proj.weight": ParamSpec((self.q_dim + 2 * self.kv_dim, self.hidden)),
+            "o_proj.weight": ParamSpec((self.hidden, self.q_dim)),
+        }
+        if self.qk_norm:
+            init = ("normal", 0.0, 0.02) if self.gemma else ("normal", 1.0, 0.02)
+            out["q_norm.weight"] = ParamSpec((self.head_dim,), "float32", init, store="bfloat16")
+            out["k_norm.weight"] = ParamSpec((self.head_dim,), "float32", init, store="bfloat16")
+        return out
+
+    def cache_need(self):
+        return PagedKVNeed((("k", self.n_kv_heads, self.head_dim),
+                            ("v", self.n_kv_heads, self.head_dim)), self.window)
+
+    # ------------------------------------------------------------------ step
+    def plan_key(self):
+        return ("attention", self.group, self.tile_rows, self.window, self.n_kv_heads, self.head_dim)
+
+    def prepare(self, builder) -> None:
+        """Ask the step for the work list this mixer's attention kernel runs from."""
+        builder.attention_plan(self.group, self.tile_rows, self.window, self.n_kv_heads, self.head_dim)
+
+    def forward(self, h: torch.Tensor, step: StepState, cache: Any, writes_cache: bool) -> torch.Tensor:
+        T = h.shape[0]
+        ws, dt = self.env.workspace, self.env.dtype
+        cap = self.env.max_step_tokens
+        n_proj = self.q_dim + (2 * self.kv_dim if writes_cache else 0)
+        qkv = ws.get("attn.qkv", (T, n_proj), dt, (cap, self.q_dim + 2 * self.kv_dim))
+        w = self.params["qkv_proj.weight"]
+        torch.matmul(h, (w if writes_cache else w[: self.q_dim]).t(), out=qkv)
+        q = ws.get("attn.q", (T, self.n_heads, self.head_dim), dt, (cap, self.n_heads, self.head_dim))
+        sections = [dict(first_head=0, n_heads=self.n_heads,
+                         norm_weight=self.params.get("q_norm.weight"), rotate=True, dense_out=q)]
+        if writes_cache:
+            sections.append(dict(first_head=self.n_heads, n_heads=self.n_kv_heads,
+                                 norm_weight=self.params.get("k_norm.weight"), rotate=True,
+                                 slab=cache.slabs["k"], slot_map=cache.slot_map))
+            sections.append(dict(first_head=self.n_heads + self.n_kv_heads, n_heads=self.n_kv_heads,
+                                 norm_weight=None, rotate=False,
+                                 slab=cache.slabs["v"], slot_map=cache.slot_map))
+        ops.norm_rope_store(qkv, self.head_dim, self.rotary_dim, step.positions,
+                            self.position.table(), self.eps, self.gemma, sections)
+        plan = step.attention_plans[self.plan_key()]
+        o = ws.get("attn.o", (T, self.n_heads, self.head_dim), dt, (cap, self.n_heads, self.head_dim))
+        ops.paged_attention(q, cache.slabs["k"], cache.slabs["v"], cache.block_table, step.seg_info,
+                            len(step.segments), plan.items_dev, plan.n_items, plan.part_o, plan.part_ml,
+                            o, self.tile_rows, self.scale, self.window)
+        out = ws.get("attn.out", (T, self.hidden), dt, (cap, self.hidden))
+        torch.matmul(o.view(T, self.q_dim), self.params["o_proj.weight"].t(), out=out)
+        return out

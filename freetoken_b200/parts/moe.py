@@ -1,0 +1,104 @@
+"""Mixture-of-experts feed-forward: router, routed experts, optional shared expert.
+
+Router, all in 32-bit (python/freetoken/models/minimax_m3/moe.py:71-81): logits =
+``float32(h) @ W_g^T`` with ``W_g`` stored in 32-bit; ``s = sigmoid(logits)``; the choice is
+``topk(s + bias)``, the weights are the unbiased ``s`` of the chosen experts divided by their
+sum (+1e-20) and multiplied by ``routed_scaling_factor``.  The softmax form takes
+``s = softmax(logits)`` (python/freetoken/moe/fused.py:27-31).
+
+Experts (python/freetoken/moe/fused_nvfp4.py:317-344): routes sorted by expert, grouped
+product with ``gate_up_proj [E, 2I, H]``, activation on the two halves, grouped product with
+``down_proj [E, H, I]`` whose 32-bit accumulator is multiplied by the route weight
+(python/freetoken/kernel/triton/fused_moe.py:292-296), then the sum over a token's routes in
+route order with a 32-bit accumulator (:111-153).  The shared expert runs on the same input
+and is added (moe.py:87-88).
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..config.spec import ParamSpec, PartSpec
+from ..errors import ConfigError
+from ..kernels import ops
+from .base import FEED_FORWARDS, BuildEnv, FeedForward, Part, StepState
+from .mlp import GatedMLP
+
+
+@FEED_FORWARDS.register("moe")
+class MoE(FeedForward):
+    """params: ``hidden``, ``inter``, ``n_experts``, ``top_k``, ``scoring`` ("sigmoid" |
+    "softmax"), ``bias`` (bool), ``scale``, ``act``, ``alpha``, ``limit``,
+    ``shared_inter`` (0 = no shared expert)."""
+
+    wants_f32_input = True
+
+    def __init__(self, spec: PartSpec, env: BuildEnv):
+        super().__init__(spec, env)
+        self.hidden = int(spec["hidden"])
+        self.inter = int(spec["inter"])
+        self.n_experts = int(spec["n_experts"])
+        self.top_k = int(spec["top_k"])
+        if not 1 <= self.top_k <= self.n_experts:
+            raise ConfigError("moe: top_k must be in [1, n_experts]")
+        self.scoring = spec.get("scoring", "sigmoid")
+        if self.scoring not in ops.SCORE_CODES:
+            raise ConfigError(f"moe: unknown scoring '{self.scoring}'")
+        self.has_bias = bool(spec.get("bias", False))
+        self.scale = float(spec.get("scale", 1.0))
+        self.act = spec.get("act", "swigluoai")
+        self.alpha = float(spec.get("alpha", 1.702))
+        self.limit = float(spec.get("limit", 7.0))
+        self.shared_inter = int(spec.get("shared_inter", 0) or 0)
+        self.shared: Optional[GatedMLP] = None
+        if self.shared_inter:
+            self.shared = GatedMLP(PartSpec("gated_mlp", dict(
+                hidden=self.hidden, inter=self.shared_inter, act=self.act, alpha=self.alpha,
+                limit=self.limit)), env, tag="moe.shared")
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        out = {
+            "gate.weight": ParamSpec((self.n_experts, self.hidden), "float32"),
+            "experts.gate_up_proj": ParamSpec((self.n_experts, 2 * self.inter, self.hidden)),
+            "experts.down_proj": ParamSpec((self.n_experts, self.hidden, self.inter)),
+        }
+        if self.has_bias:
+            out["e_score_correction_bias"] = ParamSpec((self.n_experts,), "float32", ("normal", 0.0, 0.01))
+        return out
+
+    def children(self) -> Dict[str, Part]:
+        return {"shared_experts": self.shared} if self.shared is not None else {}
+
+    def forward(self, h: torch.Tensor, step: StepState, h_f32: Optional[torch.Tensor] = None) -> torch.Tensor:
+        T = h.shape[0]
+        ws, dt, cap = self.env.workspace, self.env.dtype, self.env.max_step_tokens
+        k, E, R = self.top_k, self.n_experts, T * self.top_k
+        if h_f32 is None:
+            if h.dtype == torch.float32:
+                h_f32 = h
+            else:
+                h_f32 = ws.get("moe.h_f32", (T, self.hidden), torch.float32, (cap, self.hidden))
+                ops.cast(h, h_f32)
+        logits = ws.get("moe.logits", (T, E), torch.float32, (cap, E))
+        torch.matmul(h_f32, self.params["gate.weight"].t(), out=logits)
+        ids = ws.get("moe.ids", (T, k), torch.int32, (cap, k))
+        wts = ws.get("moe.weights", (T, k), torch.float32, (cap, k))
+        ops.router_topk(logits, self.params.get("e_score_correction_bias"), k, self.scoring,
+                        self.scale, ids, wts)
+        offsets = ws.get("moe.offsets", (E + 1,), torch.int32)
+        routes = ws.get("moe.routes", (R,), torch.int32, (cap * k,))
+        pos = ws.get("moe.pos", (R,), torch.int32, (cap * k,))
+        ops.moe_permute(ids, E, offsets, routes, pos)
+        x = ws.get("moe.x", (R, self.hidden), dt, (cap * k, self.hidden))
+        ops.moe_gather(h, routes, k, x)
+        a = ws.get("moe.act", (R, self.inter), dt, (cap * k, self.inter))
+        ops.moe_gemm1_act(x, self.params["experts.gate_up_proj"], offsets, self.act, self.alpha,
+                          self.limit, a)
+        y = ws.get("moe.y", (R, self.hidden), dt, (cap * k, self.hidden))
+        ops.moe_gemm2(a, self.params["experts.down_proj"], offsets, routes, wts.view(-1), y)
+        shared = self.shared.forward(h, step) if self.shared is not None else None
+        out = ws.get("moe.out", (T, self.hidden), dt, (cap, self.hidden))
+        ops.moe_combine(y, pos, T, k, shared, out)
+        return out
