@@ -1,0 +1,72 @@
+// C interface of the native library: every entry point validates its arguments on the host,
+// launches on the given stream, allocates nothing and returns 0 or a non-zero status whose
+// text ftk_last_error() gives.  Pointers are device pointers unless said otherwise.
+#pragma once
+#include <stdint.h>
+
+#define FTK_F32 0
+#define FTK_BF16 1
+#define FTK_ACT_SILU 0
+#define FTK_ACT_SWIGLUOAI 1
+#define FTK_SCORE_SIGMOID 0
+#define FTK_SCORE_SOFTMAX 1
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// One destination of ftk_norm_rope_store: heads [first_head, first_head + n_heads) of every
+// token, optionally normed and rotated, written densely or scattered into a paged slab.
+typedef struct {
+  int first_head;
+  int n_heads;
+  const float* norm_weight;  // [head_dim] or null
+  int rotate;
+  void* dense_out;           // [T, n_heads, head_dim] or null
+  void* slab;                // [num_pages, n_heads, page_size, head_dim] or null
+  const int32_t* slot_map;   // [T] slot = page * page_size + offset; negative skips the token
+  int page_size;
+  int num_pages;
+} FtkSection;
+
+const char* ftk_last_error(void);
+
+int ftk_embedding_gather(const void* table, int dtype, const int32_t* ids, int n_tokens, int hidden,
+                         int vocab, float* out, void* stream);
+int ftk_add_rmsnorm(const void* x, int x_dtype, float* residual, const float* weight, void* out,
+                    int out_dtype, float* out_f32, const int32_t* rows, int n_rows, int hidden,
+                    float eps, int gemma, void* stream);
+int ftk_act_and_mul(const void* gate_up, int dtype, int n_rows, int inter, int act, float alpha,
+                    float limit, void* out, void* stream);
+int ftk_cast(const void* src, int src_dtype, void* dst, int dst_dtype, long long n, void* stream);
+int ftk_table_update(int32_t* table, long long table_len, const int32_t* updates, int n_updates,
+                     void* stream);
+int ftk_norm_rope_store(const void* x, int dtype, int n_tokens, int row_elems, int head_dim,
+                        int rotary_dim, const int32_t* positions, const float* rope_table, int max_pos,
+                        float eps, int gemma, int n_sections, const FtkSection* sections, void* stream);
+int ftk_paged_attention(const void* q, const void* k_slab, const void* v_slab, int dtype,
+                        const int32_t* block_table, int bt_stride, const int32_t* seg_info, int n_segs,
+                        const int32_t* items, int n_items, float* part_o, float* part_ml, int n_slots,
+                        void* out, int n_q_heads, int n_kv_heads, int head_dim, int page_size,
+                        int num_pages, int tile_rows, float scale, int window, void* stream);
+int ftk_router_topk(const float* logits, const float* bias, int n_tokens, int n_experts, int top_k,
+                    int scoring, float scale, int32_t* ids, float* weights, void* stream);
+int ftk_moe_permute(const int32_t* topk_ids, int n_tokens, int top_k, int n_experts,
+                    int32_t* expert_counts, int32_t* expert_offsets, int32_t* sorted_routes,
+                    int32_t* route_pos, void* stream);
+int ftk_moe_gather(const void* h, int dtype, const int32_t* sorted_routes, int n_routes, int top_k,
+                   int hidden, void* out, void* stream);
+int ftk_moe_gemm1_act(const void* x_sorted, const void* w1, int dtype, const int32_t* expert_offsets,
+                      int n_experts, int n_routes, int hidden, int inter, int act, float alpha,
+                      float limit, void* out, void* stream);
+int ftk_moe_gemm2(const void* a, const void* w2, int dtype, const int32_t* expert_offsets,
+                  const int32_t* sorted_routes, const float* topk_weights, int n_experts, int n_routes,
+                  int hidden, int inter, void* out, void* stream);
+int ftk_moe_combine(const void* y, int dtype, const int32_t* route_pos, int n_tokens, int top_k,
+                    int hidden, const void* shared, void* out, void* stream);
+int ftk_sample(const float* logits, int n_rows, int vocab, const float* temperature,
+               const int32_t* top_k, const float* top_p, const float* u, int32_t* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

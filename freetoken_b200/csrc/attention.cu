@@ -1,0 +1,516 @@
+// Causal softmax attention of a step's queries over paged keys and values.
+//
+// One interface serves prompt portions and single decoded tokens side by side: the host cuts the
+// step's queries into tiles of whole tokens (a tile = `group` query heads of one KV head for a few
+// consecutive tokens of one segment) and, where that leaves SMs idle, splits a tile's key range;
+// each work item is 8 int32 (see engine/attention_plan.py).  grid = (items, KV heads).  A split tile
+// writes (max, sum, unnormalised output) per row to scratch and merge_kernel combines the splits in
+// split order.  The reference has three kernels for this: tiled extend
+// (python/freetoken/kernel/triton/attention.py:469-880), split-KV decode (:147-466) and a scalar
+// fallback for float32 (:45-144).
+//
+// Two implementations share the indexing code below:
+//   * attention_f32_kernel: the true 32-bit path.  One warp per query row, keys in chunks of 32
+//     staged in shared memory, IEEE expf, float32 everywhere.
+//   * attention_bf16_kernel: 64 query rows per CTA on mma.sync m16n8k16 (bf16 in, float32
+//     accumulate), K/V tiles of 64 keys brought in by cp.async through the block table, online
+//     softmax in float32 with exp2; probabilities are rounded to bfloat16 before P.V, as in the
+//     reference (attention.py:252,573).
+// Keys that a tile may not read (beyond its range) are never loaded: fresh pages may hold anything.
+#include <mma.h>
+
+#include "common.cuh"
+
+namespace ftk {
+
+struct AttnParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  const int32_t* block_table;
+  int bt_stride;
+  const int32_t* seg_info;
+  int n_segs;
+  const int32_t* items;
+  int n_items;
+  float* part_o;
+  float* part_ml;
+  int n_slots;
+  int Hq, Hkv, G, D, P, num_pages, tile_rows;
+  float scale;
+  int window;
+};
+
+struct Item {
+  int seg, tok0, ntok, kb, ke, nsplit, split, base;
+  int q_start, q_len, kv_len, bt_row;
+  bool ok;
+};
+
+__device__ __forceinline__ Item load_item(const AttnParams& p, int idx) {
+  Item it;
+  const int32_t* w = p.items + (size_t)idx * 8;
+  it.seg = w[0]; it.tok0 = w[1]; it.ntok = w[2]; it.kb = w[3]; it.ke = w[4];
+  it.nsplit = w[5]; it.split = w[6]; it.base = w[7];
+  it.ok = it.seg >= 0 && it.seg < p.n_segs && it.ntok > 0 && it.ntok * p.G <= p.tile_rows;
+  if (it.ok) {
+    const int32_t* s = p.seg_info + (size_t)it.seg * 4;
+    it.q_start = s[0]; it.q_len = s[1]; it.kv_len = s[2]; it.bt_row = s[3];
+    it.ok = it.tok0 >= 0 && it.tok0 + it.ntok <= it.q_len && it.kb >= 0 && it.ke <= it.kv_len &&
+            it.q_len <= it.kv_len && it.bt_row >= 0 &&
+            (it.nsplit == 1 || (it.base >= 0 && it.base + it.nsplit <= p.n_slots && p.part_o != nullptr));
+  }
+  return it;
+}
+
+// Address of key/value row `pos` of the request (element offset into a [pages, Hkv, P, D] slab),
+// or -1 when the block table names a page outside the pool.
+__device__ __forceinline__ long long kv_row_offset(const AttnParams& p, const Item& it, int kvh, int pos) {
+  const int page = p.block_table[(size_t)it.bt_row * p.bt_stride + pos / p.P];
+  if (page < 0 || page >= p.num_pages) return -1;
+  return (((long long)page * p.Hkv + kvh) * p.P + pos % p.P) * p.D;
+}
+
+// ================================================================= float32 path
+constexpr int kF32Rows = 16;   // warps per block = query rows per tile
+constexpr int kF32Chunk = 32;  // keys per chunk
+
+template <typename T>
+__global__ void __launch_bounds__(kF32Rows * 32) attention_f32_kernel(AttnParams p) {
+  extern __shared__ float smem[];
+  const Item it = load_item(p, blockIdx.x);
+  if (!it.ok) return;
+  const int kvh = blockIdx.y;
+  const int D = p.D, G = p.G;
+  const int ldk = D + 1;
+  float* sq = smem;                       // [rows][D]
+  float* sk = sq + kF32Rows * D;          // [chunk][D + 1]
+  float* sv = sk + kF32Chunk * ldk;       // [chunk][D]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int R = it.ntok * G;
+  const T* q = (const T*)p.q;
+  const T* kbase = (const T*)p.k;
+  const T* vbase = (const T*)p.v;
+
+  for (int i = threadIdx.x; i < R * D; i += blockDim.x) {
+    const int r = i / D, d = i % D;
+    const int tok = it.q_start + it.tok0 + r / G;
+    sq[i] = to_float(q[((size_t)tok * p.Hq + kvh * G + r % G) * D + d]);
+  }
+  const bool active = warp < R;
+  const int q_pos = it.kv_len - it.q_len + it.tok0 + warp / G;
+  const int lo_row = p.window > 0 ? q_pos - p.window + 1 : 0;
+  constexpr int kPer = 8;  // D <= 256
+  float acc[kPer];
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) acc[i] = 0.f;
+  float m = -INFINITY, l = 0.f;
+
+  for (int c0 = it.kb; c0 < it.ke; c0 += kF32Chunk) {
+    __syncthreads();
+    const int nk = min(kF32Chunk, it.ke - c0);
+    for (int i = threadIdx.x; i < kF32Chunk * D; i += blockDim.x) {
+      const int j = i / D, d = i % D;
+      float kval = 0.f, vval = 0.f;
+      if (j < nk) {
+        const long long off = kv_row_offset(p, it, kvh, c0 + j);
+        if (off >= 0) {
+          kval = to_float(kbase[off + d]);
+          vval = to_float(vbase[off + d]);
+        }
+      }
+      sk[j * ldk + d] = kval;
+      sv[j * D + d] = vval;
+    }
+    __syncthreads();
+    if (!active) continue;
+    const int key = c0 + lane;
+    const bool vis = lane < nk && key <= q_pos && key >= lo_row;
+    float s = -INFINITY;
+    if (vis) {
+      const float* qr = sq + warp * D;
+      const float* kr = sk + lane * ldk;
+      float dot = 0.f;
+      for (int d = 0; d < D; ++d) dot = fmaf(qr[d], kr[d], dot);
+      s = dot * p.scale;
+    }
+    const float cm = warp_max(s);
+    if (cm == -INFINITY) continue;  // nothing visible in this chunk
+    const float m_new = fmaxf(m, cm);
+    const float corr = m == -INFINITY ? 0.f : expf(m - m_new);
+    const float pj = vis ? expf(s - m_new) : 0.f;
+    l = l * corr + warp_sum(pj);
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) acc[i] *= corr;
+    for (int j = 0; j < nk; ++j) {
+      const float pb = __shfl_sync(0xffffffffu, pj, j);
+      if (pb != 0.f) {
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+          const int d = lane + 32 * i;
+          if (d < D) acc[i] = fmaf(pb, sv[j * D + d], acc[i]);
+        }
+      }
+    }
+  }
+  if (!active) return;
+  const int tok = it.q_start + it.tok0 + warp / G;
+  if (it.nsplit == 1) {
+    T* o = (T*)p.out + ((size_t)tok * p.Hq + kvh * G + warp % G) * D;
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+      const int d = lane + 32 * i;
+      if (d < D) o[d] = from_float<T>(acc[i] * inv);
+    }
+  } else {
+    const size_t slot = ((size_t)(it.base + it.split) * p.Hkv + kvh) * p.tile_rows + warp;
+    float* po = p.part_o + slot * D;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+      const int d = lane + 32 * i;
+      if (d < D) po[d] = acc[i];
+    }
+    if (lane == 0) {
+      p.part_ml[slot * 2] = m;
+      p.part_ml[slot * 2 + 1] = l;
+    }
+  }
+}
+
+// ================================================================= merge of split tiles
+// out = sum_i acc_i e^(m_i - M) / sum_i l_i e^(m_i - M), splits taken in order.
+template <typename T>
+__global__ void attention_merge_kernel(AttnParams p) {
+  const Item it = load_item(p, blockIdx.x);
+  if (!it.ok || it.nsplit <= 1 || it.split != 0) return;
+  const int kvh = blockIdx.y;
+  const int D = p.D, G = p.G;
+  const int R = it.ntok * G;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int r = warp; r < R; r += nw) {
+    float M = -INFINITY;
+    for (int i = 0; i < it.nsplit; ++i) {
+      const size_t slot = ((size_t)(it.base + i) * p.Hkv + kvh) * p.tile_rows + r;
+      M = fmaxf(M, p.part_ml[slot * 2]);
+    }
+    const int tok = it.q_start + it.tok0 + r / G;
+    T* o = (T*)p.out + ((size_t)tok * p.Hq + kvh * G + r % G) * D;
+    for (int d = lane; d < D; d += 32) {
+      float acc = 0.f, L = 0.f;
+      for (int i = 0; i < it.nsplit; ++i) {
+        const size_t slot = ((size_t)(it.base + i) * p.Hkv + kvh) * p.tile_rows + r;
+        const float mi = p.part_ml[slot * 2];
+        if (mi == -INFINITY) continue;
+        const float w = expf(mi - M);
+        L += p.part_ml[slot * 2 + 1] * w;
+        acc += p.part_o[slot * D + d] * w;
+      }
+      o[d] = from_float<T>(L > 0.f ? acc / L : 0.f);
+    }
+  }
+}
+
+// ================================================================= bfloat16 path (mma.sync)
+constexpr int kBM = 64;  // query rows per CTA (4 warps x 16)
+constexpr int kBN = 64;  // keys per iteration
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Bring keys/values [c0, c0 + 64) of the request into a [64][ld] tile; rows outside [.., ke) are zero.
+__device__ __forceinline__ void load_kv_tile(const AttnParams& p, const Item& it, int kvh, int c0,
+                                             __nv_bfloat16* sk, __nv_bfloat16* sv, int ld) {
+  const int chunks = p.D >> 3;
+  const __nv_bfloat16* kb = (const __nv_bfloat16*)p.k;
+  const __nv_bfloat16* vb = (const __nv_bfloat16*)p.v;
+  for (int i = threadIdx.x; i < kBN * chunks; i += blockDim.x) {
+    const int j = i / chunks, c = i % chunks;
+    const int pos = c0 + j;
+    long long off = -1;
+    if (pos < it.ke) off = kv_row_offset(p, it, kvh, pos);
+    const bool valid = off >= 0;
+    const long long o = valid ? off + c * 8 : 0;
+    cp_async16(sk + j * ld + c * 8, kb + o, valid);
+    cp_async16(sv + j * ld + c * 8, vb + o, valid);
+  }
+}
+
+template <int DMAX>
+__global__ void __launch_bounds__(128) attention_bf16_kernel(AttnParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const Item it = load_item(p, blockIdx.x);
+  if (!it.ok) return;
+  const int kvh = blockIdx.y;
+  const int D = p.D, G = p.G;
+  const int ld = D + 8;  // 16 bytes of padding keep ldmatrix free of bank conflicts for every D
+  __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  __nv_bfloat16* sk0 = sq + kBM * ld;
+  __nv_bfloat16* sv0 = sk0 + 2 * kBN * ld;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int R = it.ntok * G;
+  const int chunks = D >> 3;
+  const __nv_bfloat16* q = (const __nv_bfloat16*)p.q;
+
+  // queries of the tile (rows beyond R are zero)
+  for (int i = threadIdx.x; i < kBM * chunks; i += blockDim.x) {
+    const int r = i / chunks, c = i % chunks;
+    const bool valid = r < R;
+    const int tok = it.q_start + it.tok0 + (valid ? r / G : 0);
+    const size_t off = ((size_t)tok * p.Hq + kvh * G + (valid ? r % G : 0)) * D + c * 8;
+    cp_async16(sq + r * ld + c * 8, q + off, valid);
+  }
+  const int n_iter = (it.ke - it.kb + kBN - 1) / kBN;
+  if (n_iter > 0) load_kv_tile(p, it, kvh, it.kb, sk0, sv0, ld);
+  cp_async_commit();
+
+  const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
+  const int pos_base = it.kv_len - it.q_len + it.tok0;
+  const int qp0 = r0 < R ? pos_base + r0 / G : -1;
+  const int qp1 = r1 < R ? pos_base + r1 / G : -1;
+  const int lo0 = p.window > 0 ? qp0 - p.window + 1 : 0;
+  const int lo1 = p.window > 0 ? qp1 - p.window + 1 : 0;
+  const float sl2 = p.scale * 1.4426950408889634f;
+
+  float o[DMAX / 8][4];
+#pragma unroll
+  for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+  for (int iter = 0; iter < n_iter; ++iter) {
+    const int buf = iter & 1;
+    __nv_bfloat16* sk = sk0 + buf * kBN * ld;
+    __nv_bfloat16* sv = sv0 + buf * kBN * ld;
+    if (iter + 1 < n_iter)
+      load_kv_tile(p, it, kvh, it.kb + (iter + 1) * kBN, sk0 + (buf ^ 1) * kBN * ld, sv0 + (buf ^ 1) * kBN * ld, ld);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+
+    // S = Q K^T  (16 rows x 64 keys per warp)
+    float s[kBN / 8][4];
+#pragma unroll
+    for (int n = 0; n < kBN / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < DMAX / 16; ++kk) {
+      if (kk * 16 < D) {
+        uint32_t a[4];
+        ldsm_x4(a, sq + (warp * 16 + (lane & 15)) * ld + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int n2 = 0; n2 < kBN / 16; ++n2) {
+          uint32_t b[4];
+          ldsm_x4(b, sk + (n2 * 16 + (lane & 7) + ((lane >> 4) << 3)) * ld + kk * 16 + ((lane >> 3) & 1) * 8);
+          mma_bf16(s[2 * n2], a, b[0], b[1]);
+          mma_bf16(s[2 * n2 + 1], a, b[2], b[3]);
+        }
+      }
+    }
+    // mask, running max
+    const int c0 = it.kb + iter * kBN;
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < kBN / 8; ++n) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int key = c0 + n * 8 + (lane & 3) * 2 + e;
+        const bool in = key < it.ke;
+        const bool v0 = in && key <= qp0 && key >= lo0;
+        const bool v1 = in && key <= qp1 && key >= lo1;
+        s[n][e] = v0 ? s[n][e] * sl2 : -INFINITY;
+        s[n][2 + e] = v1 ? s[n][2 + e] * sl2 : -INFINITY;
+        mx0 = fmaxf(mx0, s[n][e]);
+        mx1 = fmaxf(mx1, s[n][2 + e]);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float base0 = mn0 == -INFINITY ? 0.f : mn0, base1 = mn1 == -INFINITY ? 0.f : mn1;
+    const float cr0 = m0 == -INFINITY ? 0.f : fast_exp2(m0 - base0);
+    const float cr1 = m1 == -INFINITY ? 0.f : fast_exp2(m1 - base1);
+    m0 = mn0; m1 = mn1;
+    float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+    for (int n = 0; n < kBN / 8; ++n) {
+      s[n][0] = fast_exp2(s[n][0] - base0); s[n][1] = fast_exp2(s[n][1] - base0);
+      s[n][2] = fast_exp2(s[n][2] - base1); s[n][3] = fast_exp2(s[n][3] - base1);
+      sum0 += s[n][0] + s[n][1];
+      sum1 += s[n][2] + s[n][3];
+    }
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1); sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1); sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+    l0 = l0 * cr0 + sum0;
+    l1 = l1 * cr1 + sum1;
+#pragma unroll
+    for (int i = 0; i < DMAX / 8; ++i) {
+      o[i][0] *= cr0; o[i][1] *= cr0; o[i][2] *= cr1; o[i][3] *= cr1;
+    }
+    // O += P V
+#pragma unroll
+    for (int kk = 0; kk < kBN / 16; ++kk) {
+      uint32_t a[4];
+      a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+      a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int d2 = 0; d2 < DMAX / 16; ++d2) {
+        if (d2 * 16 < D) {
+          uint32_t b[4];
+          ldsm_x4_trans(b, sv + (kk * 16 + (lane & 15)) * ld + d2 * 16 + (lane >> 4) * 8);
+          mma_bf16(o[2 * d2], a, b[0], b[1]);
+          mma_bf16(o[2 * d2 + 1], a, b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+
+  // epilogue
+  if (it.nsplit == 1) {
+    __nv_bfloat16* out = (__nv_bfloat16*)p.out;
+    const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    if (r0 < R) {
+      __nv_bfloat16* dst = out + ((size_t)(it.q_start + it.tok0 + r0 / G) * p.Hq + kvh * G + r0 % G) * D;
+#pragma unroll
+      for (int i = 0; i < DMAX / 8; ++i)
+        if (i * 8 < D) *reinterpret_cast<uint32_t*>(dst + i * 8 + (lane & 3) * 2) = pack_bf16(o[i][0] * i0, o[i][1] * i0);
+    }
+    if (r1 < R) {
+      __nv_bfloat16* dst = out + ((size_t)(it.q_start + it.tok0 + r1 / G) * p.Hq + kvh * G + r1 % G) * D;
+#pragma unroll
+      for (int i = 0; i < DMAX / 8; ++i)
+        if (i * 8 < D) *reinterpret_cast<uint32_t*>(dst + i * 8 + (lane & 3) * 2) = pack_bf16(o[i][2] * i1, o[i][3] * i1);
+    }
+  } else {
+    // the running max is in the exp2 domain (scores were multiplied by scale*log2 e); the merge
+    // works with natural exponentials, so convert
+    const float ln2 = 0.6931471805599453f;
+    const size_t slot0 = ((size_t)(it.base + it.split) * p.Hkv + kvh) * p.tile_rows;
+    if (r0 < R) {
+      float* po = p.part_o + (slot0 + r0) * D;
+#pragma unroll
+      for (int i = 0; i < DMAX / 8; ++i)
+        if (i * 8 < D) *reinterpret_cast<float2*>(po + i * 8 + (lane & 3) * 2) = make_float2(o[i][0], o[i][1]);
+      if ((lane & 3) == 0) {
+        p.part_ml[(slot0 + r0) * 2] = m0 == -INFINITY ? -INFINITY : m0 * ln2;
+        p.part_ml[(slot0 + r0) * 2 + 1] = l0;
+      }
+    }
+    if (r1 < R) {
+      float* po = p.part_o + (slot0 + r1) * D;
+#pragma unroll
+      for (int i = 0; i < DMAX / 8; ++i)
+        if (i * 8 < D) *reinterpret_cast<float2*>(po + i * 8 + (lane & 3) * 2) = make_float2(o[i][2], o[i][3]);
+      if ((lane & 3) == 0) {
+        p.part_ml[(slot0 + r1) * 2] = m1 == -INFINITY ? -INFINITY : m1 * ln2;
+        p.part_ml[(slot0 + r1) * 2 + 1] = l1;
+      }
+    }
+  }
+}
+
+template <int DMAX>
+static int launch_bf16(const AttnParams& p, cudaStream_t s) {
+  const size_t smem = (size_t)(kBM + 4 * kBN) * (p.D + 8) * sizeof(__nv_bfloat16);
+  auto kern = attention_bf16_kernel<DMAX>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  dim3 grid(p.n_items, p.Hkv);
+  kern<<<grid, 128, smem, s>>>(p);
+  return 0;
+}
+
+}  // namespace ftk
+
+using namespace ftk;
+
+extern "C" int ftk_paged_attention(const void* q, const void* k_slab, const void* v_slab, int dtype,
+                                   const int32_t* block_table, int bt_stride, const int32_t* seg_info,
+                                   int n_segs, const int32_t* items, int n_items, float* part_o,
+                                   float* part_ml, int n_slots, void* out, int n_q_heads, int n_kv_heads,
+                                   int head_dim, int page_size, int num_pages, int tile_rows, float scale,
+                                   int window, void* stream) {
+  FTK_REQUIRE(dtype_ok(dtype), "paged_attention: bad dtype %d", dtype);
+  FTK_REQUIRE(n_items >= 0 && n_segs >= 0, "paged_attention: bad counts");
+  if (n_items == 0) return 0;
+  FTK_REQUIRE(q && k_slab && v_slab && block_table && seg_info && items && out, "paged_attention: null pointer");
+  FTK_REQUIRE(n_kv_heads >= 1 && n_kv_heads <= 65535 && n_q_heads % n_kv_heads == 0,
+              "paged_attention: %d query heads do not divide into %d KV heads", n_q_heads, n_kv_heads);
+  FTK_REQUIRE(head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 256,
+              "paged_attention: head_dim=%d must be a multiple of 16 in [16, 256]", head_dim);
+  FTK_REQUIRE(page_size >= 1 && num_pages >= 1 && bt_stride >= 1, "paged_attention: bad page geometry");
+  FTK_REQUIRE(window >= 0, "paged_attention: negative window");
+  FTK_REQUIRE(n_slots == 0 || (part_o && part_ml), "paged_attention: split tiles need scratch");
+  AttnParams p;
+  p.q = q; p.k = k_slab; p.v = v_slab; p.out = out;
+  p.block_table = block_table; p.bt_stride = bt_stride;
+  p.seg_info = seg_info; p.n_segs = n_segs; p.items = items; p.n_items = n_items;
+  p.part_o = part_o; p.part_ml = part_ml; p.n_slots = n_slots;
+  p.Hq = n_q_heads; p.Hkv = n_kv_heads; p.G = n_q_heads / n_kv_heads; p.D = head_dim; p.P = page_size;
+  p.num_pages = num_pages; p.tile_rows = tile_rows; p.scale = scale; p.window = window;
+  cudaStream_t s = (cudaStream_t)stream;
+  dim3 grid(n_items, n_kv_heads);
+  if (dtype == FTK_F32) {
+    FTK_REQUIRE(tile_rows == kF32Rows, "paged_attention: the float32 kernel works on %d-row tiles, got %d",
+                kF32Rows, tile_rows);
+    FTK_REQUIRE(p.G <= kF32Rows, "paged_attention: %d query heads per KV head exceed the %d-row tile", p.G, kF32Rows);
+    const size_t smem = ((size_t)kF32Rows * head_dim + (size_t)kF32Chunk * (2 * head_dim + 1)) * sizeof(float);
+    auto kern = attention_f32_kernel<float>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kern<<<grid, kF32Rows * 32, smem, s>>>(p);
+    FTK_LAUNCH_CHECK("paged_attention (float32)");
+    if (n_slots > 0) {
+      attention_merge_kernel<float><<<grid, 128, 0, s>>>(p);
+      FTK_LAUNCH_CHECK("paged_attention merge");
+    }
+  } else {
+    FTK_REQUIRE(tile_rows == kBM, "paged_attention: the bfloat16 kernel works on %d-row tiles, got %d", kBM, tile_rows);
+    FTK_REQUIRE(p.G <= kBM, "paged_attention: %d query heads per KV head exceed the %d-row tile", p.G, kBM);
+    if (head_dim <= 64) launch_bf16<64>(p, s);
+    else if (head_dim <= 128) launch_bf16<128>(p, s);
+    else launch_bf16<256>(p, s);
+    FTK_LAUNCH_CHECK("paged_attention (bfloat16)");
+    if (n_slots > 0) {
+      attention_merge_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(p);
+      FTK_LAUNCH_CHECK("paged_attention merge");
+    }
+  }
+  return 0;
+}

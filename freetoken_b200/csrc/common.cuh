@@ -1,0 +1,100 @@
+// Shared host and device helpers: checked launches, dtype-generic loads and stores, reductions.
+//
+// Host side: every entry point checks sizes and pointers with FTK_REQUIRE before it launches and
+// reads the launch status afterwards; the text of the first failure is kept per thread for
+// ftk_last_error().  (The reference wraps its launches the same way: TensorMatcher / RuntimeCheck /
+// LaunchKernel in python/freetoken/kernel/csrc/include/freetoken/{tensor.h,utils.h,utils.cuh}.)
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "api.h"
+
+namespace ftk {
+
+void set_error(const char* fmt, ...);
+
+#define FTK_REQUIRE(cond, ...)        \
+  do {                                \
+    if (!(cond)) {                    \
+      ftk::set_error(__VA_ARGS__);    \
+      return 1;                       \
+    }                                 \
+  } while (0)
+
+#define FTK_LAUNCH_CHECK(name)                                              \
+  do {                                                                      \
+    cudaError_t e_ = cudaGetLastError();                                    \
+    if (e_ != cudaSuccess) {                                                \
+      ftk::set_error("%s: launch failed: %s", name, cudaGetErrorString(e_)); \
+      return 2;                                                             \
+    }                                                                       \
+  } while (0)
+
+inline bool dtype_ok(int d) { return d == FTK_F32 || d == FTK_BF16; }
+inline int dtype_size(int d) { return d == FTK_F32 ? 4 : 2; }
+
+// ---------------------------------------------------------------- device helpers
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over the block in a fixed order (warp shuffles, then warp 0 over the warp sums); every
+// thread gets the result.  `scratch` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? scratch[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+// Gated activations on float inputs (python/freetoken/kernel/triton/activation.py:96-107).
+__device__ __forceinline__ float gated_act(float g, float u, int act, float alpha, float limit) {
+  if (act == FTK_ACT_SILU) return g / (1.f + expf(-g)) * u;
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+}
+
+}  // namespace ftk

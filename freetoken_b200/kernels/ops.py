@@ -59,7 +59,7 @@ _SIGNATURES = {
     "ftk_paged_attention": [_vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
                             _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "ftk_router_topk": [_vp, _vp, _i, _i, _i, _i, _f, _vp, _vp, _vp],
-    "ftk_moe_permute": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp],
+    "ftk_moe_permute": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp],
     "ftk_moe_gather": [_vp, _i, _vp, _i, _i, _i, _vp, _vp],
     "ftk_moe_gemm1_act": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _f, _f, _vp, _vp],
     "ftk_moe_gemm2": [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
@@ -304,18 +304,21 @@ def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, 
                                   _stream()), "router_topk")
 
 
-def moe_permute(topk_ids: torch.Tensor, n_experts: int, expert_offsets: torch.Tensor,
-                sorted_routes: torch.Tensor, route_pos: torch.Tensor) -> None:
+def moe_permute(topk_ids: torch.Tensor, n_experts: int, expert_counts: torch.Tensor,
+                expert_offsets: torch.Tensor, sorted_routes: torch.Tensor, route_pos: torch.Tensor) -> None:
     """Sort the routes ``(t, j)`` by expert, keeping their order within an expert.
 
+    ``expert_counts [E]``: routes per expert;
     ``expert_offsets [E + 1]``: rows of expert ``e`` are ``[offsets[e], offsets[e+1])``;
     ``sorted_routes [T*k]``: route index ``t*k + j`` at each sorted row;
     ``route_pos [T*k]``: sorted row of each route."""
     T, k = topk_ids.shape
-    if expert_offsets.shape != (n_experts + 1,) or sorted_routes.numel() != T * k \
+    if expert_offsets.shape != (n_experts + 1,) or expert_counts.shape != (n_experts,) \
+            or sorted_routes.numel() != T * k \
             or route_pos.numel() != T * k:
         raise KernelError("moe_permute: output shapes are wrong")
     _check(_lib().ftk_moe_permute(_dev(topk_ids, "topk_ids", torch.int32), T, k, n_experts,
+                                  _dev(expert_counts, "expert_counts", torch.int32),
                                   _dev(expert_offsets, "expert_offsets", torch.int32),
                                   _dev(sorted_routes, "sorted_routes", torch.int32),
                                   _dev(route_pos, "route_pos", torch.int32), _stream()), "moe_permute", 2)

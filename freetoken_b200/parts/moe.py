@@ -87,10 +87,11 @@ class MoE(FeedForward):
         wts = ws.get("moe.weights", (T, k), torch.float32, (cap, k))
         ops.router_topk(logits, self.params.get("e_score_correction_bias"), k, self.scoring,
                         self.scale, ids, wts)
+        counts = ws.get("moe.counts", (E,), torch.int32)
         offsets = ws.get("moe.offsets", (E + 1,), torch.int32)
         routes = ws.get("moe.routes", (R,), torch.int32, (cap * k,))
         pos = ws.get("moe.pos", (R,), torch.int32, (cap * k,))
-        ops.moe_permute(ids, E, offsets, routes, pos)
+        ops.moe_permute(ids, E, counts, offsets, routes, pos)
         x = ws.get("moe.x", (R, self.hidden), dt, (cap * k, self.hidden))
         ops.moe_gather(h, routes, k, x)
         a = ws.get("moe.act", (R, self.inter), dt, (cap * k, self.inter))

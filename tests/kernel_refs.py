@@ -122,10 +122,11 @@ def router_topk(logits, bias, top_k, scoring, scale, ids, weights):
     weights.copy_(w * scale)
 
 
-def moe_permute(topk_ids, n_experts, expert_offsets, sorted_routes, route_pos):
+def moe_permute(topk_ids, n_experts, expert_counts, expert_offsets, sorted_routes, route_pos):
     flat = topk_ids.reshape(-1).long()
     order = torch.argsort(flat, stable=True)
     counts = torch.bincount(flat, minlength=n_experts)
+    expert_counts.copy_(counts.to(torch.int32))
     expert_offsets[0] = 0
     expert_offsets[1:] = torch.cumsum(counts, 0).to(torch.int32)
     sorted_routes.copy_(order.to(torch.int32))

@@ -1,0 +1,333 @@
+"""Each CUDA kernel alone against its plain PyTorch reference (tests/kernel_refs.py), in float32
+and bfloat16, at sizes other than the engine's tiny configurations: widths and vocabularies that
+are no power of two, head sizes in steps of 16, odd numbers of heads and groups, pages of several
+sizes, fresh pages filled with NaN so that a read of an unwritten slot shows."""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import kernel_refs as ref
+from freetoken_b200.engine.attention_plan import build_plan
+from freetoken_b200.kernels import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-6) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-3)
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("V,H,T", [(331, 112, 9), (1000, 3072, 33), (77, 50, 5)])
+def test_embedding_gather(dtype, V, H, T):
+    table = rnd(V, H, dtype=dtype)
+    ids = torch.randint(0, V, (T,), dtype=torch.int32, device=DEV)
+    out = torch.empty(T, H, dtype=torch.float32, device=DEV)
+    want = torch.empty_like(out)
+    ops.embedding_gather(table, ids, out)
+    ref.embedding_gather(table, ids, want)
+    assert torch.equal(out, want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,T,gemma", [(112, 7, True), (3072, 19, True), (50, 3, False), (6144, 4, False)])
+def test_add_rmsnorm(dtype, H, T, gemma):
+    x = rnd(T, H, dtype=dtype)
+    res = rnd(T, H, seed=1)
+    w = rnd(H, scale=0.1, seed=2)
+    for mode in ("add", "residual_only", "x_only", "rows"):
+        r1, r2 = res.clone(), res.clone()
+        rows = torch.tensor([T - 1, 0, T // 2], dtype=torch.int32, device=DEV) if mode == "rows" else None
+        n = 3 if mode == "rows" else T
+        out = torch.empty(n, H, dtype=dtype, device=DEV)
+        want = torch.empty_like(out)
+        o32 = torch.empty(n, H, dtype=torch.float32, device=DEV)
+        w32 = torch.empty_like(o32)
+        xa = None if mode == "residual_only" else x
+        ra, rb = (None, None) if mode == "x_only" else (r1, r2)
+        ops.add_rmsnorm(xa, ra, w, 1e-5, gemma, out, out_f32=o32, rows=rows)
+        ref.add_rmsnorm(xa, rb, w, 1e-5, gemma, want, out_f32=w32, rows=rows)
+        torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+        torch.testing.assert_close(o32, out.float(), rtol=0, atol=0)
+        if mode == "add":
+            torch.testing.assert_close(r1, r2, rtol=1e-6, atol=1e-6)
+        elif ra is not None:
+            assert torch.equal(r1, res)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("act", ["silu", "swigluoai"])
+def test_act_and_mul(dtype, act):
+    gu = rnd(13, 2 * 72, dtype=dtype, scale=4.0)
+    out = torch.empty(13, 72, dtype=dtype, device=DEV)
+    want = torch.empty_like(out)
+    ops.act_and_mul(gu, out, act, 1.702, 7.0)
+    ref.act_and_mul(gu, want, act, 1.702, 7.0)
+    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+
+
+def test_cast_and_table_update():
+    x = rnd(1000)
+    y = torch.empty(1000, dtype=torch.bfloat16, device=DEV)
+    ops.cast(x, y)
+    assert torch.equal(y, x.to(torch.bfloat16))
+    z = torch.empty(1000, dtype=torch.float32, device=DEV)
+    ops.cast(y, z)
+    assert torch.equal(z, y.float())
+    table = torch.zeros(4, 10, dtype=torch.int32, device=DEV)
+    ups = torch.tensor([[3, 7], [-1, -1], [39, 2], [11, 5]], dtype=torch.int32, device=DEV)
+    ops.table_update(table, ups, 4)
+    want = torch.zeros(40, dtype=torch.int32)
+    want[3], want[39], want[11] = 7, 2, 5
+    assert torch.equal(table.view(-1).cpu(), want)
+
+
+def make_rope(max_pos, rd, theta=10000.0):
+    inv = 1.0 / (theta ** (torch.arange(0, rd, 2, dtype=torch.float) / rd))
+    f = torch.einsum("i,j->ij", torch.arange(max_pos, dtype=torch.float), inv)
+    return torch.cat((f.cos(), f.sin()), -1).contiguous().to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,D,rd,P,gemma,norm", [
+    (7, 1, 48, 24, 4, True, True), (6, 3, 32, 32, 8, False, False), (48, 8, 128, 64, 16, True, True),
+    (5, 5, 80, 16, 3, True, True), (2, 2, 256, 128, 16, False, True)])
+def test_norm_rope_store(dtype, Hq, Hkv, D, rd, P, gemma, norm):
+    T, pages = 21, 12
+    x = rnd(T, (Hq + 2 * Hkv) * D, dtype=dtype)
+    pos = torch.randint(0, 100, (T,), dtype=torch.int32, device=DEV)
+    table = make_rope(100, rd) if rd else None
+    slots = torch.randperm(pages * P)[:T].to(torch.int32).to(DEV)
+    slots[5] = -1
+    qw = rnd(D, scale=0.1, seed=3) if norm else None
+    kw = rnd(D, scale=0.1, seed=4) if norm else None
+    got, want = [], []
+    for fn, store in ((ops.norm_rope_store, got), (ref.norm_rope_store, want)):
+        q = torch.zeros(T, Hq, D, dtype=dtype, device=DEV)
+        ks = torch.full((pages, Hkv, P, D), float("nan"), dtype=dtype, device=DEV)
+        vs = torch.full((pages, Hkv, P, D), float("nan"), dtype=dtype, device=DEV)
+        fn(x, D, rd, pos, table, 1e-6, gemma, [
+            dict(first_head=0, n_heads=Hq, norm_weight=qw, rotate=True, dense_out=q),
+            dict(first_head=Hq, n_heads=Hkv, norm_weight=kw, rotate=True, slab=ks, slot_map=slots),
+            dict(first_head=Hq + Hkv, n_heads=Hkv, norm_weight=None, rotate=False, slab=vs, slot_map=slots)])
+        store.extend([q, ks, vs])
+    for a, b in zip(got, want):
+        assert torch.equal(torch.isnan(a), torch.isnan(b))
+        torch.testing.assert_close(torch.nan_to_num(a.float()), torch.nan_to_num(b.float()), **tol(dtype))
+
+
+def run_attention(dtype, Hq, Hkv, D, P, segs, window, fixed_splits=None, force_split=False, seed=0):
+    """segs: list of (q_len, kv_len).  Builds a shuffled page layout with NaN in every unwritten
+    slot, runs kernel and reference, returns both outputs."""
+    G = Hq // Hkv
+    tile = 64 if dtype == torch.bfloat16 else 16
+    width = max(-(-kv // P) for _, kv in segs) + 1
+    n_pages = sum(-(-kv // P) for _, kv in segs) + 3
+    g = torch.Generator().manual_seed(seed)
+    perm = (torch.randperm(n_pages - 1, generator=g) + 1).tolist()
+    bt = torch.zeros(len(segs) + 1, width, dtype=torch.int32)
+    ks = torch.full((n_pages, Hkv, P, D), float("nan"), dtype=dtype)
+    vs = torch.full((n_pages, Hkv, P, D), float("nan"), dtype=dtype)
+    seg_info, q_start = [], 0
+    rows = list(range(len(segs), 0, -1))  # block-table rows in reverse order
+    for (q_len, kv_len), row in zip(segs, rows):
+        for b in range(-(-kv_len // P)):
+            page = perm.pop()
+            bt[row, b] = page
+            n = min(P, kv_len - b * P)
+            ks[page, :, :n] = torch.randn(Hkv, n, D, generator=g).to(dtype)
+            vs[page, :, :n] = torch.randn(Hkv, n, D, generator=g).to(dtype)
+        seg_info.append([q_start, q_len, kv_len, row])
+        q_start += q_len
+    T = q_start
+    q = torch.randn(T, Hq, D, generator=g).to(dtype).to(DEV)
+    ks, vs, bt = ks.to(DEV), vs.to(DEV), bt.to(DEV)
+    seg = torch.tensor(seg_info, dtype=torch.int32, device=DEV)
+    kw = dict(sm_count=148)
+    if force_split:
+        kw = dict(sm_count=4096, min_split_keys=32)
+    plan = build_plan(segs, G, tile, window, Hkv, fixed_splits=fixed_splits, **kw)
+    items = torch.from_numpy(plan.items).to(DEV)
+    part_o = part_ml = None
+    if plan.n_slots:
+        part_o = torch.full((plan.n_slots, Hkv, tile, D), float("nan"), dtype=torch.float32, device=DEV)
+        part_ml = torch.full((plan.n_slots, Hkv, tile, 2), float("nan"), dtype=torch.float32, device=DEV)
+    out = torch.full((T, Hq, D), float("nan"), dtype=dtype, device=DEV)
+    want = torch.empty_like(out)
+    scale = D ** -0.5
+    ops.paged_attention(q, ks, vs, bt, seg, len(segs), items, plan.n_items, part_o, part_ml, out, tile,
+                        scale, window)
+    ref.paged_attention(q, ks, vs, bt, seg, len(segs), items, plan.n_items, None, None, want, tile, scale,
+                        window)
+    return out, want, plan
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,D,P", [(7, 1, 48, 4), (6, 3, 32, 8), (12, 2, 128, 16), (4, 4, 80, 5),
+                                        (2, 1, 256, 16), (3, 3, 16, 1), (16, 2, 64, 32)])
+def test_attention_mixed_batch(dtype, Hq, Hkv, D, P):
+    segs = [(1, 1), (1, 130), (17, 17), (5, 69), (2, 64), (33, 200), (1, 65)]
+    out, want, _ = run_attention(dtype, Hq, Hkv, D, P, segs, None)
+    assert not torch.isnan(out).any()
+    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("fixed", [None, 5])
+def test_attention_split_keys(dtype, fixed):
+    segs = [(1, 1000), (1, 3), (2, 517), (1, 64)]
+    out, want, plan = run_attention(dtype, 12, 2, 64, 16, segs, None, fixed_splits=fixed, force_split=True)
+    assert plan.n_slots > 0
+    assert not torch.isnan(out).any()
+    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 7, 64, 100])
+def test_attention_window(dtype, window):
+    segs = [(1, 150), (40, 40), (9, 120)]
+    out, want, _ = run_attention(dtype, 6, 3, 32, 8, segs, window)
+    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_far_key_stands_out(dtype):
+    """One key far back gets a large score: every query must put almost all its weight there,
+    so a kernel that drops or misplaces a far page cannot pass."""
+    Hq, Hkv, D, P = 4, 2, 64, 16
+    segs = [(1, 700), (3, 515)]
+    G = Hq // Hkv
+    tile = 64 if dtype == torch.bfloat16 else 16
+    out, want, _ = run_attention(dtype, Hq, Hkv, D, P, segs, None, force_split=True, seed=5)
+    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+    # now make position 3 of segment 0 dominate and check the output equals its value row
+    g = torch.Generator().manual_seed(9)
+    kv = 700
+    ks = torch.randn(50, Hkv, P, D, generator=g).to(dtype).to(DEV) * 0.1
+    vs = torch.randn(50, Hkv, P, D, generator=g).to(dtype).to(DEV)
+    bt = torch.arange(1, 46, dtype=torch.int32).view(1, -1).to(DEV)
+    q = torch.randn(1, Hq, D, generator=g).to(dtype).to(DEV)
+    for h in range(Hkv):
+        ks[1, h, 3] = (q[0, h * G].float() * 8).to(dtype)  # page 1 holds positions 0..15
+    seg = torch.tensor([[0, 1, kv, 0]], dtype=torch.int32, device=DEV)
+    plan = build_plan([(1, kv)], G, tile, None, Hkv, sm_count=4096, min_split_keys=32)
+    items = torch.from_numpy(plan.items).to(DEV)
+    po = torch.empty(max(plan.n_slots, 1), Hkv, tile, D, dtype=torch.float32, device=DEV)
+    pm = torch.empty(max(plan.n_slots, 1), Hkv, tile, 2, dtype=torch.float32, device=DEV)
+    out = torch.empty(1, Hq, D, dtype=dtype, device=DEV)
+    ops.paged_attention(q, ks, vs, bt, seg, 1, items, plan.n_items, po, pm, out, tile, D ** -0.5, None)
+    for h in range(Hkv):
+        torch.testing.assert_close(out[0, h * G].float(), vs[1, h, 3].float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("scoring,bias", [("sigmoid", True), ("sigmoid", False), ("softmax", False), ("softmax", True)])
+@pytest.mark.parametrize("T,E,k", [(1, 8, 2), (37, 256, 8), (5, 6, 3), (64, 100, 100), (3, 1, 1)])
+def test_router_topk(scoring, bias, T, E, k):
+    logits = rnd(T, E, scale=2.0)
+    logits[0, : min(E, 4)] = 0.5  # ties: the lower index must win
+    b = rnd(E, scale=0.01, seed=7) if bias else None
+    ids = torch.empty(T, k, dtype=torch.int32, device=DEV)
+    w = torch.empty(T, k, dtype=torch.float32, device=DEV)
+    ids2, w2 = torch.empty_like(ids), torch.empty_like(w)
+    ops.router_topk(logits, b, k, scoring, 2.0, ids, w)
+    ref.router_topk(logits, b, k, scoring, 2.0, ids2, w2)
+    assert torch.equal(ids, ids2)
+    torch.testing.assert_close(w, w2, rtol=1e-5, atol=1e-7)
+
+
+@pytest.mark.parametrize("T,k,E", [(1, 2, 8), (50, 4, 16), (300, 8, 256), (7, 3, 6), (2, 1, 40)])
+def test_moe_permute_gather_combine(T, k, E):
+    ids = torch.stack([torch.randperm(E)[:k] for _ in range(T)]).to(torch.int32).to(DEV)
+    if T > 4:
+        ids[:4] = ids[0]  # several tokens to the same experts
+    outs = []
+    for fn in (ops.moe_permute, ref.moe_permute):
+        counts = torch.empty(E, dtype=torch.int32, device=DEV)
+        off = torch.empty(E + 1, dtype=torch.int32, device=DEV)
+        routes = torch.empty(T * k, dtype=torch.int32, device=DEV)
+        pos = torch.empty(T * k, dtype=torch.int32, device=DEV)
+        fn(ids, E, counts, off, routes, pos)
+        outs.append((counts, off, routes, pos))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+    counts, off, routes, pos = outs[0]
+    for dtype in DTYPES:
+        h = rnd(T, 56, dtype=dtype)
+        x, x2 = torch.empty(T * k, 56, dtype=dtype, device=DEV), torch.empty(T * k, 56, dtype=dtype, device=DEV)
+        ops.moe_gather(h, routes, k, x)
+        ref.moe_gather(h, routes, k, x2)
+        assert torch.equal(x, x2)
+        y = rnd(T * k, 56, dtype=dtype, seed=3)
+        sh = rnd(T, 56, dtype=dtype, seed=4)
+        for shared in (None, sh):
+            o, o2 = torch.empty(T, 56, dtype=dtype, device=DEV), torch.empty(T, 56, dtype=dtype, device=DEV)
+            ops.moe_combine(y, pos, T, k, shared, o)
+            ref.moe_combine(y, pos, T, k, shared, o2)
+            torch.testing.assert_close(o.float(), o2.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("E,H,I,counts", [
+    (6, 112, 40, [0, 5, 1, 0, 33, 2]), (4, 96, 48, [64, 0, 0, 1]), (8, 64, 32, [3] * 8),
+    (3, 200, 72, [130, 1, 70]), (5, 128, 256, [0, 0, 0, 0, 9])])
+@pytest.mark.parametrize("act", ["silu", "swigluoai"])
+def test_moe_grouped_gemms(dtype, E, H, I, counts, act):
+    R = sum(counts)
+    off = torch.tensor([0] + list(np.cumsum(counts)), dtype=torch.int32, device=DEV)
+    x = rnd(R, H, dtype=dtype)
+    w1 = rnd(E, 2 * I, H, dtype=dtype, scale=0.1)
+    w2 = rnd(E, H, I, dtype=dtype, scale=0.1)
+    a, a2 = torch.empty(R, I, dtype=dtype, device=DEV), torch.empty(R, I, dtype=dtype, device=DEV)
+    ops.moe_gemm1_act(x, w1, off, act, 1.702, 7.0, a)
+    ref.moe_gemm1_act(x, w1, off, act, 1.702, 7.0, a2)
+    torch.testing.assert_close(a.float(), a2.float(), **tol(dtype))
+    routes = torch.randperm(R).to(torch.int32).to(DEV)
+    wts = torch.rand(R, device=DEV) + 0.5
+    y, y2 = torch.empty(R, H, dtype=dtype, device=DEV), torch.empty(R, H, dtype=dtype, device=DEV)
+    ops.moe_gemm2(a2, w2, off, routes, wts, y)
+    ref.moe_gemm2(a2, w2, off, routes, wts, y2)
+    torch.testing.assert_close(y.float(), y2.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("V", [256, 331, 50000])
+def test_sample(V):
+    R = 9
+    logits = rnd(R, V, scale=3.0)
+    logits[0, 7] = logits[0, 3] = logits[0].max() + 1  # tie: index 3 wins
+    temp = torch.tensor([0.0, 0.8, 1.0, 0.5, 1.3, 0.0, 1.0, 1.0, 2.0], device=DEV)
+    top_k = torch.tensor([0, 0, 5, 0, 40, 0, 1, 0, 3], dtype=torch.int32, device=DEV)
+    top_p = torch.tensor([1.0, 1.0, 1.0, 0.9, 0.7, 1.0, 1.0, 0.3, 0.95], device=DEV)
+    for trial in range(6):
+        u = torch.rand(R, generator=torch.Generator().manual_seed(trial)).to(DEV)
+        out = torch.empty(R, dtype=torch.int32, device=DEV)
+        want = torch.empty_like(out)
+        ops.sample(logits, temp, top_k, top_p, u, out)
+        ref.sample(logits, temp, top_k, top_p, u, want)
+        assert out[0].item() == 3
+        assert torch.equal(out, want), (trial, out, want)
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    from freetoken_b200.errors import KernelError
+
+    q = torch.zeros(1, 2, 24, device=DEV)  # head size 24 is no multiple of 16
+    slab = torch.zeros(2, 2, 4, 24, device=DEV)
+    with pytest.raises(KernelError):
+        ops.paged_attention(q, slab, slab, torch.zeros(1, 1, dtype=torch.int32, device=DEV),
+                            torch.zeros(1, 4, dtype=torch.int32, device=DEV), 1,
+                            torch.zeros(1, 8, dtype=torch.int32, device=DEV), 1, None, None,
+                            torch.zeros_like(q), 16, 1.0, None)
+    with pytest.raises(KernelError):  # tensors on the CPU never reach a kernel
+        ops.cast(torch.zeros(4), torch.zeros(4, dtype=torch.bfloat16))
