@@ -18,7 +18,7 @@ memory that is left, then the sampler and the CUDA graphs of decode steps
 
 from __future__ import annotations
 
-import time
+import os
 from dataclasses import dataclass, field
 from typing import Any, Dict, Hashable, List, Optional, Sequence, Tuple
 
@@ -55,8 +55,9 @@ class StepOutput:
 class Engine:
     def __init__(self, config: EngineConfig, spec: Optional[ModelSpec] = None,
                  raw_config: Optional[dict] = None):
-        """``spec`` (with ``config.use_dummy_weight``) builds a model that has no folder;
-        tests use it for models made of toy parts."""
+        """``spec`` replaces the model description that the architecture would build from
+        config.json (another schedule, toy parts); with ``config.use_dummy_weight`` no folder is
+        needed at all."""
         self.config = config
         self.device = torch.device(config.device)
         if self.device.type == "cuda":
@@ -65,14 +66,17 @@ class Engine:
             torch.backends.cudnn.allow_tf32 = False
             torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
         self.arch = self.typed = None
-        if spec is None:
-            raw = raw_config if raw_config is not None else read_config_json(config.model_path)
+        raw = raw_config
+        if raw is None and os.path.isfile(os.path.join(config.model_path, "config.json")):
+            raw = read_config_json(config.model_path)
+        if raw is not None:
             self.arch = architecture_of(raw)
             self.typed = self.arch.parse_config(raw, num_layers=config.num_layers)
+        if spec is None:
+            if self.arch is None:
+                raise ConfigError(f"{config.model_path}: no config.json in the model folder")
             spec = self.arch.build_spec(self.typed)
-            file_dtype = getattr(self.typed, "torch_dtype", None)
-        else:
-            file_dtype = None
+        file_dtype = getattr(self.typed, "torch_dtype", None)
         dtype = config.dtype
         if dtype == "auto":  # python/freetoken/server/args.py:660-679
             try:

@@ -1,0 +1,6 @@
+"""Sampling parameters and the sampler."""
+
+from .params import SamplingParams
+from .sampler import Sampler, uniform_for
+
+__all__ = ["SamplingParams", "Sampler", "uniform_for"]

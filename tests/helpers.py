@@ -1,0 +1,146 @@
+"""Helpers shared by the tests: model folders in temp dirs, engines, traces of steps."""
+
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from freetoken_b200.config.engine_config import EngineConfig
+from freetoken_b200.engine.engine import Engine, StepEntry
+from freetoken_b200.weights.random_init import write_model_folder
+from plain.m3_plain import PlainM3
+
+_FOLDERS: Dict[Tuple[str, int], str] = {}
+
+# Router gaps (in units of the router logit) below this are within the noise of bfloat16
+# activations: the hidden state carries a relative error of a few 1e-3 after some layers, which
+# moves a logit of size ~0.2-1 by ~1e-3.  At such a token a bfloat16 run may pick another expert
+# than the 32-bit run, which changes its logits by more than rounding.  bfloat16 comparisons check
+# those tokens only loosely and require them to be a minority.
+NEAR_TIE = 4e-3
+# bfloat16 logits against the 32-bit plain model: the bound the reference uses for its own
+# bfloat16 kernels (tests/kernels/test_minimax_m3_sparse.py:275-276) is 3e-2 max-abs.
+BF16_TOL = dict(rtol=3e-2, atol=2e-2)
+F32_TOL = dict(rtol=1e-4, atol=2e-5)
+
+
+def assert_bf16_close(got: torch.Tensor, ref: torch.Tensor, margins: torch.Tensor, what: str = "") -> None:
+    """``got`` (bfloat16 engine) against ``ref`` (32-bit plain) at every position whose router
+    gaps are clear of bfloat16 noise, from the first position on up to (not including) the
+    first near-tie; later positions see that token's keys and are checked loosely."""
+    sure = margins[: got.shape[0]] > NEAR_TIE
+    assert sure.float().mean() > 0.5, f"{what}: too many near-ties for a meaningful comparison"
+    torch.testing.assert_close(got[sure], ref[: got.shape[0]][sure], **BF16_TOL, msg=lambda m: f"{what}: {m}")
+    assert torch.isfinite(got).all()
+    assert (got - ref[: got.shape[0]]).abs().max() < 0.5, what
+
+
+def model_folder(tmp_root, name: str, raw: dict, seed: int = 1) -> str:
+    key = (name, seed)
+    if key not in _FOLDERS or not os.path.isdir(_FOLDERS[key]):
+        d = os.path.join(str(tmp_root), f"model_{name}_{seed}")
+        write_model_folder(raw, d, seed=seed)
+        _FOLDERS[key] = d
+    return _FOLDERS[key]
+
+
+def make_engine(folder: str, dtype: str, device: str, page_size: int, pages: int, max_step: int = 256,
+                reqs: int = 4, **kw) -> Engine:
+    return Engine(EngineConfig(model_path=folder, dtype=dtype, device=device, page_size=page_size,
+                               num_page_override=pages, max_step_tokens=max_step, max_extend_tokens=max_step,
+                               max_running_req=reqs, check_cache=True, **kw))
+
+
+def tokens_for(vocab: int, n: int, seed: int) -> List[int]:
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def replay_whole(engine: Engine, rid, toks: Sequence[int]) -> torch.Tensor:
+    out = engine.step([StepEntry(rid, list(toks), list(range(len(toks))))])
+    engine.close(rid)
+    return out.logits.float().cpu().clone()
+
+
+def replay_cuts(engine: Engine, rid, toks: Sequence[int], cuts: Sequence[int]) -> torch.Tensor:
+    """Feed ``toks`` in portions of the given sizes (the rest one by one); logits at every place."""
+    got, i = [], 0
+    cuts = list(cuts)
+    while i < len(toks):
+        c = min(cuts.pop(0) if cuts else 1, len(toks) - i)
+        out = engine.step([StepEntry(rid, list(toks[i:i + c]), list(range(c)))])
+        got.append(out.logits.float().cpu().clone())
+        i += c
+    engine.close(rid)
+    return torch.cat(got)
+
+
+def replay_mixed(engine: Engine, seqs: Dict[str, Sequence[int]], schedule: Sequence[Dict[str, int]],
+                 max_live: int = 4) -> Dict[str, torch.Tensor]:
+    """``schedule``: per step, request -> number of its next tokens.  A request ends (and gives
+    its pages back) right after the step that fed its last token.  Returns logits at every place."""
+    fed = {r: 0 for r in seqs}
+    got: Dict[str, List[torch.Tensor]] = {r: [] for r in seqs}
+    for stepdef in schedule:
+        entries, order = [], []
+        for r, n in stepdef.items():
+            n = min(n, len(seqs[r]) - fed[r])
+            if n <= 0:
+                continue
+            entries.append(StepEntry(r, list(seqs[r][fed[r]:fed[r] + n]), list(range(n))))
+            order.append((r, n))
+        if not entries:
+            continue
+        out = engine.step(entries)
+        logits = out.logits.float().cpu()
+        i = 0
+        for r, n in order:
+            got[r].append(logits[i:i + n].clone())
+            i += n
+            fed[r] += n
+            if fed[r] == len(seqs[r]):
+                engine.close(r)
+    assert all(fed[r] == len(seqs[r]) for r in seqs), "the schedule did not feed every token"
+    return {r: torch.cat(v) for r, v in got.items()}
+
+
+def mixed_schedule(lengths: Dict[str, int], seed: int, max_live: int = 4, budget: int = 40) -> List[Dict[str, int]]:
+    """A schedule with up to ``max_live`` live requests: new ones start while others decode one
+    token at a time; portion sizes change from step to step, down to two tokens."""
+    import random
+
+    rng = random.Random(seed)
+    waiting = list(lengths)
+    live: Dict[str, int] = {}
+    left = dict(lengths)
+    phase: Dict[str, str] = {}
+    steps = []
+    while waiting or live:
+        while waiting and len(live) < max_live and rng.random() < 0.7:
+            r = waiting.pop(0)
+            live[r] = 0
+            phase[r] = "prompt"
+        step: Dict[str, int] = {}
+        room = budget
+        for r in list(live):
+            if rng.random() < 0.15 and len(live) > 1:
+                continue  # a request may sit a step out
+            if phase[r] == "decode":
+                n = 1
+            else:
+                n = rng.choice([2, 2, 3, 5, 7, 11, 13])
+            n = min(n, left[r], room)
+            if n <= 0:
+                continue
+            step[r] = n
+            room -= n
+            left[r] -= n
+            if phase[r] == "prompt" and left[r] <= 32:
+                phase[r] = "decode"
+            if left[r] == 0:
+                del live[r]
+        if step:
+            steps.append(step)
+    return steps

@@ -258,13 +258,32 @@ def router(h: torch.Tensor, w_gate: torch.Tensor, bias: Optional[torch.Tensor], 
     return w * cfg.scale, ids
 
 
-def moe_block(h, W, prefix: str, cfg: PlainConfig, rounding):
+def router_margin(h: torch.Tensor, w_gate: torch.Tensor, bias: Optional[torch.Tensor], cfg: PlainConfig):
+    """Per token, the gap between the last chosen and the first rejected expert's choice score,
+    expressed in units of the router logit (the gap divided by the score's slope there:
+    ``s (1 - s)`` for sigmoid, ``p`` for softmax).  A gap below the noise that reduced
+    precision puts on the logits means that run may legitimately pick another expert."""
+    logits = h.float() @ w_gate.float().T
+    scores = torch.sigmoid(logits) if cfg.scoring == "sigmoid" else torch.softmax(logits, dim=-1)
+    choice = scores + bias.float() if bias is not None else scores
+    if cfg.top_k >= choice.shape[-1]:
+        return torch.full((h.shape[0],), float("inf"))
+    srt, idx = torch.sort(choice, dim=-1, descending=True)
+    gap = srt[:, cfg.top_k - 1] - srt[:, cfg.top_k]
+    s = scores.gather(-1, idx[:, cfg.top_k - 1: cfg.top_k])[:, 0]
+    slope = s * (1 - s) if cfg.scoring == "sigmoid" else s
+    return gap / slope.clamp_min(1e-12)
+
+
+def moe_block(h, W, prefix: str, cfg: PlainConfig, rounding, margins: Optional[list] = None):
     """Routed experts: ``sum_j (act(h W1^T) W2^T) w_j`` with the weight applied to the
     unrounded product and the sum over routes in route order
     (python/freetoken/moe/fused_nvfp4.py:317-344; python/freetoken/kernel/triton/fused_moe.py:287-296,142-152),
     plus the shared expert on the same input (moe.py:87-88)."""
     bias = W.get(prefix + "e_score_correction_bias") if cfg.bias else None
     w, ids = router(h, W[prefix + "gate.weight"], bias, cfg)
+    if margins is not None:
+        margins.append(router_margin(h, W[prefix + "gate.weight"], bias, cfg))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         acc = torch.zeros(h.shape[1], dtype=h.dtype)
@@ -319,7 +338,15 @@ class PlainM3:
         self.dtype = dtype
         self.rounding = rounding
 
-    def hidden_states(self, tokens: Sequence[int], return_layers: bool = False):
+    def router_margins(self, tokens: Sequence[int]) -> torch.Tensor:
+        """``[T]``: each token's smallest router gap over the MoE layers (inf without MoE layers)."""
+        margins: list = []
+        self.hidden_states(tokens, margins=margins)
+        if not margins:
+            return torch.full((len(tokens),), float("inf"))
+        return torch.stack(margins).min(0).values
+
+    def hidden_states(self, tokens: Sequence[int], return_layers: bool = False, margins: Optional[list] = None):
         """Residual stream after the last layer, before the final norm, ``[T, hidden]``.
 
         Pre-norm with the residual carried beside the sub-layer output
@@ -339,7 +366,7 @@ class PlainM3:
             r = r + a
             h = _rnd(rms_norm(r, W[p + "post_attention_layernorm.weight"], cfg.eps, cfg.gemma), rd)
             if cfg.moe_layers[l]:
-                f = moe_block(h, W, p + "block_sparse_moe.", cfg, rd)
+                f = moe_block(h, W, p + "block_sparse_moe.", cfg, rd, margins)
             else:
                 f = gated_mlp(h, W[p + "mlp.gate_proj.weight"], W[p + "mlp.up_proj.weight"],
                               W[p + "mlp.down_proj.weight"], cfg, rd)

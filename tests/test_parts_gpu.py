@@ -1,0 +1,338 @@
+"""Each part alone against the plain implementation's function for it, and the framework's
+openness: a toy mixer with state of its own and a toy architecture, both defined here, are
+registered, built and stepped without any change to the framework's files; a schedule may run a
+layer twice and let a layer read another layer's cache."""
+
+from __future__ import annotations
+
+import json
+import os
+import types
+
+import numpy as np
+import pytest
+import torch
+
+from freetoken_b200.cache import CacheManager
+from freetoken_b200.config.engine_config import EngineConfig
+from freetoken_b200.config.spec import (LayerSpec, ModelSpec, ParamSpec, PartSpec, ScheduleEntry,
+                                        StateNeed)
+from freetoken_b200.engine.engine import Engine, StepEntry
+from freetoken_b200.engine.step import StepBuffers, StepBuilder
+from freetoken_b200.parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, BuildEnv, Mixer, Segment,
+                                  StepState, Workspace)
+from freetoken_b200.registry import Architecture, register_architecture, unregister_architecture
+from freetoken_b200.weights.random_init import random_tensors_cpu, write_model_folder
+from helpers import F32_TOL
+from plain import m3_plain
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def env_for(dtype, max_step=64, max_seq=128):
+    return BuildEnv(dtype=dtype, device=DEV, max_seq_len=max_seq, max_step_tokens=max_step,
+                    workspace=Workspace(DEV))
+
+
+def bind_random(part, dtype, seed=0, scale=None):
+    specs = {}
+
+    def walk(prefix, p):
+        for n, ps in p.param_specs().items():
+            specs[prefix + n] = (p, n, ps)
+        for cn, c in p.children().items():
+            walk(prefix + cn + ".", c)
+
+    walk("", part)
+    cpu = random_tensors_cpu({k: v[2] for k, v in specs.items()}, seed)
+    if scale:
+        cpu = {k: (v.float() * scale).to(v.dtype) for k, v in cpu.items()}
+    per = {}
+    for name, (p, local, ps) in specs.items():
+        dt = dtype if ps.dtype == "compute" else torch.float32
+        per.setdefault(id(p), (p, {}))[1][local] = cpu[name].to(DEV, dt)
+    for p, ts in per.values():
+        p.bind(ts)
+    return {k: v.float() for k, v in cpu.items()}
+
+
+def tol(dtype):
+    return F32_TOL if dtype == torch.float32 else dict(rtol=3e-2, atol=1e-2)
+
+
+def plain_cfg(**kw):
+    base = dict(act="swigluoai", alpha=1.702, limit=7.0, scoring="sigmoid", top_k=2, scale=1.0, bias=True,
+                n_shared=0)
+    base.update(kw)
+    return types.SimpleNamespace(**base)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("gemma", [True, False])
+def test_rmsnorm_part(dtype, gemma):
+    env = env_for(dtype)
+    norm = NORMS.build(PartSpec("rmsnorm", dict(size=88, eps=1e-5, gemma=gemma)), env)
+    W = bind_random(norm, dtype)
+    x = torch.randn(9, 88, device=DEV).to(dtype)
+    res = torch.randn(9, 88, device=DEV)
+    r0 = res.clone()
+    out = torch.empty(9, 88, dtype=dtype, device=DEV)
+    norm.add_forward(x, res, out)
+    want = m3_plain.rms_norm((r0 + x.float()).cpu(), W["weight"], 1e-5, gemma)
+    torch.testing.assert_close(out.float().cpu(), want, **tol(dtype))
+    torch.testing.assert_close(res, r0 + x.float())
+    out2 = torch.empty(9, 88, dtype=dtype, device=DEV)
+    norm.forward(x, out2)
+    torch.testing.assert_close(out2.float().cpu(), m3_plain.rms_norm(x.float().cpu(), W["weight"], 1e-5, gemma),
+                               **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("act", ["silu", "swigluoai"])
+def test_gated_mlp_part(dtype, act):
+    env = env_for(dtype)
+    mlp = FEED_FORWARDS.build(PartSpec("gated_mlp", dict(hidden=80, inter=56, act=act, alpha=1.702, limit=7.0)), env)
+    W = bind_random(mlp, dtype, scale=5.0)
+    h = torch.randn(11, 80, device=DEV).to(dtype)
+    out = mlp.forward(h, None)
+    gu = W["gate_up_proj.weight"]
+    want = m3_plain.gated_mlp(h.float().cpu(), gu[:56], gu[56:], W["down_proj.weight"], plain_cfg(act=act), None)
+    torch.testing.assert_close(out.float().cpu(), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("scoring,bias,shared", [("sigmoid", True, 24), ("softmax", False, 0)])
+def test_moe_part(dtype, scoring, bias, shared):
+    env = env_for(dtype)
+    E, k, H, I = 10, 3, 72, 40
+    moe = FEED_FORWARDS.build(PartSpec("moe", dict(hidden=H, inter=I, n_experts=E, top_k=k, scoring=scoring,
+                                                   bias=bias, scale=2.0, act="silu", shared_inter=shared)), env)
+    W = bind_random(moe, dtype, scale=5.0)
+    h = torch.randn(13, H, device=DEV).to(dtype)
+    out = moe.forward(h, None)
+    pw = {"gate.weight": W["gate.weight"]}
+    if bias:
+        pw["e_score_correction_bias"] = W["e_score_correction_bias"]
+    for e in range(E):
+        pw[f"experts.{e}.w1.weight"] = W["experts.gate_up_proj"][e, :I]
+        pw[f"experts.{e}.w3.weight"] = W["experts.gate_up_proj"][e, I:]
+        pw[f"experts.{e}.w2.weight"] = W["experts.down_proj"][e]
+    if shared:
+        g = W["shared_experts.gate_up_proj.weight"]
+        pw["shared_experts.gate_proj.weight"], pw["shared_experts.up_proj.weight"] = g[:shared], g[shared:]
+        pw["shared_experts.down_proj.weight"] = W["shared_experts.down_proj.weight"]
+    cfg = plain_cfg(act="silu", scoring=scoring, top_k=k, scale=2.0, bias=bias, n_shared=1 if shared else 0)
+    hc = h.float().cpu()
+    want = m3_plain.moe_block(hc, pw, "", cfg, None)
+    margin = m3_plain.router_margin(hc, pw["gate.weight"], pw.get("e_score_correction_bias"), cfg)
+    sure = margin > (0 if dtype == torch.float32 else 1e-2)
+    torch.testing.assert_close(out.float().cpu()[sure], want[sure], **tol(dtype))
+
+
+class AttentionHarness:
+    """A cache manager, a metadata buffer and a step builder around one attention part."""
+
+    def __init__(self, mixer, dtype, page=4, pages=40):
+        self.mixer = mixer
+        self.cache = CacheManager([(0, mixer.cache_need())], page, pages, 4, 128, dtype, DEV, poison=True)
+        self.buffers = StepBuffers(DEV, 1 << 16)
+        self.ws = mixer.env.workspace
+
+    def run(self, entries, h):
+        plan = self.cache.begin_step(entries)
+        segs, info, pos, q0 = [], [], [], 0
+        for (rid, n), kv, row in zip(entries, plan.kv_lens, plan.rows):
+            segs.append(Segment(rid, q0, n, kv))
+            info.append([q0, n, kv, row])
+            pos += list(range(kv - n, kv))
+            q0 += n
+        b = StepBuilder(None, [(s.q_len, s.kv_len) for s in segs], fixed=False, sm_count=148)
+        b.add("positions", np.asarray(pos))
+        b.add("seg_info", np.asarray(info))
+        b.add("slot_map", plan.slot_maps[0])
+        ups = self.cache.take_updates(0)
+        b.add("updates", np.asarray(ups if ups else [[-1, -1]]))
+        self.mixer.prepare(b)
+        tensors, plans = b.finish(self.buffers, self.ws)
+        from freetoken_b200.kernels import ops
+
+        view = self.cache.view(0)
+        ops.table_update(view.block_table, tensors["updates"], max(len(ups), 1))
+        view.slot_map = tensors["slot_map"]
+        step = StepState(n_tokens=q0, segments=segs, token_ids=None, positions=tensors["positions"],
+                         seg_info=tensors["seg_info"], state_slots=None, logit_rows=None, n_logit_rows=0,
+                         attention_plans=plans)
+        out = self.mixer.forward(h, step, view, True).clone()
+        self.cache.end_step()
+        return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv,dim,rd,qk_norm,gemma", [(6, 2, 32, 16, True, True), (5, 5, 48, 48, False, False),
+                                                           (8, 1, 64, 0, True, False)])
+def test_attention_part(dtype, heads, kv, dim, rd, qk_norm, gemma):
+    env = env_for(dtype)
+    H = 96
+    pos = PartSpec("rope_neox", dict(rotary_dim=rd, theta=1234.0)) if rd else PartSpec("none")
+    mixer = MIXERS.build(PartSpec("gqa_attention", dict(hidden=H, n_heads=heads, n_kv_heads=kv, head_dim=dim,
+                                                        qk_norm=qk_norm, eps=1e-5, gemma=gemma, position=pos)), env)
+    W = bind_random(mixer, dtype, scale=3.0)
+    T = 50
+    h = torch.randn(T, H, device=DEV).to(dtype)
+    cfg = types.SimpleNamespace(heads=heads, kv_heads=kv, head_dim=dim, qk_norm=qk_norm, eps=1e-5, gemma=gemma,
+                                rotary_dim=rd)
+    qkv = W["qkv_proj.weight"]
+    pw = {"q_proj.weight": qkv[: heads * dim], "k_proj.weight": qkv[heads * dim: (heads + kv) * dim],
+          "v_proj.weight": qkv[(heads + kv) * dim:], "o_proj.weight": W["o_proj.weight"]}
+    if qk_norm:
+        pw["q_norm.weight"], pw["k_norm.weight"] = W["q_norm.weight"], W["k_norm.weight"]
+    cos, sin = m3_plain.rope_table(rd, 1234.0, T, torch.float32) if rd else (None, None)
+    want = m3_plain.attention_layer(h.float().cpu(), pw, "", cfg, cos, sin, False, None)
+    harness = AttentionHarness(mixer, dtype)
+    harness.cache.open("a")
+    got = torch.cat([harness.run([("a", n)], h[s:s + n]) for s, n in ((0, 17), (17, 2), (19, 30), (49, 1))])
+    torch.testing.assert_close(got.float().cpu(), want, **tol(dtype))
+
+
+# --------------------------------------------------------------------------- toy parts
+DECAY = 0.5
+
+
+class ToyDecayMixer(Mixer):
+    """State of its own: s <- DECAY * s + h_t per request; output = s @ W^T.  Pure PyTorch."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = int(spec["hidden"])
+
+    def param_specs(self):
+        return {"mix.weight": ParamSpec((self.hidden, self.hidden), init=("normal", 0.0, 0.1))}
+
+    def cache_need(self):
+        return StateNeed((("s", (self.hidden,), "float32"),))
+
+    def forward(self, h, step, cache, writes_cache):
+        state = cache.tensors["s"]
+        out = torch.empty_like(h)
+        W = self.params["mix.weight"].float()
+        for seg in step.segments:
+            s = state[seg.state_slot]
+            if seg.is_fresh:
+                s.zero_()
+            for i in range(seg.q_start, seg.q_start + seg.q_len):
+                s.mul_(DECAY).add_(h[i].float())
+                out[i] = (W @ s).to(h.dtype)
+        return out
+
+
+def toy_reference(W, tokens):
+    """Plain statement of the toy model: embedding -> [norm, decay mixer, norm, mlp] x L -> head."""
+    emb = W["model.embed_tokens.weight"]
+    r = emb[torch.as_tensor(tokens)]
+    L = len({k.split(".")[2] for k in W if k.startswith("model.layers.")})
+    for l in range(L):
+        p = f"model.layers.{l}."
+        h = m3_plain.rms_norm(r, W[p + "input_layernorm.weight"], 1e-6, True)
+        s = torch.zeros(h.shape[1])
+        a = torch.empty_like(h)
+        for t in range(h.shape[0]):
+            s = DECAY * s + h[t]
+            a[t] = W[p + "mixer.mix.weight"] @ s
+        r = r + a
+        h = m3_plain.rms_norm(r, W[p + "post_attention_layernorm.weight"], 1e-6, True)
+        gu = W[p + "mlp.gate_up_proj.weight"]
+        I = gu.shape[0] // 2
+        r = r + m3_plain.gated_mlp(h, gu[:I], gu[I:], W[p + "mlp.down_proj.weight"], plain_cfg(act="silu"), None)
+    y = m3_plain.rms_norm(r, W["model.norm.weight"], 1e-6, True)
+    return y @ W["lm_head.weight"].T
+
+
+@pytest.fixture
+def toy_architecture():
+    MIXERS.register("toy_decay")(ToyDecayMixer)
+
+    def parse(raw, num_layers=None):
+        return types.SimpleNamespace(**raw)
+
+    def build_spec(cfg):
+        norm = PartSpec("rmsnorm", dict(size=cfg.hidden, eps=1e-6, gemma=True))
+        block = PartSpec("prenorm_residual", dict(hidden=cfg.hidden, norm=norm))
+        layers = tuple(LayerSpec(name=f"model.layers.{l}", block=block,
+                                 mixer=PartSpec("toy_decay", dict(hidden=cfg.hidden)),
+                                 ffn=PartSpec("gated_mlp", dict(hidden=cfg.hidden, inter=cfg.inter, act="silu")),
+                                 mixer_name="mixer", ffn_name="mlp") for l in range(cfg.layers))
+        return ModelSpec(architecture="ToyStateLM", vocab_size=cfg.vocab, hidden_size=cfg.hidden, layers=layers,
+                         schedule=tuple(ScheduleEntry(l) for l in range(cfg.layers)),
+                         embedding=PartSpec("token_embedding"), final_norm=norm,
+                         head=PartSpec("linear_head", dict(tied=False)), max_position=256)
+
+    register_architecture(Architecture(names=("ToyStateLM",), parse_config=parse, build_spec=build_spec))
+    yield
+    unregister_architecture("ToyStateLM")
+    MIXERS.unregister("toy_decay")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_state_mixer_registers_builds_and_steps(dtype, toy_architecture, tmp_path):
+    from safetensors.torch import load_file
+
+    raw = {"architectures": ["ToyStateLM"], "vocab": 97, "hidden": 48, "inter": 40, "layers": 2}
+    folder = write_model_folder(raw, str(tmp_path / "toy"), seed=4)
+    W = {k: v.float() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    eng = Engine(EngineConfig(model_path=folder, dtype=dtype, page_size=4, num_page_override=8,
+                              max_running_req=3, max_step_tokens=64, check_cache=True))
+    assert not eng.use_graphs and len(eng.cache.state) == 1 and not eng.cache.paged
+    seqs = {r: torch.randint(0, 97, (n,), generator=torch.Generator().manual_seed(n)).tolist()
+            for r, n in (("a", 23), ("b", 31), ("c", 12), ("d", 19))}
+    want = {r: toy_reference(W, t) for r, t in seqs.items()}
+    tolr = F32_TOL if dtype == "float32" else dict(rtol=3e-2, atol=2e-2)
+    fed = {r: 0 for r in seqs}
+    got = {r: [] for r in seqs}
+    plan = [{"a": 5}, {"a": 2, "b": 7}, {"a": 1, "b": 1, "c": 12}, {"a": 15, "b": 2}, {"b": 21, "d": 3},
+            {"d": 1}, {"d": 15}]  # c ends early: d takes over its state slot and must start from zero
+    for stepdef in plan:
+        entries = [StepEntry(r, seqs[r][fed[r]:fed[r] + n], list(range(n))) for r, n in stepdef.items()]
+        out = eng.step(entries).logits.float().cpu()
+        i = 0
+        for r, n in stepdef.items():
+            got[r].append(out[i:i + n].clone())
+            i += n
+            fed[r] += n
+            if fed[r] == len(seqs[r]):
+                eng.close(r)
+    for r in seqs:
+        torch.testing.assert_close(torch.cat(got[r]), want[r], **tolr)
+    eng.cache.check()
+    assert eng.cache.slots.free_count == 3
+
+
+def test_a_schedule_may_repeat_a_layer_and_share_a_cache(tmp_path):
+    """Layer 0 runs twice (entries 0 and 2, each with a cache of its own); entry 3 runs layer 1
+    again but reads the keys and values that entry 1 wrote."""
+    from tiny_configs import TINY_A
+    from freetoken_b200.engine.build import describe_model
+
+    folder = write_model_folder(TINY_A, str(tmp_path / "a"), seed=2)
+    arch, typed, spec, _ = describe_model(TINY_A)
+    sched = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(1, cache_from=1))
+    spec2 = ModelSpec(**{**spec.__dict__, "schedule": sched})
+    cfg = EngineConfig(model_path=folder, dtype="float32", page_size=4, num_page_override=30,
+                       max_step_tokens=64, check_cache=True)
+    eng = Engine(cfg, spec=spec2)
+    from freetoken_b200.engine.build import load_weights
+
+    assert len(eng.cache.paged) == 1 and eng.cache.paged[0].entries == [0, 1, 2]
+    toks = torch.randint(0, 256, (33,), generator=torch.Generator().manual_seed(1)).tolist()
+    whole = eng.step([StepEntry("w", toks, list(range(33)))]).logits.cpu().clone()
+    eng.close("w")
+    parts, i = [], 0
+    for n in (9, 2, 14, 1, 1, 6):
+        parts.append(eng.step([StepEntry("c", toks[i:i + n], list(range(n)))]).logits.cpu().clone())
+        i += n
+    torch.testing.assert_close(torch.cat(parts), whole, **F32_TOL)
+    # and it is a different function from the plain two-layer stack
+    from plain.m3_plain import PlainM3
+
+    assert (PlainM3(folder).logits(toks) - whole).abs().max() > 1e-3

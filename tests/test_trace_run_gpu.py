@@ -1,0 +1,127 @@
+"""bin/trace_run as a user runs it: a trace on standard input, logits in files, compared with the
+plain implementation under every way of cutting and batching, in 32-bit and in bfloat16."""
+
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import F32_TOL, assert_bf16_close, mixed_schedule, model_folder, tokens_for
+from plain.m3_plain import PlainM3
+from tiny_configs import ALL
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TRACE_RUN = os.path.join(ROOT, "bin", "trace_run")
+
+
+def run_trace(folder, dtype, out_dir, max_tokens, steps):
+    lines = "".join(json.dumps(s) + "\n" for s in steps)
+    p = subprocess.run([sys.executable, TRACE_RUN, "--model", folder, "--dtype", dtype, "--out", out_dir,
+                        "--max-tokens", str(max_tokens)], input=lines, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    done = [l for l in p.stdout.splitlines() if l.startswith("done ")]
+    assert done == [f"done {s['step']}" for s in steps]
+    return p
+
+
+def read_logits(out_dir, step, vocab):
+    a = np.fromfile(os.path.join(out_dir, f"{step}.f32"), dtype="<f4")
+    return torch.from_numpy(a.reshape(-1, vocab).copy())
+
+
+def check(got, ref, dtype, margins, what):
+    if dtype == "float32":
+        torch.testing.assert_close(got, ref[: got.shape[0]], **F32_TOL, msg=lambda m: f"{what}: {m}")
+    else:
+        assert_bf16_close(got, ref, margins, what)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_trace_replay(name, dtype, tmp_path_factory, tmp_path):
+    folder = model_folder(tmp_path_factory.getbasetemp(), name, ALL[name])
+    plain = PlainM3(folder)
+    V = plain.cfg.vocab
+    lengths = {"a": 70, "b": 100, "c": 45, "d": 64, "e": 90, "f": 33}
+    seqs = {r: tokens_for(V, n, 50 + i) for i, (r, n) in enumerate(lengths.items())}
+    steps, where = [], {}  # where[(request, mode)] = list of (step, rows, first position)
+    n = 0
+
+    def add(entries, end=()):
+        nonlocal n
+        steps.append({"step": n, "entries": entries, "end": list(end)})
+        n += 1
+        return n - 1
+
+    # 1. whole, every position wanted
+    s = add([{"id": "w", "tokens": seqs["a"], "want": list(range(70))}], end=["w"])
+    where["whole"] = [(s, 70, 0)]
+    # 2. most of it in one step (nothing wanted), then the last 32 one by one
+    add([{"id": "t", "tokens": seqs["a"][:38], "want": []}])
+    where["tail"] = []
+    for i in range(38, 70):
+        s = add([{"id": "t", "tokens": [seqs["a"][i]], "want": [0]}], end=["t"] if i == 69 else [])
+        where["tail"].append((s, 1, i))
+    # 3. portions of changing size, down to two tokens; only some places wanted
+    i, where["cuts"] = 0, []
+    for c in [7, 2, 13, 2, 5, 3, 2, 17, 2, 9, 2, 6]:
+        s = add([{"id": "c", "tokens": seqs["a"][i:i + c], "want": [0, c - 1]}], end=["c"] if i + c == 70 else [])
+        where["cuts"].append((s, c, i))
+        i += c
+    assert i == 70
+    # 4. mixed, up to four live, in a pool of 4 x 128 tokens so that pages are used again
+    fed = {r: 0 for r in seqs}
+    mixed = {r: [] for r in seqs}
+    for stepdef in mixed_schedule(lengths, seed=8):
+        entries, ends = [], []
+        for r, k in stepdef.items():
+            entries.append({"id": "m" + r, "tokens": seqs[r][fed[r]:fed[r] + k], "want": list(range(k))})
+        s = add(entries)
+        for r, k in stepdef.items():
+            mixed[r].append((s, k, fed[r]))
+            fed[r] += k
+            if fed[r] == lengths[r]:
+                steps[-1]["end"].append("m" + r)
+    out_dir = str(tmp_path / "out")
+    run_trace(folder, dtype, out_dir, 4 * 128, steps)
+
+    ref = {r: plain.logits(t) for r, t in seqs.items()}
+    marg = {r: plain.router_margins(t) for r, t in seqs.items()}
+    check(read_logits(out_dir, where["whole"][0][0], V), ref["a"], dtype, marg["a"], "whole")
+    tail = torch.cat([read_logits(out_dir, s, V) for s, _, _ in where["tail"]])
+    check(tail, ref["a"][38:], dtype, marg["a"][38:], "tail")
+    assert not os.path.exists(os.path.join(out_dir, "1.f32"))  # nothing was wanted in that step
+    for s, c, i in where["cuts"]:
+        got = read_logits(out_dir, s, V)
+        assert got.shape[0] == 2
+        idx = torch.tensor([i, i + c - 1])
+        check(got, ref["a"][idx], dtype, marg["a"][idx], f"cut at {i}")
+    files = {}
+    for r in seqs:
+        rows = []
+        for s, k, pos in mixed[r]:
+            if s not in files:
+                files[s] = read_logits(out_dir, s, V)
+            entry_ids = [e["id"] for e in steps[s]["entries"]]
+            off = sum(len(e["want"]) for e in steps[s]["entries"][: entry_ids.index("m" + r)])
+            rows.append(files[s][off:off + k])
+        check(torch.cat(rows), ref[r], dtype, marg[r], f"mixed {r}")
+
+
+def test_trace_run_reports_errors(tmp_path_factory, tmp_path):
+    folder = model_folder(tmp_path_factory.getbasetemp(), "A", ALL["A"])
+    p = subprocess.run([sys.executable, TRACE_RUN, "--model", str(tmp_path / "nothing"), "--dtype", "float32",
+                        "--out", str(tmp_path / "o"), "--max-tokens", "64"], input="", capture_output=True, text=True)
+    assert p.returncode != 0 and "config.json" in p.stderr
+    too_many = json.dumps({"step": 0, "entries": [{"id": "a", "tokens": list(range(100)), "want": []}], "end": []})
+    p = subprocess.run([sys.executable, TRACE_RUN, "--model", folder, "--dtype", "float32",
+                        "--out", str(tmp_path / "o"), "--max-tokens", "64"], input=too_many + "\n",
+                       capture_output=True, text=True)
+    assert p.returncode != 0 and "done 0" not in p.stdout
