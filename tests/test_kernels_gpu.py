@@ -24,6 +24,13 @@ def tol(dtype):
     return dict(rtol=2e-5, atol=2e-6) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-3)
 
 
+def attn_tol(dtype):
+    """Attention outputs: the probabilities are rounded to bfloat16 before P.V (as the reference
+    does, python/freetoken/kernel/triton/attention.py:252,573), an error of up to 2^-9 per
+    probability times values of size up to ~4, plus the rounding of the output itself."""
+    return tol(dtype) if dtype == torch.float32 else dict(rtol=2e-2, atol=1.5e-2)
+
+
 def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
     g = torch.Generator(device="cpu").manual_seed(seed + sum(shape))
     return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
@@ -181,7 +188,7 @@ def test_attention_mixed_batch(dtype, Hq, Hkv, D, P):
     segs = [(1, 1), (1, 130), (17, 17), (5, 69), (2, 64), (33, 200), (1, 65)]
     out, want, _ = run_attention(dtype, Hq, Hkv, D, P, segs, None)
     assert not torch.isnan(out).any()
-    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+    torch.testing.assert_close(out.float(), want.float(), **attn_tol(dtype))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -191,7 +198,7 @@ def test_attention_split_keys(dtype, fixed):
     out, want, plan = run_attention(dtype, 12, 2, 64, 16, segs, None, fixed_splits=fixed, force_split=True)
     assert plan.n_slots > 0
     assert not torch.isnan(out).any()
-    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+    torch.testing.assert_close(out.float(), want.float(), **attn_tol(dtype))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -199,7 +206,7 @@ def test_attention_split_keys(dtype, fixed):
 def test_attention_window(dtype, window):
     segs = [(1, 150), (40, 40), (9, 120)]
     out, want, _ = run_attention(dtype, 6, 3, 32, 8, segs, window)
-    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+    torch.testing.assert_close(out.float(), want.float(), **attn_tol(dtype))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -211,7 +218,7 @@ def test_attention_far_key_stands_out(dtype):
     G = Hq // Hkv
     tile = 64 if dtype == torch.bfloat16 else 16
     out, want, _ = run_attention(dtype, Hq, Hkv, D, P, segs, None, force_split=True, seed=5)
-    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+    torch.testing.assert_close(out.float(), want.float(), **attn_tol(dtype))
     # now make position 3 of segment 0 dominate and check the output equals its value row
     g = torch.Generator().manual_seed(9)
     kv = 700

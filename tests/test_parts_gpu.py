@@ -47,8 +47,9 @@ def bind_random(part, dtype, seed=0, scale=None):
 
     walk("", part)
     cpu = random_tensors_cpu({k: v[2] for k, v in specs.items()}, seed)
-    if scale:
-        cpu = {k: (v.float() * scale).to(v.dtype) for k, v in cpu.items()}
+    if scale:  # matrices only: norm scales and router biases keep their distribution
+        cpu = {k: (v.float() * scale).to(v.dtype) if specs[k][2].dtype == "compute" else v
+               for k, v in cpu.items()}
     per = {}
     for name, (p, local, ps) in specs.items():
         dt = dtype if ps.dtype == "compute" else torch.float32
