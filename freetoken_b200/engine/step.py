@@ -49,6 +49,7 @@ class StepBuffers:
         self.dev = torch.zeros(capacity_ints, dtype=torch.int32, device=device)
         self.events: List[Optional[Any]] = [None, None]
         self.turn = 0
+        self.last_upload_bytes = 0
 
     def grow(self, need: int) -> None:
         if need <= self.capacity:
@@ -71,6 +72,7 @@ class StepBuffers:
         buf = self.host_np[i]
         for (name, arr), off in zip(sections, offsets):
             buf[off:off + arr.size] = arr.reshape(-1)
+        self.last_upload_bytes = 4 * n
         if n:
             self.dev[:n].copy_(self.host[i][:n], non_blocking=True)
         if self.device.type == "cuda":

@@ -92,6 +92,9 @@ class MoE(FeedForward):
         routes = ws.get("moe.routes", (R,), torch.int32, (cap * k,))
         pos = ws.get("moe.pos", (R,), torch.int32, (cap * k,))
         ops.moe_permute(ids, E, counts, offsets, routes, pos)
+        record = self.env.shared.get("record_expert_counts")
+        if record is not None:  # measurement hook: which experts a step touched, layer by layer
+            record.append(counts.clone())
         x = ws.get("moe.x", (R, self.hidden), dt, (cap * k, self.hidden))
         ops.moe_gather(h, routes, k, x)
         a = ws.get("moe.act", (R, self.inter), dt, (cap * k, self.inter))
