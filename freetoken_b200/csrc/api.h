@@ -64,6 +64,11 @@ int ftk_moe_gemm2(const void* a, const void* w2, int dtype, const int32_t* exper
                   int hidden, int inter, void* out, void* stream);
 int ftk_moe_combine(const void* y, int dtype, const int32_t* route_pos, int n_tokens, int top_k,
                     int hidden, const void* shared, void* out, void* stream);
+// Status words of the kernels' bounded waits: out[0] = first code since the last call (0 = none),
+// out[1] = block that recorded it.  Synchronises with the device and clears the words.
+int ftk_read_status(int* out);
+// 0 sends bfloat16 grouped expert products to the CUDA-core kernels; default 1 (tcgen05).
+int ftk_set_moe_tensor_cores(int enabled);
 int ftk_sample(const float* logits, int n_rows, int vocab, const float* temperature,
                const int32_t* top_k, const float* top_p, const float* u, int32_t* out, void* stream);
 

@@ -1,11 +1,523 @@
-// Placeholder until the tcgen05 grouped GEMMs are in: report "not my sizes".
+// Grouped expert matrix products on the 5th-generation tensor cores (tcgen05), bfloat16.
+//
+// Both products are computed transposed ("swap-AB"): the weight tile is the M side of the MMA
+// (128 output features per tile, always full), the expert's token rows are the N side (BN = 16 to
+// 256), so a decode step with a handful of rows per expert still issues full-width MMAs and the
+// kernel's time is the time to stream the weights from HBM once.
+//
+//   D^T[feature, token] = sum_k W[e][feature][k] * X[row(token)][k]
+//
+//   A (weights)      : TMA tiles of bf16, K-major, 128-byte swizzle, from a 3-D tensor map over
+//                      [E, rows, K].  gemm2 takes 128 consecutive rows in one box.  gemm1 interleaves, per
+//                      TMEM lane quadrant, 16 gate rows with the 16 matching up rows (8 boxes of 16 rows),
+//                      so one accumulator holds both halves and a warp finds gate and up of a feature
+//                      16 lanes apart.
+//   B (activations)  : TMA tile [BN rows x 64 k] from a 2-D map over the expert-sorted rows [R, K].
+//   D (accumulator)  : TMEM, 128 lanes x BN float32 columns, two buffers so the epilogue of one tile
+//                      overlaps the main loop of the next.
+//
+// One CTA = 6 warps: warp 0 issues TMA loads, warp 1 allocates TMEM and issues tcgen05.mma, warps 2-5
+// read the accumulator (tcgen05.ld, one TMEM lane quadrant each), apply the epilogue and store.
+//   gemm1 epilogue: gate and up are rounded to bfloat16 (where the reference stores them), the up
+//                   half reaches the gate half's lanes by a warp shuffle, act(g, u) is stored.
+//   gemm2 epilogue: accumulator x route weight (float32), stored as bfloat16.
+// CTAs are persistent: tile t -> (expert, token tile, feature tile) is derived from the device-side
+// expert offsets, so ragged row counts need no padding and no host round trip.
+//
+// No cluster launch and no multicast: every CTA loads its own tiles.  Every wait on an mbarrier is
+// bounded; on a timeout the CTA records a status code, lets copies in flight land, frees its TMEM and
+// returns, and the host reports the code (ftk_read_status).
+//
+// Stands for the reference's Triton grouped GEMM, its per-route decode GEMV and the activation kernel
+// (python/freetoken/kernel/triton/fused_moe.py:156-302, python/freetoken/kernel/triton/decode_moe.py:5-75,
+// python/freetoken/kernel/triton/activation.py:67-112).
+#include <cuda.h>
+
 #include "common.cuh"
 
-int ftk_moe_gemm1_act_tc(const void*, const void*, const int32_t*, int, int, int, int, int, float, float, void*,
-                         cudaStream_t) {
-  return -1;
+namespace ftk {
+
+__device__ int g_status[4];  // [0] first error code, [1] block, [2] detail; 0 = fine
+
+constexpr int kThreads = 192;
+constexpr int kBK = 64;          // k elements per stage (128 bytes: one swizzle row)
+constexpr int kTileM = 128;      // accumulator rows (TMEM lanes)
+constexpr int kABytes = kTileM * kBK * 2;
+constexpr int kMaxExperts = 2048;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
 }
-int ftk_moe_gemm2_tc(const void*, const void*, const int32_t*, const int32_t*, const float*, int, int, int, int, void*,
-                     cudaStream_t) {
-  return -1;
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the barrier did not flip within the limit (or another role gave up).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if ((i & 63) == 63) {
+      if (*abort_flag) return false;
+      __nanosleep(64);
+    }
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(slot)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(addr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3fff);       // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                      // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;            // stride byte offset: next 8-row group
+  d |= (uint64_t)1 << 46;                      // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                      // 128-byte swizzle
+  return d;
+}
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t instr_desc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+}
+
+struct TcParams {
+  const int32_t* offsets;        // [E + 1]
+  int n_experts;
+  int K;                         // reduction length
+  int n_out;                     // output features per row (I for gemm1, H for gemm2)
+  int m_tiles;                   // feature tiles per expert
+  int up_row_offset;             // gemm1: I (row of the up half that matches gate row 0)
+  const int32_t* sorted_routes;  // gemm2
+  const float* route_weights;    // gemm2
+  int n_routes;
+  int act;
+  float alpha, limit;
+  __nv_bfloat16* out;
+};
+
+template <int BN>
+struct Smem {
+  static constexpr int kStages = BN <= 32 ? 6 : (BN <= 128 ? 4 : 3);
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int kDynamic = kStages * kStageBytes + 1024;
+};
+
+template <int BN, bool GATED>
+__global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                               const __grid_constant__ CUtensorMap map_b,
+                                                               TcParams p) {
+  using S = Smem<BN>;
+  extern __shared__ unsigned char dyn_smem[];
+  __shared__ uint64_t full_bar[S::kStages], empty_bar[S::kStages], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  __shared__ int tile_prefix[kMaxExperts + 1];  // token tiles of experts 0..e-1
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t tiles_base = (smem_addr(dyn_smem) + 1023u) & ~1023u;
+  unsigned char* tiles = dyn_smem + (tiles_base - smem_addr(dyn_smem));
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);
+    }
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(&tmem_slot, S::kTmemCols);
+  // token tiles per expert, prefix-summed by warp 0
+  if (warp == 0) {
+    const int E = p.n_experts;
+    const int per = (E + 31) / 32;
+    int local = 0;
+    for (int i = 0; i < per; ++i) {
+      const int e = lane * per + i;
+      if (e < E) local += (p.offsets[e + 1] - p.offsets[e] + BN - 1) / BN;
+    }
+    int incl = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    int run = incl - local;
+    for (int i = 0; i < per; ++i) {
+      const int e = lane * per + i;
+      if (e < E) {
+        tile_prefix[e] = run;
+        run += (p.offsets[e + 1] - p.offsets[e] + BN - 1) / BN;
+      }
+    }
+    if (lane == 31) tile_prefix[E] = incl;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  const int total_tiles = tile_prefix[p.n_experts] * p.m_tiles;
+  const int k_blocks = (p.K + kBK - 1) / kBK;
+  volatile int* abortp = &abort_flag;
+
+  // tile -> expert, token tile, feature tile
+  auto locate = [&](int t, int& e, int& row0, int& rows, int& m0) {
+    const int g = t / p.m_tiles;
+    m0 = (t % p.m_tiles) * (GATED ? 64 : 128);
+    int lo = 0, hi = p.n_experts - 1;  // last e with tile_prefix[e] <= g
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (tile_prefix[mid] <= g) lo = mid; else hi = mid - 1;
+    }
+    e = lo;
+    const int start = p.offsets[e], end = p.offsets[e + 1];
+    row0 = start + (g - tile_prefix[e]) * BN;
+    rows = min(BN, end - row0);
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int e, row0, rows, m0;
+        locate(t, e, row0, rows, m0);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[s], phase ^ 1, abortp)) {
+            ok = false;
+            atomicCAS(&g_status[0], 0, 101);
+            abort_flag = 1;
+            break;
+          }
+          unsigned char* a = tiles + s * S::kStageBytes;
+          mbar_expect_tx(&full_bar[s], S::kStageBytes);
+          if (GATED) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {  // quadrant j/2: 16 gate rows, then the 16 up rows of the same features
+              const int src_row = ((j & 1) ? p.up_row_offset : 0) + m0 + (j >> 1) * 16;
+              tma_load_3d(a + j * 16 * 128, &map_a, &full_bar[s], kb * kBK, src_row, e);
+            }
+          } else {
+            tma_load_3d(a, &map_a, &full_bar[s], kb * kBK, m0, e);
+          }
+          tma_load_2d(a + kABytes, &map_b, &full_bar[s], kb * kBK, row0);
+          if (++s == S::kStages) {
+            s = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BN);
+      int s = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase = 0;  // bit a: phase of accumulator buffer a
+      int acc = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&acc_empty[acc], ((acc_phase >> acc) & 1u) ^ 1u, abortp)) {
+          atomicCAS(&g_status[0], 0, 102);
+          abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[s], phase, abortp)) {
+            ok = false;
+            atomicCAS(&g_status[0], 0, 103);
+            abort_flag = 1;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = tiles_base + s * S::kStageBytes;
+          const uint64_t a_desc = smem_desc(a_addr), b_desc = smem_desc(a_addr + kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k)  // 16 k elements = 32 bytes = 2 descriptor units
+            tc_mma(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+          tc_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
+          if (++s == S::kStages) {
+            s = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        tc_commit(&acc_full[acc]);
+        acc_phase ^= 1u << acc;
+        acc ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quad = warp & 3;               // TMEM lanes [32 quad, 32 quad + 32)
+    const int row_in_tile = quad * 32 + lane;  // accumulator row = feature within the tile
+    uint32_t acc_phase = 0;
+    int acc = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      int e, row0, rows, m0;
+      locate(t, e, row0, rows, m0);
+      // the whole warp takes one decision: the loads below need all 32 lanes
+      if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[acc], (acc_phase >> acc) & 1u, abortp))) {
+        if (lane == 0) atomicCAS(&g_status[0], 0, 104);
+        abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        float v[16];
+        tmem_ld16(t_addr + c, v);
+        if (c + 16 >= BN) {  // last read of this accumulator buffer: hand it back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        }
+        if (GATED) {
+          // lanes 0-15 of a quadrant hold gate, lanes 16-31 the up values of the same 16 features
+          const int f = m0 + quad * 16 + (lane & 15);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float up = __shfl_down_sync(0xffffffffu, v[i], 16);
+            const int n = c + i;
+            if (lane < 16 && f < p.n_out && n < rows) {
+              const float g = to_float(__float2bfloat16_rn(v[i]));
+              const float u = to_float(__float2bfloat16_rn(up));
+              p.out[(size_t)(row0 + n) * p.n_out + f] = __float2bfloat16_rn(gated_act(g, u, p.act, p.alpha, p.limit));
+            }
+          }
+        } else {
+          const int f = m0 + row_in_tile;
+          if (f < p.n_out) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int n = c + i;
+              if (n < rows) {
+                const int route = p.sorted_routes[row0 + n];
+                const float w = (route >= 0 && route < p.n_routes) ? p.route_weights[route] : 0.f;
+                p.out[(size_t)(row0 + n) * p.n_out + f] = __float2bfloat16_rn(v[i] * w);
+              }
+            }
+          }
+        }
+      }
+      acc_phase ^= 1u << acc;
+      acc ^= 1;
+    }
+  }
+  // ---------------------------------------------------------------- teardown
+  if (abort_flag) {
+    if (threadIdx.x == 0) g_status[1] = blockIdx.x;
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);  // let copies in flight land before the CTA leaves
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, S::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  }
+  return fn;
+}
+
+// bf16 tensor [d2][d1][d0] (d0 innermost), box [b1][b0] of one d2 slice (rank 2 when d2 == 0).
+static bool make_map(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t b0,
+                     uint32_t b1) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint32_t rank = d2 ? 3 : 2;
+  cuuint64_t dims[3] = {d0, d1, d2 ? d2 : 1};
+  cuuint64_t strides[2] = {d0 * 2, d0 * d1 * 2};
+  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t elem[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int pick_bn(int n_routes, int n_experts) {
+  const int want = (int)(1.5 * n_routes / n_experts) + 8;
+  for (int bn : {16, 32, 64, 128}) if (want <= bn) return bn;
+  return 256;
+}
+
+template <int BN, bool GATED>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int max_tiles, cudaStream_t s) {
+  using S = Smem<BN>;
+  auto kern = moe_gemm_tc_kernel<BN, GATED>;
+  static int ctas_per_sm = 0, sms = 0;
+  if (!ctas_per_sm) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic) != cudaSuccess) return 2;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int n = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kThreads, S::kDynamic);
+    const int by_tmem = 512 / S::kTmemCols;
+    ctas_per_sm = n < 1 ? 1 : (n > by_tmem ? by_tmem : n);
+  }
+  int grid = sms * ctas_per_sm;
+  if (grid > max_tiles) grid = max_tiles;
+  if (grid < 1) grid = 1;
+  kern<<<grid, kThreads, S::kDynamic, s>>>(ma, mb, p);
+  return 0;
+}
+
+template <bool GATED>
+static int run_tc(const void* x, int x_cols, const void* w, int w_rows, const TcParams& p0, cudaStream_t s,
+                  const char* name) {
+  TcParams p = p0;
+  if (x_cols % 8 != 0 || p.n_experts > kMaxExperts) return -1;  // TMA needs 16-byte row strides
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -1;
+  const int bn = pick_bn(p.n_routes, p.n_experts);
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, w, (uint64_t)x_cols, (uint64_t)w_rows, (uint64_t)p.n_experts, kBK, GATED ? 16 : 128)) return -1;
+  if (!make_map(&mb, x, (uint64_t)x_cols, (uint64_t)p.n_routes, 0, kBK, (uint32_t)bn)) return -1;
+  const int max_tiles = ((p.n_routes + bn - 1) / bn + p.n_experts) * p.m_tiles;
+  int rc;
+  switch (bn) {
+    case 16: rc = launch_tc<16, GATED>(ma, mb, p, max_tiles, s); break;
+    case 32: rc = launch_tc<32, GATED>(ma, mb, p, max_tiles, s); break;
+    case 64: rc = launch_tc<64, GATED>(ma, mb, p, max_tiles, s); break;
+    case 128: rc = launch_tc<128, GATED>(ma, mb, p, max_tiles, s); break;
+    default: rc = launch_tc<256, GATED>(ma, mb, p, max_tiles, s); break;
+  }
+  if (rc) {
+    set_error("%s: cannot configure the tensor-core kernel", name);
+    return rc;
+  }
+  FTK_LAUNCH_CHECK(name);
+  return 0;
+}
+
+}  // namespace ftk
+
+using namespace ftk;
+
+static int g_tc_enabled = 1;
+
+// 0 sends bfloat16 grouped products to the CUDA-core kernels (for comparisons); default 1.
+extern "C" int ftk_set_moe_tensor_cores(int enabled) {
+  g_tc_enabled = enabled ? 1 : 0;
+  return 0;
+}
+
+int ftk_moe_gemm1_act_tc(const void* x_sorted, const void* w1, const int32_t* expert_offsets, int n_experts,
+                         int n_routes, int hidden, int inter, int act, float alpha, float limit, void* out,
+                         cudaStream_t stream) {
+  if (!g_tc_enabled) return -1;
+  TcParams p{};
+  p.offsets = expert_offsets; p.n_experts = n_experts; p.K = hidden; p.n_out = inter;
+  p.m_tiles = (inter + 63) / 64; p.up_row_offset = inter; p.n_routes = n_routes;
+  p.act = act; p.alpha = alpha; p.limit = limit; p.out = (__nv_bfloat16*)out;
+  return run_tc<true>(x_sorted, hidden, w1, 2 * inter, p, stream, "moe_gemm1_act (tcgen05)");
+}
+
+int ftk_moe_gemm2_tc(const void* a, const void* w2, const int32_t* expert_offsets, const int32_t* sorted_routes,
+                     const float* topk_weights, int n_experts, int n_routes, int hidden, int inter, void* out,
+                     cudaStream_t stream) {
+  if (!g_tc_enabled) return -1;
+  TcParams p{};
+  p.offsets = expert_offsets; p.n_experts = n_experts; p.K = inter; p.n_out = hidden;
+  p.m_tiles = (hidden + 127) / 128; p.sorted_routes = sorted_routes; p.route_weights = topk_weights;
+  p.n_routes = n_routes; p.out = (__nv_bfloat16*)out;
+  return run_tc<false>(a, inter, w2, hidden, p, stream, "moe_gemm2 (tcgen05)");
+}
+
+// Status of the bounded waits: out[0] = first code recorded since the last call (0 = none),
+// out[1] = block, then cleared.  Synchronises with the device.
+extern "C" int ftk_read_status(int* out) {
+  int host[4] = {0, 0, 0, 0};
+  if (cudaMemcpyFromSymbol(host, g_status, sizeof(host)) != cudaSuccess) {
+    set_error("read_status: cannot read the status words");
+    return 2;
+  }
+  out[0] = host[0];
+  out[1] = host[1];
+  if (host[0]) {
+    int zero[4] = {0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_status, zero, sizeof(zero));
+  }
+  return 0;
 }

@@ -68,6 +68,8 @@ _SIGNATURES = {
     "ftk_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
     "ftk_cast": [_vp, _i, _vp, _i, ctypes.c_longlong, _vp],
     "ftk_table_update": [_vp, ctypes.c_longlong, _vp, _i, _vp],
+    "ftk_read_status": [ctypes.POINTER(ctypes.c_int)],
+    "ftk_set_moe_tensor_cores": [_i],
 }
 _bound = False
 _launches = 0
@@ -125,6 +127,28 @@ def _dev(t: Optional[torch.Tensor], what: str, dtype: Optional[torch.dtype] = No
     if dtype is not None and t.dtype != dtype:
         raise KernelError(f"{what}: expected {dtype}, got {t.dtype}")
     return t.data_ptr()
+
+
+def read_status() -> int:
+    """Code left by a kernel whose bounded wait ran out since the last call (0 = none).  Waits
+    for the device.  101-104 come from the tensor-core grouped GEMM (producer, accumulator
+    hand-back, operand arrival, accumulator arrival)."""
+    out = (ctypes.c_int * 2)()
+    status = _lib().ftk_read_status(out)
+    if status != 0:
+        raise KernelError("read_status: " + library.load().ftk_last_error().decode())
+    return int(out[0])
+
+
+def check_status() -> None:
+    code = read_status()
+    if code:
+        raise KernelError(f"a kernel gave up waiting (status {code}); its results are not valid")
+
+
+def set_moe_tensor_cores(enabled: bool) -> None:
+    """False sends bfloat16 grouped expert products to the CUDA-core kernels (comparisons only)."""
+    _lib().ftk_set_moe_tensor_cores(1 if enabled else 0)
 
 
 # --------------------------------------------------------------------------- elementwise

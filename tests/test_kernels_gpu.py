@@ -308,6 +308,42 @@ def test_moe_grouped_gemms(dtype, E, H, I, counts, act):
     torch.testing.assert_close(y.float(), y2.float(), **tol(dtype))
 
 
+@pytest.mark.parametrize("E,H,I,R,k", [(256, 3072, 1536, 64, 8), (256, 3072, 1536, 2048, 8), (32, 512, 256, 700, 4),
+                                       (8, 64, 32, 9, 2), (16, 1024, 1000, 300, 2)])
+def test_moe_tensor_core_gemms_match_cuda_core_gemms(E, H, I, R, k):
+    """The tcgen05 kernels against the CUDA-core kernels on the same inputs (and, for the small
+    cases, against the plain reference), at decode-like and prefill-like row counts, including
+    experts without rows and experts with more rows than one token tile."""
+    g = torch.Generator().manual_seed(R)
+    ids = torch.randint(0, E, (R,), generator=g)
+    if R > 100:
+        ids[: R // 3] = 3  # one crowded expert: several token tiles
+    counts = torch.bincount(ids, minlength=E)
+    off = torch.tensor([0] + counts.cumsum(0).tolist(), dtype=torch.int32, device=DEV)
+    x = rnd(R, H, dtype=torch.bfloat16)
+    w1 = rnd(E, 2 * I, H, dtype=torch.bfloat16, scale=0.05)
+    w2 = rnd(E, H, I, dtype=torch.bfloat16, scale=0.05)
+    routes = torch.randperm(R).to(torch.int32).to(DEV)
+    wts = torch.rand(R, device=DEV) + 0.5
+    outs = []
+    for tc in (True, False):
+        ops.set_moe_tensor_cores(tc)
+        a = torch.full((R, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+        y = torch.full((R, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.moe_gemm1_act(x, w1, off, "swigluoai", 1.702, 7.0, a)
+        ops.moe_gemm2(a, w2, off, routes, wts, y)
+        outs.append((a, y))
+    ops.set_moe_tensor_cores(True)
+    assert ops.read_status() == 0
+    for got, want in zip(*outs):
+        assert not torch.isnan(got).any()
+        torch.testing.assert_close(got.float(), want.float(), **tol(torch.bfloat16))
+    if R <= 700:
+        a2 = torch.empty(R, I, dtype=torch.bfloat16, device=DEV)
+        ref.moe_gemm1_act(x, w1, off, "swigluoai", 1.702, 7.0, a2)
+        torch.testing.assert_close(outs[0][0].float(), a2.float(), **tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("V", [256, 331, 50000])
 def test_sample(V):
     R = 9
