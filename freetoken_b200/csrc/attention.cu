@@ -514,3 +514,63 @@ extern "C" int ftk_paged_attention(const void* q, const void* k_slab, const void
   }
   return 0;
 }
+
+// ================================================================= entry point without allocation
+// See no_alloc.h.  The split-tile scratch lives in this file-scope device array; host code must not
+// pass the array's name to a kernel (on the host it is only a stand-in), so the device address is
+// looked up once per device with cudaGetSymbolAddress and handed to the launch as a pointer.
+#include "no_alloc.h"
+
+static __device__ __align__(256) float g_static_scratch[FTK_STATIC_SCRATCH_BYTES / sizeof(float)];
+
+static float* static_scratch_address() {
+  constexpr int kMaxDevices = 64;
+  static float* addr[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    ftk::set_error("paged_attention_static_scratch: cannot tell the current device");
+    return nullptr;
+  }
+  if (!addr[dev]) {  // set-up, once per device, with that device current
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p) {
+      ftk::set_error("paged_attention_static_scratch: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    addr[dev] = static_cast<float*>(p);
+  }
+  return addr[dev];
+}
+
+extern "C" int ftk_paged_attention_static_scratch(const void* q, const void* k_slab, const void* v_slab, int dtype,
+                                                  const int32_t* block_table, int bt_stride, const int32_t* seg_info,
+                                                  int n_segs, const int32_t* items_host_copy, const int32_t* items,
+                                                  int n_items, void* out, int n_q_heads, int n_kv_heads, int head_dim,
+                                                  int page_size, int num_pages, int tile_rows, float scale, int window,
+                                                  void* stream) {
+  FTK_REQUIRE(n_items >= 0, "paged_attention_static_scratch: bad item count");
+  FTK_REQUIRE(n_items == 0 || items_host_copy, "paged_attention_static_scratch: the host copy of the work list is needed to size the scratch");
+  FTK_REQUIRE(n_kv_heads >= 1 && tile_rows >= 1 && head_dim >= 1, "paged_attention_static_scratch: bad sizes");
+  // slots the work list uses: a split tile owns slots [base, base + n_splits)
+  long long n_slots = 0;
+  for (int i = 0; i < n_items; ++i) {
+    const int32_t* w = items_host_copy + (size_t)i * 8;
+    if (w[5] > 1 && (long long)w[7] + w[5] > n_slots) n_slots = (long long)w[7] + w[5];
+  }
+  const long long rows = n_slots * n_kv_heads * tile_rows;
+  const long long need = rows * (head_dim + 2) * (long long)sizeof(float);
+  FTK_REQUIRE(need <= (long long)FTK_STATIC_SCRATCH_BYTES,
+              "paged_attention_static_scratch: the work list needs %lld bytes of scratch, the static array holds %u "
+              "(use ftk_paged_attention with your own scratch, or fewer splits)", need, FTK_STATIC_SCRATCH_BYTES);
+  float* base = nullptr;
+  if (n_slots > 0) {
+    base = static_scratch_address();
+    if (!base) return 3;
+  }
+  float* part_o = base;
+  float* part_ml = base ? base + rows * head_dim : nullptr;
+  return ftk_paged_attention(q, k_slab, v_slab, dtype, block_table, bt_stride, seg_info, n_segs, items, n_items,
+                             part_o, part_ml, (int)n_slots, out, n_q_heads, n_kv_heads, head_dim, page_size, num_pages,
+                             tile_rows, scale, window, stream);
+}
