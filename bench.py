@@ -160,6 +160,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
+                    help="run only that phase and bracket `--steps` steps of it with cudaProfilerStart/Stop "
+                         "(for ncu --profile-from-start off); prints no bench line")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is outside its scope")
@@ -197,6 +200,29 @@ def main():
 
     def ev():
         return torch.cuda.Event(enable_timing=True)
+
+    if args.profile:
+        if args.profile == "prefill":
+            for i in range(args.warmup + args.steps):
+                if i == args.warmup:
+                    torch.cuda.synchronize()
+                    torch.cuda.profiler.start()
+                engine.step([StepEntry(("p", i), rng.integers(0, V, PROMPT).tolist(), [PROMPT - 1])])
+                engine.close(("p", i))
+        else:
+            rids = [("d", i) for i in range(args.batch)]
+            for r in rids:
+                engine.step([StepEntry(r, rng.integers(0, V, PROMPT).tolist(), [])])
+            for i in range(args.warmup + args.steps):
+                if i == args.warmup:
+                    torch.cuda.synchronize()
+                    torch.cuda.profiler.start()
+                out = engine.step([StepEntry(r, [int(rng.integers(0, V))], [0]) for r in rids])
+                sampler.sample(out.logits, [SamplingParams()] * len(rids), rids, [i] * len(rids))
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(f"profiled {args.steps} {args.profile} step(s)")
+        return 0
 
     # ------------------------------------------------------------------ prefill of one 2048-token prompt
     prefill = None

@@ -9,9 +9,10 @@
 //
 //   A (weights)      : TMA tiles of bf16, K-major, 128-byte swizzle, from a 3-D tensor map over
 //                      [E, rows, K].  gemm2 takes 128 consecutive rows in one box.  gemm1 interleaves, per
-//                      TMEM lane quadrant, 16 gate rows with the 16 matching up rows (8 boxes of 16 rows),
-//                      so one accumulator holds both halves and a warp finds gate and up of a feature
-//                      16 lanes apart.
+//                      TMEM lane quadrant, 16 gate rows with the 16 matching up rows, so one accumulator
+//                      holds both halves and a warp finds gate and up of a feature 16 lanes apart; the
+//                      interleave is done by the tensor map itself (a 5-D view [E, I/16, 2, 16, K] of the
+//                      weights), so it is still one TMA instruction per stage.
 //   B (activations)  : TMA tile [BN rows x 64 k] from a 2-D map over the expert-sorted rows [R, K].
 //   D (accumulator)  : TMEM, 128 lanes x BN float32 columns, two buffers so the epilogue of one tile
 //                      overlaps the main loop of the next.
@@ -21,6 +22,8 @@
 //   gemm1 epilogue: gate and up are rounded to bfloat16 (where the reference stores them), the up
 //                   half reaches the gate half's lanes by a warp shuffle, act(g, u) is stored.
 //   gemm2 epilogue: accumulator x route weight (float32), stored as bfloat16.
+//   Both epilogues turn the (feature x token) accumulator chunk round in a warp-private piece of
+//   shared memory and store 16 bytes per thread.
 // CTAs are persistent: tile t -> (expert, token tile, feature tile) is derived from the device-side
 // expert offsets, so ragged row counts need no padding and no host round trip.
 //
@@ -43,7 +46,7 @@ constexpr int kThreads = 192;
 constexpr int kBK = 64;          // k elements per stage (128 bytes: one swizzle row)
 constexpr int kTileM = 128;      // accumulator rows (TMEM lanes)
 constexpr int kABytes = kTileM * kBK * 2;
-constexpr int kMaxExperts = 2048;
+constexpr int kMaxExperts = 1024;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -88,6 +91,12 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, u
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
+__device__ __forceinline__ void tma_load_5d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
+                                            int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(slot)), "r"(cols) : "memory");
   asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -117,6 +126,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t addr, float (&v)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&t);
 }
 
 // Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
@@ -151,7 +165,7 @@ struct TcParams {
 
 template <int BN>
 struct Smem {
-  static constexpr int kStages = BN <= 32 ? 6 : (BN <= 128 ? 4 : 3);
+  static constexpr int kStages = BN <= 16 ? 5 : (BN <= 128 ? 4 : 3);  // two CTAs per SM up to BN = 64
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
@@ -168,6 +182,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   __shared__ int tile_prefix[kMaxExperts + 1];  // token tiles of experts 0..e-1
+  __shared__ float turn[4][16][33];             // per epilogue warp: a 16-token chunk turned round
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t tiles_base = (smem_addr(dyn_smem) + 1023u) & ~1023u;
@@ -252,12 +267,8 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
           }
           unsigned char* a = tiles + s * S::kStageBytes;
           mbar_expect_tx(&full_bar[s], S::kStageBytes);
-          if (GATED) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {  // quadrant j/2: 16 gate rows, then the 16 up rows of the same features
-              const int src_row = ((j & 1) ? p.up_row_offset : 0) + m0 + (j >> 1) * 16;
-              tma_load_3d(a + j * 16 * 128, &map_a, &full_bar[s], kb * kBK, src_row, e);
-            }
+          if (GATED) {  // (k, row in group, gate|up, group of 16 features, expert)
+            tma_load_5d(a, &map_a, &full_bar[s], kb * kBK, 0, 0, m0 >> 4, e);
           } else {
             tma_load_3d(a, &map_a, &full_bar[s], kb * kBK, m0, e);
           }
@@ -314,7 +325,6 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quad = warp & 3;               // TMEM lanes [32 quad, 32 quad + 32)
-    const int row_in_tile = quad * 32 + lane;  // accumulator row = feature within the tile
     uint32_t acc_phase = 0;
     int acc = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
@@ -337,32 +347,63 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[acc]);
         }
+        float (*tb)[33] = turn[quad];
         if (GATED) {
           // lanes 0-15 of a quadrant hold gate, lanes 16-31 the up values of the same 16 features
-          const int f = m0 + quad * 16 + (lane & 15);
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float up = __shfl_down_sync(0xffffffffu, v[i], 16);
-            const int n = c + i;
-            if (lane < 16 && f < p.n_out && n < rows) {
+            if (lane < 16) {
               const float g = to_float(__float2bfloat16_rn(v[i]));
               const float u = to_float(__float2bfloat16_rn(up));
-              p.out[(size_t)(row0 + n) * p.n_out + f] = __float2bfloat16_rn(gated_act(g, u, p.act, p.alpha, p.limit));
+              tb[i][lane] = gated_act(g, u, p.act, p.alpha, p.limit);
             }
           }
+          __syncwarp();
+          // 16 tokens x 16 features: one 16-byte store (8 features of one token) per thread
+          const int n = c + (lane >> 1), f0 = m0 + quad * 16 + (lane & 1) * 8;
+          if (n < rows && f0 < p.n_out) {
+            const float* src = &tb[lane >> 1][(lane & 1) * 8];
+            __nv_bfloat16* dst = p.out + (size_t)(row0 + n) * p.n_out + f0;
+            if (f0 + 8 <= p.n_out) {
+              uint4 pk;
+              pk.x = pack2(src[0], src[1]); pk.y = pack2(src[2], src[3]);
+              pk.z = pack2(src[4], src[5]); pk.w = pack2(src[6], src[7]);
+              *reinterpret_cast<uint4*>(dst) = pk;
+            } else {
+              for (int e2 = 0; f0 + e2 < p.n_out; ++e2) dst[e2] = __float2bfloat16_rn(src[e2]);
+            }
+          }
+          __syncwarp();
         } else {
-          const int f = m0 + row_in_tile;
-          if (f < p.n_out) {
+          // route weights of this chunk's 16 tokens: lanes 0-15 fetch one each
+          float wl = 0.f;
+          if (lane < 16 && c + lane < rows) {
+            const int route = p.sorted_routes[row0 + c + lane];
+            wl = (route >= 0 && route < p.n_routes) ? p.route_weights[route] : 0.f;
+          }
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int n = c + i;
-              if (n < rows) {
-                const int route = p.sorted_routes[row0 + n];
-                const float w = (route >= 0 && route < p.n_routes) ? p.route_weights[route] : 0.f;
-                p.out[(size_t)(row0 + n) * p.n_out + f] = __float2bfloat16_rn(v[i] * w);
+          for (int i = 0; i < 16; ++i) tb[i][lane] = v[i] * __shfl_sync(0xffffffffu, wl, i);
+          __syncwarp();
+          // 16 tokens x 32 features: two 16-byte stores per thread
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int tk = (lane >> 2) + 8 * j;
+            const int n = c + tk, f0 = m0 + quad * 32 + (lane & 3) * 8;
+            if (n < rows && f0 < p.n_out) {
+              const float* src = &tb[tk][(lane & 3) * 8];
+              __nv_bfloat16* dst = p.out + (size_t)(row0 + n) * p.n_out + f0;
+              if (f0 + 8 <= p.n_out) {
+                uint4 pk;
+                pk.x = pack2(src[0], src[1]); pk.y = pack2(src[2], src[3]);
+                pk.z = pack2(src[4], src[5]); pk.w = pack2(src[6], src[7]);
+                *reinterpret_cast<uint4*>(dst) = pk;
+              } else {
+                for (int e2 = 0; f0 + e2 < p.n_out; ++e2) dst[e2] = __float2bfloat16_rn(src[e2]);
               }
             }
           }
+          __syncwarp();
         }
       }
       acc_phase ^= 1u << acc;
@@ -401,17 +442,20 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// bf16 tensor [d2][d1][d0] (d0 innermost), box [b1][b0] of one d2 slice (rank 2 when d2 == 0).
-static bool make_map(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t b0,
-                     uint32_t b1) {
+// bf16 tensor map with 128-byte swizzle: `rank` dims (innermost first), byte strides of dims 1.., box.
+static bool make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
+                     const uint32_t* box) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
-  const cuuint32_t rank = d2 ? 3 : 2;
-  cuuint64_t dims[3] = {d0, d1, d2 ? d2 : 1};
-  cuuint64_t strides[2] = {d0 * 2, d0 * d1 * 2};
-  cuuint32_t box[3] = {b0, b1, 1};
-  cuuint32_t elem[3] = {1, 1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, elem,
+  cuuint64_t d[5], st[4];
+  cuuint32_t b[5], elem[5];
+  for (int i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    b[i] = box[i];
+    elem[i] = 1;
+    if (i) st[i - 1] = strides[i - 1];
+  }
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), d, st, b, elem,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -448,12 +492,43 @@ template <bool GATED>
 static int run_tc(const void* x, int x_cols, const void* w, int w_rows, const TcParams& p0, cudaStream_t s,
                   const char* name) {
   TcParams p = p0;
-  if (x_cols % 8 != 0 || p.n_experts > kMaxExperts) return -1;  // TMA needs 16-byte row strides
+  // TMA needs 16-byte row strides; the epilogue stores 8 features at a time; the gate/up interleave
+  // works on groups of 16 features
+  if (x_cols % 8 != 0 || p.n_out % 8 != 0 || p.n_experts > kMaxExperts) return -1;
+  if (GATED && p.n_out % 16 != 0) return -1;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -1;
   const int bn = pick_bn(p.n_routes, p.n_experts);
   CUtensorMap ma, mb;
-  if (!make_map(&ma, w, (uint64_t)x_cols, (uint64_t)w_rows, (uint64_t)p.n_experts, kBK, GATED ? 16 : 128)) return -1;
-  if (!make_map(&mb, x, (uint64_t)x_cols, (uint64_t)p.n_routes, 0, kBK, (uint32_t)bn)) return -1;
+  const uint64_t K = (uint64_t)x_cols;
+  if (GATED) {
+    // [E][2][I/16][16][K] seen as (K, 16, 2, I/16, E): a box of (64, 16, 2, 4, 1) lands in shared memory as
+    // 4 groups of [16 gate rows, 16 up rows]
+    const uint64_t I = (uint64_t)p.n_out;
+    const uint64_t dims[5] = {K, 16, 2, I / 16, (uint64_t)p.n_experts};
+    const uint64_t strides[4] = {K * 2, I * K * 2, 16 * K * 2, 2 * I * K * 2};
+    const uint32_t box[5] = {kBK, 16, 2, 4, 1};
+    if (!make_map(&ma, w, 5, dims, strides, box)) {
+      set_error("%s: cuTensorMapEncodeTiled refused the weight map", name);
+      return 4;
+    }
+  } else {
+    const uint64_t dims[3] = {K, (uint64_t)w_rows, (uint64_t)p.n_experts};
+    const uint64_t strides[2] = {K * 2, (uint64_t)w_rows * K * 2};
+    const uint32_t box[3] = {kBK, 128, 1};
+    if (!make_map(&ma, w, 3, dims, strides, box)) {
+      set_error("%s: cuTensorMapEncodeTiled refused the weight map", name);
+      return 4;
+    }
+  }
+  {
+    const uint64_t dims[2] = {K, (uint64_t)p.n_routes};
+    const uint64_t strides[1] = {K * 2};
+    const uint32_t box[2] = {kBK, (uint32_t)bn};
+    if (!make_map(&mb, x, 2, dims, strides, box)) {
+      set_error("%s: cuTensorMapEncodeTiled refused the activation map", name);
+      return 4;
+    }
+  }
   const int max_tiles = ((p.n_routes + bn - 1) / bn + p.n_experts) * p.m_tiles;
   int rc;
   switch (bn) {

@@ -1,0 +1,176 @@
+"""Times one kernel at a time at given sizes and reports it against its roofline.
+
+    python -m freetoken_b200.kernels.microbench moe --experts 256 --tokens 8 [--hidden 3072 --inter 1536 --top-k 8]
+    python -m freetoken_b200.kernels.microbench attention --batch 8 --context 2048
+    python -m freetoken_b200.kernels.microbench attention --prefill 2048
+    python -m freetoken_b200.kernels.microbench sample --rows 8 --vocab 200064
+
+Each case allocates its inputs once (larger than L2 where the real workload is), warms up, then
+times ``--iters`` launches with CUDA events and prints one JSON line: time, the bytes the kernel has
+to move (or its flops), and the fraction of the HBM or tensor peak that this is.  ``--profile`` brackets
+a few launches with cudaProfilerStart/Stop for ``ncu --profile-from-start off`` on a small case.
+The reference reports per-kernel bandwidth the same way (python/freetoken/benchmark/perf.py:60-74).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import torch
+
+from ..engine.attention_plan import build_plan
+from . import ops
+
+HBM_GBS = 6650.0
+BF16_TFLOPS = 1590.0
+
+
+def _time(fn, iters: int, warmup: int, profile: bool) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if profile:
+        torch.cuda.profiler.start()
+        for _ in range(min(iters, 3)):
+            fn()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        return float("nan")
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters * 1e3  # microseconds
+
+
+def bench_moe(a) -> dict:
+    dev = "cuda"
+    E, H, I, k, T = a.experts, a.hidden, a.inter, a.top_k, a.tokens
+    g = torch.Generator(device=dev).manual_seed(0)
+    w1 = torch.empty(E, 2 * I, H, dtype=torch.bfloat16, device=dev).normal_(0, 0.02, generator=g)
+    w2 = torch.empty(E, H, I, dtype=torch.bfloat16, device=dev).normal_(0, 0.02, generator=g)
+    ids = torch.stack([torch.randperm(E, device=dev, generator=g)[:k] for _ in range(T)]).to(torch.int32)
+    counts = torch.empty(E, dtype=torch.int32, device=dev)
+    off = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    routes = torch.empty(T * k, dtype=torch.int32, device=dev)
+    pos = torch.empty(T * k, dtype=torch.int32, device=dev)
+    ops.moe_permute(ids, E, counts, off, routes, pos)
+    h = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+    x = torch.empty(T * k, H, dtype=torch.bfloat16, device=dev)
+    ops.moe_gather(h, routes, k, x)
+    act = torch.empty(T * k, I, dtype=torch.bfloat16, device=dev)
+    y = torch.empty(T * k, H, dtype=torch.bfloat16, device=dev)
+    wts = torch.rand(T * k, device=dev)
+    distinct = int((counts > 0).sum())
+    out = {}
+    for name, fn, wbytes, flops in (
+            ("gemm1", lambda: ops.moe_gemm1_act(x, w1, off, "silu", 1.702, 7.0, act), distinct * 2 * I * H * 2,
+             2 * T * k * 2 * I * H),
+            ("gemm2", lambda: ops.moe_gemm2(act, w2, off, routes, wts, y), distinct * H * I * 2, 2 * T * k * H * I)):
+        if a.only and a.only != name:
+            continue
+        us = _time(fn, a.iters, a.warmup, a.profile)
+        out[name] = {"us": round(us, 2), "weight_bytes": wbytes, "gbs": round(wbytes / us / 1e3, 1),
+                     "hbm_frac": round(wbytes / us / 1e3 / HBM_GBS, 3),
+                     "tflops": round(flops / us / 1e6, 1), "tensor_frac": round(flops / us / 1e6 / BF16_TFLOPS, 3)}
+    out["distinct_experts"] = distinct
+    out["status"] = ops.read_status()
+    return out
+
+
+def bench_attention(a) -> dict:
+    dev = "cuda"
+    Hq, Hkv, D, P = a.q_heads, a.kv_heads, a.head_dim, a.page_size
+    G = Hq // Hkv
+    if a.prefill:
+        segs = [(a.prefill, a.prefill)]
+    else:
+        segs = [(1, a.context)] * a.batch
+    n_pages = sum(-(-kv // P) for _, kv in segs) + 1
+    g = torch.Generator(device=dev).manual_seed(0)
+    ks = torch.empty(n_pages, Hkv, P, D, dtype=torch.bfloat16, device=dev).normal_(0, 1, generator=g)
+    vs = torch.empty(n_pages, Hkv, P, D, dtype=torch.bfloat16, device=dev).normal_(0, 1, generator=g)
+    width = max(-(-kv // P) for _, kv in segs)
+    bt = torch.zeros(len(segs), width, dtype=torch.int32)
+    info, q0, page = [], 0, 1
+    for row, (ql, kv) in enumerate(segs):
+        n = -(-kv // P)
+        bt[row, :n] = torch.arange(page, page + n)
+        page += n
+        info.append([q0, ql, kv, row])
+        q0 += ql
+    bt = bt.to(dev)
+    seg = torch.tensor(info, dtype=torch.int32, device=dev)
+    q = torch.randn(q0, Hq, D, device=dev, generator=g).to(torch.bfloat16)
+    fixed = None
+    if not a.prefill:
+        fixed = int(min(16, max(1, -(-2 * 148 // (len(segs) * Hkv))))) if a.splits is None else a.splits
+    plan = build_plan(segs, G, 64, None, Hkv, fixed_splits=fixed)
+    items = torch.from_numpy(plan.items).to(dev)
+    po = pm = None
+    if plan.n_slots:
+        po = torch.empty(plan.n_slots, Hkv, 64, D, dtype=torch.float32, device=dev)
+        pm = torch.empty(plan.n_slots, Hkv, 64, 2, dtype=torch.float32, device=dev)
+    out = torch.empty_like(q)
+    us = _time(lambda: ops.paged_attention(q, ks, vs, bt, seg, len(segs), items, plan.n_items, po, pm, out, 64,
+                                           D ** -0.5, None), a.iters, a.warmup, a.profile)
+    kv_bytes = sum(kv for _, kv in segs) * Hkv * D * 2 * 2
+    flops = sum(4 * (ql * kv - ql * (ql - 1) // 2) * Hq * D for ql, kv in segs)
+    return {"us": round(us, 2), "items": plan.n_items, "kv_bytes": kv_bytes, "gbs": round(kv_bytes / us / 1e3, 1),
+            "hbm_frac": round(kv_bytes / us / 1e3 / HBM_GBS, 3), "tflops": round(flops / us / 1e6, 1),
+            "tensor_frac": round(flops / us / 1e6 / BF16_TFLOPS, 3)}
+
+
+def bench_sample(a) -> dict:
+    dev = "cuda"
+    logits = torch.randn(a.rows, a.vocab, device=dev)
+    temp = torch.full((a.rows,), a.temperature, device=dev)
+    top_k = torch.zeros(a.rows, dtype=torch.int32, device=dev)
+    top_p = torch.ones(a.rows, device=dev)
+    u = torch.rand(a.rows, device=dev)
+    out = torch.empty(a.rows, dtype=torch.int32, device=dev)
+    us = _time(lambda: ops.sample(logits, temp, top_k, top_p, u, out), a.iters, a.warmup, a.profile)
+    nbytes = a.rows * a.vocab * 4
+    return {"us": round(us, 2), "bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1)}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="microbench")
+    sub = ap.add_subparsers(dest="case", required=True)
+    for name in ("moe", "attention", "sample"):
+        p = sub.add_parser(name)
+        p.add_argument("--iters", type=int, default=20)
+        p.add_argument("--warmup", type=int, default=5)
+        p.add_argument("--profile", action="store_true")
+        if name == "moe":
+            p.add_argument("--experts", type=int, default=256)
+            p.add_argument("--tokens", type=int, default=8)
+            p.add_argument("--hidden", type=int, default=3072)
+            p.add_argument("--inter", type=int, default=1536)
+            p.add_argument("--top-k", type=int, default=8)
+            p.add_argument("--only", choices=["gemm1", "gemm2"], default=None)
+        elif name == "attention":
+            p.add_argument("--batch", type=int, default=8)
+            p.add_argument("--context", type=int, default=2048)
+            p.add_argument("--prefill", type=int, default=0)
+            p.add_argument("--q-heads", type=int, default=48)
+            p.add_argument("--kv-heads", type=int, default=8)
+            p.add_argument("--head-dim", type=int, default=128)
+            p.add_argument("--page-size", type=int, default=16)
+            p.add_argument("--splits", type=int, default=None)
+        else:
+            p.add_argument("--rows", type=int, default=8)
+            p.add_argument("--vocab", type=int, default=200064)
+            p.add_argument("--temperature", type=float, default=0.0)
+    a = ap.parse_args(argv)
+    res = {"moe": bench_moe, "attention": bench_attention, "sample": bench_sample}[a.case](a)
+    print(json.dumps({"case": a.case, **{k: v for k, v in vars(a).items() if k != "case"}, "result": res}))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
