@@ -16,6 +16,9 @@
 //     accumulate), K/V tiles of 64 keys brought in by cp.async through the block table, online
 //     softmax in float32 with exp2; probabilities are rounded to bfloat16 before P.V, as in the
 //     reference (attention.py:252,573).
+//   * attention_decode_bf16_kernel: the same arithmetic for tiles of at most 16 query rows (steps of
+//     single decoded tokens): the four warps split each key tile between them and a three-stage
+//     pipeline keeps two key/value tiles in flight.
 // Keys that a tile may not read (beyond its range) are never loaded: fresh pages may hold anything.
 #include <mma.h>
 
@@ -42,6 +45,8 @@ struct AttnParams {
   int window;
 };
 
+constexpr int kMaxMergeSplits = 64;  // most splits of one tile that the merge step takes
+
 struct Item {
   int seg, tok0, ntok, kb, ke, nsplit, split, base;
   int q_start, q_len, kv_len, bt_row;
@@ -59,7 +64,8 @@ __device__ __forceinline__ Item load_item(const AttnParams& p, int idx) {
     it.q_start = s[0]; it.q_len = s[1]; it.kv_len = s[2]; it.bt_row = s[3];
     it.ok = it.tok0 >= 0 && it.tok0 + it.ntok <= it.q_len && it.kb >= 0 && it.ke <= it.kv_len &&
             it.q_len <= it.kv_len && it.bt_row >= 0 &&
-            (it.nsplit == 1 || (it.base >= 0 && it.base + it.nsplit <= p.n_slots && p.part_o != nullptr));
+            (it.nsplit == 1 || (it.nsplit <= kMaxMergeSplits && it.base >= 0 &&
+                                it.base + it.nsplit <= p.n_slots && p.part_o != nullptr));
   }
   return it;
 }
@@ -181,34 +187,58 @@ __global__ void __launch_bounds__(kF32Rows * 32) attention_f32_kernel(AttnParams
 }
 
 // ================================================================= merge of split tiles
-// out = sum_i acc_i e^(m_i - M) / sum_i l_i e^(m_i - M), splits taken in order.
+// out = sum_i acc_i e^(m_i - M) / sum_i l_i e^(m_i - M), splits taken in order.  The CTA of split s
+// merges the tile's rows s, s + n_splits, ...; a thread owns output columns and fetches the splits'
+// values eight at a time, so a row costs a few memory round trips however many splits there are.
 template <typename T>
 __global__ void attention_merge_kernel(AttnParams p) {
   const Item it = load_item(p, blockIdx.x);
-  if (!it.ok || it.nsplit <= 1 || it.split != 0) return;
+  if (!it.ok || it.nsplit <= 1) return;
   const int kvh = blockIdx.y;
   const int D = p.D, G = p.G;
   const int R = it.ntok * G;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  for (int r = warp; r < R; r += nw) {
+  const int lane = threadIdx.x & 31;
+  const size_t slot_step = (size_t)p.Hkv * p.tile_rows;
+  for (int r = it.split; r < R; r += it.nsplit) {
+    const size_t slot0 = ((size_t)it.base * p.Hkv + kvh) * p.tile_rows + r;
+    // weights of the splits, spread over the lanes of every warp (each warp computes them itself)
+    float wgt[kMaxMergeSplits / 32];
     float M = -INFINITY;
-    for (int i = 0; i < it.nsplit; ++i) {
-      const size_t slot = ((size_t)(it.base + i) * p.Hkv + kvh) * p.tile_rows + r;
-      M = fmaxf(M, p.part_ml[slot * 2]);
+#pragma unroll
+    for (int j = 0; j < kMaxMergeSplits / 32; ++j) {
+      const int i = lane + 32 * j;
+      wgt[j] = i < it.nsplit ? p.part_ml[(slot0 + i * slot_step) * 2] : -INFINITY;
+      M = fmaxf(M, wgt[j]);
     }
+    M = warp_max(M);
+    float L = 0.f;
+#pragma unroll
+    for (int j = 0; j < kMaxMergeSplits / 32; ++j) {
+      const int i = lane + 32 * j;
+      const float w = (i < it.nsplit && wgt[j] != -INFINITY) ? expf(wgt[j] - M) : 0.f;
+      wgt[j] = w;
+      if (i < it.nsplit) L += p.part_ml[(slot0 + i * slot_step) * 2 + 1] * w;
+    }
+    L = warp_sum(L);
+    const float inv = L > 0.f ? 1.f / L : 0.f;
     const int tok = it.q_start + it.tok0 + r / G;
     T* o = (T*)p.out + ((size_t)tok * p.Hq + kvh * G + r % G) * D;
-    for (int d = lane; d < D; d += 32) {
-      float acc = 0.f, L = 0.f;
-      for (int i = 0; i < it.nsplit; ++i) {
-        const size_t slot = ((size_t)(it.base + i) * p.Hkv + kvh) * p.tile_rows + r;
-        const float mi = p.part_ml[slot * 2];
-        if (mi == -INFINITY) continue;
-        const float w = expf(mi - M);
-        L += p.part_ml[slot * 2 + 1] * w;
-        acc += p.part_o[slot * D + d] * w;
+    for (int d0 = 0; d0 < D; d0 += blockDim.x) {
+      const int d = d0 + threadIdx.x;
+      float acc = 0.f;
+      for (int i0 = 0; i0 < it.nsplit; i0 += 8) {  // eight loads in flight before the first use
+        float x[8], w[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = i0 + u;
+          const float wsrc = (i >> 5) ? wgt[1] : wgt[0];
+          w[u] = __shfl_sync(0xffffffffu, wsrc, i & 31);
+          x[u] = (i < it.nsplit && d < D && w[u] != 0.f) ? p.part_o[(slot0 + i * slot_step) * D + d] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc += x[u] * w[u];
       }
-      o[d] = from_float<T>(L > 0.f ? acc / L : 0.f);
+      if (d < D) o[d] = from_float<T>(acc * inv);
     }
   }
 }
@@ -252,21 +282,47 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-// Bring keys/values [c0, c0 + 64) of the request into a [64][ld] tile; rows outside [.., ke) are zero.
-__device__ __forceinline__ void load_kv_tile(const AttnParams& p, const Item& it, int kvh, int c0,
+// Element offsets of key rows [c0, c0 + 64) of the request (-1 for rows outside [.., ke)), one row per
+// thread of the first 64.  Computed one tile ahead of the copy that uses them, so that the block-table
+// lookups are off the copy's critical path.
+__device__ __forceinline__ long long fetch_row_offset(const AttnParams& p, const Item& it, int kvh, int c0) {
+  const int pos = c0 + (int)threadIdx.x;
+  return (threadIdx.x < kBN && pos < it.ke) ? kv_row_offset(p, it, kvh, pos) : -1;
+}
+__device__ __forceinline__ void publish_row_offset(long long* row_off, long long v) {
+  if (threadIdx.x < kBN) row_off[threadIdx.x] = v;
+}
+__device__ __forceinline__ void tile_row_offsets(const AttnParams& p, const Item& it, int kvh, int c0, long long* row_off) {
+  publish_row_offset(row_off, fetch_row_offset(p, it, kvh, c0));
+}
+
+// Bring keys/values of one tile into [64][ld] buffers; consecutive threads copy consecutive 16-byte
+// pieces of a row, rows without an offset are zero-filled.  When the pieces per row divide the 128
+// threads, a thread keeps its column and only steps through rows (no division in the loop).
+__device__ __forceinline__ void load_kv_tile(const AttnParams& p, const long long* row_off,
                                              __nv_bfloat16* sk, __nv_bfloat16* sv, int ld) {
   const int chunks = p.D >> 3;
   const __nv_bfloat16* kb = (const __nv_bfloat16*)p.k;
   const __nv_bfloat16* vb = (const __nv_bfloat16*)p.v;
-  for (int i = threadIdx.x; i < kBN * chunks; i += blockDim.x) {
-    const int j = i / chunks, c = i % chunks;
-    const int pos = c0 + j;
-    long long off = -1;
-    if (pos < it.ke) off = kv_row_offset(p, it, kvh, pos);
-    const bool valid = off >= 0;
-    const long long o = valid ? off + c * 8 : 0;
-    cp_async16(sk + j * ld + c * 8, kb + o, valid);
-    cp_async16(sv + j * ld + c * 8, vb + o, valid);
+  if ((chunks & (chunks - 1)) == 0) {  // 2, 4, 8, 16 or 32 pieces per row
+    const int c = threadIdx.x & (chunks - 1);
+    const int step = 128 / chunks;
+    for (int j = threadIdx.x / chunks; j < kBN; j += step) {
+      const long long off = row_off[j];
+      const bool valid = off >= 0;
+      const long long o = valid ? off + c * 8 : 0;
+      cp_async16(sk + j * ld + c * 8, kb + o, valid);
+      cp_async16(sv + j * ld + c * 8, vb + o, valid);
+    }
+  } else {
+    for (int i = threadIdx.x; i < kBN * chunks; i += blockDim.x) {
+      const int j = i / chunks, c = i - j * chunks;
+      const long long off = row_off[j];
+      const bool valid = off >= 0;
+      const long long o = valid ? off + c * 8 : 0;
+      cp_async16(sk + j * ld + c * 8, kb + o, valid);
+      cp_async16(sv + j * ld + c * 8, vb + o, valid);
+    }
   }
 }
 
@@ -295,7 +351,11 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(AttnParams p) {
     cp_async16(sq + r * ld + c * 8, q + off, valid);
   }
   const int n_iter = (it.ke - it.kb + kBN - 1) / kBN;
-  if (n_iter > 0) load_kv_tile(p, it, kvh, it.kb, sk0, sv0, ld);
+  __shared__ long long row_off[3][kBN];  // offsets of tile t live in row_off[t % 3]
+  tile_row_offsets(p, it, kvh, it.kb, row_off[0]);
+  tile_row_offsets(p, it, kvh, it.kb + kBN, row_off[1]);
+  __syncthreads();
+  if (n_iter > 0) load_kv_tile(p, row_off[0], sk0, sv0, ld);
   cp_async_commit();
 
   const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
@@ -316,8 +376,10 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(AttnParams p) {
     __nv_bfloat16* sk = sk0 + buf * kBN * ld;
     __nv_bfloat16* sv = sv0 + buf * kBN * ld;
     if (iter + 1 < n_iter)
-      load_kv_tile(p, it, kvh, it.kb + (iter + 1) * kBN, sk0 + (buf ^ 1) * kBN * ld, sv0 + (buf ^ 1) * kBN * ld, ld);
+      load_kv_tile(p, row_off[(iter + 1) % 3], sk0 + (buf ^ 1) * kBN * ld, sv0 + (buf ^ 1) * kBN * ld, ld);
     cp_async_commit();
+    // the block-table lookup for the tile after next travels while this tile is computed
+    const long long next_off = fetch_row_offset(p, it, kvh, it.kb + (iter + 2) * kBN);
     cp_async_wait<1>();
     __syncthreads();
 
@@ -399,6 +461,7 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(AttnParams p) {
         }
       }
     }
+    publish_row_offset(row_off[(iter + 2) % 3], next_off);
     __syncthreads();
   }
   cp_async_wait<0>();
@@ -445,6 +508,220 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(AttnParams p) {
       }
     }
   }
+}
+
+// ----------------------------------------------------------------- decode tiles (at most 16 query rows)
+// A step of single decoded tokens has `group` query rows per (request, KV head): too few to fill a
+// 64-row tile.  Here the four warps share the 16-row query tile and split each 64-key tile between
+// them (16 keys per warp); every warp keeps its own running max / sum / output and the four are merged
+// through shared memory at the end.  Key/value tiles arrive through a three-stage cp.async pipeline so
+// that two tiles are always in flight per CTA: the kernel's job is to keep HBM busy.
+constexpr int kDecRows = 16;
+constexpr int kDecStages = 3;
+
+template <int DMAX>
+__global__ void __launch_bounds__(128) attention_decode_bf16_kernel(AttnParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const Item it = load_item(p, blockIdx.x);
+  if (!it.ok) return;
+  const int kvh = blockIdx.y;
+  const int D = p.D, G = p.G;
+  const int ld = D + 8;
+  __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  __nv_bfloat16* sk0 = sq + kDecRows * ld;
+  __nv_bfloat16* sv0 = sk0 + kDecStages * kBN * ld;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int R = it.ntok * G;
+  const int chunks = D >> 3;
+  const __nv_bfloat16* q = (const __nv_bfloat16*)p.q;
+
+  for (int i = threadIdx.x; i < kDecRows * chunks; i += blockDim.x) {
+    const int r = i / chunks, c = i % chunks;
+    const bool valid = r < R;
+    const int tok = it.q_start + it.tok0 + (valid ? r / G : 0);
+    const size_t off = ((size_t)tok * p.Hq + kvh * G + (valid ? r % G : 0)) * D + c * 8;
+    cp_async16(sq + r * ld + c * 8, q + off, valid);
+  }
+  const int n_iter = (it.ke - it.kb + kBN - 1) / kBN;
+  __shared__ long long row_off[4][kBN];  // offsets of tile t live in row_off[t % 4]
+  tile_row_offsets(p, it, kvh, it.kb, row_off[0]);
+  tile_row_offsets(p, it, kvh, it.kb + kBN, row_off[1]);
+  tile_row_offsets(p, it, kvh, it.kb + 2 * kBN, row_off[2]);
+  __syncthreads();
+  if (n_iter > 0) load_kv_tile(p, row_off[0], sk0, sv0, ld);
+  cp_async_commit();
+  if (n_iter > 1) load_kv_tile(p, row_off[1], sk0 + kBN * ld, sv0 + kBN * ld, ld);
+  cp_async_commit();
+
+  const int r0 = lane >> 2, r1 = r0 + 8;
+  const int pos_base = it.kv_len - it.q_len + it.tok0;
+  const int qp0 = r0 < R ? pos_base + r0 / G : -1;
+  const int qp1 = r1 < R ? pos_base + r1 / G : -1;
+  const int lo0 = p.window > 0 ? qp0 - p.window + 1 : 0;
+  const int lo1 = p.window > 0 ? qp1 - p.window + 1 : 0;
+  const float sl2 = p.scale * 1.4426950408889634f;
+
+  float o[DMAX / 8][4];
+#pragma unroll
+  for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+  for (int iter = 0; iter < n_iter; ++iter) {
+    cp_async_wait<1>();
+    __syncthreads();  // tile `iter` has landed for everyone, and everyone is done with tile `iter - 1`
+    if (iter + 2 < n_iter) {
+      const int st = (iter + 2) % kDecStages;
+      load_kv_tile(p, row_off[(iter + 2) & 3], sk0 + st * kBN * ld, sv0 + st * kBN * ld, ld);
+    }
+    cp_async_commit();
+    const long long next_off = fetch_row_offset(p, it, kvh, it.kb + (iter + 3) * kBN);
+    const int stage = iter % kDecStages;
+    const __nv_bfloat16* sk = sk0 + stage * kBN * ld + warp * 16 * ld;  // this warp's 16 keys
+    const __nv_bfloat16* sv = sv0 + stage * kBN * ld + warp * 16 * ld;
+
+    float s[2][4];
+    s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < DMAX / 16; ++kk) {
+      if (kk * 16 < D) {
+        uint32_t a[4], b[4];
+        ldsm_x4(a, sq + (lane & 15) * ld + kk * 16 + (lane >> 4) * 8);
+        ldsm_x4(b, sk + ((lane & 7) + ((lane >> 4) << 3)) * ld + kk * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[0], a, b[0], b[1]);
+        mma_bf16(s[1], a, b[2], b[3]);
+      }
+    }
+    const int c0 = it.kb + iter * kBN + warp * 16;
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+    // a 16-key slice that every row of the tile may read in full needs no mask (rows beyond the
+    // tile's last are never stored, so what they compute does not matter)
+    const bool interior = p.window == 0 && c0 + 16 <= it.ke && c0 + 16 <= pos_base + 1;
+    if (interior) {
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[n][e] *= sl2;
+        mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
+        mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
+      }
+    } else {
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int key = c0 + n * 8 + (lane & 3) * 2 + e;
+          const bool in = key < it.ke;
+          const bool v0 = in && key <= qp0 && key >= lo0;
+          const bool v1 = in && key <= qp1 && key >= lo1;
+          s[n][e] = v0 ? s[n][e] * sl2 : -INFINITY;
+          s[n][2 + e] = v1 ? s[n][2 + e] * sl2 : -INFINITY;
+          mx0 = fmaxf(mx0, s[n][e]);
+          mx1 = fmaxf(mx1, s[n][2 + e]);
+        }
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float base0 = mn0 == -INFINITY ? 0.f : mn0, base1 = mn1 == -INFINITY ? 0.f : mn1;
+    const float cr0 = m0 == -INFINITY ? 0.f : fast_exp2(m0 - base0);
+    const float cr1 = m1 == -INFINITY ? 0.f : fast_exp2(m1 - base1);
+    m0 = mn0; m1 = mn1;
+    float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      s[n][0] = fast_exp2(s[n][0] - base0); s[n][1] = fast_exp2(s[n][1] - base0);
+      s[n][2] = fast_exp2(s[n][2] - base1); s[n][3] = fast_exp2(s[n][3] - base1);
+      sum0 += s[n][0] + s[n][1];
+      sum1 += s[n][2] + s[n][3];
+    }
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1); sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1); sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+    l0 = l0 * cr0 + sum0;
+    l1 = l1 * cr1 + sum1;
+    uint32_t a[4];
+    a[0] = pack_bf16(s[0][0], s[0][1]);
+    a[1] = pack_bf16(s[0][2], s[0][3]);
+    a[2] = pack_bf16(s[1][0], s[1][1]);
+    a[3] = pack_bf16(s[1][2], s[1][3]);
+    // the running maximum rarely moves once a few tiles are in: then nothing has to be rescaled
+    if (__any_sync(0xffffffffu, cr0 != 1.f || cr1 != 1.f)) {
+#pragma unroll
+      for (int i = 0; i < DMAX / 8; ++i) {
+        o[i][0] *= cr0; o[i][1] *= cr0; o[i][2] *= cr1; o[i][3] *= cr1;
+      }
+    }
+#pragma unroll
+    for (int d2 = 0; d2 < DMAX / 16; ++d2) {
+      if (d2 * 16 < D) {
+        uint32_t b[4];
+        ldsm_x4_trans(b, sv + (lane & 15) * ld + d2 * 16 + (lane >> 4) * 8);
+        mma_bf16(o[2 * d2], a, b[0], b[1]);
+        mma_bf16(o[2 * d2 + 1], a, b[2], b[3]);
+      }
+    }
+    publish_row_offset(row_off[(iter + 3) & 3], next_off);  // read after the next iteration's barrier
+  }
+  cp_async_wait<0>();
+  __syncthreads();  // the key/value stages are free: reuse them for the merge of the four warps
+
+  float* sm_m = reinterpret_cast<float*>(sk0);          // [4][16]
+  float* sm_l = sm_m + 4 * kDecRows;                    // [4][16]
+  float* sm_o = sm_l + 4 * kDecRows;                    // [4][16][D]
+  if ((lane & 3) == 0) {
+    sm_m[warp * kDecRows + r0] = m0; sm_m[warp * kDecRows + r1] = m1;
+    sm_l[warp * kDecRows + r0] = l0; sm_l[warp * kDecRows + r1] = l1;
+  }
+#pragma unroll
+  for (int i = 0; i < DMAX / 8; ++i) {
+    if (i * 8 < D) {
+      const int d = i * 8 + (lane & 3) * 2;
+      *reinterpret_cast<float2*>(sm_o + ((size_t)warp * kDecRows + r0) * D + d) = make_float2(o[i][0], o[i][1]);
+      *reinterpret_cast<float2*>(sm_o + ((size_t)warp * kDecRows + r1) * D + d) = make_float2(o[i][2], o[i][3]);
+    }
+  }
+  __syncthreads();
+  const float ln2 = 0.6931471805599453f;
+  for (int i = threadIdx.x; i < R * D; i += blockDim.x) {
+    const int r = i / D, d = i % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w * kDecRows + r]);
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = sm_m[w * kDecRows + r];
+      const float f = mw == -INFINITY ? 0.f : fast_exp2(mw - M);
+      L += sm_l[w * kDecRows + r] * f;
+      acc += sm_o[((size_t)w * kDecRows + r) * D + d] * f;
+    }
+    const int tok = it.q_start + it.tok0 + r / G;
+    if (it.nsplit == 1) {
+      __nv_bfloat16* out = (__nv_bfloat16*)p.out + ((size_t)tok * p.Hq + kvh * G + r % G) * D;
+      out[d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    } else {
+      const size_t slot = ((size_t)(it.base + it.split) * p.Hkv + kvh) * p.tile_rows + r;
+      p.part_o[slot * D + d] = acc;
+      if (d == 0) {
+        p.part_ml[slot * 2] = M == -INFINITY ? -INFINITY : M * ln2;
+        p.part_ml[slot * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+template <int DMAX>
+static int launch_decode_bf16(const AttnParams& p, cudaStream_t s) {
+  const size_t kv = (size_t)2 * kDecStages * kBN * (p.D + 8) * sizeof(__nv_bfloat16);
+  const size_t merge = (size_t)(8 * kDecRows + 4 * kDecRows * p.D) * sizeof(float);
+  const size_t smem = (size_t)kDecRows * (p.D + 8) * sizeof(__nv_bfloat16) + (kv > merge ? kv : merge);
+  auto kern = attention_decode_bf16_kernel<DMAX>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  dim3 grid(p.n_items, p.Hkv);
+  kern<<<grid, 128, smem, s>>>(p);
+  return 0;
 }
 
 template <int DMAX>
@@ -501,11 +778,19 @@ extern "C" int ftk_paged_attention(const void* q, const void* k_slab, const void
       FTK_LAUNCH_CHECK("paged_attention merge");
     }
   } else {
-    FTK_REQUIRE(tile_rows == kBM, "paged_attention: the bfloat16 kernel works on %d-row tiles, got %d", kBM, tile_rows);
-    FTK_REQUIRE(p.G <= kBM, "paged_attention: %d query heads per KV head exceed the %d-row tile", p.G, kBM);
-    if (head_dim <= 64) launch_bf16<64>(p, s);
-    else if (head_dim <= 128) launch_bf16<128>(p, s);
-    else launch_bf16<256>(p, s);
+    FTK_REQUIRE(tile_rows == kBM || tile_rows == kDecRows,
+                "paged_attention: the bfloat16 kernels work on %d-row tiles (%d for decode steps), got %d", kBM,
+                kDecRows, tile_rows);
+    FTK_REQUIRE(p.G <= tile_rows, "paged_attention: %d query heads per KV head exceed the %d-row tile", p.G, tile_rows);
+    if (tile_rows == kDecRows) {
+      if (head_dim <= 64) launch_decode_bf16<64>(p, s);
+      else if (head_dim <= 128) launch_decode_bf16<128>(p, s);
+      else launch_decode_bf16<256>(p, s);
+    } else {
+      if (head_dim <= 64) launch_bf16<64>(p, s);
+      else if (head_dim <= 128) launch_bf16<128>(p, s);
+      else launch_bf16<256>(p, s);
+    }
     FTK_LAUNCH_CHECK("paged_attention (bfloat16)");
     if (n_slots > 0) {
       attention_merge_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(p);

@@ -34,6 +34,24 @@ class AttentionPlan:
     max_splits: int
 
 
+FIXED_COST_KEYS = 100  # what a CTA's start-up, write-out and merge cost, in keys' worth of time
+
+
+def wave_splits(base_ctas: int, slots: int, limit: int, span: int = 2048) -> int:
+    """Number of key splits (1..limit) with the shortest estimated time.
+
+    ``base_ctas`` CTAs would run without splitting, ``slots`` CTAs are resident at once, ``span`` keys
+    lie in a tile's range.  Time ~ waves x (fixed cost + keys per split): a last, partly filled wave
+    costs a whole wave, and every split pays the fixed cost again.  Ties go to fewer splits."""
+    best, best_t = 1, None
+    for s in range(1, max(1, limit) + 1):
+        waves = -(-base_ctas * s // slots)
+        t = waves * (FIXED_COST_KEYS + span / s)
+        if best_t is None or t < best_t * 0.98:
+            best, best_t = s, t
+    return best
+
+
 def tokens_per_tile(tile_rows: int, group: int) -> int:
     return max(1, tile_rows // group)
 
@@ -69,8 +87,8 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
         elif n_tiles * n_kv_heads >= target:
             want = 1
         else:
-            want = min(max_splits, -(-target // max(1, n_tiles * n_kv_heads)),
-                       max(1, span // min_split_keys))
+            # splits that fill whole waves of resident CTAs, none shorter than min_split_keys
+            want = wave_splits(n_tiles * n_kv_heads, target, min(max_splits, max(1, span // min_split_keys)), span)
         quanta = -(-span // SPLIT_QUANTUM)
         n_real = max(1, min(want, quanta))
         per = -(-quanta // n_real) * SPLIT_QUANTUM

@@ -134,9 +134,9 @@ class Engine:
             owner = i if e.cache_from is None else e.cache_from
             self._views.append(self.cache.view(owner))
         self.buffers = StepBuffers(self.device, self._metadata_capacity())
-        self.graphs: Dict[int, Any] = {}
-        self.graph_logits: Dict[int, torch.Tensor] = {}
-        self.graph_launches: Dict[int, int] = {}
+        self.graphs: Dict[Any, Any] = {}
+        self.graph_logits: Dict[Any, torch.Tensor] = {}
+        self.graph_launches: Dict[Any, int] = {}
         # a graph's warm-up runs the step once more, so only mixers whose step can be repeated
         # without changing the result (they say so with ``graph_safe``) may be replayed
         self.use_graphs = (bool(config.cuda_graph) and self.device.type == "cuda"
@@ -171,7 +171,7 @@ class Engine:
         n_groups = max(1, len(self.cache.paged))
         core = 3 * T + 6 * S
         per_group = T + 2 * (T // self.config.page_size + 2 * S + 4)
-        n_plans = max(1, len({m.plan_key() for m in self.model.mixers() if hasattr(m, "plan_key")}))
+        n_plans = max(1, 2 * len({m.plan_key() for m in self.model.mixers() if hasattr(m, "plan_key")}))
         items = 8 * (T + S + 2 * self.sm_count * 32)
         return core + n_groups * per_group + n_plans * items + 4096
 
@@ -297,7 +297,9 @@ class Engine:
 
         if not graphable:
             return body()
-        key = S
+        # one graph per batch size and metadata layout (the attention split count moves with the
+        # longest request, which changes the size of the work list a few times over a long decode)
+        key = (S, tuple(arr.size for _, arr in builder.sections))
         if key not in self.graphs:
             body()  # warm-up: allocates work buffers and library workspaces outside the capture
             torch.cuda.synchronize(self.device)

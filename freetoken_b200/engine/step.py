@@ -21,7 +21,7 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from .attention_plan import AttentionPlan, build_plan
+from .attention_plan import AttentionPlan, build_plan, wave_splits
 
 ALIGN = 4  # int32 elements = 16 bytes
 
@@ -94,6 +94,7 @@ class StepBuilder:
         self.fixed = fixed
         self.sm_count = sm_count
         self.sections: List[Tuple[str, np.ndarray]] = []
+        self.decode_only = all(q == 1 for q, _ in self.seg_lens)
         self.plans: Dict[Any, AttentionPlan] = {}
         self.plan_dims: Dict[Any, Tuple[int, int, int]] = {}
 
@@ -104,7 +105,11 @@ class StepBuilder:
         """Splits per tile of a graph-replayed decode step: enough CTAs to fill the GPU at
         this batch size, independent of the requests' lengths."""
         b = max(1, len(self.seg_lens))
-        return int(min(16, max(1, -(-2 * self.sm_count // (b * n_kv_heads)))))
+        longest = max(kv for _, kv in self.seg_lens)
+        # the count may only depend on what a graph's replays share (the batch size), so the span is
+        # rounded up to a power of two: the split count then changes a handful of times as requests grow
+        span = 1 << max(6, (longest - 1).bit_length())
+        return wave_splits(b * n_kv_heads, 2 * self.sm_count, 16, span)
 
     def attention_plan(self, group: int, tile_rows: int, window: Optional[int], n_kv_heads: int,
                        head_dim: int) -> Any:
@@ -125,7 +130,7 @@ class StepBuilder:
             n_kv, rows, dim = self.plan_dims[key]
             part_o = part_ml = None
             if plan.n_slots:
-                tag = f"attn.part.{i}.fixed{len(self.seg_lens)}" if self.fixed else f"attn.part.{i}"
+                tag = f"attn.part.{i}.fixed{len(self.seg_lens)}x{plan.n_slots}" if self.fixed else f"attn.part.{i}"
                 part_o = workspace.get(tag + ".o", (plan.n_slots, n_kv, rows, dim), torch.float32)
                 part_ml = workspace.get(tag + ".ml", (plan.n_slots, n_kv, rows, 2), torch.float32)
             plans[key] = DevicePlan(tensors[f"plan.{i}"], plan.n_items, part_o, part_ml, plan)

@@ -20,7 +20,7 @@ import sys
 
 import torch
 
-from ..engine.attention_plan import build_plan
+from ..engine.attention_plan import build_plan, wave_splits
 from . import ops
 
 HBM_GBS = 6650.0
@@ -38,10 +38,17 @@ def _time(fn, iters: int, warmup: int, profile: bool) -> float:
         torch.cuda.synchronize()
         torch.cuda.profiler.stop()
         return float("nan")
+    # the launches are replayed from a CUDA graph so that the figure is device time, not the
+    # Python call overhead of issuing them
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(iters):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
-    for _ in range(iters):
-        fn()
+    graph.replay()
     b.record()
     torch.cuda.synchronize()
     return a.elapsed_time(b) / iters * 1e3  # microseconds
@@ -107,16 +114,18 @@ def bench_attention(a) -> dict:
     seg = torch.tensor(info, dtype=torch.int32, device=dev)
     q = torch.randn(q0, Hq, D, device=dev, generator=g).to(torch.bfloat16)
     fixed = None
+    tile = 64
     if not a.prefill:
-        fixed = int(min(16, max(1, -(-2 * 148 // (len(segs) * Hkv))))) if a.splits is None else a.splits
-    plan = build_plan(segs, G, 64, None, Hkv, fixed_splits=fixed)
+        fixed = wave_splits(len(segs) * Hkv, 2 * 148, 16) if a.splits is None else a.splits
+        tile = 16 if G <= 16 else 64
+    plan = build_plan(segs, G, tile, None, Hkv, fixed_splits=fixed)
     items = torch.from_numpy(plan.items).to(dev)
     po = pm = None
     if plan.n_slots:
-        po = torch.empty(plan.n_slots, Hkv, 64, D, dtype=torch.float32, device=dev)
-        pm = torch.empty(plan.n_slots, Hkv, 64, 2, dtype=torch.float32, device=dev)
+        po = torch.empty(plan.n_slots, Hkv, tile, D, dtype=torch.float32, device=dev)
+        pm = torch.empty(plan.n_slots, Hkv, tile, 2, dtype=torch.float32, device=dev)
     out = torch.empty_like(q)
-    us = _time(lambda: ops.paged_attention(q, ks, vs, bt, seg, len(segs), items, plan.n_items, po, pm, out, 64,
+    us = _time(lambda: ops.paged_attention(q, ks, vs, bt, seg, len(segs), items, plan.n_items, po, pm, out, tile,
                                            D ** -0.5, None), a.iters, a.warmup, a.profile)
     kv_bytes = sum(kv for _, kv in segs) * Hkv * D * 2 * 2
     flops = sum(4 * (ql * kv - ql * (ql - 1) // 2) * Hq * D for ql, kv in segs)

@@ -23,9 +23,12 @@ from .base import MIXERS, BuildEnv, Mixer, StepState
 from .rope import shared_position
 
 
-def attention_tile_rows(dtype: torch.dtype) -> int:
-    """Query rows (tokens x group heads) one attention CTA handles."""
-    return 64 if dtype == torch.bfloat16 else 16
+def attention_tile_rows(dtype: torch.dtype, decode_only: bool = False, group: int = 1) -> int:
+    """Query rows (tokens x group heads) one attention CTA handles: 16 in the 32-bit kernel and in
+    the bfloat16 kernel for steps of single decoded tokens, 64 in the bfloat16 kernel otherwise."""
+    if dtype != torch.bfloat16 or (decode_only and group <= 16):
+        return 16
+    return 64
 
 
 @MIXERS.register("gqa_attention")
@@ -57,11 +60,10 @@ class GQAttention(Mixer):
         self.rotary_dim = int(getattr(self.position, "rotary_dim", 0))
         if self.rotary_dim > self.head_dim:
             raise ConfigError("gqa_attention: rotary_dim exceeds head_dim")
-        self.tile_rows = attention_tile_rows(env.dtype)
-        if self.group > self.tile_rows:
+        if self.group > attention_tile_rows(env.dtype):
             raise ConfigError(
                 f"gqa_attention: {self.group} query heads per KV head exceed the kernel's "
-                f"{self.tile_rows}-row tile")
+                f"{attention_tile_rows(env.dtype)}-row tile")
         self.q_dim = self.n_heads * self.head_dim
         self.kv_dim = self.n_kv_heads * self.head_dim
 
@@ -82,12 +84,16 @@ class GQAttention(Mixer):
                             ("v", self.n_kv_heads, self.head_dim)), self.window)
 
     # ------------------------------------------------------------------ step
-    def plan_key(self):
-        return ("attention", self.group, self.tile_rows, self.window, self.n_kv_heads, self.head_dim)
+    def tile_rows(self, decode_only: bool) -> int:
+        return attention_tile_rows(self.env.dtype, decode_only, self.group)
+
+    def plan_key(self, decode_only: bool = False):
+        return ("attention", self.group, self.tile_rows(decode_only), self.window, self.n_kv_heads, self.head_dim)
 
     def prepare(self, builder) -> None:
         """Ask the step for the work list this mixer's attention kernel runs from."""
-        builder.attention_plan(self.group, self.tile_rows, self.window, self.n_kv_heads, self.head_dim)
+        builder.attention_plan(self.group, self.tile_rows(builder.decode_only), self.window, self.n_kv_heads,
+                               self.head_dim)
 
     def forward(self, h: torch.Tensor, step: StepState, cache: Any, writes_cache: bool) -> torch.Tensor:
         T = h.shape[0]
@@ -109,11 +115,11 @@ class GQAttention(Mixer):
                                  slab=cache.slabs["v"], slot_map=cache.slot_map))
         ops.norm_rope_store(qkv, self.head_dim, self.rotary_dim, step.positions,
                             self.position.table(), self.eps, self.gemma, sections)
-        plan = step.attention_plans[self.plan_key()]
+        plan = step.attention_plans[self.plan_key(step.decode_only)]
         o = ws.get("attn.o", (T, self.n_heads, self.head_dim), dt, (cap, self.n_heads, self.head_dim))
         ops.paged_attention(q, cache.slabs["k"], cache.slabs["v"], cache.block_table, step.seg_info,
                             len(step.segments), plan.items_dev, plan.n_items, plan.part_o, plan.part_ml,
-                            o, self.tile_rows, self.scale, self.window)
+                            o, self.tile_rows(step.decode_only), self.scale, self.window)
         out = ws.get("attn.out", (T, self.hidden), dt, (cap, self.hidden))
         torch.matmul(o.view(T, self.q_dim), self.params["o_proj.weight"].t(), out=out)
         return out

@@ -56,9 +56,8 @@ class BlockSparseAttention(GQAttention):
         return PagedKVNeed((("k", self.n_kv_heads, self.head_dim), ("v", self.n_kv_heads, self.head_dim),
                             ("index_k", 1, self.index_dim)), None)
 
-    def plan_key(self):
-        return ("sparse_attention", self.group, self.tile_rows, self.n_kv_heads, self.head_dim,
-                self.block_size, self.topk_blocks)
+    def plan_key(self, decode_only: bool = False):
+        return ("sparse_attention", self.group, self.n_kv_heads, self.head_dim, self.block_size, self.topk_blocks)
 
     def prepare(self, builder) -> None:
         builder.sparse_attention_plan(self)

@@ -135,11 +135,11 @@ def test_norm_rope_store(dtype, Hq, Hkv, D, rd, P, gemma, norm):
         torch.testing.assert_close(torch.nan_to_num(a.float()), torch.nan_to_num(b.float()), **tol(dtype))
 
 
-def run_attention(dtype, Hq, Hkv, D, P, segs, window, fixed_splits=None, force_split=False, seed=0):
+def run_attention(dtype, Hq, Hkv, D, P, segs, window, fixed_splits=None, force_split=False, seed=0, tile=None):
     """segs: list of (q_len, kv_len).  Builds a shuffled page layout with NaN in every unwritten
     slot, runs kernel and reference, returns both outputs."""
     G = Hq // Hkv
-    tile = 64 if dtype == torch.bfloat16 else 16
+    tile = tile or (64 if dtype == torch.bfloat16 else 16)
     width = max(-(-kv // P) for _, kv in segs) + 1
     n_pages = sum(-(-kv // P) for _, kv in segs) + 3
     g = torch.Generator().manual_seed(seed)
@@ -199,6 +199,19 @@ def test_attention_split_keys(dtype, fixed):
     assert plan.n_slots > 0
     assert not torch.isnan(out).any()
     torch.testing.assert_close(out.float(), want.float(), **attn_tol(dtype))
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,P", [(12, 2, 128, 16), (7, 1, 48, 4), (16, 1, 64, 8), (3, 3, 16, 1), (8, 4, 256, 32),
+                                        (48, 8, 128, 16)])
+@pytest.mark.parametrize("fixed", [None, 1, 4, 16])
+@pytest.mark.parametrize("window", [None, 50])
+def test_attention_decode_tiles(Hq, Hkv, D, P, fixed, window):
+    """Steps of single decoded tokens use 16-row tiles in bfloat16 (keys split between the warps)."""
+    segs = [(1, 1), (1, 130), (1, 17), (1, 700), (1, 64), (1, 65), (1, 1999), (1, 63)]
+    out, want, plan = run_attention(torch.bfloat16, Hq, Hkv, D, P, segs, window, fixed_splits=fixed, tile=16,
+                                    force_split=fixed is None)
+    assert not torch.isnan(out.float()).any()
+    torch.testing.assert_close(out.float(), want.float(), **attn_tol(torch.bfloat16))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -164,7 +164,7 @@ class AttentionHarness:
         view.slot_map = tensors["slot_map"]
         step = StepState(n_tokens=q0, segments=segs, token_ids=None, positions=tensors["positions"],
                          seg_info=tensors["seg_info"], state_slots=None, logit_rows=None, n_logit_rows=0,
-                         attention_plans=plans)
+                         attention_plans=plans, decode_only=b.decode_only)
         out = self.mixer.forward(h, step, view, True).clone()
         self.cache.end_step()
         return out
