@@ -163,20 +163,24 @@ struct TcParams {
   __nv_bfloat16* out;
 };
 
-template <int BN>
+// DEEP: one CTA per SM (many tiles: each SM streams on its own, with a longer pipeline for the large
+// token tiles); otherwise two CTAs per SM (few tiles: more of them run at once).
+template <int BN, bool DEEP>
 struct Smem {
-  static constexpr int kStages = BN <= 16 ? 5 : (BN <= 128 ? 4 : 3);  // two CTAs per SM up to BN = 64
+  // (measured: more than ~90 KB of loads in flight per SM buys nothing for the small token tiles)
+  static constexpr int kStages = DEEP ? (BN <= 16 ? 5 : (BN <= 64 ? 4 : (BN <= 128 ? 6 : 4)))
+                                      : (BN <= 16 ? 5 : (BN <= 128 ? 4 : 3));
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int kDynamic = kStages * kStageBytes + 1024;
 };
 
-template <int BN, bool GATED>
+template <int BN, bool GATED, bool DEEP>
 __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_b,
                                                                TcParams p) {
-  using S = Smem<BN>;
+  using S = Smem<BN, DEEP>;
   extern __shared__ unsigned char dyn_smem[];
   __shared__ uint64_t full_bar[S::kStages], empty_bar[S::kStages], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_slot;
@@ -466,26 +470,49 @@ static int pick_bn(int n_routes, int n_experts) {
   return 256;
 }
 
-template <int BN, bool GATED>
-static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int max_tiles, cudaStream_t s) {
-  using S = Smem<BN>;
-  auto kern = moe_gemm_tc_kernel<BN, GATED>;
+template <int BN, bool GATED, bool DEEP>
+static int launch_tc_impl(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int max_tiles, cudaStream_t s) {
+  using S = Smem<BN, DEEP>;
+  auto kern = moe_gemm_tc_kernel<BN, GATED, DEEP>;
   static int ctas_per_sm = 0, sms = 0;
   if (!ctas_per_sm) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic) != cudaSuccess) return 2;
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     int n = 0;
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kThreads, S::kDynamic);
+    // the query can answer for the current carve-out rather than the largest one: also count by hand
+    cudaFuncAttributes fa;
+    int smem_sm = 0;
+    cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
+    if (cudaFuncGetAttributes(&fa, kern) == cudaSuccess && smem_sm > 0) {
+      const int per_cta = S::kDynamic + (int)fa.sharedSizeBytes + 1024;
+      const int by_hand = smem_sm / per_cta;
+      if (by_hand > n) n = by_hand;
+    }
     const int by_tmem = 512 / S::kTmemCols;
     ctas_per_sm = n < 1 ? 1 : (n > by_tmem ? by_tmem : n);
+    if (ctas_per_sm > 2) ctas_per_sm = 2;
+    if (DEEP) ctas_per_sm = 1;
   }
   int grid = sms * ctas_per_sm;
   if (grid > max_tiles) grid = max_tiles;
   if (grid < 1) grid = 1;
   kern<<<grid, kThreads, S::kDynamic, s>>>(ma, mb, p);
   return 0;
+}
+
+// Few tiles: shallow pipelines, two CTAs per SM.  Many tiles (several per SM): one deep pipeline per SM.
+template <int BN, bool GATED>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int max_tiles, int likely_tiles,
+                     cudaStream_t s) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (likely_tiles > 3 * sms) return launch_tc_impl<BN, GATED, true>(ma, mb, p, max_tiles, s);
+  return launch_tc_impl<BN, GATED, false>(ma, mb, p, max_tiles, s);
 }
 
 template <bool GATED>
@@ -530,13 +557,17 @@ static int run_tc(const void* x, int x_cols, const void* w, int w_rows, const Tc
     }
   }
   const int max_tiles = ((p.n_routes + bn - 1) / bn + p.n_experts) * p.m_tiles;
+  // token tiles when the routes spread evenly: experts that got rows, each with its share of tiles
+  const int busy = p.n_routes < p.n_experts ? p.n_routes : p.n_experts;
+  const int per_expert = (p.n_routes / (busy > 0 ? busy : 1) + bn - 1) / bn;
+  const int likely_tiles = busy * (per_expert > 0 ? per_expert : 1) * p.m_tiles;
   int rc;
   switch (bn) {
-    case 16: rc = launch_tc<16, GATED>(ma, mb, p, max_tiles, s); break;
-    case 32: rc = launch_tc<32, GATED>(ma, mb, p, max_tiles, s); break;
-    case 64: rc = launch_tc<64, GATED>(ma, mb, p, max_tiles, s); break;
-    case 128: rc = launch_tc<128, GATED>(ma, mb, p, max_tiles, s); break;
-    default: rc = launch_tc<256, GATED>(ma, mb, p, max_tiles, s); break;
+    case 16: rc = launch_tc<16, GATED>(ma, mb, p, max_tiles, likely_tiles, s); break;
+    case 32: rc = launch_tc<32, GATED>(ma, mb, p, max_tiles, likely_tiles, s); break;
+    case 64: rc = launch_tc<64, GATED>(ma, mb, p, max_tiles, likely_tiles, s); break;
+    case 128: rc = launch_tc<128, GATED>(ma, mb, p, max_tiles, likely_tiles, s); break;
+    default: rc = launch_tc<256, GATED>(ma, mb, p, max_tiles, likely_tiles, s); break;
   }
   if (rc) {
     set_error("%s: cannot configure the tensor-core kernel", name);
