@@ -49,6 +49,16 @@ int ftk_paged_attention(const void* q, const void* k_slab, const void* v_slab, i
                         const int32_t* items, int n_items, float* part_o, float* part_ml, int n_slots,
                         void* out, int n_q_heads, int n_kv_heads, int head_dim, int page_size,
                         int num_pages, int tile_rows, float scale, int window, void* stream);
+int ftk_paged_attention_sparse(const void* q, const void* k_slab, const void* v_slab, int dtype,
+                               const int32_t* block_table, int bt_stride, const int32_t* seg_info, int n_segs,
+                               const int32_t* items, int n_items, float* part_o, float* part_ml, int n_slots,
+                               void* out, int n_q_heads, int n_kv_heads, int head_dim, int page_size,
+                               int num_pages, int tile_rows, float scale, const int32_t* sel, int sel_stride,
+                               int block_size, void* stream);
+int ftk_sparse_select(const void* iq, const void* ik_slab, int dtype, const int32_t* block_table, int bt_stride,
+                      const int32_t* seg_info, int n_segs, int n_tokens, int n_heads, int dim, int page_size,
+                      int num_pages, int block_size, int topk, int local_blocks, int init_blocks, int max_blocks,
+                      int32_t* sel, void* stream);
 int ftk_router_topk(const float* logits, const float* bias, int n_tokens, int n_experts, int top_k,
                     int scoring, float scale, int32_t* ids, float* weights, void* stream);
 int ftk_moe_permute(const int32_t* topk_ids, int n_tokens, int top_k, int n_experts,

@@ -43,6 +43,11 @@ struct AttnParams {
   int Hq, Hkv, G, D, P, num_pages, tile_rows;
   float scale;
   int window;
+  // block-sparse layers: per (token, KV head) the chosen key blocks, ascending, -1 padded; the work
+  // items' key ranges then count *chosen* keys (block 0 of the list first) instead of positions
+  const int32_t* sel;
+  int sel_stride;
+  int block_size;
 };
 
 constexpr int kMaxMergeSplits = 64;  // most splits of one tile that the merge step takes
@@ -62,7 +67,9 @@ __device__ __forceinline__ Item load_item(const AttnParams& p, int idx) {
   if (it.ok) {
     const int32_t* s = p.seg_info + (size_t)it.seg * 4;
     it.q_start = s[0]; it.q_len = s[1]; it.kv_len = s[2]; it.bt_row = s[3];
-    it.ok = it.tok0 >= 0 && it.tok0 + it.ntok <= it.q_len && it.kb >= 0 && it.ke <= it.kv_len &&
+    const int key_limit = p.sel ? p.sel_stride * p.block_size : it.kv_len;
+    it.ok = it.tok0 >= 0 && it.tok0 + it.ntok <= it.q_len && it.kb >= 0 && it.ke <= key_limit &&
+            (!p.sel || it.ntok == 1) &&
             it.q_len <= it.kv_len && it.bt_row >= 0 &&
             (it.nsplit == 1 || (it.nsplit <= kMaxMergeSplits && it.base >= 0 &&
                                 it.base + it.nsplit <= p.n_slots && p.part_o != nullptr));
@@ -72,7 +79,22 @@ __device__ __forceinline__ Item load_item(const AttnParams& p, int idx) {
 
 // Address of key/value row `pos` of the request (element offset into a [pages, Hkv, P, D] slab),
 // or -1 when the block table names a page outside the pool.
-__device__ __forceinline__ long long kv_row_offset(const AttnParams& p, const Item& it, int kvh, int pos) {
+// Position in the sequence of key number `v` of the tile's range: `v` itself, or, in a block-sparse
+// layer, the v-th key of the chosen blocks of the tile's (single) token; -1 when there is none.
+__device__ __forceinline__ int key_position(const AttnParams& p, const Item& it, int kvh, int v) {
+  if (!p.sel) return v;
+  const int32_t* chosen = p.sel + ((size_t)(it.q_start + it.tok0) * p.Hkv + kvh) * p.sel_stride;
+  const int slot = v / p.block_size;
+  if (slot >= p.sel_stride) return -1;
+  const int b = chosen[slot];
+  if (b < 0) return -1;
+  const int pos = b * p.block_size + v % p.block_size;
+  return pos < it.kv_len ? pos : -1;
+}
+
+__device__ __forceinline__ long long kv_row_offset(const AttnParams& p, const Item& it, int kvh, int v) {
+  const int pos = key_position(p, it, kvh, v);
+  if (pos < 0) return -1;
   const int page = p.block_table[(size_t)it.bt_row * p.bt_stride + pos / p.P];
   if (page < 0 || page >= p.num_pages) return -1;
   return (((long long)page * p.Hkv + kvh) * p.P + pos % p.P) * p.D;
@@ -93,6 +115,7 @@ __global__ void __launch_bounds__(kF32Rows * 32) attention_f32_kernel(AttnParams
   float* sq = smem;                       // [rows][D]
   float* sk = sq + kF32Rows * D;          // [chunk][D + 1]
   float* sv = sk + kF32Chunk * ldk;       // [chunk][D]
+  __shared__ int spos[kF32Chunk];         // position in the sequence of each key of the chunk (-1: none)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int R = it.ntok * G;
   const T* q = (const T*)p.q;
@@ -125,14 +148,15 @@ __global__ void __launch_bounds__(kF32Rows * 32) attention_f32_kernel(AttnParams
           kval = to_float(kbase[off + d]);
           vval = to_float(vbase[off + d]);
         }
+        if (d == 0) spos[j] = off >= 0 ? key_position(p, it, kvh, c0 + j) : -1;
       }
       sk[j * ldk + d] = kval;
       sv[j * D + d] = vval;
     }
     __syncthreads();
     if (!active) continue;
-    const int key = c0 + lane;
-    const bool vis = lane < nk && key <= q_pos && key >= lo_row;
+    const int key = lane < nk ? spos[lane] : -1;
+    const bool vis = key >= 0 && key <= q_pos && key >= lo_row;
     float s = -INFINITY;
     if (vis) {
       const float* qr = sq + warp * D;
@@ -291,6 +315,11 @@ __device__ __forceinline__ long long fetch_row_offset(const AttnParams& p, const
 }
 __device__ __forceinline__ void publish_row_offset(long long* row_off, long long v) {
   if (threadIdx.x < kBN) row_off[threadIdx.x] = v;
+}
+// block-sparse layers: the sequence position of key c0 + thread of the tile (for the mask)
+__device__ __forceinline__ void publish_row_position(const AttnParams& p, const Item& it, int kvh, int c0, int* row_pos,
+                                                     long long off) {
+  if (p.sel && threadIdx.x < kBN) row_pos[threadIdx.x] = off >= 0 ? key_position(p, it, kvh, c0 + (int)threadIdx.x) : -1;
 }
 __device__ __forceinline__ void tile_row_offsets(const AttnParams& p, const Item& it, int kvh, int c0, long long* row_off) {
   publish_row_offset(row_off, fetch_row_offset(p, it, kvh, c0));
@@ -544,9 +573,13 @@ __global__ void __launch_bounds__(128) attention_decode_bf16_kernel(AttnParams p
   }
   const int n_iter = (it.ke - it.kb + kBN - 1) / kBN;
   __shared__ long long row_off[4][kBN];  // offsets of tile t live in row_off[t % 4]
-  tile_row_offsets(p, it, kvh, it.kb, row_off[0]);
-  tile_row_offsets(p, it, kvh, it.kb + kBN, row_off[1]);
-  tile_row_offsets(p, it, kvh, it.kb + 2 * kBN, row_off[2]);
+  __shared__ int row_pos[4][kBN];        // block-sparse layers: sequence positions of the tile's keys
+#pragma unroll
+  for (int t = 0; t < 3; ++t) {
+    const long long off = fetch_row_offset(p, it, kvh, it.kb + t * kBN);
+    publish_row_offset(row_off[t], off);
+    publish_row_position(p, it, kvh, it.kb + t * kBN, row_pos[t], off);
+  }
   __syncthreads();
   if (n_iter > 0) load_kv_tile(p, row_off[0], sk0, sv0, ld);
   cp_async_commit();
@@ -595,7 +628,7 @@ __global__ void __launch_bounds__(128) attention_decode_bf16_kernel(AttnParams p
     float mx0 = -INFINITY, mx1 = -INFINITY;
     // a 16-key slice that every row of the tile may read in full needs no mask (rows beyond the
     // tile's last are never stored, so what they compute does not matter)
-    const bool interior = p.window == 0 && c0 + 16 <= it.ke && c0 + 16 <= pos_base + 1;
+    const bool interior = p.window == 0 && !p.sel && c0 + 16 <= it.ke && c0 + 16 <= pos_base + 1;
     if (interior) {
 #pragma unroll
       for (int n = 0; n < 2; ++n) {
@@ -609,10 +642,12 @@ __global__ void __launch_bounds__(128) attention_decode_bf16_kernel(AttnParams p
       for (int n = 0; n < 2; ++n) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const int key = c0 + n * 8 + (lane & 3) * 2 + e;
+          const int col = n * 8 + (lane & 3) * 2 + e;
+          int key = c0 + col;
           const bool in = key < it.ke;
-          const bool v0 = in && key <= qp0 && key >= lo0;
-          const bool v1 = in && key <= qp1 && key >= lo1;
+          if (p.sel) key = in ? row_pos[iter & 3][warp * 16 + col] : -1;
+          const bool v0 = in && key >= 0 && key <= qp0 && key >= lo0;
+          const bool v1 = in && key >= 0 && key <= qp1 && key >= lo1;
           s[n][e] = v0 ? s[n][e] * sl2 : -INFINITY;
           s[n][2 + e] = v1 ? s[n][2 + e] * sl2 : -INFINITY;
           mx0 = fmaxf(mx0, s[n][e]);
@@ -663,6 +698,7 @@ __global__ void __launch_bounds__(128) attention_decode_bf16_kernel(AttnParams p
       }
     }
     publish_row_offset(row_off[(iter + 3) & 3], next_off);  // read after the next iteration's barrier
+    publish_row_position(p, it, kvh, it.kb + (iter + 3) * kBN, row_pos[(iter + 3) & 3], next_off);
   }
   cp_async_wait<0>();
   __syncthreads();  // the key/value stages are free: reuse them for the merge of the four warps
@@ -738,12 +774,12 @@ static int launch_bf16(const AttnParams& p, cudaStream_t s) {
 
 using namespace ftk;
 
-extern "C" int ftk_paged_attention(const void* q, const void* k_slab, const void* v_slab, int dtype,
-                                   const int32_t* block_table, int bt_stride, const int32_t* seg_info,
-                                   int n_segs, const int32_t* items, int n_items, float* part_o,
-                                   float* part_ml, int n_slots, void* out, int n_q_heads, int n_kv_heads,
-                                   int head_dim, int page_size, int num_pages, int tile_rows, float scale,
-                                   int window, void* stream) {
+static int paged_attention_impl(const void* q, const void* k_slab, const void* v_slab, int dtype,
+                                const int32_t* block_table, int bt_stride, const int32_t* seg_info,
+                                int n_segs, const int32_t* items, int n_items, float* part_o,
+                                float* part_ml, int n_slots, void* out, int n_q_heads, int n_kv_heads,
+                                int head_dim, int page_size, int num_pages, int tile_rows, float scale,
+                                int window, const int32_t* sel, int sel_stride, int block_size, void* stream) {
   FTK_REQUIRE(dtype_ok(dtype), "paged_attention: bad dtype %d", dtype);
   FTK_REQUIRE(n_items >= 0 && n_segs >= 0, "paged_attention: bad counts");
   if (n_items == 0) return 0;
@@ -762,6 +798,13 @@ extern "C" int ftk_paged_attention(const void* q, const void* k_slab, const void
   p.part_o = part_o; p.part_ml = part_ml; p.n_slots = n_slots;
   p.Hq = n_q_heads; p.Hkv = n_kv_heads; p.G = n_q_heads / n_kv_heads; p.D = head_dim; p.P = page_size;
   p.num_pages = num_pages; p.tile_rows = tile_rows; p.scale = scale; p.window = window;
+  p.sel = sel; p.sel_stride = sel_stride; p.block_size = block_size;
+  if (sel) {
+    FTK_REQUIRE(sel_stride >= 1 && block_size >= 1, "paged_attention: bad block selection geometry");
+    FTK_REQUIRE(window == 0, "paged_attention: a window cannot be combined with block selection");
+    FTK_REQUIRE(tile_rows == 16, "paged_attention: block selection works on one token per tile (16-row tiles), got %d",
+                tile_rows);
+  }
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid(n_items, n_kv_heads);
   if (dtype == FTK_F32) {
@@ -798,6 +841,32 @@ extern "C" int ftk_paged_attention(const void* q, const void* k_slab, const void
     }
   }
   return 0;
+}
+
+extern "C" int ftk_paged_attention(const void* q, const void* k_slab, const void* v_slab, int dtype,
+                                   const int32_t* block_table, int bt_stride, const int32_t* seg_info,
+                                   int n_segs, const int32_t* items, int n_items, float* part_o,
+                                   float* part_ml, int n_slots, void* out, int n_q_heads, int n_kv_heads,
+                                   int head_dim, int page_size, int num_pages, int tile_rows, float scale,
+                                   int window, void* stream) {
+  return paged_attention_impl(q, k_slab, v_slab, dtype, block_table, bt_stride, seg_info, n_segs, items, n_items, part_o,
+                              part_ml, n_slots, out, n_q_heads, n_kv_heads, head_dim, page_size, num_pages, tile_rows,
+                              scale, window, nullptr, 0, 0, stream);
+}
+
+// Block-sparse layers: `sel [T, n_kv_heads, sel_stride]` lists, per token and KV head, the chosen key
+// blocks of `block_size` positions (ascending, -1 padded); the work items then hold one token each
+// and their key ranges count chosen keys.
+extern "C" int ftk_paged_attention_sparse(const void* q, const void* k_slab, const void* v_slab, int dtype,
+                                          const int32_t* block_table, int bt_stride, const int32_t* seg_info,
+                                          int n_segs, const int32_t* items, int n_items, float* part_o,
+                                          float* part_ml, int n_slots, void* out, int n_q_heads, int n_kv_heads,
+                                          int head_dim, int page_size, int num_pages, int tile_rows, float scale,
+                                          const int32_t* sel, int sel_stride, int block_size, void* stream) {
+  FTK_REQUIRE(sel != nullptr, "paged_attention_sparse: no block selection given");
+  return paged_attention_impl(q, k_slab, v_slab, dtype, block_table, bt_stride, seg_info, n_segs, items, n_items, part_o,
+                              part_ml, n_slots, out, n_q_heads, n_kv_heads, head_dim, page_size, num_pages, tile_rows,
+                              scale, 0, sel, sel_stride, block_size, stream);
 }
 
 // ================================================================= entry point without allocation

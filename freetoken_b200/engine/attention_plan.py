@@ -59,13 +59,18 @@ def tokens_per_tile(tile_rows: int, group: int) -> int:
 def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
                window: Optional[int], n_kv_heads: int, sm_count: int = 148,
                max_splits: int = 32, min_split_keys: int = 256,
-               fixed_splits: Optional[int] = None) -> AttentionPlan:
+               fixed_splits: Optional[int] = None,
+               sparse: Optional[Tuple[int, int]] = None) -> AttentionPlan:
     """``segments`` holds (q_len, kv_len) per segment, in step order.
 
     ``fixed_splits`` forces every tile to be planned with exactly that many item rows
     (unused ones get an empty key range); CUDA-graph replay uses it so that the item
-    count of a step never changes."""
-    tpt = tokens_per_tile(tile_rows, group)
+    count of a step never changes.
+
+    ``sparse = (block_size, topk)`` plans a block-sparse layer: one token per tile (every token has
+    its own choice of key blocks) and key ranges that count chosen keys: ``min(topk, visible
+    blocks) * block_size`` of them."""
+    tpt = 1 if sparse else tokens_per_tile(tile_rows, group)
     tiles: List[Tuple[int, int, int, int, int]] = []  # seg, tok0, ntok, lo, hi
     for s, (q_len, kv_len) in enumerate(segments):
         pos0 = kv_len - q_len
@@ -75,6 +80,9 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
             lo = 0
             if window is not None:
                 lo = max(0, pos0 + tok0 - window + 1)
+            if sparse:
+                block, topk = sparse
+                lo, hi = 0, min(topk, (pos0 + tok0) // block + 1) * block
             tiles.append((s, tok0, ntok, lo, hi))
     n_tiles = len(tiles)
     target = 2 * sm_count

@@ -123,6 +123,19 @@ class StepBuilder:
             self.add(f"plan.{len(self.plans) - 1}", plan.items)
         return key
 
+    def sparse_attention_plan(self, group: int, tile_rows: int, n_kv_heads: int, head_dim: int,
+                              block_size: int, topk: int) -> Any:
+        """Work list of a block-sparse layer: one token per tile, key ranges over chosen keys."""
+        key = ("sparse_attention", group, tile_rows, n_kv_heads, head_dim, block_size, topk)
+        if key not in self.plans:
+            plan = build_plan(self.seg_lens, group, tile_rows, None, n_kv_heads, sm_count=self.sm_count,
+                              fixed_splits=self.fixed_splits(n_kv_heads) if self.fixed else None,
+                              sparse=(block_size, topk))
+            self.plans[key] = plan
+            self.plan_dims[key] = (n_kv_heads, tile_rows, head_dim)
+            self.add(f"plan.{len(self.plans) - 1}", plan.items)
+        return key
+
     def finish(self, buffers: StepBuffers, workspace) -> Tuple[Dict[str, torch.Tensor], Dict[Any, DevicePlan]]:
         tensors = buffers.upload(self.sections)
         plans: Dict[Any, DevicePlan] = {}

@@ -58,6 +58,9 @@ _SIGNATURES = {
                             ctypes.POINTER(_Section), _vp],
     "ftk_paged_attention": [_vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
                             _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "ftk_paged_attention_sparse": [_vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
+                                   _i, _i, _i, _i, _i, _i, _f, _vp, _i, _i, _vp],
+    "ftk_sparse_select": [_vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "ftk_router_topk": [_vp, _vp, _i, _i, _i, _i, _f, _vp, _vp, _vp],
     "ftk_moe_permute": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp],
     "ftk_moe_gather": [_vp, _i, _vp, _i, _i, _i, _vp, _vp],
@@ -278,7 +281,7 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
                     block_table: torch.Tensor, seg_info: torch.Tensor, n_segs: int,
                     items: torch.Tensor, n_items: int, part_o: Optional[torch.Tensor],
                     part_ml: Optional[torch.Tensor], out: torch.Tensor, tile_rows: int, scale: float,
-                    window: Optional[int]) -> None:
+                    window: Optional[int], sel: Optional[torch.Tensor] = None, block_size: int = 0) -> None:
     """Causal softmax attention of the step's queries over the paged keys and values.
 
     ``q, out [T, Hq, D]``; slabs ``[pages, Hkv, page_size, D]``; ``block_table [rows, width]``
@@ -287,6 +290,11 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
     tile_rows, D]`` and ``part_ml [slots, Hkv, tile_rows, 2]`` float32 scratch for split
     tiles.  Query ``t`` of a segment sits at position ``kv_len - q_len + t`` and reads keys at
     positions ``<=`` its own (and ``>`` its own minus ``window`` when a window is given).
+
+    Block-sparse layers pass ``sel [T, Hkv, topk]`` (chosen key blocks of ``block_size`` positions
+    per token and KV head, ascending, -1 padded, from :func:`sparse_select`); a query then reads only
+    the keys of its chosen blocks, the work items hold one token each and their key ranges count
+    chosen keys.
     """
     T, Hq, D = q.shape
     pages, Hkv, P, D2 = k_slab.shape
@@ -298,6 +306,19 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
     if part_o is not None and (part_o.shape[1:] != (Hkv, tile_rows, D) or part_ml is None
                                or part_ml.shape != (n_slots, Hkv, tile_rows, 2)):
         raise KernelError("paged_attention: scratch shapes do not match tile_rows / heads")
+    if sel is not None:
+        if sel.dim() != 3 or sel.shape[0] < T or sel.shape[1] != Hkv or block_size < 1:
+            raise KernelError("paged_attention: sel must be [T, Hkv, topk] with a positive block_size")
+        _check(_lib().ftk_paged_attention_sparse(
+            _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"), _code(q, "q"),
+            _dev(block_table, "block_table", torch.int32), block_table.shape[1],
+            _dev(seg_info, "seg_info", torch.int32), n_segs,
+            _dev(items, "items", torch.int32), n_items,
+            _dev(part_o, "part_o", torch.float32), _dev(part_ml, "part_ml", torch.float32), n_slots,
+            _dev(out, "out"), Hq, Hkv, D, P, pages, tile_rows, float(scale),
+            _dev(sel, "sel", torch.int32), sel.shape[2], int(block_size), _stream()),
+            "paged_attention (block-sparse)", 2 if n_slots else 1)
+        return
     _check(_lib().ftk_paged_attention(
         _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"), _code(q, "q"),
         _dev(block_table, "block_table", torch.int32), block_table.shape[1],
@@ -306,6 +327,29 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
         _dev(part_o, "part_o", torch.float32), _dev(part_ml, "part_ml", torch.float32), n_slots,
         _dev(out, "out"), Hq, Hkv, D, P, pages, tile_rows, float(scale),
         int(window) if window else 0, _stream()), "paged_attention", 2 if n_slots else 1)
+
+
+def sparse_select(iq: torch.Tensor, ik_slab: torch.Tensor, block_table: torch.Tensor, seg_info: torch.Tensor,
+                  n_segs: int, block_size: int, local_blocks: int, init_blocks: int, max_blocks: int,
+                  sel: torch.Tensor) -> None:
+    """Key blocks each new token of a block-sparse layer attends to.
+
+    ``iq [T, Hi, Di]`` index queries, ``ik_slab [pages, 1, page_size, Di]`` cached index keys.  A
+    block's score is the largest ``iq . ik`` over its visible positions; the first ``init_blocks``
+    and the newest ``local_blocks`` blocks are always taken; the ``min(topk, visible)`` best go to
+    ``sel [T, Hi, topk]`` in ascending order, padded with -1.  ``max_blocks`` bounds the blocks of
+    the longest request (sizes the kernel's shared memory)."""
+    T, Hi, Di = iq.shape
+    pages, one, P, Di2 = ik_slab.shape
+    if one != 1 or Di2 != Di or ik_slab.dtype != iq.dtype:
+        raise KernelError("sparse_select: ik_slab must be [pages, 1, page_size, Di] of iq's dtype")
+    if sel.dim() != 3 or sel.shape[0] < T or sel.shape[1] != Hi:
+        raise KernelError("sparse_select: sel must be [T, Hi, topk]")
+    _check(_lib().ftk_sparse_select(_dev(iq, "iq"), _dev(ik_slab, "ik_slab"), _code(iq, "iq"),
+                                    _dev(block_table, "block_table", torch.int32), block_table.shape[1],
+                                    _dev(seg_info, "seg_info", torch.int32), n_segs, T, Hi, Di, P, pages,
+                                    int(block_size), sel.shape[2], int(local_blocks), int(init_blocks),
+                                    int(max_blocks), _dev(sel, "sel", torch.int32), _stream()), "sparse_select")
 
 
 # --------------------------------------------------------------------------- experts

@@ -43,6 +43,9 @@ class BlockSparseAttention(GQAttention):
             raise ConfigError("block_sparse_attention: index_dim must equal head_dim (shared rotation)")
         if self.window is not None:
             raise ConfigError("block_sparse_attention: a window cannot be combined with block selection")
+        if self.group > 16:
+            raise ConfigError(f"block_sparse_attention: {self.group} query heads per KV head exceed the "
+                              f"kernel's 16-row tile")
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         out = super().param_specs()
@@ -56,17 +59,58 @@ class BlockSparseAttention(GQAttention):
         return PagedKVNeed((("k", self.n_kv_heads, self.head_dim), ("v", self.n_kv_heads, self.head_dim),
                             ("index_k", 1, self.index_dim)), None)
 
+    graph_safe = True
+
     def plan_key(self, decode_only: bool = False):
-        return ("sparse_attention", self.group, self.n_kv_heads, self.head_dim, self.block_size, self.topk_blocks)
+        return ("sparse_attention", self.group, 16, self.n_kv_heads, self.head_dim, self.block_size,
+                self.topk_blocks)
 
     def prepare(self, builder) -> None:
-        builder.sparse_attention_plan(self)
+        builder.sparse_attention_plan(self.group, 16, self.n_kv_heads, self.head_dim, self.block_size,
+                                      self.topk_blocks)
 
     def forward(self, h: torch.Tensor, step: StepState, cache: Any, writes_cache: bool) -> torch.Tensor:
-        return sparse_forward(self, h, step, cache, writes_cache)
-
-
-def sparse_forward(m: BlockSparseAttention, h, step, cache, writes_cache):
-    from ..errors import KernelError
-
-    raise KernelError("block_sparse_attention: the block-selection kernels are not built yet")
+        T = h.shape[0]
+        ws, dt, cap = self.env.workspace, self.env.dtype, self.env.max_step_tokens
+        Hq, Hkv, D, Hi = self.n_heads, self.n_kv_heads, self.head_dim, self.n_index_heads
+        # main projection, norm, rotation, cache write: as in the dense mixer
+        n_proj = self.q_dim + (2 * self.kv_dim if writes_cache else 0)
+        qkv = ws.get("attn.qkv", (T, n_proj), dt, (cap, self.q_dim + 2 * self.kv_dim))
+        w = self.params["qkv_proj.weight"]
+        torch.matmul(h, (w if writes_cache else w[: self.q_dim]).t(), out=qkv)
+        q = ws.get("attn.q", (T, Hq, D), dt, (cap, Hq, D))
+        sections = [dict(first_head=0, n_heads=Hq, norm_weight=self.params.get("q_norm.weight"), rotate=True,
+                         dense_out=q)]
+        if writes_cache:
+            sections.append(dict(first_head=Hq, n_heads=Hkv, norm_weight=self.params.get("k_norm.weight"),
+                                 rotate=True, slab=cache.slabs["k"], slot_map=cache.slot_map))
+            sections.append(dict(first_head=Hq + Hkv, n_heads=Hkv, norm_weight=None, rotate=False,
+                                 slab=cache.slabs["v"], slot_map=cache.slot_map))
+        ops.norm_rope_store(qkv, D, self.rotary_dim, step.positions, self.position.table(), self.eps,
+                            self.gemma, sections)
+        # index queries (one per KV head) and the shared index key, normed and rotated the same way
+        n_index = (Hi + (1 if writes_cache else 0)) * self.index_dim
+        iqk = ws.get("attn.iqk", (T, n_index), dt, (cap, (Hi + 1) * self.index_dim))
+        wi = self.params["index_qk_proj.weight"]
+        torch.matmul(h, (wi if writes_cache else wi[: Hi * self.index_dim]).t(), out=iqk)
+        iq = ws.get("attn.iq", (T, Hi, self.index_dim), dt, (cap, Hi, self.index_dim))
+        sections = [dict(first_head=0, n_heads=Hi, norm_weight=self.params["index_q_norm.weight"], rotate=True,
+                         dense_out=iq)]
+        if writes_cache:
+            sections.append(dict(first_head=Hi, n_heads=1, norm_weight=self.params["index_k_norm.weight"],
+                                 rotate=True, slab=cache.slabs["index_k"], slot_map=cache.slot_map))
+        ops.norm_rope_store(iqk, self.index_dim, self.rotary_dim, step.positions, self.position.table(),
+                            self.eps, self.gemma, sections)
+        # which key blocks each token reads, then attention over those
+        sel = ws.get("attn.sel", (T, Hkv, self.topk_blocks), torch.int32, (cap, Hkv, self.topk_blocks))
+        max_blocks = -(-self.env.max_seq_len // self.block_size)
+        ops.sparse_select(iq, cache.slabs["index_k"], cache.block_table, step.seg_info, len(step.segments),
+                          self.block_size, self.local_blocks, self.init_blocks, max_blocks, sel)
+        plan = step.attention_plans[self.plan_key()]
+        o = ws.get("attn.o", (T, Hq, D), dt, (cap, Hq, D))
+        ops.paged_attention(q, cache.slabs["k"], cache.slabs["v"], cache.block_table, step.seg_info,
+                            len(step.segments), plan.items_dev, plan.n_items, plan.part_o, plan.part_ml, o, 16,
+                            self.scale, None, sel=sel, block_size=self.block_size)
+        out = ws.get("attn.out", (T, self.hidden), dt, (cap, self.hidden))
+        torch.matmul(o.view(T, self.q_dim), self.params["o_proj.weight"].t(), out=out)
+        return out

@@ -88,12 +88,14 @@ def norm_rope_store(x, head_dim, rotary_dim, positions, rope_table, eps, gemma, 
 
 
 def paged_attention(q, k_slab, v_slab, block_table, seg_info, n_segs, items, n_items, part_o, part_ml,
-                    out, tile_rows, scale, window):
+                    out, tile_rows, scale, window, sel=None, block_size=0):
     """Per query token, softmax over the visible keys gathered through the block table; the
-    work list and the scratch are ignored (they only steer how the kernel splits the work)."""
+    work list and the scratch are ignored (they only steer how the kernel splits the work).
+    With ``sel`` a query reads only the keys of its chosen blocks."""
     T, Hq, D = q.shape
     P = k_slab.shape[2]
-    G = Hq // k_slab.shape[1]
+    Hkv = k_slab.shape[1]
+    G = Hq // Hkv
     info = seg_info.view(-1, 4)[:n_segs].tolist()
     for q_start, q_len, kv_len, row in info:
         pos = torch.arange(kv_len, device=q.device)
@@ -103,12 +105,48 @@ def paged_attention(q, k_slab, v_slab, block_table, seg_info, n_segs, items, n_i
         for t in range(q_len):
             p_q = kv_len - q_len + t
             lo = 0 if not window else max(0, p_q - window + 1)
-            kk, vv = K[lo:p_q + 1], V[lo:p_q + 1]
             qq = q[q_start + t].float().view(-1, G, D)  # [Hkv, G, D]
-            s = torch.einsum("hgd,khd->hgk", qq, kk) * scale
-            p = torch.softmax(s, dim=-1)
-            o = torch.einsum("hgk,khd->hgd", p, vv)
+            if sel is None:
+                kk, vv = K[lo:p_q + 1], V[lo:p_q + 1]
+                s = torch.einsum("hgd,khd->hgk", qq, kk) * scale
+                p = torch.softmax(s, dim=-1)
+                o = torch.einsum("hgk,khd->hgd", p, vv)
+            else:
+                o = torch.zeros(Hkv, G, D, device=q.device)
+                for h in range(Hkv):
+                    blocks = [int(b) for b in sel[q_start + t, h].tolist() if b >= 0]
+                    idx = torch.cat([torch.arange(b * block_size, min((b + 1) * block_size, p_q + 1))
+                                     for b in blocks]).to(q.device)
+                    s = (qq[h] @ K[idx, h].T) * scale
+                    o[h] = torch.softmax(s, dim=-1) @ V[idx, h]
             out[q_start + t] = o.reshape(Hq, D).to(out.dtype)
+
+
+def sparse_select(iq, ik_slab, block_table, seg_info, n_segs, block_size, local_blocks, init_blocks, max_blocks, sel):
+    T, Hi, Di = iq.shape
+    P = ik_slab.shape[2]
+    topk = sel.shape[2]
+    sel[:T] = -1
+    for q_start, q_len, kv_len, row in seg_info.view(-1, 4)[:n_segs].tolist():
+        pos = torch.arange(kv_len, device=iq.device)
+        pages = block_table[row, (pos // P).long()].long()
+        IK = ik_slab[pages, 0, (pos % P).long(), :].float()  # [kv, Di]
+        for t in range(q_len):
+            p_q = kv_len - q_len + t
+            nb = p_q // block_size + 1
+            scores = iq[q_start + t].float() @ IK[: p_q + 1].T  # [Hi, p_q + 1]
+            pad = nb * block_size - (p_q + 1)
+            if pad:
+                scores = torch.nn.functional.pad(scores, (0, pad), value=float("-inf"))
+            bs = scores.view(Hi, nb, block_size).amax(-1)
+            bs = torch.where(torch.isnan(bs), torch.full_like(bs, -1e30), bs)
+            if init_blocks:
+                bs[:, : min(init_blocks, nb)] = 1e30
+            if local_blocks:
+                bs[:, max(0, nb - local_blocks):] = 1e29
+            order = torch.argsort(bs, dim=-1, descending=True, stable=True)[:, : min(topk, nb)]
+            chosen = torch.sort(order, dim=-1).values
+            sel[q_start + t, :, : chosen.shape[1]] = chosen.to(torch.int32)
 
 
 def router_topk(logits, bias, top_k, scoring, scale, ids, weights):
@@ -195,7 +233,7 @@ def sample(logits, temperature, top_k, top_p, u, out):
         out[r] = idx
 
 
-ALL = ["embedding_gather", "add_rmsnorm", "act_and_mul", "cast", "table_update", "norm_rope_store",
+ALL = ["sparse_select", "embedding_gather", "add_rmsnorm", "act_and_mul", "cast", "table_update", "norm_rope_store",
        "paged_attention", "router_topk", "moe_permute", "moe_gather", "moe_gemm1_act", "moe_gemm2",
        "moe_combine", "sample"]
 

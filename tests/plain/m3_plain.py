@@ -133,6 +133,11 @@ def read_weights(folder: str, dtype: torch.dtype) -> Dict[str, torch.Tensor]:
     return out
 
 
+# A discrete choice (expert, key block) counts as safe against bfloat16 rounding when its gap is this
+# many times the movement that rounding causes in the plain model's own scores.
+SAFETY = 4.0
+
+
 # --------------------------------------------------------------------------- parts
 def _rnd(x: torch.Tensor, rounding: Optional[str]) -> torch.Tensor:
     if rounding == "bfloat16":
@@ -190,7 +195,7 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group: i
 
 
 def sparse_block_selection(iq: torch.Tensor, ik: torch.Tensor, block: int, topk: int,
-                           local: int, init: int) -> torch.Tensor:
+                           local: int, init: int, margins: Optional[list] = None) -> torch.Tensor:
     """Which keys each (kv head, query) may read in a block-sparse layer -> bool ``[Hi, T, T]``.
 
     Block score = max over the block's visible positions of ``iq . ik``, unscaled
@@ -218,6 +223,10 @@ def sparse_block_selection(iq: torch.Tensor, ik: torch.Tensor, block: int, topk:
             order = sorted(range(nb), key=lambda b: (-float(s[b]), b))
             for b in order[: min(topk, nb)]:
                 allowed[h, t, b * block: min((b + 1) * block, T)] = True
+            if margins is not None and nb > topk:  # gap between the last taken and the first dropped block
+                margins.append((t, float(s[order[topk - 1]] - s[order[topk]])))
+    if margins is not None:
+        margins.append(("scores", bscore.clone()))
     return allowed
 
 
@@ -283,7 +292,8 @@ def moe_block(h, W, prefix: str, cfg: PlainConfig, rounding, margins: Optional[l
     bias = W.get(prefix + "e_score_correction_bias") if cfg.bias else None
     w, ids = router(h, W[prefix + "gate.weight"], bias, cfg)
     if margins is not None:
-        margins.append(router_margin(h, W[prefix + "gate.weight"], bias, cfg))
+        margins.append((router_margin(h, W[prefix + "gate.weight"], bias, cfg),
+                        h.float() @ W[prefix + "gate.weight"].float().T))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         acc = torch.zeros(h.shape[1], dtype=h.dtype)
@@ -304,7 +314,8 @@ def moe_block(h, W, prefix: str, cfg: PlainConfig, rounding, margins: Optional[l
     return out
 
 
-def attention_layer(h, W, prefix: str, cfg: PlainConfig, cos, sin, sparse: bool, rounding):
+def attention_layer(h, W, prefix: str, cfg: PlainConfig, cos, sin, sparse: bool, rounding,
+                    sel_margins: Optional[list] = None):
     """qkv projection, per-head q/k norm, partial rope, causal softmax attention, output
     projection (python/freetoken/models/minimax_m3/attention.py:79-119)."""
     T = h.shape[0]
@@ -325,7 +336,7 @@ def attention_layer(h, W, prefix: str, cfg: PlainConfig, cos, sin, sparse: bool,
         iq = _rnd(apply_rope(iq, cos, sin, cfg.rotary_dim), rounding)
         ik = _rnd(apply_rope(ik, cos, sin, cfg.rotary_dim), rounding)
         allowed = sparse_block_selection(iq, ik[:, 0], cfg.sparse_block, cfg.sparse_topk,
-                                         cfg.sparse_local, cfg.sparse_init)
+                                         cfg.sparse_local, cfg.sparse_init, sel_margins)
     o = _rnd(causal_attention(q, k, v, cfg.heads // cfg.kv_heads, rounding, allowed), rounding)
     return _rnd(o.reshape(T, -1) @ W[prefix + "o_proj.weight"].T, rounding)
 
@@ -339,14 +350,45 @@ class PlainM3:
         self.rounding = rounding
 
     def router_margins(self, tokens: Sequence[int]) -> torch.Tensor:
-        """``[T]``: each token's smallest router gap over the MoE layers (inf without MoE layers)."""
-        margins: list = []
-        self.hidden_states(tokens, margins=margins)
-        if not margins:
-            return torch.full((len(tokens),), float("inf"))
-        return torch.stack(margins).min(0).values
+        """``[T]``: how safe each token's discrete choices are against bfloat16 rounding; values at or
+        below ``tests.helpers.NEAR_TIE`` mean "may legitimately differ in bfloat16".
 
-    def hidden_states(self, tokens: Sequence[int], return_layers: bool = False, margins: Optional[list] = None):
+        The model is run twice, in the working precision and with bfloat16 rounding.  Per MoE layer
+        the router gap of a token (in logit units) is set against how far the rounding moved that
+        token's router logits; per block-sparse layer the gap between the last taken and the first
+        dropped block score against how far its block scores moved.  A choice whose gap is less than
+        ``SAFETY`` times that movement (the engine rounds in another order than this emulation, so
+        its noise is of the same size but not the same sign) is reported as 0, otherwise as the gap."""
+        exact_r, exact_s, rough_r, rough_s = [], [], [], []
+        self.hidden_states(tokens, margins=exact_r, sel_margins=exact_s)
+        keep = self.rounding
+        self.rounding = "bfloat16"
+        try:
+            self.hidden_states(tokens, margins=rough_r, sel_margins=rough_s)
+        finally:
+            self.rounding = keep
+        T = len(tokens)
+        out = torch.full((T,), float("inf"))
+        for (gap, logits), (_, logits_b) in zip(exact_r, rough_r):
+            noise = (logits - logits_b).abs().max(-1).values
+            safe = gap > SAFETY * noise + 1e-4
+            out = torch.minimum(out, torch.where(safe, gap, torch.zeros_like(gap)))
+        scores = [x[1] for x in exact_s if x[0] == "scores"]
+        scores_b = [x[1] for x in rough_s if x[0] == "scores"]
+        gaps = [x for x in exact_s if x[0] != "scores"]
+        layer = 0
+        per_layer = len(gaps) // max(1, len(scores))
+        for i, (t, gap) in enumerate(gaps):
+            layer = min(i // max(1, per_layer), len(scores) - 1)
+            a, b = scores[layer][:, t], scores_b[layer][:, t]
+            ok = torch.isfinite(a) & torch.isfinite(b)
+            noise = float((a[ok] - b[ok]).abs().max()) if ok.any() else 0.0
+            if gap <= SAFETY * noise + 1e-3:
+                out[t] = 0.0
+        return out
+
+    def hidden_states(self, tokens: Sequence[int], return_layers: bool = False, margins: Optional[list] = None,
+                      sel_margins: Optional[list] = None):
         """Residual stream after the last layer, before the final norm, ``[T, hidden]``.
 
         Pre-norm with the residual carried beside the sub-layer output
@@ -362,7 +404,7 @@ class PlainM3:
         for l in range(cfg.layers):
             p = f"model.layers.{l}."
             h = _rnd(rms_norm(r, W[p + "input_layernorm.weight"], cfg.eps, cfg.gemma), rd)
-            a = attention_layer(h, W, p + "self_attn.", cfg, cos, sin, cfg.sparse_layers[l], rd)
+            a = attention_layer(h, W, p + "self_attn.", cfg, cos, sin, cfg.sparse_layers[l], rd, sel_margins)
             r = r + a
             h = _rnd(rms_norm(r, W[p + "post_attention_layernorm.weight"], cfg.eps, cfg.gemma), rd)
             if cfg.moe_layers[l]:

@@ -12,7 +12,7 @@ from plain.m3_plain import PlainM3
 from tiny_configs import ALL
 
 TOL = dict(rtol=1e-4, atol=2e-5)
-PAGE = {"A": 4, "B": 8, "C": 4}
+PAGE = {"A": 4, "B": 8, "C": 4, "D": 4}
 
 
 @pytest.fixture
@@ -20,7 +20,7 @@ def cpu_ops(monkeypatch):
     kernel_refs.install(monkeypatch)
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_cuts_and_batches_agree_with_the_plain_model(name, cpu_ops, tmp_path_factory):
     folder = model_folder(tmp_path_factory.getbasetemp(), name, ALL[name])
     plain = PlainM3(folder)
@@ -35,7 +35,7 @@ def test_cuts_and_batches_agree_with_the_plain_model(name, cpu_ops, tmp_path_fac
     assert all(g.pool.free_count == g.pool.num_pages for g in eng.cache.paged)
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 def test_mixed_steps_with_few_pages(name, cpu_ops, tmp_path_factory):
     folder = model_folder(tmp_path_factory.getbasetemp(), name, ALL[name])
     plain = PlainM3(folder)

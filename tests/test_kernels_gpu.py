@@ -214,6 +214,69 @@ def test_attention_decode_tiles(Hq, Hkv, D, P, fixed, window):
     torch.testing.assert_close(out.float(), want.float(), **attn_tol(torch.bfloat16))
 
 
+def sparse_problem(dtype, Hq, Hkv, D, P, segs, block, seed=0):
+    """Paged keys, values and index keys of a few requests (NaN in every unwritten slot)."""
+    g = torch.Generator().manual_seed(seed)
+    n_pages = sum(-(-kv // P) for _, kv in segs) + 2
+    perm = (torch.randperm(n_pages - 1, generator=g) + 1).tolist()
+    bt = torch.zeros(len(segs), max(-(-kv // P) for _, kv in segs), dtype=torch.int32)
+    ks = torch.full((n_pages, Hkv, P, D), float("nan"), dtype=dtype)
+    vs = torch.full((n_pages, Hkv, P, D), float("nan"), dtype=dtype)
+    iks = torch.full((n_pages, 1, P, D), float("nan"), dtype=dtype)
+    info, q0 = [], 0
+    for row, (q_len, kv_len) in enumerate(segs):
+        for b in range(-(-kv_len // P)):
+            page = perm.pop()
+            bt[row, b] = page
+            n = min(P, kv_len - b * P)
+            ks[page, :, :n] = torch.randn(Hkv, n, D, generator=g).to(dtype)
+            vs[page, :, :n] = torch.randn(Hkv, n, D, generator=g).to(dtype)
+            iks[page, :, :n] = torch.randn(1, n, D, generator=g).to(dtype)
+        info.append([q0, q_len, kv_len, row])
+        q0 += q_len
+    q = torch.randn(q0, Hq, D, generator=g).to(dtype)
+    iq = torch.randn(q0, Hkv, D, generator=g).to(dtype)
+    seg = torch.tensor(info, dtype=torch.int32)
+    return [t.to(DEV) for t in (q, iq, ks, vs, iks, bt, seg)], q0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,D,P,block,topk,local,init", [(4, 2, 16, 4, 8, 3, 1, 0), (12, 2, 128, 16, 128, 4, 1, 0),
+                                                               (6, 3, 32, 8, 16, 5, 2, 1), (7, 1, 48, 4, 8, 2, 1, 0)])
+def test_block_sparse_selection_and_attention(dtype, Hq, Hkv, D, P, block, topk, local, init):
+    segs = [(1, 1), (1, 9 * block + 3), (5, 5), (9, 4 * block + 2), (1, block), (2, block + 1)]
+    (q, iq, ks, vs, iks, bt, seg), T = sparse_problem(dtype, Hq, Hkv, D, P, segs, block)
+    max_blocks = max(kv for _, kv in segs) // block + 1
+    sel = torch.full((T, Hkv, topk), -7, dtype=torch.int32, device=DEV)
+    want_sel = torch.full_like(sel, -7)
+    ops.sparse_select(iq, iks, bt, seg, len(segs), block, local, init, max_blocks, sel)
+    ref.sparse_select(iq, iks, bt, seg, len(segs), block, local, init, max_blocks, want_sel)
+    assert torch.equal(sel, want_sel)
+    # the local block is always there, the list ascends, and short sequences take every block
+    assert (sel[0, :, 0] == 0).all() and (sel[0, :, 1:] == -1).all()
+    plan = build_plan(segs, Hq // Hkv, 16, None, Hkv, sm_count=4096, min_split_keys=32, sparse=(block, topk))
+    items = torch.from_numpy(plan.items).to(DEV)
+    po = pm = None
+    if plan.n_slots:
+        po = torch.full((plan.n_slots, Hkv, 16, D), float("nan"), dtype=torch.float32, device=DEV)
+        pm = torch.full((plan.n_slots, Hkv, 16, 2), float("nan"), dtype=torch.float32, device=DEV)
+    out = torch.full((T, Hq, D), float("nan"), dtype=dtype, device=DEV)
+    want = torch.empty_like(out)
+    ops.paged_attention(q, ks, vs, bt, seg, len(segs), items, plan.n_items, po, pm, out, 16, D ** -0.5, None,
+                        sel=sel, block_size=block)
+    ref.paged_attention(q, ks, vs, bt, seg, len(segs), items, plan.n_items, None, None, want, 16, D ** -0.5, None,
+                        sel=sel, block_size=block)
+    assert not torch.isnan(out.float()).any()
+    torch.testing.assert_close(out.float(), want.float(), **attn_tol(dtype))
+    # while nothing is dropped the result is dense attention
+    dense = torch.empty_like(out)
+    ref.paged_attention(q, ks, vs, bt, seg, len(segs), items, plan.n_items, None, None, dense, 16, D ** -0.5, None)
+    short = [i for i, (ql, kv) in enumerate(segs) if kv <= topk * block]
+    for i in short:
+        q0, ql = int(seg[i, 0]), int(seg[i, 1])
+        torch.testing.assert_close(out[q0:q0 + ql].float(), dense[q0:q0 + ql].float(), **attn_tol(dtype))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [1, 7, 64, 100])
 def test_attention_window(dtype, window):

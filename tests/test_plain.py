@@ -28,7 +28,7 @@ def test_causal_and_deterministic(name, tmp_path_factory):
     mb = PlainM3(folder, rounding="bfloat16")
     sure = m.router_margins(toks) > NEAR_TIE  # elsewhere rounding may pick another expert
     assert sure.float().mean() > 0.5
-    assert (mb.logits(toks) - full)[sure].abs().max() < 0.02
+    assert (mb.logits(toks) - full)[sure].abs().max() < 0.03
 
 
 def test_sparse_attention_equals_dense_when_every_block_is_chosen(tmp_path_factory):

@@ -43,8 +43,8 @@ def check(got, ref, dtype, margins, what):
         assert_bf16_close(got, ref, margins, what)
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "C"])
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("A", "bfloat16"), ("C", "float32"), ("C", "bfloat16"),
+                                        ("D", "float32")])
 def test_trace_replay(name, dtype, tmp_path_factory, tmp_path):
     folder = model_folder(tmp_path_factory.getbasetemp(), name, ALL[name])
     plain = PlainM3(folder)

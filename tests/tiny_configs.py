@@ -6,7 +6,8 @@ B: 3 layers, hidden 96, 6 q / 3 kv heads, head 32, full rotary, theta 1e6, no QK
    16 experts top-4 width 48, softmax without bias, vocab 384, eps 1e-5, tied head.
 C: the reference's real options on small sizes: swigluoai, one dense prefix layer, a shared
    expert, routed_scaling_factor 2, 7 q / 1 kv heads of 48 (no power of two anywhere).
-D: block-sparse attention layers after one full layer (index heads, 8-token blocks).
+D: block-sparse attention layers after one full layer (index heads, 8-token blocks, top-3), two
+   experts that every token uses.
 """
 
 from __future__ import annotations
@@ -54,6 +55,9 @@ TINY_C = {
 
 TINY_D = dict(copy.deepcopy(TINY_A), **{
     "num_hidden_layers": 3,
+    # every token uses both experts: the only discrete choice left is the choice of key blocks, so
+    # bfloat16 runs can be compared over long stretches
+    "num_local_experts": 2, "num_experts_per_tok": 2,
     "sparse_attention_config": {
         "use_sparse_attention": True, "sparse_attention_freq": [0, 1, 1],
         "sparse_num_index_heads": 2, "sparse_index_dim": 16, "sparse_block_size": 8,
@@ -62,4 +66,4 @@ TINY_D = dict(copy.deepcopy(TINY_A), **{
     },
 })
 
-ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
