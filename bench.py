@@ -260,8 +260,8 @@ def main():
 
         def one(i):
             out = engine.step([StepEntry(r, [int(rng.integers(0, V))], [0]) for r in rids])
-            if sample:
-                sampler.sample(out.logits, params, rids, [i] * B)
+            if sample:  # the tokens stay on the device here; the end-to-end loop below reads them
+                sampler.launch(out.logits, params, rids, [i] * B)
 
         for i in range(warmup):
             one(i)
@@ -300,16 +300,24 @@ def main():
     n_e2e = args.warmup + args.steps
     for i in range(args.batch):
         sched.add_request(rng.integers(0, V, PROMPT).tolist(),
-                          SamplingParams(max_tokens=n_e2e + 4, ignore_eos=True), rid=("e", i))
+                          SamplingParams(max_tokens=n_e2e + 4 * args.batch + 8, ignore_eos=True), rid=("e", i))
     while any(not r.decoding for r in sched.running) or sched.waiting:
         sched.step()
+    # the entry point's own loop (LLM.generate -> Scheduler.run): step N+1 is launched before step
+    # N's tokens are read; every timed call uploads one step's metadata from pinned memory and
+    # brings one step's tokens back to host lists
     for _ in range(args.warmup):
-        sched.step()
+        sched.step_overlapped()
+    sched.drain()
     torch.cuda.synchronize()
     t1 = time.perf_counter()
+    got = 0
     for _ in range(args.steps):
-        sched.step()
+        got += len(sched.step_overlapped().sampled)
+    last = sched.drain()
+    got += len(last.sampled) if last is not None else 0
     torch.cuda.synchronize()
+    assert got == args.steps * args.batch, (got, args.steps, args.batch)
     e2e_ms = (time.perf_counter() - t1) * 1e3 / args.steps
     h2d = engine.buffers.last_upload_bytes + 16 * sampler.max_rows
     e2e = {"value": round(args.batch / (e2e_ms / 1e3), 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 3),

@@ -52,6 +52,9 @@ class EngineConfig:
     cuda_graph: bool = True  # replay decode-only steps from CUDA graphs
     cuda_graph_max_bs: Optional[int] = None
     check_cache: bool = False  # run the cache manager's conservation check after every step
+    # launch step N+1 before step N's tokens are read; the reference's switch is the environment
+    # variable FREETOKEN_DISABLE_OVERLAP_SCHEDULING (python/freetoken/env.py:72), honoured here too
+    overlap_scheduling: bool = True
 
     def __post_init__(self) -> None:
         if self.dtype != "auto":

@@ -41,6 +41,8 @@ int ftk_act_and_mul(const void* gate_up, int dtype, int n_rows, int inter, int a
 int ftk_cast(const void* src, int src_dtype, void* dst, int dst_dtype, long long n, void* stream);
 int ftk_table_update(int32_t* table, long long table_len, const int32_t* updates, int n_updates,
                      void* stream);
+int ftk_copy_tokens(int32_t* dst, int dst_len, const int32_t* pairs, const int32_t* src, int src_len, int n,
+                    int vocab, void* stream);
 int ftk_norm_rope_store(const void* x, int dtype, int n_tokens, int row_elems, int head_dim,
                         int rotary_dim, const int32_t* positions, const float* rope_table, int max_pos,
                         float eps, int gemma, int n_sections, const FtkSection* sections, void* stream);

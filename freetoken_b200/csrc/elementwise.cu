@@ -153,6 +153,18 @@ __global__ void table_update_kernel(int32_t* table, long long table_len, const i
   if (idx >= 0 && idx < table_len) table[idx] = updates[2 * i + 1];
 }
 
+// dst[pairs[i][0]] = src[pairs[i][1]]: tokens sampled by the previous step become inputs of this one
+// without a round trip through the host.  Values outside [0, vocab) become 0.
+__global__ void copy_tokens_kernel(int32_t* dst, int dst_len, const int32_t* pairs, const int32_t* src, int src_len,
+                                   int n, int vocab) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int d = pairs[2 * i], s = pairs[2 * i + 1];
+  if (d < 0 || d >= dst_len || s < 0 || s >= src_len) return;
+  const int v = src[s];
+  dst[d] = (v >= 0 && v < vocab) ? v : 0;
+}
+
 // out[r, :] = h[sorted_routes[r] / top_k, :]
 template <typename T, bool VEC>
 __global__ void moe_gather_kernel(const T* __restrict__ h, const int32_t* __restrict__ sorted_routes,
@@ -299,6 +311,16 @@ extern "C" int ftk_table_update(int32_t* table, long long table_len, const int32
   FTK_REQUIRE(table && updates, "table_update: null pointer");
   table_update_kernel<<<(n_updates + 127) / 128, 128, 0, (cudaStream_t)stream>>>(table, table_len, updates, n_updates);
   FTK_LAUNCH_CHECK("table_update");
+  return 0;
+}
+
+extern "C" int ftk_copy_tokens(int32_t* dst, int dst_len, const int32_t* pairs, const int32_t* src, int src_len, int n,
+                               int vocab, void* stream) {
+  FTK_REQUIRE(n >= 0 && dst_len >= 0 && src_len >= 0 && vocab >= 1, "copy_tokens: bad sizes");
+  if (n == 0) return 0;
+  FTK_REQUIRE(dst && pairs && src, "copy_tokens: null pointer");
+  copy_tokens_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(dst, dst_len, pairs, src, src_len, n, vocab);
+  FTK_LAUNCH_CHECK("copy_tokens");
   return 0;
 }
 

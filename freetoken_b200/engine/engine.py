@@ -44,6 +44,9 @@ class StepEntry:
     request_id: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()  # indices into ``tokens`` whose logits are wanted
+    # (int32 device tensor, index): the entry's single token is still on the device (sampled by a
+    # step whose result the host has not read yet); ``tokens`` then holds a placeholder
+    device_token: Optional[Tuple[torch.Tensor, int]] = None
 
 
 @dataclass
@@ -169,7 +172,7 @@ class Engine:
         T = self.max_step_tokens
         S = self.config.max_running_req
         n_groups = max(1, len(self.cache.paged))
-        core = 3 * T + 6 * S
+        core = 3 * T + 8 * S + 64
         per_group = T + 2 * (T // self.config.page_size + 2 * S + 4)
         n_plans = max(1, 2 * len({m.plan_key() for m in self.model.mixers() if hasattr(m, "plan_key")}))
         items = 8 * (T + S + 2 * self.sm_count * 32)
@@ -212,6 +215,10 @@ class Engine:
             if n < 1:
                 raise SchedulerError(f"request {e.request_id!r}: an entry needs at least one token")
             ids = np.asarray(e.tokens, dtype=np.int64)
+            if e.device_token is not None:
+                if n != 1:
+                    raise SchedulerError(f"request {e.request_id!r}: a token taken from the device stands alone")
+                ids = np.zeros(1, dtype=np.int64)
             if ids.min() < 0 or ids.max() >= vocab:
                 raise SchedulerError(f"request {e.request_id!r}: token id outside [0, {vocab})")
             token_ids[t0:t0 + n] = ids
@@ -260,6 +267,17 @@ class Engine:
         builder.add("seg_info", seg_info)
         builder.add("state_slots", np.asarray(plan.state_slots, dtype=np.int32))
         builder.add("logit_rows", np.asarray(logit_rows, dtype=np.int32))
+        # tokens that are still on the device: (place among this step's tokens, index in the source)
+        pending = np.full((S, 2), -1, dtype=np.int32)
+        pending_src = None
+        for i, e in enumerate(entries):
+            if e.device_token is not None:
+                src, idx = e.device_token
+                if pending_src is not None and src is not pending_src:
+                    raise SchedulerError("tokens taken from the device must come from one tensor per step")
+                pending_src = src
+                pending[i] = (segments[i].q_start, idx)
+        builder.add("pending", pending)
         n_updates = []
         for g in self.cache.paged:
             builder.add(f"slot_map.{g.index}", plan.slot_maps[g.index])
@@ -289,6 +307,9 @@ class Engine:
             n_logit_rows=len(logit_rows), attention_plans=plans, decode_only=decode_only)
         step.extras["tensors"] = tensors
         views = self._step_views(tensors)
+
+        if pending_src is not None:  # before the step (and outside its graph): fill in the device tokens
+            ops.copy_tokens(tensors["token_ids"], tensors["pending"], pending_src, S, self.spec.vocab_size)
 
         def body() -> torch.Tensor:
             for g, n_up in zip(self.cache.paged, n_updates):

@@ -54,7 +54,8 @@ class LLM:
         sched = Scheduler(self.engine, self.sampler, self.eos_token_ids)
         for i, (p, sp) in enumerate(zip(prompts, sampling_params)):
             sched.add_request(self._ids(p), sp, rid=i)
-        sched.run()
+        off = os.environ.get("FREETOKEN_DISABLE_OVERLAP_SCHEDULING", "").lower() in ("1", "true", "yes", "on")
+        sched.run(overlap=self.config.overlap_scheduling and not off)
         results = []
         for i in range(len(prompts)):
             req = sched.done[i]

@@ -41,6 +41,8 @@ class Request:
     finish_reason: Optional[str] = None
     error: Optional[str] = None
     reserved: List[int] = field(default_factory=list)  # pages reserved per cache group
+    in_flight: int = 0  # tokens sampled on the device and not yet read by the host
+    source: Optional[Tuple[Any, int]] = None  # (device tensor, index) of the newest such token
 
     @property
     def decoding(self) -> bool:
@@ -57,6 +59,16 @@ class StepReport:
     admitted: List[Hashable]
 
 
+@dataclass
+class Flight:
+    """A step that runs on the device: what it fed, whom it samples for, and the sampler's ticket."""
+
+    entries: List[Tuple[Hashable, int]]
+    rows: List[Request]
+    ticket: Any
+    admitted: List[Hashable]
+
+
 class Scheduler:
     def __init__(self, engine, sampler, eos_token_ids: Sequence[int] = ()):
         self.engine = engine
@@ -66,6 +78,7 @@ class Scheduler:
         self.running: List[Request] = []
         self.done: Dict[Hashable, Request] = {}
         self._next_id = 0
+        self._flight: Optional[Flight] = None
         cache = engine.cache
         self.pool_pages = [g.pool.num_pages for g in cache.paged]
         self.reserved = [0] * len(cache.paged)
@@ -118,12 +131,16 @@ class Scheduler:
         return admitted
 
     def plan_step(self) -> List[Tuple[Request, List[int], List[int]]]:
-        """(request, tokens, wanted places) for the next step: decodes first, then prompt portions."""
+        """(request, tokens, wanted places) for the next step: decodes first, then prompt portions.
+
+        A request whose newest token is still on the device (``in_flight``) is planned with a
+        placeholder token; a request whose launched tokens already reach ``max_tokens`` is left
+        out (it finishes by length when its last launch is resolved)."""
         plan = []
         budget = self.max_step_tokens
         for req in self.running:
-            if req.decoding and budget > 0:
-                plan.append((req, [req.last_token], [0]))
+            if req.decoding and budget > 0 and len(req.output) + req.in_flight < req.max_tokens:
+                plan.append((req, [0 if req.in_flight else req.last_token], [0]))
                 budget -= 1
         for req in self.running:
             if not req.decoding and budget > 0:
@@ -134,23 +151,35 @@ class Scheduler:
         return plan
 
     # ------------------------------------------------------------------ one step
-    def step(self) -> StepReport:
+    def _launch(self) -> Optional[Flight]:
+        """Admit, plan and start one step on the device; nothing waits for it."""
         admitted = self._admit()
         plan = self.plan_step()
         if not plan:
-            if self.waiting and not self.running:
-                raise SchedulerError("a waiting request cannot be admitted into an empty engine")
-            return StepReport([], [], [], admitted)
-        out = self.engine.step([StepEntry(r.rid, toks, want) for r, toks, want in plan])
+            return Flight([], [], None, admitted) if admitted else None
+        entries = [StepEntry(r.rid, toks, want, device_token=r.source if (r.decoding and r.in_flight) else None)
+                   for r, toks, want in plan]
+        out = self.engine.step(entries)
         by_rid = {r.rid: r for r, _, _ in plan}
         for req, toks, _ in plan:
             if not req.decoding:
                 req.fed += len(toks)
         rows = [by_rid[rid] for rid, _ in out.rows]
-        tokens = self.sampler.sample(out.logits, [r.params for r in rows], [r.rid for r in rows],
-                                     [len(r.output) for r in rows])
+        ticket = self.sampler.launch(out.logits, [r.params for r in rows], [r.rid for r in rows],
+                                     [len(r.output) + r.in_flight for r in rows])
+        for i, req in enumerate(rows):
+            req.in_flight += 1
+            req.source = (ticket.device_tokens, i)
+        return Flight([(r.rid, len(t)) for r, t, _ in plan], rows, ticket, admitted)
+
+    def _resolve(self, flight: Flight) -> StepReport:
+        """Take a launched step's tokens to the host; finish and free what ended."""
+        tokens = self.sampler.result(flight.ticket) if flight.ticket is not None else []
         sampled, finished = [], []
-        for req, tok in zip(rows, tokens):
+        for req, tok in zip(flight.rows, tokens):
+            req.in_flight -= 1
+            if req.finished:
+                continue  # ended by an earlier token; this one was computed ahead and is dropped
             req.output.append(tok)
             req.last_token = tok
             sampled.append((req.rid, tok))
@@ -160,17 +189,55 @@ class Scheduler:
                 req.finished, req.finish_reason = True, "length"
             if req.finished:
                 finished.append(req.rid)
-        for rid in finished:
-            req = by_rid[rid]
-            self.running.remove(req)
-            self.engine.close(rid)
-            for i, n in enumerate(req.reserved):
-                self.reserved[i] -= n
-            self.done[rid] = req
-        return StepReport([(r.rid, len(t)) for r, t, _ in plan], sampled, finished, admitted)
+                # a step that already runs with this request is ordered before any later step
+                # on the stream, so its pages can go back now
+                self.running.remove(req)
+                self.engine.close(req.rid)
+                for i, n in enumerate(req.reserved):
+                    self.reserved[i] -= n
+                self.done[req.rid] = req
+        return StepReport(flight.entries, sampled, finished, flight.admitted)
+
+    def step(self) -> StepReport:
+        """One step, launched and resolved (nothing stays in flight)."""
+        if self._flight is not None:
+            return self._resolve(self._take())
+        flight = self._launch()
+        if flight is None:
+            if self.waiting and not self.running:
+                raise SchedulerError("a waiting request cannot be admitted into an empty engine")
+            return StepReport([], [], [], [])
+        return self._resolve(flight)
+
+    def _take(self) -> Flight:
+        flight, self._flight = self._flight, None
+        return flight
+
+    def step_overlapped(self) -> StepReport:
+        """Launch the next step, then resolve the one before it: the host's work for step N+1
+        (planning, metadata, launches) runs while the device computes step N.  The newest token
+        of every decoding request stays on the device and is copied into the next step's
+        token ids there; an EOS is seen one step late and the token computed past it is dropped.
+        The reference overlaps the same way (python/freetoken/scheduler/scheduler.py:194-256)."""
+        before = self._flight
+        self._flight = self._launch()
+        if before is not None:
+            return self._resolve(before)
+        if self._flight is None:
+            if self.waiting and not self.running:
+                raise SchedulerError("a waiting request cannot be admitted into an empty engine")
+            return StepReport([], [], [], [])
+        if self._flight.ticket is None or not self._flight.rows:
+            return self._resolve(self._take())  # nothing to wait for: no token was sampled
+        return StepReport([], [], [], [])
+
+    def drain(self) -> Optional[StepReport]:
+        """Resolve what is in flight."""
+        return self._resolve(self._take()) if self._flight is not None else None
 
     def abort(self, rid: Hashable) -> bool:
-        """Drop a request between steps; its pages and slot are given back."""
+        """Drop a request between steps; its pages and slot are given back.  A token computed
+        ahead for it (overlapped scheduling) is dropped when its step is resolved."""
         for req in list(self.waiting):
             if req.rid == rid:
                 self.waiting.remove(req)
@@ -192,6 +259,10 @@ class Scheduler:
     def idle(self) -> bool:
         return not self.waiting and not self.running
 
-    def run(self) -> None:
+    def run(self, overlap: bool = True) -> None:
         while not self.idle:
-            self.step()
+            if overlap:
+                self.step_overlapped()
+            else:
+                self.step()
+        self.drain()

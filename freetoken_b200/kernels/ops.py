@@ -71,6 +71,7 @@ _SIGNATURES = {
     "ftk_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
     "ftk_cast": [_vp, _i, _vp, _i, ctypes.c_longlong, _vp],
     "ftk_table_update": [_vp, ctypes.c_longlong, _vp, _i, _vp],
+    "ftk_copy_tokens": [_vp, _i, _vp, _vp, _i, _i, _i, _vp],
     "ftk_read_status": [ctypes.POINTER(ctypes.c_int)],
     "ftk_set_moe_tensor_cores": [_i],
 }
@@ -214,6 +215,15 @@ def table_update(table: torch.Tensor, updates: torch.Tensor, n_updates: int) -> 
     _check(_lib().ftk_table_update(_dev(table, "table", torch.int32), table.numel(),
                                    _dev(updates, "updates", torch.int32), n_updates, _stream()),
            "table_update")
+
+
+def copy_tokens(dst: torch.Tensor, pairs: torch.Tensor, src: torch.Tensor, n: int, vocab: int) -> None:
+    """``dst[pairs[i, 0]] = src[pairs[i, 1]]`` for ``i < n`` (negative indices skipped; values outside
+    the vocabulary become 0): tokens sampled on the device become the next step's inputs."""
+    if pairs.numel() < 2 * n:
+        raise KernelError("copy_tokens: pairs shorter than n")
+    _check(_lib().ftk_copy_tokens(_dev(dst, "dst", torch.int32), dst.numel(), _dev(pairs, "pairs", torch.int32),
+                                  _dev(src, "src", torch.int32), src.numel(), n, vocab, _stream()), "copy_tokens")
 
 
 def cast(src: torch.Tensor, dst: torch.Tensor) -> None:

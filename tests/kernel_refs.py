@@ -55,6 +55,13 @@ def cast(src, dst):
     dst.view(-1).copy_(src.reshape(-1).to(dst.dtype))
 
 
+def copy_tokens(dst, pairs, src, n, vocab):
+    for d, s_ in pairs.view(-1, 2)[:n].tolist():
+        if d >= 0 and s_ >= 0:
+            v = int(src[s_])
+            dst[d] = v if 0 <= v < vocab else 0
+
+
 def table_update(table, updates, n_updates):
     u = updates.view(-1, 2)[:n_updates]
     ok = u[:, 0] >= 0
@@ -233,7 +240,7 @@ def sample(logits, temperature, top_k, top_p, u, out):
         out[r] = idx
 
 
-ALL = ["sparse_select", "embedding_gather", "add_rmsnorm", "act_and_mul", "cast", "table_update", "norm_rope_store",
+ALL = ["copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "act_and_mul", "cast", "table_update", "norm_rope_store",
        "paged_attention", "router_topk", "moe_permute", "moe_gather", "moe_gemm1_act", "moe_gemm2",
        "moe_combine", "sample"]
 

@@ -104,6 +104,38 @@ def test_eos_finishes_and_abort_frees(setup):
     assert all(g.pool.free_count == g.pool.num_pages for g in sched.engine.cache.paged)
 
 
+def test_overlapped_steps_give_the_same_tokens_as_plain_steps(setup):
+    """Launching step N+1 before step N's tokens are read changes nothing but the timing: the
+    same outputs, an EOS seen one step late with the token past it dropped, every page back."""
+    outs = {}
+    for overlap in (False, True):
+        sched, plain = setup(pages=14, page=4, reqs=3, max_step=9)
+        V = plain.cfg.vocab
+        prompts = [tokens_for(V, n, 50 + n) for n in (6, 13, 4, 10, 3)]
+        greedy = plain.greedy(prompts[0], 9)
+        sched.eos = {greedy[3]}
+        for i, p in enumerate(prompts):
+            sched.add_request(p, SamplingParams(max_tokens=9 if i != 2 else 1, temperature=0.0 if i % 2 == 0 else 0.7,
+                                                seed=3), rid=i)
+        fed = {i: 0 for i in range(5)}
+        while not sched.idle:
+            rep = sched.step_overlapped() if overlap else sched.step()
+            for rid, n in rep.entries:
+                fed[rid] += n
+            sched.engine.cache.check()
+            assert all(x <= p for x, p in zip(sched.reserved, sched.pool_pages))
+        assert sched.drain() is None or overlap
+        outs[overlap] = {i: (sched.done[i].output, sched.done[i].finish_reason) for i in range(5)}
+        first = greedy.index(greedy[3])
+        assert outs[overlap][0] == (greedy[:first + 1], "stop")
+        assert len(outs[overlap][2][0]) == 1
+        assert all(g.pool.free_count == g.pool.num_pages for g in sched.engine.cache.paged)
+        assert sched.reserved == [0]
+        if not overlap:  # a plain step never feeds a token past the end
+            assert fed[0] == len(prompts[0]) + first
+    assert outs[True] == outs[False]
+
+
 def test_temperature_sampling_is_seeded_and_independent_of_the_batch(setup):
     sched, plain = setup(raw=TINY_B, name="B", page=8, pages=30, max_step=7)
     V = plain.cfg.vocab
