@@ -63,6 +63,12 @@ int ftk_sparse_select(const void* iq, const void* ik_slab, int dtype, const int3
                       int32_t* sel, void* stream);
 int ftk_router_topk(const float* logits, const float* bias, int n_tokens, int n_experts, int top_k,
                     int scoring, float scale, int32_t* ids, float* weights, void* stream);
+// Router logits (float32 x [T, hidden] times gate_w [E, hidden]), choice and sort of the routes in one
+// launch, for steps of at most 64 tokens; ftk_moe_route_fits says whether the sizes are taken.
+int ftk_moe_route_fits(int n_tokens, int hidden, int n_experts, int top_k);
+int ftk_moe_route(const float* x, const float* gate_w, const float* bias, int n_tokens, int hidden, int n_experts,
+                  int top_k, int scoring, float scale, float* logits, int32_t* ids, float* weights,
+                  int32_t* counts, int32_t* offsets, int32_t* routes, int32_t* pos, void* stream);
 int ftk_moe_permute(const int32_t* topk_ids, int n_tokens, int top_k, int n_experts,
                     int32_t* expert_counts, int32_t* expert_offsets, int32_t* sorted_routes,
                     int32_t* route_pos, void* stream);

@@ -11,25 +11,21 @@ namespace ftk {
 
 constexpr int kRouterWarps = 4;
 
-__global__ void router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
-                                   int n_tokens, int n_experts, int top_k, int scoring, float scale,
-                                   int32_t* __restrict__ ids, float* __restrict__ weights) {
-  extern __shared__ float sm[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * kRouterWarps + warp;
-  if (t >= n_tokens) return;
-  float* s = sm + (size_t)warp * 2 * n_experts;  // unbiased scores
-  float* c = s + n_experts;                      // scores the choice is made by
-  const float* row = logits + (size_t)t * n_experts;
+// Scores, choice and weights of one token, by one warp.  `s` and `c` hold n_experts floats each.
+__device__ __forceinline__ void route_token(const float* __restrict__ row, const float* __restrict__ bias,
+                                            int n_experts, int top_k, int scoring, float scale, float* s, float* c,
+                                            int32_t* __restrict__ ids, float* __restrict__ weights,
+                                            int32_t* ids_copy) {
+  const int lane = threadIdx.x & 31;
   if (scoring == FTK_SCORE_SIGMOID) {
-    for (int e = lane; e < n_experts; e += 32) s[e] = 1.f / (1.f + expf(-row[e]));
+    for (int e = lane; e < n_experts; e += 32) s[e] = 1.f / (1.f + expf(-__ldcg(row + e)));
   } else {
     float mx = -INFINITY;
-    for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, row[e]);
+    for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, __ldcg(row + e));
     mx = warp_max(mx);
     float sum = 0.f;
     for (int e = lane; e < n_experts; e += 32) {
-      const float v = expf(row[e] - mx);
+      const float v = expf(__ldcg(row + e) - mx);
       s[e] = v;
       sum += v;
     }
@@ -62,18 +58,254 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, const float
     const float w = s[bi];
     wsum += w;
     if (lane == 0) {
-      ids[(size_t)t * top_k + j] = bi;
-      weights[(size_t)t * top_k + j] = w;
+      ids[j] = bi;
+      if (ids_copy) ids_copy[j] = bi;
+      weights[j] = w;
       c[bi] = -INFINITY;
     }
     __syncwarp();
   }
   const float denom = scoring == FTK_SCORE_SIGMOID ? wsum + 1e-20f : wsum;
-  if (lane < top_k || true) {
-    for (int j = lane; j < top_k; j += 32) {
-      const size_t i = (size_t)t * top_k + j;
-      weights[i] = weights[i] / denom * scale;
+  for (int j = lane; j < top_k; j += 32) weights[j] = weights[j] / denom * scale;
+}
+
+// The same with the token's scores in registers (n_experts <= 32 * PER): the largest remaining choice
+// is found with two warp reductions, first over the values (as order-preserving integers, NaN lowest),
+// then over the indices of those that have it.  Same results as route_token.
+__device__ __forceinline__ unsigned int order_key(float v) {
+  if (v != v) return 0u;
+  const unsigned int u = __float_as_uint(v + 0.f);  // -0 becomes +0
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+template <int PER>
+__device__ __forceinline__ void route_token_regs(const float* __restrict__ row, const float* __restrict__ bias,
+                                                 int n_experts, int top_k, int scoring, float scale, float* wbuf,
+                                                 int32_t* __restrict__ ids, float* __restrict__ weights,
+                                                 int32_t* ids_copy) {
+  const int lane = threadIdx.x & 31;
+  float sv[PER];
+  unsigned int key[PER];
+#pragma unroll
+  for (int q = 0; q < PER; ++q) {
+    const int e = q * 32 + lane;
+    sv[q] = e < n_experts ? __ldcg(row + e) : -INFINITY;
+  }
+  if (scoring == FTK_SCORE_SIGMOID) {
+#pragma unroll
+    for (int q = 0; q < PER; ++q) sv[q] = 1.f / (1.f + expf(-sv[q]));
+  } else {
+    float mx = -INFINITY;
+#pragma unroll
+    for (int q = 0; q < PER; ++q) mx = fmaxf(mx, sv[q]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int q = 0; q < PER; ++q) {
+      sv[q] = q * 32 + lane < n_experts ? expf(sv[q] - mx) : 0.f;
+      sum += sv[q];
     }
+    // the sum runs over experts in the order route_token takes them: lane by lane, then across lanes
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int q = 0; q < PER; ++q) sv[q] = sv[q] / sum;
+  }
+  const unsigned int floor_key = order_key(-INFINITY);  // never chosen: -inf and NaN
+#pragma unroll
+  for (int q = 0; q < PER; ++q) {
+    const int e = q * 32 + lane;
+    key[q] = e < n_experts ? order_key(bias ? sv[q] + bias[e] : sv[q]) : 0u;
+  }
+  float wsum = 0.f;
+  for (int j = 0; j < top_k; ++j) {
+    unsigned int best = 0u;
+    int slot = 0;
+#pragma unroll
+    for (int q = 0; q < PER; ++q)
+      if (key[q] > best) {
+        best = key[q];
+        slot = q;
+      }
+    const unsigned int top = __reduce_max_sync(0xffffffffu, best);
+    int bi = 0;
+    if (top > floor_key) bi = (int)__reduce_min_sync(0xffffffffu, best == top ? (unsigned)(slot * 32 + lane) : 0x7fffffffu);
+    const int owner = bi & 31, oslot = bi >> 5;
+    float mine = 0.f;
+#pragma unroll
+    for (int q = 0; q < PER; ++q)
+      if (q == oslot) mine = sv[q];
+    const float w = __shfl_sync(0xffffffffu, mine, owner);
+    wsum += w;
+    if (lane == owner && top > floor_key) {
+#pragma unroll
+      for (int q = 0; q < PER; ++q)
+        if (q == oslot) key[q] = 0u;
+    }
+    if (lane == 0) {
+      ids[j] = bi;
+      if (ids_copy) ids_copy[j] = bi;
+      wbuf[j] = w;
+    }
+  }
+  __syncwarp();
+  const float denom = scoring == FTK_SCORE_SIGMOID ? wsum + 1e-20f : wsum;
+  for (int j = lane; j < top_k; j += 32) weights[j] = wbuf[j] / denom * scale;
+  __syncwarp();
+}
+
+// One token by one warp, in registers where the experts fit; `s` holds 2 * n_experts floats.
+__device__ __forceinline__ void route_one(const float* __restrict__ row, const float* __restrict__ bias, int n_experts,
+                                          int top_k, int scoring, float scale, float* s, int32_t* __restrict__ ids,
+                                          float* __restrict__ weights, int32_t* ids_copy) {
+  if (n_experts <= 128)
+    route_token_regs<4>(row, bias, n_experts, top_k, scoring, scale, s, ids, weights, ids_copy);
+  else if (n_experts <= 256)
+    route_token_regs<8>(row, bias, n_experts, top_k, scoring, scale, s, ids, weights, ids_copy);
+  else if (n_experts <= 512)
+    route_token_regs<16>(row, bias, n_experts, top_k, scoring, scale, s, ids, weights, ids_copy);
+  else
+    route_token(row, bias, n_experts, top_k, scoring, scale, s, s + n_experts, ids, weights, ids_copy);
+}
+
+__global__ void router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                   int n_tokens, int n_experts, int top_k, int scoring, float scale,
+                                   int32_t* __restrict__ ids, float* __restrict__ weights) {
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * kRouterWarps + warp;
+  if (t >= n_tokens) return;
+  float* s = sm + (size_t)warp * 2 * n_experts;  // unbiased scores
+  route_one(logits + (size_t)t * n_experts, bias, n_experts, top_k, scoring, scale, s,
+            ids + (size_t)t * top_k, weights + (size_t)t * top_k, nullptr);
+}
+
+// The whole routing of a small step in one launch: router logits (a float32 matrix-vector product
+// per token, python/freetoken/models/minimax_m3/moe.py:71-73), then, in the block that finishes
+// last, the choice of every token (route_token) and the counting sort of the routes by expert
+// (what moe_permute does).  A block holds kRouteExperts experts; its warps share their
+// weight rows and add their parts in a fixed order, so a token's logits never depend on the
+// batch.  Blocks count their arrival in g_route_arrivals; nobody waits for anybody.
+constexpr int kRouteWarps = 16;   // all of them share the block's weight rows, each a part of the width
+constexpr int kRouteExperts = 4;  // experts per block: a token's activations are loaded once for all of them
+constexpr int kRouteTokens = 8;   // tokens per pass over the weight rows
+__device__ unsigned int g_route_arrivals = 0;
+
+__global__ void __launch_bounds__(kRouteWarps * 32)
+moe_route_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                 int n_tokens, int hidden, int n_experts, int top_k, int scoring, float scale,
+                 float* __restrict__ logits, int32_t* __restrict__ ids, float* __restrict__ weights,
+                 int32_t* __restrict__ counts, int32_t* __restrict__ offsets, int32_t* __restrict__ routes,
+                 int32_t* __restrict__ pos) {
+  extern __shared__ float sm[];
+  __shared__ float part[kRouteExperts][kRouteTokens][kRouteWarps + 1];
+  __shared__ bool last;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int e0 = blockIdx.x * kRouteExperts;
+  const int h4 = hidden >> 2;
+  const float4* w4 = reinterpret_cast<const float4*>(w);
+  const float4* x4 = reinterpret_cast<const float4*>(x);
+  // every block fetches the bias now, under the matrix product, so that the one that turns out to
+  // be last does not wait for it
+  float* sbias = sm + (size_t)kRouteWarps * 2 * n_experts;
+  if (bias)
+    for (int i = tid; i < n_experts; i += blockDim.x) sbias[i] = __ldg(bias + i);
+  for (int t0 = 0; t0 < n_tokens; t0 += kRouteTokens) {
+    const int nt = min(kRouteTokens, n_tokens - t0);
+    float acc[kRouteExperts][kRouteTokens];
+#pragma unroll
+    for (int j = 0; j < kRouteExperts; ++j)
+#pragma unroll
+      for (int u = 0; u < kRouteTokens; ++u) acc[j][u] = 0.f;
+#pragma unroll 2
+    for (int i = tid; i < h4; i += kRouteWarps * 32) {
+      float4 wv[kRouteExperts], xv[kRouteTokens];
+#pragma unroll
+      for (int j = 0; j < kRouteExperts; ++j) wv[j] = __ldg(w4 + (size_t)min(e0 + j, n_experts - 1) * h4 + i);
+#pragma unroll
+      for (int u = 0; u < kRouteTokens; ++u) xv[u] = __ldg(x4 + (size_t)min(t0 + u, n_tokens - 1) * h4 + i);
+#pragma unroll
+      for (int j = 0; j < kRouteExperts; ++j)
+#pragma unroll
+        for (int u = 0; u < kRouteTokens; ++u) {
+          acc[j][u] = fmaf(wv[j].x, xv[u].x, acc[j][u]);
+          acc[j][u] = fmaf(wv[j].y, xv[u].y, acc[j][u]);
+          acc[j][u] = fmaf(wv[j].z, xv[u].z, acc[j][u]);
+          acc[j][u] = fmaf(wv[j].w, xv[u].w, acc[j][u]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kRouteExperts; ++j)
+#pragma unroll
+      for (int u = 0; u < kRouteTokens; ++u) {
+        const float v = warp_sum(acc[j][u]);
+        if (lane == 0) part[j][u][warp] = v;
+      }
+    __syncthreads();
+    if (tid < kRouteExperts * kRouteTokens) {
+      const int j = tid / kRouteTokens, u = tid % kRouteTokens;
+      if (u < nt && e0 + j < n_experts) {
+        float v = part[j][u][0];
+#pragma unroll
+        for (int q = 1; q < kRouteWarps; ++q) v += part[j][u][q];
+        logits[(size_t)(t0 + u) * n_experts + e0 + j] = v;
+      }
+    }
+    __syncthreads();
+  }
+  if (tid < kRouteExperts * kRouteTokens) __threadfence();
+  __syncthreads();
+  if (tid == 0) last = atomicAdd(&g_route_arrivals, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  // ---- the last block: every token's choice
+  const int n_routes = n_tokens * top_k;
+  int* cnt = reinterpret_cast<int*>(sbias + n_experts);
+  int* off = cnt + n_experts;          // n_experts + 1
+  int* sid = off + n_experts + 1;      // n_routes
+  float* s = sm + (size_t)warp * 2 * n_experts;
+  for (int t = warp; t < n_tokens; t += kRouteWarps)
+    route_one(logits + (size_t)t * n_experts, bias ? sbias : nullptr, n_experts, top_k, scoring, scale, s,
+              ids + (size_t)t * top_k, weights + (size_t)t * top_k, sid + (size_t)t * top_k);
+  for (int i = tid; i < n_experts; i += blockDim.x) cnt[i] = 0;
+  __syncthreads();
+  // ---- counting sort of the routes by expert; rows of one expert keep the order of the routes
+  for (int r = tid; r < n_routes; r += blockDim.x) atomicAdd(&cnt[sid[r]], 1);
+  __syncthreads();
+  if (warp == 0) {
+    const int per = (n_experts + 31) / 32;
+    const int lo = min(lane * per, n_experts), hi = min(lo + per, n_experts);
+    int mine = 0;
+    for (int i = lo; i < hi; ++i) mine += cnt[i];
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    int run = incl - mine;
+    for (int i = lo; i < hi; ++i) {
+      off[i] = run;
+      run += cnt[i];
+    }
+    if (lane == 31) off[n_experts] = incl;
+  }
+  __syncthreads();
+  for (int i = tid; i < n_experts; i += blockDim.x) {
+    counts[i] = cnt[i];
+    offsets[i] = off[i];
+    int run = off[i];
+    if (cnt[i])
+      for (int r = 0; r < n_routes; ++r)
+        if (sid[r] == i) {
+          routes[run] = r;
+          pos[r] = run;
+          ++run;
+        }
+  }
+  if (tid == 0) {
+    offsets[n_experts] = off[n_experts];
+    g_route_arrivals = 0;  // every block has arrived: ready for the next launch
   }
 }
 
@@ -95,5 +327,34 @@ extern "C" int ftk_router_topk(const float* logits, const float* bias, int n_tok
   router_topk_kernel<<<blocks, kRouterWarps * 32, smem, (cudaStream_t)stream>>>(logits, bias, n_tokens, n_experts, top_k,
                                                                                scoring, scale, ids, weights);
   FTK_LAUNCH_CHECK("router_topk");
+  return 0;
+}
+
+static size_t route_smem(int n_tokens, int n_experts, int top_k) {
+  return (size_t)(kRouteWarps * 2 + 1) * n_experts * sizeof(float) + (size_t)(2 * n_experts + 1 + n_tokens * top_k) * sizeof(int);
+}
+
+extern "C" int ftk_moe_route_fits(int n_tokens, int hidden, int n_experts, int top_k) {
+  return n_tokens >= 1 && n_tokens <= 64 && hidden % 4 == 0 && n_experts >= 1 && top_k >= 1 && top_k <= n_experts &&
+         route_smem(n_tokens, n_experts, top_k) <= 160 * 1024;
+}
+
+extern "C" int ftk_moe_route(const float* x, const float* gate_w, const float* bias, int n_tokens, int hidden,
+                             int n_experts, int top_k, int scoring, float scale, float* logits, int32_t* ids,
+                             float* weights, int32_t* counts, int32_t* offsets, int32_t* routes, int32_t* pos,
+                             void* stream) {
+  FTK_REQUIRE(scoring == FTK_SCORE_SIGMOID || scoring == FTK_SCORE_SOFTMAX, "moe_route: unknown scoring %d", scoring);
+  FTK_REQUIRE(ftk_moe_route_fits(n_tokens, hidden, n_experts, top_k),
+              "moe_route: %d tokens, width %d, %d experts, top %d do not fit the one-launch routing (at most 64 tokens, "
+              "a width that is a multiple of 4); use the matrix product + router_topk + moe_permute",
+              n_tokens, hidden, n_experts, top_k);
+  FTK_REQUIRE(x && gate_w && logits && ids && weights && counts && offsets && routes && pos, "moe_route: null pointer");
+  FTK_REQUIRE(((uintptr_t)x | (uintptr_t)gate_w) % 16 == 0, "moe_route: x and the gate weight must be 16-byte aligned");
+  const size_t smem = route_smem(n_tokens, n_experts, top_k);
+  if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const int blocks = (n_experts + kRouteExperts - 1) / kRouteExperts;
+  moe_route_kernel<<<blocks, kRouteWarps * 32, smem, (cudaStream_t)stream>>>(
+      x, gate_w, bias, n_tokens, hidden, n_experts, top_k, scoring, scale, logits, ids, weights, counts, offsets, routes, pos);
+  FTK_LAUNCH_CHECK("moe_route");
   return 0;
 }

@@ -63,6 +63,8 @@ _SIGNATURES = {
     "ftk_sparse_select": [_vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "ftk_router_topk": [_vp, _vp, _i, _i, _i, _i, _f, _vp, _vp, _vp],
     "ftk_moe_permute": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp],
+    "ftk_moe_route_fits": [_i, _i, _i, _i],
+    "ftk_moe_route": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "ftk_moe_gather": [_vp, _i, _vp, _i, _i, _i, _vp, _vp],
     "ftk_moe_gemm1_act": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _f, _f, _vp, _vp],
     "ftk_moe_gemm2": [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
@@ -400,6 +402,35 @@ def moe_permute(topk_ids: torch.Tensor, n_experts: int, expert_counts: torch.Ten
                                   _dev(expert_offsets, "expert_offsets", torch.int32),
                                   _dev(sorted_routes, "sorted_routes", torch.int32),
                                   _dev(route_pos, "route_pos", torch.int32), _stream()), "moe_permute", 2)
+
+
+def moe_route_fits(n_tokens: int, hidden: int, n_experts: int, top_k: int) -> bool:
+    """Whether :func:`moe_route` takes these sizes (small steps only)."""
+    return bool(_lib().ftk_moe_route_fits(n_tokens, hidden, n_experts, top_k))
+
+
+def moe_route(x: torch.Tensor, gate_w: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, scoring: str,
+              scale: float, logits: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+              expert_counts: torch.Tensor, expert_offsets: torch.Tensor, sorted_routes: torch.Tensor,
+              route_pos: torch.Tensor) -> None:
+    """``logits = x @ gate_w^T`` in float32, then :func:`router_topk` and :func:`moe_permute`, in one launch."""
+    T, H = x.shape
+    E = gate_w.shape[0]
+    if gate_w.shape != (E, H) or logits.shape != (T, E) or ids.shape != (T, top_k) or weights.shape != (T, top_k):
+        raise KernelError("moe_route: shapes do not agree")
+    if expert_offsets.shape != (E + 1,) or expert_counts.shape != (E,) or sorted_routes.numel() != T * top_k \
+            or route_pos.numel() != T * top_k:
+        raise KernelError("moe_route: output shapes are wrong")
+    if bias is not None and bias.shape != (E,):
+        raise KernelError("moe_route: bias must be [E]")
+    _check(_lib().ftk_moe_route(_dev(x, "x", torch.float32), _dev(gate_w, "gate_w", torch.float32),
+                                _dev(bias, "bias", torch.float32), T, H, E, top_k, SCORE_CODES[scoring], float(scale),
+                                _dev(logits, "logits", torch.float32), _dev(ids, "ids", torch.int32),
+                                _dev(weights, "weights", torch.float32),
+                                _dev(expert_counts, "expert_counts", torch.int32),
+                                _dev(expert_offsets, "expert_offsets", torch.int32),
+                                _dev(sorted_routes, "sorted_routes", torch.int32),
+                                _dev(route_pos, "route_pos", torch.int32), _stream()), "moe_route")
 
 
 def moe_gather(h: torch.Tensor, sorted_routes: torch.Tensor, top_k: int, out: torch.Tensor) -> None:

@@ -82,16 +82,20 @@ class MoE(FeedForward):
                 h_f32 = ws.get("moe.h_f32", (T, self.hidden), torch.float32, (cap, self.hidden))
                 ops.cast(h, h_f32)
         logits = ws.get("moe.logits", (T, E), torch.float32, (cap, E))
-        torch.matmul(h_f32, self.params["gate.weight"].t(), out=logits)
         ids = ws.get("moe.ids", (T, k), torch.int32, (cap, k))
         wts = ws.get("moe.weights", (T, k), torch.float32, (cap, k))
-        ops.router_topk(logits, self.params.get("e_score_correction_bias"), k, self.scoring,
-                        self.scale, ids, wts)
         counts = ws.get("moe.counts", (E,), torch.int32)
         offsets = ws.get("moe.offsets", (E + 1,), torch.int32)
         routes = ws.get("moe.routes", (R,), torch.int32, (cap * k,))
         pos = ws.get("moe.pos", (R,), torch.int32, (cap * k,))
-        ops.moe_permute(ids, E, counts, offsets, routes, pos)
+        bias = self.params.get("e_score_correction_bias")
+        if ops.moe_route_fits(T, self.hidden, E, k):  # small steps: logits, choice and sort in one launch
+            ops.moe_route(h_f32, self.params["gate.weight"], bias, k, self.scoring, self.scale, logits, ids, wts,
+                          counts, offsets, routes, pos)
+        else:
+            torch.matmul(h_f32, self.params["gate.weight"].t(), out=logits)
+            ops.router_topk(logits, bias, k, self.scoring, self.scale, ids, wts)
+            ops.moe_permute(ids, E, counts, offsets, routes, pos)
         record = self.env.shared.get("record_expert_counts")
         if record is not None:  # measurement hook: which experts a step touched, layer by layer
             record.append(counts.clone())

@@ -178,6 +178,17 @@ def moe_permute(topk_ids, n_experts, expert_counts, expert_offsets, sorted_route
     route_pos[order] = torch.arange(flat.numel(), dtype=torch.int32, device=flat.device)
 
 
+def moe_route_fits(n_tokens, hidden, n_experts, top_k):
+    return 1 <= n_tokens <= 64 and hidden % 4 == 0
+
+
+def moe_route(x, gate_w, bias, top_k, scoring, scale, logits, ids, weights, expert_counts, expert_offsets,
+              sorted_routes, route_pos):
+    logits.copy_(x.float() @ gate_w.float().T)
+    router_topk(logits, bias, top_k, scoring, scale, ids, weights)
+    moe_permute(ids, gate_w.shape[0], expert_counts, expert_offsets, sorted_routes, route_pos)
+
+
 def moe_gather(h, sorted_routes, top_k, out):
     out.copy_(h[(sorted_routes.long() // top_k)])
 
@@ -241,7 +252,7 @@ def sample(logits, temperature, top_k, top_p, u, out):
 
 
 ALL = ["copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "act_and_mul", "cast", "table_update", "norm_rope_store",
-       "paged_attention", "router_topk", "moe_permute", "moe_gather", "moe_gemm1_act", "moe_gemm2",
+       "paged_attention", "router_topk", "moe_permute", "moe_route", "moe_route_fits", "moe_gather", "moe_gemm1_act", "moe_gemm2",
        "moe_combine", "sample"]
 
 

@@ -330,6 +330,45 @@ def test_router_topk(scoring, bias, T, E, k):
     torch.testing.assert_close(w, w2, rtol=1e-5, atol=1e-7)
 
 
+@pytest.mark.parametrize("scoring,bias", [("sigmoid", True), ("softmax", False)])
+@pytest.mark.parametrize("T,H,E,k", [(1, 64, 8, 2), (8, 3072, 256, 8), (13, 100, 7, 3), (64, 520, 33, 5), (9, 36, 301, 1)])
+def test_moe_route_in_one_launch(scoring, bias, T, H, E, k):
+    """Logits, choice and sort in one launch against the three separate statements; run several
+    times so that the arrival counter is seen to come back to zero."""
+    assert ops.moe_route_fits(T, H, E, k) and not ops.moe_route_fits(65, H, E, k) and not ops.moe_route_fits(T, H + 2, E, k)
+    x = rnd(T, H, scale=1.0)
+    w = rnd(E, H, scale=H ** -0.5, seed=5)
+    if T > 2:
+        x[2] = x[1]  # equal tokens make equal choices, whatever their place in the batch
+    b = rnd(E, scale=0.01, seed=7) if bias else None
+    ref_logits = (x.double() @ w.double().T).float()
+    ids2 = torch.empty(T, k, dtype=torch.int32, device=DEV)
+    w2 = torch.empty(T, k, dtype=torch.float32, device=DEV)
+    for rep in range(3):
+        logits = torch.full((T, E), float("nan"), device=DEV)
+        ids = torch.full((T, k), -1, dtype=torch.int32, device=DEV)
+        wts = torch.empty(T, k, dtype=torch.float32, device=DEV)
+        counts = torch.empty(E, dtype=torch.int32, device=DEV)
+        off = torch.empty(E + 1, dtype=torch.int32, device=DEV)
+        routes = torch.empty(T * k, dtype=torch.int32, device=DEV)
+        pos = torch.empty(T * k, dtype=torch.int32, device=DEV)
+        ops.moe_route(x, w, b, k, scoring, 2.5, logits, ids, wts, counts, off, routes, pos)
+        torch.testing.assert_close(logits, ref_logits, rtol=1e-5, atol=1e-5)
+        ref.router_topk(logits, b, k, scoring, 2.5, ids2, w2)  # the choice, given the kernel's own logits
+        assert torch.equal(ids, ids2)
+        torch.testing.assert_close(wts, w2, rtol=1e-5, atol=1e-7)
+        c2, o2, r2, p2 = torch.empty_like(counts), torch.empty_like(off), torch.empty_like(routes), torch.empty_like(pos)
+        ref.moe_permute(ids, E, c2, o2, r2, p2)
+        for got, want in ((counts, c2), (off, o2), (routes, r2), (pos, p2)):
+            assert torch.equal(got, want)
+        if T > 2:
+            assert torch.equal(logits[1], logits[2]) and torch.equal(ids[1], ids[2])
+    alone = torch.empty(1, E, device=DEV)
+    ops.moe_route(x[-1:].contiguous(), w, b, k, scoring, 2.5, alone, ids[:1].clone(), wts[:1].clone(), counts, off,
+                  routes[:k].clone(), pos[:k].clone())
+    assert torch.equal(alone[0], logits[-1]), "a token's logits must not depend on the batch"
+
+
 @pytest.mark.parametrize("T,k,E", [(1, 2, 8), (50, 4, 16), (300, 8, 256), (7, 3, 6), (2, 1, 40)])
 def test_moe_permute_gather_combine(T, k, E):
     ids = torch.stack([torch.randperm(E)[:k] for _ in range(T)]).to(torch.int32).to(DEV)
