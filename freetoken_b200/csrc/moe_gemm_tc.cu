@@ -161,17 +161,23 @@ struct TcParams {
   int act;
   float alpha, limit;
   __nv_bfloat16* out;
+  int depth;                     // loads a CTA keeps in flight while every CTA has a tile (<= stages)
 };
 
 // DEEP: one CTA per SM (many tiles: each SM streams on its own, with a longer pipeline for the large
 // token tiles); otherwise two CTAs per SM (few tiles: more of them run at once).
 template <int BN, bool DEEP>
 struct Smem {
-  // (measured: more than ~90 KB of loads in flight per SM buys nothing for the small token tiles)
-  static constexpr int kStages = DEEP ? (BN <= 16 ? 5 : (BN <= 64 ? 4 : (BN <= 128 ? 6 : 4)))
+  // 64-element pieces of k per stage.  Two of them make every row of a weight tile a 256-byte read,
+  // which the memory serves faster than twice 128 bytes (measured: 6.7 against 6.1 TB/s).
+  static constexpr int kAtoms = DEEP ? 2 : 1;
+  static constexpr int kStages = DEEP ? (BN <= 16 ? 5 : (BN <= 64 ? 4 : (BN <= 128 ? 3 : 2)))
                                       : (BN <= 16 ? 5 : (BN <= 128 ? 4 : 3));
+  // loads kept in flight while every CTA streams (measured for the small token tiles: 144 KB per SM
+  // is the best; more of them from all SMs at once slow the memory down)
+  static constexpr int kDepth = (DEEP && BN <= 16) ? 4 : kStages;
   static constexpr int kBBytes = BN * kBK * 2;
-  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStageBytes = kAtoms * (kABytes + kBBytes);
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int kDynamic = kStages * kStageBytes + 1024;
 };
@@ -235,7 +241,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
   const int total_tiles = tile_prefix[p.n_experts] * p.m_tiles;
-  const int k_blocks = (p.K + kBK - 1) / kBK;
+  const int k_blocks = (p.K + S::kAtoms * kBK - 1) / (S::kAtoms * kBK);  // k past the end reads as zero
   volatile int* abortp = &abort_flag;
 
   // tile -> expert, token tile, feature tile
@@ -256,30 +262,39 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      int s = 0;
-      uint32_t phase = 0;
+      // Load i goes to stage i % kStages.  While every CTA streams, a CTA keeps only `depth` loads in
+      // flight (more of them from all SMs at once slow the memory down); in the last, partly filled
+      // wave of tiles the few CTAs that still work use every stage, since each of them is then bound
+      // by the latency of its own loads.
+      int i = 0;
       bool ok = true;
+      const int full_waves = total_tiles / (int)gridDim.x * (int)gridDim.x;
+      const bool thin_tail = 2 * (total_tiles - full_waves) <= (int)gridDim.x;
+      const int depth_main = p.depth > 0 ? min(p.depth, S::kStages) : S::kDepth;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         int e, row0, rows, m0;
         locate(t, e, row0, rows, m0);
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(&empty_bar[s], phase ^ 1, abortp)) {
+        const int depth = (t >= full_waves && thin_tail) ? S::kStages : depth_main;
+        for (int kb = 0; kb < k_blocks; ++kb, ++i) {
+          const int j = i - depth;  // the load whose stage must have been read before load i goes out
+          if (j >= 0 && !mbar_wait(&empty_bar[j % S::kStages], (uint32_t)(j / S::kStages) & 1u, abortp)) {
             ok = false;
             atomicCAS(&g_status[0], 0, 101);
             abort_flag = 1;
             break;
           }
+          const int s = i % S::kStages;
           unsigned char* a = tiles + s * S::kStageBytes;
           mbar_expect_tx(&full_bar[s], S::kStageBytes);
-          if (GATED) {  // (k, row in group, gate|up, group of 16 features, expert)
-            tma_load_5d(a, &map_a, &full_bar[s], kb * kBK, 0, 0, m0 >> 4, e);
-          } else {
-            tma_load_3d(a, &map_a, &full_bar[s], kb * kBK, m0, e);
-          }
-          tma_load_2d(a + kABytes, &map_b, &full_bar[s], kb * kBK, row0);
-          if (++s == S::kStages) {
-            s = 0;
-            phase ^= 1;
+#pragma unroll
+          for (int h = 0; h < S::kAtoms; ++h) {
+            const int k0 = (kb * S::kAtoms + h) * kBK;
+            if (GATED) {  // (k, row in group, gate|up, group of 16 features, expert)
+              tma_load_5d(a + h * kABytes, &map_a, &full_bar[s], k0, 0, 0, m0 >> 4, e);
+            } else {
+              tma_load_3d(a + h * kABytes, &map_a, &full_bar[s], k0, m0, e);
+            }
+            tma_load_2d(a + S::kAtoms * kABytes + h * S::kBBytes, &map_b, &full_bar[s], k0, row0);
           }
         }
       }
@@ -310,10 +325,14 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
           }
           tc_fence_after();
           const uint32_t a_addr = tiles_base + s * S::kStageBytes;
-          const uint64_t a_desc = smem_desc(a_addr), b_desc = smem_desc(a_addr + kABytes);
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k)  // 16 k elements = 32 bytes = 2 descriptor units
-            tc_mma(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+          for (int h = 0; h < S::kAtoms; ++h) {
+            const uint64_t a_desc = smem_desc(a_addr + h * kABytes);
+            const uint64_t b_desc = smem_desc(a_addr + S::kAtoms * kABytes + h * S::kBBytes);
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k)  // 16 k elements = 32 bytes = 2 descriptor units
+              tc_mma(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | h | k) != 0);
+          }
           tc_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
           if (++s == S::kStages) {
             s = 0;
@@ -519,6 +538,12 @@ template <bool GATED>
 static int run_tc(const void* x, int x_cols, const void* w, int w_rows, const TcParams& p0, cudaStream_t s,
                   const char* name) {
   TcParams p = p0;
+  static int depth_env = -1;
+  if (depth_env < 0) {
+    const char* v = getenv("FTK_TC_DEPTH");
+    depth_env = v ? atoi(v) : 0;
+  }
+  p.depth = depth_env;  // 0: the variant's own choice
   // TMA needs 16-byte row strides; the epilogue stores 8 features at a time; the gate/up interleave
   // works on groups of 16 features
   if (x_cols % 8 != 0 || p.n_out % 8 != 0 || p.n_experts > kMaxExperts) return -1;
