@@ -106,6 +106,8 @@ constexpr int kF32Chunk = 32;  // keys per chunk
 
 template <typename T>
 __global__ void __launch_bounds__(kF32Rows * 32) attention_f32_kernel(AttnParams p) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ float smem[];
   const Item it = load_item(p, blockIdx.x);
   if (!it.ok) return;
@@ -216,6 +218,8 @@ __global__ void __launch_bounds__(kF32Rows * 32) attention_f32_kernel(AttnParams
 // values eight at a time, so a row costs a few memory round trips however many splits there are.
 template <typename T>
 __global__ void attention_merge_kernel(AttnParams p) {
+  pdl_wait();
+  pdl_trigger();
   const Item it = load_item(p, blockIdx.x);
   if (!it.ok || it.nsplit <= 1) return;
   const int kvh = blockIdx.y;
@@ -357,6 +361,8 @@ __device__ __forceinline__ void load_kv_tile(const AttnParams& p, const long lon
 
 template <int DMAX>
 __global__ void __launch_bounds__(128) attention_bf16_kernel(AttnParams p) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const Item it = load_item(p, blockIdx.x);
   if (!it.ok) return;
@@ -550,6 +556,8 @@ constexpr int kDecStages = 3;
 
 template <int DMAX>
 __global__ void __launch_bounds__(128) attention_decode_bf16_kernel(AttnParams p) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const Item it = load_item(p, blockIdx.x);
   if (!it.ok) return;
@@ -756,7 +764,7 @@ static int launch_decode_bf16(const AttnParams& p, cudaStream_t s) {
   auto kern = attention_decode_bf16_kernel<DMAX>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   dim3 grid(p.n_items, p.Hkv);
-  kern<<<grid, 128, smem, s>>>(p);
+  FTK_LAUNCH(kern, grid, 128, smem, s, p);
   return 0;
 }
 
@@ -766,7 +774,7 @@ static int launch_bf16(const AttnParams& p, cudaStream_t s) {
   auto kern = attention_bf16_kernel<DMAX>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   dim3 grid(p.n_items, p.Hkv);
-  kern<<<grid, 128, smem, s>>>(p);
+  FTK_LAUNCH(kern, grid, 128, smem, s, p);
   return 0;
 }
 
@@ -814,10 +822,10 @@ static int paged_attention_impl(const void* q, const void* k_slab, const void* v
     const size_t smem = ((size_t)kF32Rows * head_dim + (size_t)kF32Chunk * (2 * head_dim + 1)) * sizeof(float);
     auto kern = attention_f32_kernel<float>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kern<<<grid, kF32Rows * 32, smem, s>>>(p);
+    FTK_LAUNCH(kern, grid, kF32Rows * 32, smem, s, p);
     FTK_LAUNCH_CHECK("paged_attention (float32)");
     if (n_slots > 0) {
-      attention_merge_kernel<float><<<grid, 128, 0, s>>>(p);
+      FTK_LAUNCH(attention_merge_kernel<float>, grid, 128, 0, s, p);
       FTK_LAUNCH_CHECK("paged_attention merge");
     }
   } else {
@@ -836,7 +844,7 @@ static int paged_attention_impl(const void* q, const void* k_slab, const void* v
     }
     FTK_LAUNCH_CHECK("paged_attention (bfloat16)");
     if (n_slots > 0) {
-      attention_merge_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(p);
+      FTK_LAUNCH(attention_merge_kernel<__nv_bfloat16>, grid, 128, 0, s, p);
       FTK_LAUNCH_CHECK("paged_attention merge");
     }
   }

@@ -33,10 +33,37 @@ void set_error(const char* fmt, ...);
     }                                                                       \
   } while (0)
 
+// Every kernel is launched so that it may start while the kernel before it in the stream is still
+// running (programmatic dependent launch): a kernel calls pdl_wait() before it touches anything that
+// an earlier kernel wrote or still reads, and pdl_trigger() when the next kernel's blocks may come
+// onto the SMs.  A kernel that never triggers lets the next one in when it ends.  FTK_PDL=0 in the
+// environment launches everything the plain way.
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#define FTK_LAUNCH(kernel, grid, block, smem, stream, ...) \
+  ftk::launch_kernel(kernel, dim3(grid), dim3(block), (size_t)(smem), (cudaStream_t)(stream), __VA_ARGS__)
+
 inline bool dtype_ok(int d) { return d == FTK_F32 || d == FTK_BF16; }
 inline int dtype_size(int d) { return d == FTK_F32 ? 4 : 2; }
 
 // ---------------------------------------------------------------- device helpers
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

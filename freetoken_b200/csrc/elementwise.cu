@@ -45,6 +45,8 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 template <typename T, bool VEC>
 __global__ void embedding_gather_kernel(const T* __restrict__ table, const int32_t* __restrict__ ids,
                                         int hidden, int vocab, float* __restrict__ out) {
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* o = out + (size_t)t * hidden;
@@ -70,6 +72,8 @@ __global__ void add_rmsnorm_kernel(const XT* __restrict__ x, float* __restrict__
                                    const float* __restrict__ weight, OT* __restrict__ out,
                                    float* __restrict__ out_f32, const int32_t* __restrict__ rows,
                                    int hidden, float eps, int gemma) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ float zrow[];
   __shared__ float red[33];
   const int r = blockIdx.x;
@@ -132,6 +136,8 @@ __global__ void add_rmsnorm_kernel(const XT* __restrict__ x, float* __restrict__
 template <typename T>
 __global__ void act_and_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int act,
                                    float alpha, float limit) {
+  pdl_wait();
+  pdl_trigger();
   const size_t row = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= inter) return;
@@ -141,12 +147,16 @@ __global__ void act_and_mul_kernel(const T* __restrict__ gate_up, T* __restrict_
 
 template <typename S, typename D>
 __global__ void cast_kernel(const S* __restrict__ src, D* __restrict__ dst, long long n) {
+  pdl_wait();
+  pdl_trigger();
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (; i < n; i += stride) dst[i] = from_float<D>(to_float(src[i]));
 }
 
 __global__ void table_update_kernel(int32_t* table, long long table_len, const int32_t* updates, int n) {
+  pdl_wait();
+  pdl_trigger();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const long long idx = updates[2 * i];
@@ -157,6 +167,8 @@ __global__ void table_update_kernel(int32_t* table, long long table_len, const i
 // without a round trip through the host.  Values outside [0, vocab) become 0.
 __global__ void copy_tokens_kernel(int32_t* dst, int dst_len, const int32_t* pairs, const int32_t* src, int src_len,
                                    int n, int vocab) {
+  pdl_wait();
+  pdl_trigger();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int d = pairs[2 * i], s = pairs[2 * i + 1];
@@ -169,6 +181,8 @@ __global__ void copy_tokens_kernel(int32_t* dst, int dst_len, const int32_t* pai
 template <typename T, bool VEC>
 __global__ void moe_gather_kernel(const T* __restrict__ h, const int32_t* __restrict__ sorted_routes,
                                   int top_k, int hidden, int n_tokens, T* __restrict__ out) {
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x;
   const int route = sorted_routes[r];
   const int t = route / top_k;
@@ -189,6 +203,8 @@ __global__ void moe_gather_kernel(const T* __restrict__ h, const int32_t* __rest
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const int32_t* __restrict__ route_pos, int top_k,
                                    int hidden, int n_routes, const T* __restrict__ shared, T* __restrict__ out) {
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= hidden) return;
@@ -216,11 +232,11 @@ extern "C" int ftk_embedding_gather(const void* table, int dtype, const int32_t*
   const bool vec = hidden % 4 == 0 && aligned16(table) && aligned16(out) && (dtype == FTK_F32 || hidden % 8 == 0);
   const int threads = hidden >= 1024 ? 256 : 128;
   if (dtype == FTK_F32) {
-    if (vec) embedding_gather_kernel<float, true><<<n_tokens, threads, 0, s>>>((const float*)table, ids, hidden, vocab, out);
-    else embedding_gather_kernel<float, false><<<n_tokens, threads, 0, s>>>((const float*)table, ids, hidden, vocab, out);
+    if (vec) FTK_LAUNCH((embedding_gather_kernel<float, true>), n_tokens, threads, 0, s, (const float*)table, ids, hidden, vocab, out);
+    else FTK_LAUNCH((embedding_gather_kernel<float, false>), n_tokens, threads, 0, s, (const float*)table, ids, hidden, vocab, out);
   } else {
-    if (vec) embedding_gather_kernel<__nv_bfloat16, true><<<n_tokens, threads, 0, s>>>((const __nv_bfloat16*)table, ids, hidden, vocab, out);
-    else embedding_gather_kernel<__nv_bfloat16, false><<<n_tokens, threads, 0, s>>>((const __nv_bfloat16*)table, ids, hidden, vocab, out);
+    if (vec) FTK_LAUNCH((embedding_gather_kernel<__nv_bfloat16, true>), n_tokens, threads, 0, s, (const __nv_bfloat16*)table, ids, hidden, vocab, out);
+    else FTK_LAUNCH((embedding_gather_kernel<__nv_bfloat16, false>), n_tokens, threads, 0, s, (const __nv_bfloat16*)table, ids, hidden, vocab, out);
   }
   FTK_LAUNCH_CHECK("embedding_gather");
   return 0;
@@ -240,8 +256,8 @@ static int launch_norm(const void* x, float* residual, const float* weight, void
     cudaFuncSetAttribute(kv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaFuncSetAttribute(ks, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   }
-  if (vec) kv<<<n_rows, threads, smem, s>>>((const XT*)x, residual, weight, (OT*)out, out_f32, rows, hidden, eps, gemma);
-  else ks<<<n_rows, threads, smem, s>>>((const XT*)x, residual, weight, (OT*)out, out_f32, rows, hidden, eps, gemma);
+  if (vec) FTK_LAUNCH(kv, n_rows, threads, smem, s, (const XT*)x, residual, weight, (OT*)out, out_f32, rows, hidden, eps, gemma);
+  else FTK_LAUNCH(ks, n_rows, threads, smem, s, (const XT*)x, residual, weight, (OT*)out, out_f32, rows, hidden, eps, gemma);
   FTK_LAUNCH_CHECK("add_rmsnorm");
   return 0;
 }
@@ -275,10 +291,10 @@ extern "C" int ftk_act_and_mul(const void* gate_up, int dtype, int n_rows, int i
     const int nr = n_rows - r0 < 65535 ? n_rows - r0 : 65535;
     dim3 grid((inter + 255) / 256, nr);
     if (dtype == FTK_F32)
-      act_and_mul_kernel<float><<<grid, 256, 0, s>>>((const float*)gate_up + (size_t)r0 * 2 * inter,
+      FTK_LAUNCH(act_and_mul_kernel<float>, grid, 256, 0, s, (const float*)gate_up + (size_t)r0 * 2 * inter,
                                                      (float*)out + (size_t)r0 * inter, inter, act, alpha, limit);
     else
-      act_and_mul_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)gate_up + (size_t)r0 * 2 * inter,
+      FTK_LAUNCH(act_and_mul_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)gate_up + (size_t)r0 * 2 * inter,
                                                              (__nv_bfloat16*)out + (size_t)r0 * inter, inter, act, alpha, limit);
   }
   FTK_LAUNCH_CHECK("act_and_mul");
@@ -293,13 +309,13 @@ extern "C" int ftk_cast(const void* src, int src_dtype, void* dst, int dst_dtype
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (src_dtype == FTK_F32 && dst_dtype == FTK_BF16)
-    cast_kernel<float, __nv_bfloat16><<<(int)blocks, 256, 0, s>>>((const float*)src, (__nv_bfloat16*)dst, n);
+    FTK_LAUNCH((cast_kernel<float, __nv_bfloat16>), (int)blocks, 256, 0, s, (const float*)src, (__nv_bfloat16*)dst, n);
   else if (src_dtype == FTK_BF16 && dst_dtype == FTK_F32)
-    cast_kernel<__nv_bfloat16, float><<<(int)blocks, 256, 0, s>>>((const __nv_bfloat16*)src, (float*)dst, n);
+    FTK_LAUNCH((cast_kernel<__nv_bfloat16, float>), (int)blocks, 256, 0, s, (const __nv_bfloat16*)src, (float*)dst, n);
   else if (src_dtype == FTK_F32)
-    cast_kernel<float, float><<<(int)blocks, 256, 0, s>>>((const float*)src, (float*)dst, n);
+    FTK_LAUNCH((cast_kernel<float, float>), (int)blocks, 256, 0, s, (const float*)src, (float*)dst, n);
   else
-    cast_kernel<__nv_bfloat16, __nv_bfloat16><<<(int)blocks, 256, 0, s>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, n);
+    FTK_LAUNCH((cast_kernel<__nv_bfloat16, __nv_bfloat16>), (int)blocks, 256, 0, s, (const __nv_bfloat16*)src, (__nv_bfloat16*)dst, n);
   FTK_LAUNCH_CHECK("cast");
   return 0;
 }
@@ -309,7 +325,7 @@ extern "C" int ftk_table_update(int32_t* table, long long table_len, const int32
   FTK_REQUIRE(n_updates >= 0 && table_len >= 0, "table_update: bad sizes");
   if (n_updates == 0) return 0;
   FTK_REQUIRE(table && updates, "table_update: null pointer");
-  table_update_kernel<<<(n_updates + 127) / 128, 128, 0, (cudaStream_t)stream>>>(table, table_len, updates, n_updates);
+  FTK_LAUNCH(table_update_kernel, (n_updates + 127) / 128, 128, 0, (cudaStream_t)stream, table, table_len, updates, n_updates);
   FTK_LAUNCH_CHECK("table_update");
   return 0;
 }
@@ -319,7 +335,7 @@ extern "C" int ftk_copy_tokens(int32_t* dst, int dst_len, const int32_t* pairs, 
   FTK_REQUIRE(n >= 0 && dst_len >= 0 && src_len >= 0 && vocab >= 1, "copy_tokens: bad sizes");
   if (n == 0) return 0;
   FTK_REQUIRE(dst && pairs && src, "copy_tokens: null pointer");
-  copy_tokens_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(dst, dst_len, pairs, src, src_len, n, vocab);
+  FTK_LAUNCH(copy_tokens_kernel, (n + 127) / 128, 128, 0, (cudaStream_t)stream, dst, dst_len, pairs, src, src_len, n, vocab);
   FTK_LAUNCH_CHECK("copy_tokens");
   return 0;
 }
@@ -335,11 +351,11 @@ extern "C" int ftk_moe_gather(const void* h, int dtype, const int32_t* sorted_ro
   const bool vec = aligned16(h) && aligned16(out) && (hidden * dtype_size(dtype)) % 16 == 0;
   const int threads = hidden >= 2048 ? 256 : 128;
   if (dtype == FTK_F32) {
-    if (vec) moe_gather_kernel<float, true><<<n_routes, threads, 0, s>>>((const float*)h, sorted_routes, top_k, hidden, n_tokens, (float*)out);
-    else moe_gather_kernel<float, false><<<n_routes, threads, 0, s>>>((const float*)h, sorted_routes, top_k, hidden, n_tokens, (float*)out);
+    if (vec) FTK_LAUNCH((moe_gather_kernel<float, true>), n_routes, threads, 0, s, (const float*)h, sorted_routes, top_k, hidden, n_tokens, (float*)out);
+    else FTK_LAUNCH((moe_gather_kernel<float, false>), n_routes, threads, 0, s, (const float*)h, sorted_routes, top_k, hidden, n_tokens, (float*)out);
   } else {
-    if (vec) moe_gather_kernel<__nv_bfloat16, true><<<n_routes, threads, 0, s>>>((const __nv_bfloat16*)h, sorted_routes, top_k, hidden, n_tokens, (__nv_bfloat16*)out);
-    else moe_gather_kernel<__nv_bfloat16, false><<<n_routes, threads, 0, s>>>((const __nv_bfloat16*)h, sorted_routes, top_k, hidden, n_tokens, (__nv_bfloat16*)out);
+    if (vec) FTK_LAUNCH((moe_gather_kernel<__nv_bfloat16, true>), n_routes, threads, 0, s, (const __nv_bfloat16*)h, sorted_routes, top_k, hidden, n_tokens, (__nv_bfloat16*)out);
+    else FTK_LAUNCH((moe_gather_kernel<__nv_bfloat16, false>), n_routes, threads, 0, s, (const __nv_bfloat16*)h, sorted_routes, top_k, hidden, n_tokens, (__nv_bfloat16*)out);
   }
   FTK_LAUNCH_CHECK("moe_gather");
   return 0;
@@ -356,11 +372,11 @@ extern "C" int ftk_moe_combine(const void* y, int dtype, const int32_t* route_po
     const int nt = n_tokens - t0 < 65535 ? n_tokens - t0 : 65535;
     dim3 grid((hidden + 255) / 256, nt);
     if (dtype == FTK_F32)
-      moe_combine_kernel<float><<<grid, 256, 0, s>>>((const float*)y, route_pos + (size_t)t0 * top_k, top_k, hidden,
+      FTK_LAUNCH(moe_combine_kernel<float>, grid, 256, 0, s, (const float*)y, route_pos + (size_t)t0 * top_k, top_k, hidden,
                                                      n_tokens * top_k, shared ? (const float*)shared + (size_t)t0 * hidden : nullptr,
                                                      (float*)out + (size_t)t0 * hidden);
     else
-      moe_combine_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)y, route_pos + (size_t)t0 * top_k, top_k, hidden,
+      FTK_LAUNCH(moe_combine_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)y, route_pos + (size_t)t0 * top_k, top_k, hidden,
                                                              n_tokens * top_k, shared ? (const __nv_bfloat16*)shared + (size_t)t0 * hidden : nullptr,
                                                              (__nv_bfloat16*)out + (size_t)t0 * hidden);
   }

@@ -41,6 +41,8 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ x, 
                                                        const int32_t* __restrict__ sorted_routes,
                                                        const float* __restrict__ route_weights, int n_routes,
                                                        int act, float alpha, float limit, T* __restrict__ out) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float As[kBM][kBK + 1];
   __shared__ float Bs[kBN][kBK + 1];
   __shared__ float Bu[GATED ? kBN : 1][kBK + 1];
@@ -145,11 +147,11 @@ extern "C" int ftk_moe_gemm1_act(const void* x_sorted, const void* w1, int dtype
   FTK_REQUIRE(tiles <= 65535, "moe_gemm1_act: too many row tiles (%d)", tiles);
   dim3 grid((inter + kBN - 1) / kBN, tiles);
   if (dtype == FTK_F32)
-    moe_gemm_kernel<float, true><<<grid, 256, 0, s>>>((const float*)x_sorted, (const float*)w1, expert_offsets, n_experts,
+    FTK_LAUNCH((moe_gemm_kernel<float, true>), grid, 256, 0, s, (const float*)x_sorted, (const float*)w1, expert_offsets, n_experts,
                                                       hidden, inter, 2 * inter, nullptr, nullptr, n_routes, act, alpha,
                                                       limit, (float*)out);
   else
-    moe_gemm_kernel<__nv_bfloat16, true><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x_sorted, (const __nv_bfloat16*)w1,
+    FTK_LAUNCH((moe_gemm_kernel<__nv_bfloat16, true>), grid, 256, 0, s, (const __nv_bfloat16*)x_sorted, (const __nv_bfloat16*)w1,
                                                               expert_offsets, n_experts, hidden, inter, 2 * inter, nullptr,
                                                               nullptr, n_routes, act, alpha, limit, (__nv_bfloat16*)out);
   FTK_LAUNCH_CHECK("moe_gemm1_act");
@@ -173,11 +175,11 @@ extern "C" int ftk_moe_gemm2(const void* a, const void* w2, int dtype, const int
   FTK_REQUIRE(tiles <= 65535, "moe_gemm2: too many row tiles (%d)", tiles);
   dim3 grid((hidden + kBN - 1) / kBN, tiles);
   if (dtype == FTK_F32)
-    moe_gemm_kernel<float, false><<<grid, 256, 0, s>>>((const float*)a, (const float*)w2, expert_offsets, n_experts, inter,
+    FTK_LAUNCH((moe_gemm_kernel<float, false>), grid, 256, 0, s, (const float*)a, (const float*)w2, expert_offsets, n_experts, inter,
                                                        hidden, hidden, sorted_routes, topk_weights, n_routes, 0, 0.f, 0.f,
                                                        (float*)out);
   else
-    moe_gemm_kernel<__nv_bfloat16, false><<<grid, 256, 0, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w2,
+    FTK_LAUNCH((moe_gemm_kernel<__nv_bfloat16, false>), grid, 256, 0, s, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w2,
                                                                expert_offsets, n_experts, inter, hidden, hidden,
                                                                sorted_routes, topk_weights, n_routes, 0, 0.f, 0.f,
                                                                (__nv_bfloat16*)out);

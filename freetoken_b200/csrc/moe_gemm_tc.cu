@@ -186,6 +186,11 @@ template <int BN, bool GATED, bool DEEP>
 __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_b,
                                                                TcParams p) {
+  // The expert offsets are read before pdl_wait(): whoever writes them (the routing kernels) never lets
+  // the next kernel in early, so they are complete when any block of this kernel runs.  The weight
+  // tiles of the first loads go out before the wait too; what the kernel before wrote (the activations)
+  // is read after it, and nothing is stored before it.
+  pdl_trigger();
   using S = Smem<BN, DEEP>;
   extern __shared__ unsigned char dyn_smem[];
   __shared__ uint64_t full_bar[S::kStages], empty_bar[S::kStages], acc_full[2], acc_empty[2];
@@ -271,11 +276,45 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
       const int full_waves = total_tiles / (int)gridDim.x * (int)gridDim.x;
       const bool thin_tail = 2 * (total_tiles - full_waves) <= (int)gridDim.x;
       const int depth_main = p.depth > 0 ? min(p.depth, S::kStages) : S::kDepth;
+      auto load_a = [&](int s, int kb, int m0, int e) {
+        unsigned char* a = tiles + s * S::kStageBytes;
+#pragma unroll
+        for (int h = 0; h < S::kAtoms; ++h) {
+          const int k0 = (kb * S::kAtoms + h) * kBK;
+          if (GATED) {  // (k, row in group, gate|up, group of 16 features, expert)
+            tma_load_5d(a + h * kABytes, &map_a, &full_bar[s], k0, 0, 0, m0 >> 4, e);
+          } else {
+            tma_load_3d(a + h * kABytes, &map_a, &full_bar[s], k0, m0, e);
+          }
+        }
+      };
+      auto load_b = [&](int s, int kb, int row0) {
+        unsigned char* b = tiles + s * S::kStageBytes + S::kAtoms * kABytes;
+#pragma unroll
+        for (int h = 0; h < S::kAtoms; ++h)
+          tma_load_2d(b + h * S::kBBytes, &map_b, &full_bar[s], (kb * S::kAtoms + h) * kBK, row0);
+      };
+      // the weights of the first loads, while the kernel before this one may still be running
+      int ahead = 0;
+      if ((int)blockIdx.x < total_tiles) {
+        int e, row0, rows, m0;
+        locate(blockIdx.x, e, row0, rows, m0);
+        ahead = min(depth_main, k_blocks);
+        for (int kb = 0; kb < ahead; ++kb) {
+          mbar_expect_tx(&full_bar[kb], S::kStageBytes);
+          load_a(kb, kb, m0, e);
+        }
+        pdl_wait();
+        for (int kb = 0; kb < ahead; ++kb) load_b(kb, kb, row0);
+      } else {
+        pdl_wait();
+      }
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         int e, row0, rows, m0;
         locate(t, e, row0, rows, m0);
         const int depth = (t >= full_waves && thin_tail) ? S::kStages : depth_main;
         for (int kb = 0; kb < k_blocks; ++kb, ++i) {
+          if (t == (int)blockIdx.x && kb < ahead) continue;  // already on its way
           const int j = i - depth;  // the load whose stage must have been read before load i goes out
           if (j >= 0 && !mbar_wait(&empty_bar[j % S::kStages], (uint32_t)(j / S::kStages) & 1u, abortp)) {
             ok = false;
@@ -284,18 +323,9 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
             break;
           }
           const int s = i % S::kStages;
-          unsigned char* a = tiles + s * S::kStageBytes;
           mbar_expect_tx(&full_bar[s], S::kStageBytes);
-#pragma unroll
-          for (int h = 0; h < S::kAtoms; ++h) {
-            const int k0 = (kb * S::kAtoms + h) * kBK;
-            if (GATED) {  // (k, row in group, gate|up, group of 16 features, expert)
-              tma_load_5d(a + h * kABytes, &map_a, &full_bar[s], k0, 0, 0, m0 >> 4, e);
-            } else {
-              tma_load_3d(a + h * kABytes, &map_a, &full_bar[s], k0, m0, e);
-            }
-            tma_load_2d(a + S::kAtoms * kABytes + h * S::kBBytes, &map_b, &full_bar[s], k0, row0);
-          }
+          load_a(s, kb, m0, e);
+          load_b(s, kb, row0);
         }
       }
     }
@@ -350,6 +380,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
     const int quad = warp & 3;               // TMEM lanes [32 quad, 32 quad + 32)
     uint32_t acc_phase = 0;
     int acc = 0;
+    pdl_wait();  // nothing is stored while the kernel before this one runs; a block without tiles waits too
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       int e, row0, rows, m0;
       locate(t, e, row0, rows, m0);
@@ -519,7 +550,7 @@ static int launch_tc_impl(const CUtensorMap& ma, const CUtensorMap& mb, const Tc
   int grid = sms * ctas_per_sm;
   if (grid > max_tiles) grid = max_tiles;
   if (grid < 1) grid = 1;
-  kern<<<grid, kThreads, S::kDynamic, s>>>(ma, mb, p);
+  FTK_LAUNCH(kern, grid, kThreads, S::kDynamic, s, ma, mb, p);
   return 0;
 }
 

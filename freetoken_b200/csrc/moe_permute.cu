@@ -13,6 +13,7 @@ namespace ftk {
 constexpr int kPermThreads = 256;
 
 __global__ void moe_count_kernel(const int32_t* __restrict__ ids, int n_routes, int32_t* __restrict__ counts) {
+  pdl_wait();
   __shared__ float red[33];
   const int e = blockIdx.x;
   int n = 0;
@@ -25,6 +26,7 @@ __global__ void moe_count_kernel(const int32_t* __restrict__ ids, int n_routes, 
 __global__ void moe_place_kernel(const int32_t* __restrict__ ids, int n_routes, int n_experts,
                                  const int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
                                  int32_t* __restrict__ sorted_routes, int32_t* __restrict__ route_pos) {
+  pdl_wait();
   __shared__ float red[33];
   __shared__ int warp_base[kPermThreads / 32 + 1];
   __shared__ int run;
@@ -83,9 +85,9 @@ extern "C" int ftk_moe_permute(const int32_t* topk_ids, int n_tokens, int top_k,
               "moe_permute: null pointer");
   cudaStream_t s = (cudaStream_t)stream;
   const int n_routes = n_tokens * top_k;
-  moe_count_kernel<<<n_experts, kPermThreads, 0, s>>>(topk_ids, n_routes, expert_counts);
+  FTK_LAUNCH(moe_count_kernel, n_experts, kPermThreads, 0, s, topk_ids, n_routes, expert_counts);
   FTK_LAUNCH_CHECK("moe_permute (count)");
-  moe_place_kernel<<<n_experts, kPermThreads, 0, s>>>(topk_ids, n_routes, n_experts, expert_counts, expert_offsets,
+  FTK_LAUNCH(moe_place_kernel, n_experts, kPermThreads, 0, s, topk_ids, n_routes, n_experts, expert_counts, expert_offsets,
                                                       sorted_routes, route_pos);
   FTK_LAUNCH_CHECK("moe_permute (place)");
   return 0;

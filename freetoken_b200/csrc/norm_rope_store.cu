@@ -29,6 +29,8 @@ __global__ void norm_rope_store_kernel(const T* __restrict__ x, int n_tokens, in
                                        int rotary_dim, const int32_t* __restrict__ positions,
                                        const float* __restrict__ rope_table, int max_pos, float eps, int gemma,
                                        Sections sec) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float park[kWarpsPerBlock][kMaxHeadDim];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.y;
@@ -148,11 +150,11 @@ extern "C" int ftk_norm_rope_store(const void* x, int dtype, int n_tokens, int r
     }
     dim3 grid(bx, nt);
     if (dtype == FTK_F32)
-      norm_rope_store_kernel<float><<<grid, kWarpsPerBlock * 32, 0, s>>>(
+      FTK_LAUNCH(norm_rope_store_kernel<float>, grid, kWarpsPerBlock * 32, 0, s, 
           (const float*)x + (size_t)t0 * row_elems, nt, row_elems, head_dim, rotary_dim,
           positions ? positions + t0 : nullptr, rope_table, max_pos, eps, gemma, part);
     else
-      norm_rope_store_kernel<__nv_bfloat16><<<grid, kWarpsPerBlock * 32, 0, s>>>(
+      FTK_LAUNCH(norm_rope_store_kernel<__nv_bfloat16>, grid, kWarpsPerBlock * 32, 0, s, 
           (const __nv_bfloat16*)x + (size_t)t0 * row_elems, nt, row_elems, head_dim, rotary_dim,
           positions ? positions + t0 : nullptr, rope_table, max_pos, eps, gemma, part);
   }

@@ -170,6 +170,8 @@ __device__ __forceinline__ void route_one(const float* __restrict__ row, const f
 __global__ void router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                    int n_tokens, int n_experts, int top_k, int scoring, float scale,
                                    int32_t* __restrict__ ids, float* __restrict__ weights) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ float sm[];
   const int warp = threadIdx.x >> 5;
   const int t = blockIdx.x * kRouterWarps + warp;
@@ -196,6 +198,7 @@ moe_route_kernel(const float* __restrict__ x, const float* __restrict__ w, const
                  float* __restrict__ logits, int32_t* __restrict__ ids, float* __restrict__ weights,
                  int32_t* __restrict__ counts, int32_t* __restrict__ offsets, int32_t* __restrict__ routes,
                  int32_t* __restrict__ pos) {
+  pdl_wait();
   extern __shared__ float sm[];
   __shared__ float part[kRouteExperts][kRouteTokens][kRouteWarps + 1];
   __shared__ bool last;
@@ -324,7 +327,7 @@ extern "C" int ftk_router_topk(const float* logits, const float* bias, int n_tok
   FTK_REQUIRE(smem <= 200 * 1024, "router_topk: %d experts exceed what one block can hold (6400)", n_experts);
   if (smem > 48 * 1024) cudaFuncSetAttribute(router_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   const int blocks = (n_tokens + kRouterWarps - 1) / kRouterWarps;
-  router_topk_kernel<<<blocks, kRouterWarps * 32, smem, (cudaStream_t)stream>>>(logits, bias, n_tokens, n_experts, top_k,
+  FTK_LAUNCH(router_topk_kernel, blocks, kRouterWarps * 32, smem, (cudaStream_t)stream, logits, bias, n_tokens, n_experts, top_k,
                                                                                scoring, scale, ids, weights);
   FTK_LAUNCH_CHECK("router_topk");
   return 0;
@@ -353,7 +356,7 @@ extern "C" int ftk_moe_route(const float* x, const float* gate_w, const float* b
   const size_t smem = route_smem(n_tokens, n_experts, top_k);
   if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   const int blocks = (n_experts + kRouteExperts - 1) / kRouteExperts;
-  moe_route_kernel<<<blocks, kRouteWarps * 32, smem, (cudaStream_t)stream>>>(
+  FTK_LAUNCH(moe_route_kernel, blocks, kRouteWarps * 32, smem, (cudaStream_t)stream, 
       x, gate_w, bias, n_tokens, hidden, n_experts, top_k, scoring, scale, logits, ids, weights, counts, offsets, routes, pos);
   FTK_LAUNCH_CHECK("moe_route");
   return 0;

@@ -21,6 +21,8 @@ __global__ void __launch_bounds__(kSelThreads) sparse_select_kernel(
     const T* __restrict__ iq, const T* __restrict__ ik_slab, const int32_t* __restrict__ block_table, int bt_stride,
     const int32_t* __restrict__ seg_info, int n_segs, int n_heads, int dim, int page_size, int num_pages,
     int block_size, int topk, int local_blocks, int init_blocks, int max_blocks, int32_t* __restrict__ sel) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ float sc[];          // [max_blocks] scores
   __shared__ float qv[kMaxIndexDim];
   __shared__ float red_v[kSelThreads / 32];
@@ -135,13 +137,13 @@ extern "C" int ftk_sparse_select(const void* iq, const void* ik_slab, int dtype,
   if (dtype == FTK_F32) {
     auto kern = sparse_select_kernel<float>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kern<<<grid, kSelThreads, smem, s>>>((const float*)iq, (const float*)ik_slab, block_table, bt_stride, seg_info, n_segs,
+    FTK_LAUNCH(kern, grid, kSelThreads, smem, s, (const float*)iq, (const float*)ik_slab, block_table, bt_stride, seg_info, n_segs,
                                          n_heads, dim, page_size, num_pages, block_size, topk, local_blocks, init_blocks,
                                          max_blocks, sel);
   } else {
     auto kern = sparse_select_kernel<__nv_bfloat16>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kern<<<grid, kSelThreads, smem, s>>>((const __nv_bfloat16*)iq, (const __nv_bfloat16*)ik_slab, block_table, bt_stride,
+    FTK_LAUNCH(kern, grid, kSelThreads, smem, s, (const __nv_bfloat16*)iq, (const __nv_bfloat16*)ik_slab, block_table, bt_stride,
                                          seg_info, n_segs, n_heads, dim, page_size, num_pages, block_size, topk,
                                          local_blocks, init_blocks, max_blocks, sel);
   }

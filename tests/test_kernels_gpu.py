@@ -477,7 +477,7 @@ def test_moe_tensor_core_gemms_match_cuda_core_gemms(E, H, I, R, k):
         assert ((got.float() - exact).abs() <= bound).all()
 
 
-@pytest.mark.parametrize("V", [256, 331, 50000])
+@pytest.mark.parametrize("V", [256, 331, 50000, 200064, 16390])
 def test_sample(V):
     R = 9
     logits = rnd(R, V, scale=3.0)
@@ -493,6 +493,22 @@ def test_sample(V):
         ref.sample(logits, temp, top_k, top_p, u, want)
         assert out[0].item() == 3
         assert torch.equal(out, want), (trial, out, want)
+
+
+@pytest.mark.parametrize("R,V", [(70, 9001), (3, 200064), (300, 520)])
+def test_sample_greedy_rows_in_chunks(R, V):
+    """Rows cut into chunks over several blocks: the argmax with the lowest index on a tie, run twice so
+    that the arrival counters are seen to come back to zero."""
+    logits = rnd(R, V, scale=2.0)
+    top = logits.max() + 1
+    logits[1, V - 1] = top
+    logits[1, V // 2] = top  # the tie lies in two different chunks
+    zeros = torch.zeros(R, device=DEV)
+    for _ in range(2):
+        out = torch.empty(R, dtype=torch.int32, device=DEV)
+        ops.sample(logits, zeros, torch.zeros(R, dtype=torch.int32, device=DEV), torch.ones(R, device=DEV), zeros, out)
+        assert torch.equal(out.long(), torch.argmax(logits, dim=-1))
+        assert out[1].item() == V // 2
 
 
 def test_kernels_refuse_what_they_cannot_do():
