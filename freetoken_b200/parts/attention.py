@@ -102,7 +102,7 @@ class GQAttention(Mixer):
         n_proj = self.q_dim + (2 * self.kv_dim if writes_cache else 0)
         qkv = ws.get("attn.qkv", (T, n_proj), dt, (cap, self.q_dim + 2 * self.kv_dim))
         w = self.params["qkv_proj.weight"]
-        torch.matmul(h, (w if writes_cache else w[: self.q_dim]).t(), out=qkv)
+        ops.linear(h, w if writes_cache else w[: self.q_dim], qkv)
         q = ws.get("attn.q", (T, self.n_heads, self.head_dim), dt, (cap, self.n_heads, self.head_dim))
         sections = [dict(first_head=0, n_heads=self.n_heads,
                          norm_weight=self.params.get("q_norm.weight"), rotate=True, dense_out=q)]
@@ -121,5 +121,5 @@ class GQAttention(Mixer):
                             len(step.segments), plan.items_dev, plan.n_items, plan.part_o, plan.part_ml,
                             o, self.tile_rows(step.decode_only), self.scale, self.window)
         out = ws.get("attn.out", (T, self.hidden), dt, (cap, self.hidden))
-        torch.matmul(o.view(T, self.q_dim), self.params["o_proj.weight"].t(), out=out)
+        ops.linear(o.view(T, self.q_dim), self.params["o_proj.weight"], out)
         return out

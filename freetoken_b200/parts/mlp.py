@@ -45,9 +45,9 @@ class GatedMLP(FeedForward):
         T = h.shape[0]
         ws, dt, cap = self.env.workspace, self.env.dtype, self.env.max_step_tokens
         gu = ws.get(f"{self.tag}.gate_up", (T, 2 * self.inter), dt, (cap, 2 * self.inter))
-        torch.matmul(h, self.params["gate_up_proj.weight"].t(), out=gu)
+        ops.linear(h, self.params["gate_up_proj.weight"], gu)
         a = ws.get(f"{self.tag}.act", (T, self.inter), dt, (cap, self.inter))
         ops.act_and_mul(gu, a, self.act, self.alpha, self.limit)
         out = ws.get(f"{self.tag}.out", (T, self.hidden), dt, (cap, self.hidden))
-        torch.matmul(a, self.params["down_proj.weight"].t(), out=out)
+        ops.linear(a, self.params["down_proj.weight"], out)
         return out

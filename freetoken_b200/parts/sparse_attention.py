@@ -77,7 +77,7 @@ class BlockSparseAttention(GQAttention):
         n_proj = self.q_dim + (2 * self.kv_dim if writes_cache else 0)
         qkv = ws.get("attn.qkv", (T, n_proj), dt, (cap, self.q_dim + 2 * self.kv_dim))
         w = self.params["qkv_proj.weight"]
-        torch.matmul(h, (w if writes_cache else w[: self.q_dim]).t(), out=qkv)
+        ops.linear(h, w if writes_cache else w[: self.q_dim], qkv)
         q = ws.get("attn.q", (T, Hq, D), dt, (cap, Hq, D))
         sections = [dict(first_head=0, n_heads=Hq, norm_weight=self.params.get("q_norm.weight"), rotate=True,
                          dense_out=q)]
@@ -92,7 +92,7 @@ class BlockSparseAttention(GQAttention):
         n_index = (Hi + (1 if writes_cache else 0)) * self.index_dim
         iqk = ws.get("attn.iqk", (T, n_index), dt, (cap, (Hi + 1) * self.index_dim))
         wi = self.params["index_qk_proj.weight"]
-        torch.matmul(h, (wi if writes_cache else wi[: Hi * self.index_dim]).t(), out=iqk)
+        ops.linear(h, wi if writes_cache else wi[: Hi * self.index_dim], iqk)
         iq = ws.get("attn.iq", (T, Hi, self.index_dim), dt, (cap, Hi, self.index_dim))
         sections = [dict(first_head=0, n_heads=Hi, norm_weight=self.params["index_q_norm.weight"], rotate=True,
                          dense_out=iq)]
@@ -112,5 +112,5 @@ class BlockSparseAttention(GQAttention):
                             len(step.segments), plan.items_dev, plan.n_items, plan.part_o, plan.part_ml, o, 16,
                             self.scale, None, sel=sel, block_size=self.block_size)
         out = ws.get("attn.out", (T, self.hidden), dt, (cap, self.hidden))
-        torch.matmul(o.view(T, self.q_dim), self.params["o_proj.weight"].t(), out=out)
+        ops.linear(o.view(T, self.q_dim), self.params["o_proj.weight"], out)
         return out

@@ -178,6 +178,14 @@ def moe_permute(topk_ids, n_experts, expert_counts, expert_offsets, sorted_route
     route_pos[order] = torch.arange(flat.numel(), dtype=torch.int32, device=flat.device)
 
 
+def dense_tc_fits(n_tokens, n_out, k):
+    return False  # the CPU tests take the library product
+
+
+def dense_tc(x, w, out):
+    out.copy_((x.float() @ w.float().T).to(out.dtype))
+
+
 def moe_route_fits(n_tokens, hidden, n_experts, top_k):
     return 1 <= n_tokens <= 64 and hidden % 4 == 0
 
@@ -252,7 +260,7 @@ def sample(logits, temperature, top_k, top_p, u, out):
 
 
 ALL = ["copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "act_and_mul", "cast", "table_update", "norm_rope_store",
-       "paged_attention", "router_topk", "moe_permute", "moe_route", "moe_route_fits", "moe_gather", "moe_gemm1_act", "moe_gemm2",
+       "paged_attention", "router_topk", "moe_permute", "moe_route", "moe_route_fits", "dense_tc", "dense_tc_fits", "moe_gather", "moe_gemm1_act", "moe_gemm2",
        "moe_combine", "sample"]
 
 
