@@ -36,6 +36,12 @@ int ftk_embedding_gather(const void* table, int dtype, const int32_t* ids, int n
 int ftk_add_rmsnorm(const void* x, int x_dtype, float* residual, const float* weight, void* out,
                     int out_dtype, float* out_f32, const int32_t* rows, int n_rows, int hidden,
                     float eps, int gemma, void* stream);
+// The same with the row that is added taken as a sum over routes: sum_j y[route_pos[row * top_k + j]]
+// (+ shared[row]), rounded to y's type (what ftk_moe_combine would have written).
+int ftk_add_rmsnorm_routes(const void* y, int y_dtype, const int32_t* route_pos, int top_k, int n_routes,
+                           const void* shared, float* residual, const float* weight, void* out, int out_dtype,
+                           float* out_f32, const int32_t* rows, int n_rows, int hidden, float eps, int gemma,
+                           void* stream);
 int ftk_act_and_mul(const void* gate_up, int dtype, int n_rows, int inter, int act, float alpha,
                     float limit, void* out, void* stream);
 int ftk_cast(const void* src, int src_dtype, void* dst, int dst_dtype, long long n, void* stream);
@@ -68,7 +74,8 @@ int ftk_router_topk(const float* logits, const float* bias, int n_tokens, int n_
 int ftk_dense_tc_fits(int n_tokens, int n_out, int k);
 int ftk_dense_tc(const void* x, const void* w, void* out, int n_tokens, int n_out, int k, void* stream);
 // Router logits (float32 x [T, hidden] times gate_w [E, hidden]), choice and sort of the routes in one
-// launch, for steps of at most 64 tokens; ftk_moe_route_fits says whether the sizes are taken.
+// launch, for steps of at most 32 tokens (beyond that the
+// separate kernels are faster); ftk_moe_route_fits says whether the sizes are taken.
 int ftk_moe_route_fits(int n_tokens, int hidden, int n_experts, int top_k);
 int ftk_moe_route(const float* x, const float* gate_w, const float* bias, int n_tokens, int hidden, int n_experts,
                   int top_k, int scoring, float scale, float* logits, int32_t* ids, float* weights,

@@ -67,17 +67,22 @@ __global__ void embedding_gather_kernel(const T* __restrict__ table, const int32
 // z = x + residual (32-bit); residual <- z; out = z * rsqrt(mean(z^2) + eps) * (1 + w)
 // (python/freetoken/kernel/triton/norm.py:65-75,101-112).  One block per row; the row's z is
 // kept in shared memory between the two passes.
+// With `route_pos`, x holds the rows of the routed experts' outputs and the row that is added is
+// sum_j x[route_pos[row * top_k + j]] (+ shared[row]), a 32-bit sum in route order rounded to XT: the
+// sum over routes (moe_combine_kernel) without its trip through memory.
 template <typename XT, typename OT, bool VEC>
 __global__ void add_rmsnorm_kernel(const XT* __restrict__ x, float* __restrict__ residual,
                                    const float* __restrict__ weight, OT* __restrict__ out,
                                    float* __restrict__ out_f32, const int32_t* __restrict__ rows,
-                                   int hidden, float eps, int gemma) {
+                                   int hidden, float eps, int gemma, const int32_t* __restrict__ route_pos,
+                                   int top_k, int n_routes, const XT* __restrict__ shared) {
   pdl_wait();
   pdl_trigger();
   extern __shared__ float zrow[];
   __shared__ float red[33];
   const int r = blockIdx.x;
-  const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
+  const int src_row = rows ? rows[r] : r;
+  const size_t src = (size_t)src_row * hidden;
   const size_t dst = (size_t)r * hidden;
   const bool update = residual != nullptr && x != nullptr && rows == nullptr;
   float ss = 0.f;
@@ -85,7 +90,26 @@ __global__ void add_rmsnorm_kernel(const XT* __restrict__ x, float* __restrict__
     for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
       float z[4] = {0.f, 0.f, 0.f, 0.f};
       if (residual) Vec4<float>::load(residual + src + i, z);
-      if (x) {
+      if (x && route_pos) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int j = 0; j < top_k; ++j) {
+          const int p = __ldg(route_pos + (size_t)src_row * top_k + j);
+          if (p >= 0 && p < n_routes) {
+            float xv[4];
+            Vec4<XT>::load(x + (size_t)p * hidden + i, xv);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc[q] += xv[q];
+          }
+        }
+        if (shared) {
+          float xv[4];
+          Vec4<XT>::load(shared + src + i, xv);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) acc[q] += xv[q];
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) z[q] += to_float(from_float<XT>(acc[q]));
+      } else if (x) {
         float xv[4];
         Vec4<XT>::load(x + src + i, xv);
 #pragma unroll
@@ -101,7 +125,17 @@ __global__ void add_rmsnorm_kernel(const XT* __restrict__ x, float* __restrict__
   } else {
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
       float z = residual ? residual[src + i] : 0.f;
-      if (x) z += to_float(x[src + i]);
+      if (x && route_pos) {
+        float acc = 0.f;
+        for (int j = 0; j < top_k; ++j) {
+          const int p = route_pos[(size_t)src_row * top_k + j];
+          if (p >= 0 && p < n_routes) acc += to_float(x[(size_t)p * hidden + i]);
+        }
+        if (shared) acc += to_float(shared[src + i]);
+        z += to_float(from_float<XT>(acc));
+      } else if (x) {
+        z += to_float(x[src + i]);
+      }
       if (update) residual[src + i] = z;
       zrow[i] = z;
       ss += z * z;
@@ -244,9 +278,10 @@ extern "C" int ftk_embedding_gather(const void* table, int dtype, const int32_t*
 
 template <typename XT, typename OT>
 static int launch_norm(const void* x, float* residual, const float* weight, void* out, float* out_f32,
-                       const int32_t* rows, int n_rows, int hidden, float eps, int gemma, cudaStream_t s) {
+                       const int32_t* rows, int n_rows, int hidden, float eps, int gemma, cudaStream_t s,
+                       const int32_t* route_pos = nullptr, int top_k = 0, int n_routes = 0, const void* shared = nullptr) {
   const bool vec = hidden % 4 == 0 && aligned16(x) && aligned16(residual) && aligned16(weight) &&
-                   aligned16(out) && aligned16(out_f32) && (hidden % 8 == 0);
+                   aligned16(out) && aligned16(out_f32) && (hidden % 8 == 0) && aligned16(shared);
   const int threads = hidden >= 2048 ? 256 : 128;
   const size_t smem = (size_t)hidden * sizeof(float);
   auto kv = add_rmsnorm_kernel<XT, OT, true>;
@@ -256,8 +291,10 @@ static int launch_norm(const void* x, float* residual, const float* weight, void
     cudaFuncSetAttribute(kv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaFuncSetAttribute(ks, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   }
-  if (vec) FTK_LAUNCH(kv, n_rows, threads, smem, s, (const XT*)x, residual, weight, (OT*)out, out_f32, rows, hidden, eps, gemma);
-  else FTK_LAUNCH(ks, n_rows, threads, smem, s, (const XT*)x, residual, weight, (OT*)out, out_f32, rows, hidden, eps, gemma);
+  if (vec) FTK_LAUNCH(kv, n_rows, threads, smem, s, (const XT*)x, residual, weight, (OT*)out, out_f32, rows, hidden, eps, gemma,
+                      route_pos, top_k, n_routes, (const XT*)shared);
+  else FTK_LAUNCH(ks, n_rows, threads, smem, s, (const XT*)x, residual, weight, (OT*)out, out_f32, rows, hidden, eps, gemma,
+                  route_pos, top_k, n_routes, (const XT*)shared);
   FTK_LAUNCH_CHECK("add_rmsnorm");
   return 0;
 }
@@ -277,6 +314,29 @@ extern "C" int ftk_add_rmsnorm(const void* x, int x_dtype, float* residual, cons
   if (x_dtype == FTK_F32 && out_dtype == FTK_BF16)
     return launch_norm<float, __nv_bfloat16>(x, residual, weight, out, out_f32, rows, n_rows, hidden, eps, gemma, s);
   return launch_norm<__nv_bfloat16, float>(x, residual, weight, out, out_f32, rows, n_rows, hidden, eps, gemma, s);
+}
+
+// The sum over a token's routes (rows of y), the residual sum and the norm in one pass.
+extern "C" int ftk_add_rmsnorm_routes(const void* y, int y_dtype, const int32_t* route_pos, int top_k, int n_routes,
+                                      const void* shared, float* residual, const float* weight, void* out,
+                                      int out_dtype, float* out_f32, const int32_t* rows, int n_rows, int hidden,
+                                      float eps, int gemma, void* stream) {
+  FTK_REQUIRE(dtype_ok(y_dtype) && dtype_ok(out_dtype), "add_rmsnorm_routes: bad dtype");
+  FTK_REQUIRE(y && route_pos && residual && weight && out, "add_rmsnorm_routes: null pointer");
+  FTK_REQUIRE(n_rows >= 0 && hidden > 0 && top_k >= 1 && n_routes >= 0, "add_rmsnorm_routes: bad sizes");
+  if (n_rows == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (y_dtype == FTK_F32 && out_dtype == FTK_F32)
+    return launch_norm<float, float>(y, residual, weight, out, out_f32, rows, n_rows, hidden, eps, gemma, s, route_pos,
+                                     top_k, n_routes, shared);
+  if (y_dtype == FTK_BF16 && out_dtype == FTK_BF16)
+    return launch_norm<__nv_bfloat16, __nv_bfloat16>(y, residual, weight, out, out_f32, rows, n_rows, hidden, eps, gemma,
+                                                     s, route_pos, top_k, n_routes, shared);
+  if (y_dtype == FTK_F32 && out_dtype == FTK_BF16)
+    return launch_norm<float, __nv_bfloat16>(y, residual, weight, out, out_f32, rows, n_rows, hidden, eps, gemma, s,
+                                             route_pos, top_k, n_routes, shared);
+  return launch_norm<__nv_bfloat16, float>(y, residual, weight, out, out_f32, rows, n_rows, hidden, eps, gemma, s,
+                                           route_pos, top_k, n_routes, shared);
 }
 
 extern "C" int ftk_act_and_mul(const void* gate_up, int dtype, int n_rows, int inter, int act, float alpha,

@@ -338,7 +338,7 @@ static size_t route_smem(int n_tokens, int n_experts, int top_k) {
 }
 
 extern "C" int ftk_moe_route_fits(int n_tokens, int hidden, int n_experts, int top_k) {
-  return n_tokens >= 1 && n_tokens <= 64 && hidden % 4 == 0 && n_experts >= 1 && top_k >= 1 && top_k <= n_experts &&
+  return n_tokens >= 1 && n_tokens <= 32 && hidden % 4 == 0 && n_experts >= 1 && top_k >= 1 && top_k <= n_experts &&
          route_smem(n_tokens, n_experts, top_k) <= 160 * 1024;
 }
 
@@ -348,7 +348,7 @@ extern "C" int ftk_moe_route(const float* x, const float* gate_w, const float* b
                              void* stream) {
   FTK_REQUIRE(scoring == FTK_SCORE_SIGMOID || scoring == FTK_SCORE_SOFTMAX, "moe_route: unknown scoring %d", scoring);
   FTK_REQUIRE(ftk_moe_route_fits(n_tokens, hidden, n_experts, top_k),
-              "moe_route: %d tokens, width %d, %d experts, top %d do not fit the one-launch routing (at most 64 tokens, "
+              "moe_route: %d tokens, width %d, %d experts, top %d do not fit the one-launch routing (at most 32 tokens, "
               "a width that is a multiple of 4); use the matrix product + router_topk + moe_permute",
               n_tokens, hidden, n_experts, top_k);
   FTK_REQUIRE(x && gate_w && logits && ids && weights && counts && offsets && routes && pos, "moe_route: null pointer");

@@ -54,6 +54,7 @@ class _Section(ctypes.Structure):
 _SIGNATURES = {
     "ftk_embedding_gather": [_vp, _i, _vp, _i, _i, _i, _vp, _vp],
     "ftk_add_rmsnorm": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _f, _i, _vp],
+    "ftk_add_rmsnorm_routes": [_vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _f, _i, _vp],
     "ftk_norm_rope_store": [_vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _f, _i, _i,
                             ctypes.POINTER(_Section), _vp],
     "ftk_paged_attention": [_vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
@@ -200,6 +201,27 @@ def add_rmsnorm(x: Optional[torch.Tensor], residual: Optional[torch.Tensor], wei
                                   _dev(out_f32, "out_f32", torch.float32),
                                   _dev(rows, "rows", torch.int32), n_rows, H, float(eps),
                                   1 if gemma else 0, _stream()), "add_rmsnorm")
+
+
+def add_rmsnorm_routes(y: torch.Tensor, route_pos: torch.Tensor, top_k: int, shared: Optional[torch.Tensor],
+                       residual: torch.Tensor, weight: torch.Tensor, eps: float, gemma: bool, out: torch.Tensor,
+                       out_f32: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> None:
+    """:func:`moe_combine` and :func:`add_rmsnorm` in one pass: the row added to ``residual[t]`` is
+    ``sum_j y[route_pos[t*k + j]] (+ shared[t])``, a 32-bit sum in route order rounded to ``y``'s type."""
+    R, H = y.shape
+    T = residual.numel() // H
+    n_rows = rows.shape[0] if rows is not None else T
+    if route_pos.numel() != T * top_k or weight.shape != (H,) or out.numel() != n_rows * H:
+        raise KernelError("add_rmsnorm_routes: shapes do not agree")
+    if shared is not None and (shared.shape != (T, H) or shared.dtype != y.dtype):
+        raise KernelError("add_rmsnorm_routes: shared must be [tokens, hidden] of y's dtype")
+    if out_f32 is not None and out_f32.numel() != n_rows * H:
+        raise KernelError("add_rmsnorm_routes: out_f32 has the wrong size")
+    _check(_lib().ftk_add_rmsnorm_routes(_dev(y, "y"), _code(y, "y"), _dev(route_pos, "route_pos", torch.int32), top_k, R,
+                                         _dev(shared, "shared"), _dev(residual, "residual", torch.float32),
+                                         _dev(weight, "weight", torch.float32), _dev(out, "out"), _code(out, "out"),
+                                         _dev(out_f32, "out_f32", torch.float32), _dev(rows, "rows", torch.int32),
+                                         n_rows, H, float(eps), 1 if gemma else 0, _stream()), "add_rmsnorm_routes")
 
 
 def act_and_mul(gate_up: torch.Tensor, out: torch.Tensor, act: str, alpha: float, limit: float) -> None:

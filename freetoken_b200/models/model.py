@@ -21,6 +21,7 @@ from ..config.spec import ModelSpec, ParamSpec
 from ..errors import ConfigError
 from ..kernels import ops
 from ..parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, BuildEnv, Part, StepState
+from ..parts.base import as_rows
 
 
 def _walk(prefix: str, part: Part, out: Dict[str, Tuple[Part, str, ParamSpec]]) -> None:
@@ -131,6 +132,6 @@ class Model:
         else:  # grows with the largest request for logits seen so far
             logits = ws.get("model.logits", (R, self.vocab), torch.float32)
         y = ws.get("model.final", (R, self.hidden), dt, (cap, self.hidden))
-        self.final_norm.add_forward(x, residual, y, rows=step.logit_rows)
+        self.final_norm.add_forward(as_rows(x, self.final_norm), residual, y, rows=step.logit_rows)
         head_matmul(y, self.head_weight, logits)
         return logits

@@ -136,7 +136,33 @@ class Part:
         return {}
 
 
+class RouteSum:
+    """A feed-forward output that is still a sum to be taken: row ``t`` is
+    ``sum_j y[pos[t * top_k + j]] (+ shared[t])``.  A norm with ``takes_route_sum`` adds it to the
+    residual without the sum's trip through memory; for any other consumer :func:`as_rows` takes it."""
+
+    def __init__(self, y: torch.Tensor, pos: torch.Tensor, top_k: int, shared: Optional[torch.Tensor],
+                 n_tokens: int, out: torch.Tensor):
+        self.y, self.pos, self.top_k, self.shared, self.n_tokens, self.out = y, pos, top_k, shared, n_tokens, out
+
+    def rows(self) -> torch.Tensor:
+        from ..kernels import ops
+
+        ops.moe_combine(self.y, self.pos, self.n_tokens, self.top_k, self.shared, self.out)
+        return self.out
+
+
+def as_rows(x: Any, consumer: Any = None) -> Any:
+    """``x`` as the consumer can take it: a :class:`RouteSum` stays one only for a norm that says it
+    takes one."""
+    if isinstance(x, RouteSum) and not getattr(consumer, "takes_route_sum", False):
+        return x.rows()
+    return x
+
+
 class Norm(Part):
+    takes_route_sum: bool = False  # add_forward accepts a RouteSum as x
+
     def forward(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """``out = norm(x)`` row by row."""
         raise NotImplementedError
@@ -175,6 +201,9 @@ class Mixer(Part):
 class FeedForward(Part):
     def forward(self, h: torch.Tensor, step: "StepState", h_f32: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
+
+    # Optional: ``forward_lazy(h, step, h_f32)`` may return a :class:`RouteSum` instead of rows; blocks
+    # call it when it exists and hand the result to :func:`as_rows` before any consumer but a norm.
 
     wants_f32_input: bool = False  # ask the preceding norm for a 32-bit copy of its output
 

@@ -23,7 +23,7 @@ import torch
 from ..config.spec import ParamSpec, PartSpec
 from ..errors import ConfigError
 from ..kernels import ops
-from .base import FEED_FORWARDS, BuildEnv, FeedForward, Part, StepState
+from .base import FEED_FORWARDS, BuildEnv, FeedForward, Part, RouteSum, StepState
 from .mlp import GatedMLP
 
 
@@ -72,6 +72,11 @@ class MoE(FeedForward):
         return {"shared_experts": self.shared} if self.shared is not None else {}
 
     def forward(self, h: torch.Tensor, step: StepState, h_f32: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return self.forward_lazy(h, step, h_f32).rows()
+
+    def forward_lazy(self, h: torch.Tensor, step: StepState, h_f32: Optional[torch.Tensor] = None) -> RouteSum:
+        """The experts' rows and where each token's routes lie among them; the sum over a token's routes
+        is left to the consumer (the next norm takes it together with the residual sum)."""
         T = h.shape[0]
         ws, dt, cap = self.env.workspace, self.env.dtype, self.env.max_step_tokens
         k, E, R = self.top_k, self.n_experts, T * self.top_k
@@ -108,5 +113,4 @@ class MoE(FeedForward):
         ops.moe_gemm2(a, self.params["experts.down_proj"], offsets, routes, wts.view(-1), y)
         shared = self.shared.forward(h, step) if self.shared is not None else None
         out = ws.get("moe.out", (T, self.hidden), dt, (cap, self.hidden))
-        ops.moe_combine(y, pos, T, k, shared, out)
-        return out
+        return RouteSum(y, pos, k, shared, T, out)

@@ -14,12 +14,14 @@ import torch
 
 from ..config.spec import ParamSpec, PartSpec
 from ..kernels import ops
-from .base import NORMS, BuildEnv, Norm
+from .base import NORMS, BuildEnv, Norm, RouteSum
 
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
     """params: ``size``, ``eps``, ``gemma`` (bool: multiply by ``1 + w``)."""
+
+    takes_route_sum = True
 
     def __init__(self, spec: PartSpec, env: BuildEnv):
         super().__init__(spec, env)
@@ -38,6 +40,10 @@ class RMSNorm(Norm):
     def add_forward(self, x: Optional[torch.Tensor], residual: torch.Tensor, out: torch.Tensor,
                     out_f32: Optional[torch.Tensor] = None,
                     rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-        ops.add_rmsnorm(x, residual, self.params["weight"], self.eps, self.gemma, out,
-                        out_f32=out_f32, rows=rows)
+        if isinstance(x, RouteSum):
+            ops.add_rmsnorm_routes(x.y, x.pos, x.top_k, x.shared, residual, self.params["weight"], self.eps,
+                                   self.gemma, out, out_f32=out_f32, rows=rows)
+        else:
+            ops.add_rmsnorm(x, residual, self.params["weight"], self.eps, self.gemma, out,
+                            out_f32=out_f32, rows=rows)
         return out

@@ -39,6 +39,13 @@ def add_rmsnorm(x, residual, weight, eps, gemma, out, out_f32=None, rows=None):
         out_f32.view(y.shape).copy_(y.float())
 
 
+def add_rmsnorm_routes(y, route_pos, top_k, shared, residual, weight, eps, gemma, out, out_f32=None, rows=None):
+    T = residual.shape[0]
+    delta = torch.empty(T, y.shape[1], dtype=y.dtype, device=y.device)
+    moe_combine(y, route_pos, T, top_k, shared, delta)
+    add_rmsnorm(delta, residual, weight, eps, gemma, out, out_f32=out_f32, rows=rows)
+
+
 def act_and_mul(gate_up, out, act, alpha, limit):
     I = gate_up.shape[1] // 2
     g, u = gate_up[:, :I].float(), gate_up[:, I:].float()
@@ -187,7 +194,7 @@ def dense_tc(x, w, out):
 
 
 def moe_route_fits(n_tokens, hidden, n_experts, top_k):
-    return 1 <= n_tokens <= 64 and hidden % 4 == 0
+    return 1 <= n_tokens <= 32 and hidden % 4 == 0
 
 
 def moe_route(x, gate_w, bias, top_k, scoring, scale, logits, ids, weights, expert_counts, expert_offsets,
@@ -259,7 +266,7 @@ def sample(logits, temperature, top_k, top_p, u, out):
         out[r] = idx
 
 
-ALL = ["copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "act_and_mul", "cast", "table_update", "norm_rope_store",
+ALL = ["copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "add_rmsnorm_routes", "act_and_mul", "cast", "table_update", "norm_rope_store",
        "paged_attention", "router_topk", "moe_permute", "moe_route", "moe_route_fits", "dense_tc", "dense_tc_fits", "moe_gather", "moe_gemm1_act", "moe_gemm2",
        "moe_combine", "sample"]
 

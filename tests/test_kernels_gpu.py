@@ -75,6 +75,33 @@ def test_add_rmsnorm(dtype, H, T, gemma):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,T,k", [(3072, 8, 8), (100, 5, 3), (520, 33, 1), (48, 2, 4)])
+def test_add_rmsnorm_routes_is_combine_then_norm(dtype, H, T, k):
+    """The sum over routes taken inside the norm kernel: the same bits as the two kernels one after
+    the other, for all rows and for chosen rows, with and without a shared expert's rows."""
+    R = T * k
+    y = rnd(R, H, dtype=dtype)
+    pos = torch.randperm(R, generator=torch.Generator().manual_seed(4)).to(torch.int32).to(DEV)
+    pos[0] = -1  # a route that went to no expert adds nothing
+    shared = rnd(T, H, dtype=dtype, seed=6)
+    w = rnd(H, scale=0.1, seed=2)
+    res = rnd(T, H, seed=1)
+    for sh in (None, shared):
+        for rows in (None, torch.tensor([T - 1, 0], dtype=torch.int32, device=DEV)):
+            n = T if rows is None else 2
+            r1, r2 = res.clone(), res.clone()
+            out, want = torch.empty(n, H, dtype=dtype, device=DEV), torch.empty(n, H, dtype=dtype, device=DEV)
+            o32, w32 = torch.empty(n, H, device=DEV), torch.empty(n, H, device=DEV)
+            ops.add_rmsnorm_routes(y, pos, k, sh, r1, w, 1e-5, True, out, out_f32=o32, rows=rows)
+            delta = torch.empty(T, H, dtype=dtype, device=DEV)
+            ops.moe_combine(y, pos, T, k, sh, delta)
+            ops.add_rmsnorm(delta, r2, w, 1e-5, True, want, out_f32=w32, rows=rows)
+            assert torch.equal(out, want) and torch.equal(o32, w32) and torch.equal(r1, r2)
+            if rows is not None:
+                assert torch.equal(r1, res)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("act", ["silu", "swigluoai"])
 def test_act_and_mul(dtype, act):
     gu = rnd(13, 2 * 72, dtype=dtype, scale=4.0)
@@ -358,11 +385,11 @@ def test_dense_tc_matches_the_plain_product(T, N, K):
 
 
 @pytest.mark.parametrize("scoring,bias", [("sigmoid", True), ("softmax", False)])
-@pytest.mark.parametrize("T,H,E,k", [(1, 64, 8, 2), (8, 3072, 256, 8), (13, 100, 7, 3), (64, 520, 33, 5), (9, 36, 301, 1)])
+@pytest.mark.parametrize("T,H,E,k", [(1, 64, 8, 2), (8, 3072, 256, 8), (13, 100, 7, 3), (32, 520, 33, 5), (9, 36, 301, 1)])
 def test_moe_route_in_one_launch(scoring, bias, T, H, E, k):
     """Logits, choice and sort in one launch against the three separate statements; run several
     times so that the arrival counter is seen to come back to zero."""
-    assert ops.moe_route_fits(T, H, E, k) and not ops.moe_route_fits(65, H, E, k) and not ops.moe_route_fits(T, H + 2, E, k)
+    assert ops.moe_route_fits(T, H, E, k) and not ops.moe_route_fits(33, H, E, k) and not ops.moe_route_fits(T, H + 2, E, k)
     x = rnd(T, H, scale=1.0)
     w = rnd(E, H, scale=H ** -0.5, seed=5)
     if T > 2:
