@@ -48,7 +48,13 @@ struct AttnParams {
   const int32_t* sel;
   int sel_stride;
   int block_size;
+  // decode tiles: one counter per (split tile, KV head), zero between launches; the last of a tile's
+  // splits to arrive merges them, so no merge kernel follows.  nullptr: the merge kernel does it.
+  unsigned int* arrivals;
 };
+
+constexpr int kAttnArrivalSlots = 1 << 16;
+__device__ unsigned int g_attn_arrivals[kAttnArrivalSlots];
 
 constexpr int kMaxMergeSplits = 64;  // most splits of one tile that the merge step takes
 
@@ -545,6 +551,59 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(AttnParams p) {
   }
 }
 
+// The same merge for all rows of one tile by one block (the split that arrived last).  The splits'
+// (max, sum) pairs are fetched once into shared memory, a thread per row turns them into weights, and
+// then every thread takes (row, four columns) items whose loads over the splits are independent.
+// `scratch` holds 3 * tile_rows * nsplit + tile_rows floats.
+__device__ __forceinline__ void merge_tile_rows_bf16(const AttnParams& p, const Item& it, int kvh, float* scratch) {
+  const int D = p.D, G = p.G, R = it.ntok * G, S = it.nsplit;
+  const size_t slot_step = (size_t)p.Hkv * p.tile_rows;
+  const size_t slot0 = ((size_t)it.base * p.Hkv + kvh) * p.tile_rows;
+  float* sm = scratch;            // [R][S] max, later the weight
+  float* sl = sm + R * S;         // [R][S] sum
+  float* sinv = sl + R * S;       // [R]
+  for (int i = threadIdx.x; i < R * S; i += blockDim.x) {
+    const int r = i / S, sp = i % S;
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + (slot0 + r + sp * slot_step) * 2));
+    sm[i] = ml.x;
+    sl[i] = ml.y;
+  }
+  __syncthreads();
+  if ((int)threadIdx.x < R) {
+    const int r = threadIdx.x;
+    float M = -INFINITY;
+    for (int sp = 0; sp < S; ++sp) M = fmaxf(M, sm[r * S + sp]);
+    float L = 0.f;
+    for (int sp = 0; sp < S; ++sp) {  // splits in order
+      const float m = sm[r * S + sp];
+      const float w = m != -INFINITY ? expf(m - M) : 0.f;
+      L += sl[r * S + sp] * w;
+      sm[r * S + sp] = w;
+    }
+    sinv[r] = L > 0.f ? 1.f / L : 0.f;
+  }
+  __syncthreads();
+  const int quads = D >> 2;  // D is a multiple of 16
+  for (int i = threadIdx.x; i < R * quads; i += blockDim.x) {
+    const int r = i / quads, d = (i % quads) << 2;
+    const float* src = p.part_o + (slot0 + r) * D + d;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int sp = 0; sp < S; ++sp) {
+      const float w = sm[r * S + sp];
+      const float4 x = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sp * slot_step * D));
+      acc.x += x.x * w; acc.y += x.y * w; acc.z += x.z * w; acc.w += x.w * w;
+    }
+    const float inv = sinv[r];
+    const int tok = it.q_start + it.tok0 + r / G;
+    __nv_bfloat16* o = (__nv_bfloat16*)p.out + ((size_t)tok * p.Hq + kvh * G + r % G) * D + d;
+    uint2 pk;
+    pk.x = pack_bf16(acc.x * inv, acc.y * inv);
+    pk.y = pack_bf16(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(o) = pk;
+  }
+}
+
 // ----------------------------------------------------------------- decode tiles (at most 16 query rows)
 // A step of single decoded tokens has `group` query rows per (request, KV head): too few to fill a
 // 64-row tile.  Here the four warps share the 16-row query tile and split each 64-key tile between
@@ -754,6 +813,22 @@ __global__ void __launch_bounds__(128) attention_decode_bf16_kernel(AttnParams p
       }
     }
   }
+  if (it.nsplit > 1 && p.arrivals) {
+    // the split that finds all the others arrived merges the tile (nobody waits for anybody)
+    __shared__ bool last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned int* cnt = p.arrivals + (size_t)it.base * p.Hkv + kvh;
+      last = atomicAdd(cnt, 1u) == (unsigned)it.nsplit - 1u;
+      if (last) *cnt = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (last) {
+      __threadfence();
+      merge_tile_rows_bf16(p, it, kvh, reinterpret_cast<float*>(sk0));
+    }
+  }
 }
 
 template <int DMAX>
@@ -807,6 +882,7 @@ static int paged_attention_impl(const void* q, const void* k_slab, const void* v
   p.Hq = n_q_heads; p.Hkv = n_kv_heads; p.G = n_q_heads / n_kv_heads; p.D = head_dim; p.P = page_size;
   p.num_pages = num_pages; p.tile_rows = tile_rows; p.scale = scale; p.window = window;
   p.sel = sel; p.sel_stride = sel_stride; p.block_size = block_size;
+  p.arrivals = nullptr;
   if (sel) {
     FTK_REQUIRE(sel_stride >= 1 && block_size >= 1, "paged_attention: bad block selection geometry");
     FTK_REQUIRE(window == 0, "paged_attention: a window cannot be combined with block selection");
@@ -833,7 +909,14 @@ static int paged_attention_impl(const void* q, const void* k_slab, const void* v
                 "paged_attention: the bfloat16 kernels work on %d-row tiles (%d for decode steps), got %d", kBM,
                 kDecRows, tile_rows);
     FTK_REQUIRE(p.G <= tile_rows, "paged_attention: %d query heads per KV head exceed the %d-row tile", p.G, tile_rows);
+    bool merged = false;
     if (tile_rows == kDecRows) {
+      if (n_slots > 0 && (long long)n_slots * p.Hkv <= kAttnArrivalSlots && p.D % 4 == 0) {
+        static unsigned int* arrivals = nullptr;
+        if (!arrivals) cudaGetSymbolAddress((void**)&arrivals, g_attn_arrivals);
+        p.arrivals = arrivals;
+        merged = true;
+      }
       if (head_dim <= 64) launch_decode_bf16<64>(p, s);
       else if (head_dim <= 128) launch_decode_bf16<128>(p, s);
       else launch_decode_bf16<256>(p, s);
@@ -843,7 +926,7 @@ static int paged_attention_impl(const void* q, const void* k_slab, const void* v
       else launch_bf16<256>(p, s);
     }
     FTK_LAUNCH_CHECK("paged_attention (bfloat16)");
-    if (n_slots > 0) {
+    if (n_slots > 0 && !merged) {
       FTK_LAUNCH(attention_merge_kernel<__nv_bfloat16>, grid, 128, 0, s, p);
       FTK_LAUNCH_CHECK("paged_attention merge");
     }
