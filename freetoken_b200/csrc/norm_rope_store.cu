@@ -103,6 +103,106 @@ __global__ void norm_rope_store_kernel(const T* __restrict__ x, int n_tokens, in
   }
 }
 
+// The same for bfloat16 heads of 64, 128 or 256 elements with 16-byte accesses: a head is spread over
+// LPH = head_dim / 8 lanes (8 consecutive elements each), a warp takes 32 / LPH heads at once, and a
+// lane gets its rotation partners from the lane half a rotary span away (rotary_dim a multiple of 16).
+template <int LPH>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+norm_rope_store_vec_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int row_elems, int rotary_dim,
+                           const int32_t* __restrict__ positions, const float* __restrict__ rope_table, int max_pos,
+                           float eps, int gemma, Sections sec) {
+  pdl_wait();
+  pdl_trigger();
+  constexpr int kHeadDim = LPH * 8;
+  constexpr int kHeadsPerWarp = 32 / LPH;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.y;
+  const int sub = lane / LPH, l = lane % LPH;
+  const int hs = (blockIdx.x * kWarpsPerBlock + warp) * kHeadsPerWarp + sub;
+  const bool live = hs < sec.total_heads;
+  int si = 0, hl = live ? hs : 0;
+  while (si < sec.n - 1 && hl >= sec.s[si].n_heads) {
+    hl -= sec.s[si].n_heads;
+    ++si;
+  }
+  const FtkSection& S = sec.s[si];
+  long long slot = 0;
+  bool store = live;
+  if (S.slab) {
+    slot = S.slot_map[t];
+    if (slot < 0 || slot >= (long long)S.num_pages * S.page_size) store = false;  // not stored
+  }
+  const __nv_bfloat16* src = x + (size_t)t * row_elems + (size_t)(S.first_head + hl) * kHeadDim + l * 8;
+  float v[8];
+  {
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (live) raw = *reinterpret_cast<const uint4*>(src);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(h2[j]);
+      v[2 * j] = f.x;
+      v[2 * j + 1] = f.y;
+    }
+  }
+  {
+    // the heads of a warp may lie in different sections (with and without a norm): every lane runs
+    // the shuffles, the ones with a norm use the result
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+#pragma unroll
+    for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (S.norm_weight) {
+      const float inv = rsqrtf(ss / (float)kHeadDim + eps);
+      const float one = gemma ? 1.f : 0.f;
+      float w[8];
+      *reinterpret_cast<float4*>(w) = *reinterpret_cast<const float4*>(S.norm_weight + l * 8);
+      *reinterpret_cast<float4*>(w + 4) = *reinterpret_cast<const float4*>(S.norm_weight + l * 8 + 4);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = v[j] * inv * (w[j] + one);
+    }
+  }
+  {
+    // rotation partners: the lane half a rotary span away, on either side
+    const int half = rotary_dim >> 1, hop = half >> 3;  // lanes per half span
+    const bool rot = S.rotate && rotary_dim > 0;
+    const bool low = l * 8 < half, in = l * 8 < rotary_dim;
+    float partner[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float up = __shfl_down_sync(0xffffffffu, v[j], hop & 31);
+      const float dn = __shfl_up_sync(0xffffffffu, v[j], hop & 31);
+      partner[j] = low ? up : dn;
+    }
+    if (rot && in) {
+      int pos = positions[t];
+      pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+      const float* cs = rope_table + (size_t)pos * rotary_dim;
+      const int d0 = l * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int d = d0 + j;
+        if (low) v[j] = v[j] * cs[d] - partner[j] * cs[half + d];
+        else v[j] = v[j] * cs[d - half] + partner[j] * cs[d];
+      }
+    }
+  }
+  if (!store) return;
+  __nv_bfloat16* dst;
+  if (S.slab) {
+    const long long page = slot / S.page_size, off = slot % S.page_size;
+    dst = (__nv_bfloat16*)S.slab + (((size_t)page * S.n_heads + hl) * S.page_size + off) * kHeadDim;
+  } else {
+    dst = (__nv_bfloat16*)S.dense_out + ((size_t)t * S.n_heads + hl) * kHeadDim;
+  }
+  uint4 pk;
+  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+  *reinterpret_cast<uint4*>(dst + l * 8) = pk;
+}
+
 }  // namespace ftk
 
 using namespace ftk;
@@ -139,6 +239,13 @@ extern "C" int ftk_norm_rope_store(const void* x, int dtype, int n_tokens, int r
   if (any_rot && rotary_dim > 0)
     FTK_REQUIRE(positions && rope_table && max_pos >= 1, "norm_rope_store: rotation needs positions and a table");
   cudaStream_t s = (cudaStream_t)stream;
+  // 16-byte accesses: bfloat16 heads of 64 / 128 / 256, rotation spans of whole lanes, aligned tensors
+  bool vec = dtype == FTK_BF16 && (head_dim == 64 || head_dim == 128 || head_dim == 256) && rotary_dim % 16 == 0 &&
+             row_elems % 8 == 0 && ((uintptr_t)x & 15) == 0;
+  for (int i = 0; i < n_sections && vec; ++i) {
+    const FtkSection& S = sections[i];
+    if (((uintptr_t)S.dense_out & 15) || ((uintptr_t)S.slab & 15) || ((uintptr_t)S.norm_weight & 15)) vec = false;
+  }
   const int bx = (sec.total_heads + kWarpsPerBlock - 1) / kWarpsPerBlock;
   for (int t0 = 0; t0 < n_tokens; t0 += 65535) {
     const int nt = n_tokens - t0 < 65535 ? n_tokens - t0 : 65535;
@@ -149,7 +256,21 @@ extern "C" int ftk_norm_rope_store(const void* x, int dtype, int n_tokens, int r
       if (part.s[i].slot_map) part.s[i].slot_map += t0;
     }
     dim3 grid(bx, nt);
-    if (dtype == FTK_F32)
+    if (vec) {
+      const int lph = head_dim / 8, per_block = kWarpsPerBlock * (32 / lph);
+      dim3 vgrid((sec.total_heads + per_block - 1) / per_block, nt);
+      const __nv_bfloat16* xs = (const __nv_bfloat16*)x + (size_t)t0 * row_elems;
+      const int32_t* ps = positions ? positions + t0 : nullptr;
+      if (lph == 8)
+        FTK_LAUNCH(norm_rope_store_vec_kernel<8>, vgrid, kWarpsPerBlock * 32, 0, s, xs, nt, row_elems, rotary_dim, ps,
+                   rope_table, max_pos, eps, gemma, part);
+      else if (lph == 16)
+        FTK_LAUNCH(norm_rope_store_vec_kernel<16>, vgrid, kWarpsPerBlock * 32, 0, s, xs, nt, row_elems, rotary_dim, ps,
+                   rope_table, max_pos, eps, gemma, part);
+      else
+        FTK_LAUNCH(norm_rope_store_vec_kernel<32>, vgrid, kWarpsPerBlock * 32, 0, s, xs, nt, row_elems, rotary_dim, ps,
+                   rope_table, max_pos, eps, gemma, part);
+    } else if (dtype == FTK_F32)
       FTK_LAUNCH(norm_rope_store_kernel<float>, grid, kWarpsPerBlock * 32, 0, s, 
           (const float*)x + (size_t)t0 * row_elems, nt, row_elems, head_dim, rotary_dim,
           positions ? positions + t0 : nullptr, rope_table, max_pos, eps, gemma, part);

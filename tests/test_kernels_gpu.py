@@ -137,7 +137,8 @@ def make_rope(max_pos, rd, theta=10000.0):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("Hq,Hkv,D,rd,P,gemma,norm", [
     (7, 1, 48, 24, 4, True, True), (6, 3, 32, 32, 8, False, False), (48, 8, 128, 64, 16, True, True),
-    (5, 5, 80, 16, 3, True, True), (2, 2, 256, 128, 16, False, True)])
+    (5, 5, 80, 16, 3, True, True), (2, 2, 256, 128, 16, False, True), (5, 3, 64, 16, 5, True, True),
+    (7, 3, 128, 0, 4, True, True), (5, 1, 128, 128, 8, False, True), (3, 2, 64, 64, 4, True, False)])
 def test_norm_rope_store(dtype, Hq, Hkv, D, rd, P, gemma, norm):
     T, pages = 21, 12
     x = rnd(T, (Hq + 2 * Hkv) * D, dtype=dtype)
@@ -423,7 +424,8 @@ def test_moe_route_in_one_launch(scoring, bias, T, H, E, k):
     assert torch.equal(alone[0], logits[-1]), "a token's logits must not depend on the batch"
 
 
-@pytest.mark.parametrize("T,k,E", [(1, 2, 8), (50, 4, 16), (300, 8, 256), (7, 3, 6), (2, 1, 40)])
+@pytest.mark.parametrize("T,k,E", [(1, 2, 8), (50, 4, 16), (300, 8, 256), (7, 3, 6), (2, 1, 40), (2048, 8, 256),
+                                   (3001, 3, 7), (700, 5, 1100)])
 def test_moe_permute_gather_combine(T, k, E):
     ids = torch.stack([torch.randperm(E)[:k] for _ in range(T)]).to(torch.int32).to(DEV)
     if T > 4:
@@ -452,6 +454,34 @@ def test_moe_permute_gather_combine(T, k, E):
             ops.moe_combine(y, pos, T, k, shared, o)
             ref.moe_combine(y, pos, T, k, shared, o2)
             torch.testing.assert_close(o.float(), o2.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("T,k,E", [(9, 4, 16), (2048, 8, 256), (3001, 3, 7)])
+def test_moe_permute_with_routes_to_no_expert(T, k, E):
+    """Ids outside [0, E) get no row: their position is -1 and the rows nobody claimed hold -1
+    (both the short-step and the long-step kernels)."""
+    g = torch.Generator().manual_seed(T)
+    ids = torch.randint(0, E, (T, k), generator=g).to(torch.int32)
+    ids[T // 2, 0] = -1
+    ids[T - 1, k - 1] = E
+    ids[0, 0] = E + 5
+    flat = ids.reshape(-1)
+    valid = (flat >= 0) & (flat < E)
+    order = torch.argsort(torch.where(valid, flat, torch.full_like(flat, E)), stable=True)
+    n_valid = int(valid.sum())
+    want_routes = torch.cat([order[:n_valid].to(torch.int32), torch.full((flat.numel() - n_valid,), -1, dtype=torch.int32)])
+    want_pos = torch.full((flat.numel(),), -1, dtype=torch.int32)
+    want_pos[order[:n_valid]] = torch.arange(n_valid, dtype=torch.int32)
+    want_counts = torch.bincount(flat[valid].long(), minlength=E).to(torch.int32)
+    counts = torch.empty(E, dtype=torch.int32, device=DEV)
+    off = torch.empty(E + 1, dtype=torch.int32, device=DEV)
+    routes = torch.empty(T * k, dtype=torch.int32, device=DEV)
+    pos = torch.empty(T * k, dtype=torch.int32, device=DEV)
+    ops.moe_permute(ids.to(DEV), E, counts, off, routes, pos)
+    assert torch.equal(counts.cpu(), want_counts)
+    assert torch.equal(off.cpu()[1:], torch.cumsum(want_counts, 0).to(torch.int32)) and off[0].item() == 0
+    assert torch.equal(routes.cpu(), want_routes)
+    assert torch.equal(pos.cpu(), want_pos)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
