@@ -57,6 +57,15 @@ int ftk_paged_attention(const void* q, const void* k_slab, const void* v_slab, i
                         const int32_t* items, int n_items, float* part_o, float* part_ml, int n_slots,
                         void* out, int n_q_heads, int n_kv_heads, int head_dim, int page_size,
                         int num_pages, int tile_rows, float scale, int window, void* stream);
+// Long steps in bfloat16 on tcgen05: tiles of 128 query rows (plan the items with tile_rows = 128), head
+// size 128, pages of a multiple of 16 tokens; n_tokens = rows of q.  ftk_attention_tc_fits says whether
+// the sizes are taken.
+int ftk_attention_tc_fits(int head_dim, int page_size, int group);
+int ftk_paged_attention_tc(const void* q, const void* k_slab, const void* v_slab, const int32_t* block_table,
+                           int bt_stride, const int32_t* seg_info, int n_segs, const int32_t* items, int n_items,
+                           float* part_o, float* part_ml, int n_slots, void* out, int n_tokens, int n_q_heads,
+                           int n_kv_heads, int head_dim, int page_size, int num_pages, float scale, int window,
+                           void* stream);
 int ftk_paged_attention_sparse(const void* q, const void* k_slab, const void* v_slab, int dtype,
                                const int32_t* block_table, int bt_stride, const int32_t* seg_info, int n_segs,
                                const int32_t* items, int n_items, float* part_o, float* part_ml, int n_slots,

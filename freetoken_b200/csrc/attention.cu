@@ -855,7 +855,66 @@ static int launch_bf16(const AttnParams& p, cudaStream_t s) {
 
 }  // namespace ftk
 
+#include "attention_tc.cuh"
+
 using namespace ftk;
+
+// Status of the tensor-core attention kernel's bounded waits (merged into ftk_read_status).
+int ftk_attention_tc_status(int* out) {
+  int host[4] = {0, 0, 0, 0};
+  if (cudaMemcpyFromSymbol(host, g_attn_status, sizeof(host)) != cudaSuccess) return 2;
+  out[0] = host[0];
+  out[1] = host[1];
+  if (host[0]) {
+    int zero[4] = {0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_attn_status, zero, sizeof(zero));
+  }
+  return 0;
+}
+
+extern "C" int ftk_attention_tc_fits(int head_dim, int page_size, int group) {
+  return attention_tc_fits(head_dim, page_size, group) ? 1 : 0;
+}
+
+// Long steps in bfloat16 on the tensor-core kernel: tiles of 128 query rows (`items` planned for
+// tile_rows = 128); `n_tokens` is the number of rows of q.
+extern "C" int ftk_paged_attention_tc(const void* q, const void* k_slab, const void* v_slab,
+                                      const int32_t* block_table, int bt_stride, const int32_t* seg_info,
+                                      int n_segs, const int32_t* items, int n_items, float* part_o, float* part_ml,
+                                      int n_slots, void* out, int n_tokens, int n_q_heads, int n_kv_heads,
+                                      int head_dim, int page_size, int num_pages, float scale, int window,
+                                      void* stream) {
+  FTK_REQUIRE(q && k_slab && v_slab && block_table && seg_info && items && out, "paged_attention_tc: null pointer");
+  FTK_REQUIRE(n_q_heads >= 1 && n_kv_heads >= 1 && n_q_heads % n_kv_heads == 0, "paged_attention_tc: %d query heads, %d KV heads",
+              n_q_heads, n_kv_heads);
+  FTK_REQUIRE(attention_tc_fits(head_dim, page_size, n_q_heads / n_kv_heads),
+              "paged_attention_tc: head size %d, pages of %d, %d heads per KV head: takes head size 128, pages of a "
+              "multiple of 16, at most 128 heads per KV head", head_dim, page_size, n_q_heads / n_kv_heads);
+  FTK_REQUIRE(n_tokens >= 1 && n_items >= 0 && n_segs >= 1 && num_pages >= 1 && bt_stride >= 1 && window >= 0,
+              "paged_attention_tc: bad sizes");
+  FTK_REQUIRE(n_slots == 0 || (part_o && part_ml), "paged_attention_tc: split tiles need scratch");
+  FTK_REQUIRE((((uintptr_t)q | (uintptr_t)k_slab | (uintptr_t)v_slab | (uintptr_t)out) & 15) == 0,
+              "paged_attention_tc: 16-byte aligned tensors only");
+  if (n_items == 0) return 0;
+  AttnParams p;
+  p.q = q; p.k = k_slab; p.v = v_slab; p.out = out;
+  p.block_table = block_table; p.bt_stride = bt_stride;
+  p.seg_info = seg_info; p.n_segs = n_segs; p.items = items; p.n_items = n_items;
+  p.part_o = part_o; p.part_ml = part_ml; p.n_slots = n_slots;
+  p.Hq = n_q_heads; p.Hkv = n_kv_heads; p.G = n_q_heads / n_kv_heads; p.D = head_dim; p.P = page_size;
+  p.num_pages = num_pages; p.tile_rows = kTcRows; p.scale = scale; p.window = window;
+  p.sel = nullptr; p.sel_stride = 0; p.block_size = 0; p.arrivals = nullptr;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int rc = launch_attention_tc(p, n_tokens, s);
+  FTK_REQUIRE(rc == 0, "paged_attention_tc: cannot set up the kernel (%d)", rc);
+  FTK_LAUNCH_CHECK("paged_attention_tc");
+  if (n_slots > 0) {
+    dim3 grid(n_items, n_kv_heads);
+    FTK_LAUNCH(attention_merge_kernel<__nv_bfloat16>, grid, 128, 0, s, p);
+    FTK_LAUNCH_CHECK("paged_attention_tc merge");
+  }
+  return 0;
+}
 
 static int paged_attention_impl(const void* q, const void* k_slab, const void* v_slab, int dtype,
                                 const int32_t* block_table, int bt_stride, const int32_t* seg_info,

@@ -1,0 +1,438 @@
+// Paged causal attention for long steps on the 5th-generation tensor cores (tcgen05), bfloat16,
+// head size 128.  Included by attention.cu after AttnParams / Item / load_item.
+//
+// A tile is 128 query rows: the `group` query heads of one KV head for 128 / group consecutive tokens
+// of one segment, so a key/value tile is read once for all the heads that share it.  Keys come in
+// tiles of 128.  Per key tile:
+//   S = Q K^T        tcgen05.mma, Q [128 x 128] and K [128 keys x 128] K-major in shared memory
+//                    (TMA, 128-byte swizzle; K straight from the pages, 16 keys per box), S in TMEM
+//                    (two buffers, so the next tile's product runs under this tile's softmax);
+//   softmax          one thread per row (its TMEM lane): scale, mask, running maximum, exp2, sum; the
+//                    probabilities go to shared memory as bfloat16 in the A-operand layout.  The
+//                    running maximum is only moved when it grew by more than 8 (a factor 256), so the
+//                    accumulator is rescaled a few times per row, not once per tile;
+//   O += P V         tcgen05.mma with V as the MN-major B operand (the page rows as they are), O in TMEM.
+// One CTA = 6 warps: warp 0 issues the TMA loads, warp 1 the MMAs, warps 2-5 are the softmax (and the
+// epilogue: O / l to the output, or the partial sums of a split tile for the merge kernel).
+// Every wait is bounded; a timeout records a code in g_attn_status, lets copies land, frees TMEM, returns.
+// Key rows past the end of the request are never multiplied as they lie in memory (they may hold
+// anything): whole 16-key boxes past the end are not loaded (the stages start zeroed), and the rows
+// past the end inside the last box are zeroed in shared memory before the product.
+//
+// The reference's prefill attention is a Triton kernel (python/freetoken/kernel/triton/attention.py:469-880).
+#pragma once
+#include "tc_common.cuh"
+
+namespace ftk {
+
+__device__ int g_attn_status[4];  // [0] first error code, [1] block; 0 = fine
+
+constexpr int kTcRows = 128;
+constexpr int kTcKeys = 128;
+constexpr int kTcD = 128;
+constexpr int kTcThreads = 192;
+constexpr int kTcHalf = 128 * 64 * 2;       // bytes of a [128 rows x 64 elements] swizzle-atom column
+constexpr int kTcTile = 2 * kTcHalf;        // a [128 x 128] bfloat16 tile
+constexpr int kTcSmem = 6 * kTcTile + 1024; // Q, K x2, V x2, P
+
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(addr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t addr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(addr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])),
+        "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])),
+        "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])),
+        "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])),
+        "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Shared-memory descriptor of an MN-major operand with 128-byte swizzle: 64 elements of the MN side
+// are contiguous (128 bytes), eight k rows make a 1024-byte group (stride byte offset), the next 64
+// MN elements lie `lbo` bytes further (leading byte offset).
+__device__ __forceinline__ uint64_t smem_desc_mn(uint32_t addr, uint32_t lbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3fff);
+  d |= (uint64_t)((lbo >> 4) & 0x3fff) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+__device__ __forceinline__ float tc_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t tc_pack(float lo, float hi) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+
+__global__ void __launch_bounds__(kTcThreads)
+attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, AttnParams p) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ unsigned char dyn_smem[];
+  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, pv_done;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // long tiles first: the grid runs in block order and the tiles of a segment grow with the token index
+  const Item it = load_item(p, (int)gridDim.x - 1 - (int)blockIdx.x);
+  const int kvh = blockIdx.y;
+  const uint32_t base = (smem_addr(dyn_smem) + 1023u) & ~1023u;
+  unsigned char* tiles = dyn_smem + (base - smem_addr(dyn_smem));
+  const uint32_t q_s = base, k_s = base + kTcTile, v_s = base + 3 * kTcTile, p_s = base + 5 * kTcTile;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4);
+    }
+    mbar_init(&p_full, 4);
+    mbar_init(&pv_done, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(&tmem_slot, 512);
+  // the value stages start zeroed: boxes past the end of the request are not loaded
+  for (int i = threadIdx.x; i < 2 * kTcTile / 16; i += blockDim.x)
+    reinterpret_cast<uint4*>(tiles + 3 * kTcTile)[i] = make_uint4(0u, 0u, 0u, 0u);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  volatile int* abortp = &abort_flag;
+  const int n_tiles = it.ok ? (it.ke - it.kb + kTcKeys - 1) / kTcKeys : 0;
+  const int G = p.G;
+  auto fail = [&](int code) {
+    atomicCAS(&g_attn_status[0], 0, code);
+    abort_flag = 1;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_tiles > 0) {
+      mbar_expect_tx(&q_full, (uint32_t)(2 * 128 * G * (kTcRows / G)));  // two boxes of (64, group, tokens per tile)
+      for (int h = 0; h < 2; ++h)  // (d, head, token): rows land as token-major, head-minor
+        tma_load_3d(tiles + h * kTcHalf, &map_q, &q_full, h * 64, kvh * G, it.q_start + it.tok0);
+      const int32_t* bt = p.block_table + (size_t)it.bt_row * p.bt_stride;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int st = j & 1;
+        const uint32_t par = ((j >> 1) & 1) ^ 1;
+        const int key0 = it.kb + j * kTcKeys;
+        const int n_box = min(8, (it.ke - key0 + 15) >> 4);  // boxes of 16 keys that hold keys of the request
+        int rows[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int key = key0 + 16 * i;
+          int page = 0;
+          if (i < n_box) {
+            const int slot = key / p.P;
+            page = slot < p.bt_stride ? bt[slot] : 0;
+            if (page < 0 || page >= p.num_pages) page = 0;
+          }
+          rows[i] = (page * p.Hkv + kvh) * p.P + key % p.P;
+        }
+        if (!mbar_wait(&k_empty[st], par, abortp)) { fail(201); break; }
+        mbar_expect_tx(&k_full[st], (uint32_t)n_box * 2 * 2048);
+        for (int i = 0; i < n_box; ++i)
+          for (int h = 0; h < 2; ++h)
+            tma_load_2d(tiles + kTcTile + st * kTcTile + h * kTcHalf + i * 2048, &map_k, &k_full[st], h * 64, rows[i]);
+        if (!mbar_wait(&v_empty[st], par, abortp)) { fail(202); break; }
+        mbar_expect_tx(&v_full[st], (uint32_t)n_box * 2 * 2048);
+        for (int i = 0; i < n_box; ++i)
+          for (int h = 0; h < 2; ++h)
+            tma_load_2d(tiles + 3 * kTcTile + st * kTcTile + h * kTcHalf + i * 2048, &map_v, &v_full[st], h * 64, rows[i]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (lane 0); the warp zeroes value rows past the end
+    constexpr uint32_t idesc_qk = instr_desc(kTcKeys);
+    constexpr uint32_t idesc_pv = instr_desc(kTcD) | (1u << 16);  // B (values) MN-major
+    bool ok = n_tiles > 0;
+    if (ok && !mbar_wait(&q_full, 0, abortp)) {
+      if (lane == 0) fail(203);
+      ok = false;
+    }
+    for (int j = 0; j <= n_tiles && ok; ++j) {
+      if (j < n_tiles) {
+        const int st = j & 1;
+        const uint32_t par = (j >> 1) & 1;
+        if (!mbar_wait(&k_full[st], par, abortp) || !mbar_wait(&s_empty[st], par ^ 1, abortp)) {
+          if (lane == 0) fail(204);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t d = tmem + (uint32_t)(st * kTcKeys);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {  // 16 elements of the head dimension per MMA
+            const uint64_t a = smem_desc(q_s + (kk >> 2) * kTcHalf) + 2 * (kk & 3);
+            const uint64_t b = smem_desc(k_s + st * kTcTile + (kk >> 2) * kTcHalf) + 2 * (kk & 3);
+            tc_mma(d, a, b, idesc_qk, kk != 0);
+          }
+          tc_commit(&k_empty[st]);
+          tc_commit(&s_full[st]);
+        }
+        __syncwarp();
+      }
+      if (j >= 1) {
+        const int i = j - 1, st = i & 1;
+        if (!mbar_wait(&p_full, (uint32_t)(i & 1), abortp) || !mbar_wait(&v_full[st], (uint32_t)((i >> 1) & 1), abortp)) {
+          if (lane == 0) fail(205);
+          ok = false;
+          break;
+        }
+        const int key0 = it.kb + i * kTcKeys;
+        const int live = it.ke - key0;  // keys of the request in this tile
+        if (live < kTcKeys && (live & 15)) {
+          // the rows past the end inside the last loaded box: zero, whatever the page holds there
+          const int r0 = live, r1 = (live + 15) & ~15;
+          for (int x = lane; x < (r1 - r0) * 2 * 8; x += 32) {
+            const int r = r0 + x / 16, h = (x / 8) & 1, c = x & 7;
+            *reinterpret_cast<uint4*>(tiles + 3 * kTcTile + st * kTcTile + h * kTcHalf + r * 128 + c * 16) =
+                make_uint4(0u, 0u, 0u, 0u);
+          }
+          fence_async_smem();
+        }
+        __syncwarp();
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t d = tmem + 2 * kTcKeys;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {  // 16 keys per MMA
+            const uint64_t a = smem_desc(p_s + (kk >> 2) * kTcHalf) + 2 * (kk & 3);
+            const uint64_t b = smem_desc_mn(v_s + st * kTcTile + kk * 2048, kTcHalf);
+            tc_mma(d, a, b, idesc_pv, (i | kk) != 0);
+          }
+          tc_commit(&v_empty[st]);
+          tc_commit(&pv_done);
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax and epilogue (warps 2..5), one row per thread
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;           // row of the tile = TMEM lane
+    const int R = it.ok ? it.ntok * G : 0;
+    const int pos_base = it.kv_len - it.q_len + it.tok0;
+    const int qpos = r < R ? pos_base + r / G : -1;
+    const int lo = p.window > 0 ? qpos - p.window + 1 : 0;
+    const float sl2 = p.scale * 1.4426950408889634f;
+    const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int sb = j & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb], (uint32_t)((j >> 1) & 1), abortp))) {
+        if (lane == 0) fail(206);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t s_addr = lane_addr + (uint32_t)(sb * kTcKeys);
+      const int key0 = it.kb + j * kTcKeys;
+      // keys every row of the warp may read in full need no mask
+      const int hi = min(it.ke - 1, qpos);  // last key this row may read
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float v[32];
+        tmem_ld32(s_addr + c * 32, v);
+        const int k0 = key0 + c * 32;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const bool valid = k0 + i <= hi && k0 + i >= lo;
+          mx = fmaxf(mx, valid ? v[i] * sl2 : -INFINITY);
+        }
+      }
+      // move the running maximum only when it grew by more than 8 (or is not set yet)
+      float alpha = 1.f;
+      if (mx > m_used + 8.f || (m_used == -INFINITY && mx > -INFINITY)) {
+        alpha = m_used == -INFINITY ? 0.f : tc_exp2(m_used - mx);
+        m_used = mx;
+      }
+      l *= alpha;
+      const bool rescale = __any_sync(0xffffffffu, alpha != 1.f) && j > 0;
+      if (j > 0) {  // the product before this one has read P and updated O
+        if (!__all_sync(0xffffffffu, mbar_wait(&pv_done, (uint32_t)((j - 1) & 1), abortp))) {
+          if (lane == 0) fail(207);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+      }
+      if (rescale) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          float o[32];
+          tmem_ld32(lane_addr + 2 * kTcKeys + c * 32, o);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= alpha;
+          tmem_st32(lane_addr + 2 * kTcKeys + c * 32, o);
+        }
+      }
+      const float mb = m_used == -INFINITY ? 0.f : m_used;
+      float sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float v[32];
+        tmem_ld32(s_addr + c * 32, v);
+        const int k0 = key0 + c * 32;
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const bool v0 = k0 + i <= hi && k0 + i >= lo, v1 = k0 + i + 1 <= hi && k0 + i + 1 >= lo;
+          const float p0 = v0 ? tc_exp2(v[i] * sl2 - mb) : 0.f;
+          const float p1 = v1 ? tc_exp2(v[i + 1] * sl2 - mb) : 0.f;
+          sum += p0 + p1;
+          pk[i >> 1] = tc_pack(p0, p1);
+        }
+        // row r of the [128 x 64]-key atom (c >> 1), 16-byte chunks (c & 1) * 4 .. + 3, swizzled by the row
+        unsigned char* prow = tiles + 5 * kTcTile + (c >> 1) * kTcHalf + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int chunk = (c & 1) * 4 + q4;
+          *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) =
+              make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+        }
+      }
+      l += sum;
+      fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&s_empty[sb]);
+        mbar_arrive(&p_full);
+      }
+    }
+    // ---- epilogue
+    if (ok && n_tiles > 0) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&pv_done, (uint32_t)((n_tiles - 1) & 1), abortp))) {
+        if (lane == 0) fail(208);
+        ok = false;
+      }
+      tc_fence_after();
+    }
+    if (ok && it.ok) {
+      const bool live = n_tiles > 0;
+      const int tok = it.q_start + it.tok0 + r / G;
+      if (it.nsplit == 1) {
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + ((size_t)tok * p.Hq + kvh * G + r % G) * kTcD;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          float o[32];
+          if (live) tmem_ld32(lane_addr + 2 * kTcKeys + c * 32, o);
+          if (r < R) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 pk;
+              pk.x = tc_pack(live ? o[8 * q4] * inv : 0.f, live ? o[8 * q4 + 1] * inv : 0.f);
+              pk.y = tc_pack(live ? o[8 * q4 + 2] * inv : 0.f, live ? o[8 * q4 + 3] * inv : 0.f);
+              pk.z = tc_pack(live ? o[8 * q4 + 4] * inv : 0.f, live ? o[8 * q4 + 5] * inv : 0.f);
+              pk.w = tc_pack(live ? o[8 * q4 + 6] * inv : 0.f, live ? o[8 * q4 + 7] * inv : 0.f);
+              *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = pk;
+            }
+          }
+        }
+      } else {
+        const size_t slot = ((size_t)(it.base + it.split) * p.Hkv + kvh) * p.tile_rows + r;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          float o[32];
+          if (live) tmem_ld32(lane_addr + 2 * kTcKeys + c * 32, o);
+          if (r < R) {
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4)
+              *reinterpret_cast<float4*>(p.part_o + slot * kTcD + c * 32 + q4 * 4) =
+                  live ? make_float4(o[4 * q4], o[4 * q4 + 1], o[4 * q4 + 2], o[4 * q4 + 3]) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+        if (r < R) {
+          p.part_ml[slot * 2] = m_used == -INFINITY ? -INFINITY : m_used * 0.6931471805599453f;
+          p.part_ml[slot * 2 + 1] = l;
+        }
+      }
+    }
+  }
+  // ---------------------------------------------------------------- teardown
+  if (abort_flag) {
+    if (threadIdx.x == 0) g_attn_status[1] = blockIdx.x;
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);  // let copies in flight land before the CTA leaves
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// What the kernel takes: bfloat16 heads of 128, pages of a multiple of 16 tokens, at most 128 query
+// heads per KV head, no block selection.
+inline bool attention_tc_fits(int head_dim, int page_size, int group) {
+  return head_dim == kTcD && page_size >= 16 && page_size % 16 == 0 && group >= 1 && group <= kTcRows;
+}
+
+inline int launch_attention_tc(const AttnParams& p, int n_tokens, cudaStream_t s) {
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem) != cudaSuccess)
+      return 2;
+    configured = true;
+  }
+  CUtensorMap mq, mk, mv;
+  {
+    // queries [T, Hq, D] seen as (d, head, token); a box is (64, group, tokens per tile)
+    const uint64_t dims[3] = {(uint64_t)kTcD, (uint64_t)p.Hq, (uint64_t)n_tokens};
+    const uint64_t strides[2] = {(uint64_t)kTcD * 2, (uint64_t)p.Hq * kTcD * 2};
+    const uint32_t box[3] = {64, (uint32_t)p.G, (uint32_t)(kTcRows / p.G)};
+    if (!make_map(&mq, p.q, 3, dims, strides, box)) return 4;
+  }
+  {
+    // a slab [pages, Hkv, P, D] seen as rows of D; a box is 16 rows of one page x 64 elements
+    const uint64_t dims[2] = {(uint64_t)kTcD, (uint64_t)p.num_pages * p.Hkv * p.P};
+    const uint64_t strides[1] = {(uint64_t)kTcD * 2};
+    const uint32_t box[2] = {64, 16};
+    if (!make_map(&mk, p.k, 2, dims, strides, box) || !make_map(&mv, p.v, 2, dims, strides, box)) return 4;
+  }
+  dim3 grid(p.n_items, p.Hkv);
+  FTK_LAUNCH(attention_tc_kernel, grid, kTcThreads, kTcSmem, s, mq, mk, mv, p);
+  return 0;
+}
+
+}  // namespace ftk

@@ -59,6 +59,9 @@ _SIGNATURES = {
                             ctypes.POINTER(_Section), _vp],
     "ftk_paged_attention": [_vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
                             _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "ftk_attention_tc_fits": [_i, _i, _i],
+    "ftk_paged_attention_tc": [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
+                               _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "ftk_paged_attention_sparse": [_vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
                                    _i, _i, _i, _i, _i, _i, _f, _vp, _i, _i, _vp],
     "ftk_sparse_select": [_vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
@@ -342,6 +345,18 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
     if part_o is not None and (part_o.shape[1:] != (Hkv, tile_rows, D) or part_ml is None
                                or part_ml.shape != (n_slots, Hkv, tile_rows, 2)):
         raise KernelError("paged_attention: scratch shapes do not match tile_rows / heads")
+    if tile_rows == 128:  # long bfloat16 steps: the tcgen05 kernel
+        if sel is not None or window or q.dtype != torch.bfloat16:
+            raise KernelError("paged_attention: 128-row tiles take bfloat16 without window or block selection")
+        _check(_lib().ftk_paged_attention_tc(
+            _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"),
+            _dev(block_table, "block_table", torch.int32), block_table.shape[1],
+            _dev(seg_info, "seg_info", torch.int32), n_segs,
+            _dev(items, "items", torch.int32), n_items,
+            _dev(part_o, "part_o", torch.float32), _dev(part_ml, "part_ml", torch.float32), n_slots,
+            _dev(out, "out"), T, Hq, Hkv, D, P, pages, float(scale), 0, _stream()),
+            "paged_attention (tcgen05)", 2 if n_slots else 1)
+        return
     if sel is not None:
         if sel.dim() != 3 or sel.shape[0] < T or sel.shape[1] != Hkv or block_size < 1:
             raise KernelError("paged_attention: sel must be [T, Hkv, topk] with a positive block_size")
@@ -363,6 +378,11 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
         _dev(part_o, "part_o", torch.float32), _dev(part_ml, "part_ml", torch.float32), n_slots,
         _dev(out, "out"), Hq, Hkv, D, P, pages, tile_rows, float(scale),
         int(window) if window else 0, _stream()), "paged_attention", 2 if n_slots else 1)
+
+
+def attention_tc_fits(head_dim: int, page_size: int, group: int) -> bool:
+    """Whether the tcgen05 attention kernel (tiles of 128 query rows) takes these sizes."""
+    return bool(_lib().ftk_attention_tc_fits(head_dim, page_size, group))
 
 
 def sparse_select(iq: torch.Tensor, ik_slab: torch.Tensor, block_table: torch.Tensor, seg_info: torch.Tensor,

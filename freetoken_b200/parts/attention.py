@@ -23,11 +23,19 @@ from .base import MIXERS, BuildEnv, Mixer, StepState
 from .rope import shared_position
 
 
-def attention_tile_rows(dtype: torch.dtype, decode_only: bool = False, group: int = 1) -> int:
+TC_MIN_TOKENS = 128  # shortest step that goes to the tcgen05 attention kernel
+
+
+def attention_tile_rows(dtype: torch.dtype, decode_only: bool = False, group: int = 1, n_tokens: int = 0,
+                        head_dim: int = 0, page_size: int = 0, window: Optional[int] = None) -> int:
     """Query rows (tokens x group heads) one attention CTA handles: 16 in the 32-bit kernel and in
-    the bfloat16 kernel for steps of single decoded tokens, 64 in the bfloat16 kernel otherwise."""
+    the bfloat16 kernel for steps of single decoded tokens; 128 (the tcgen05 kernel) for long bfloat16
+    steps whose sizes it takes; 64 in the bfloat16 mma.sync kernel otherwise."""
     if dtype != torch.bfloat16 or (decode_only and group <= 16):
         return 16
+    if (not decode_only and n_tokens >= TC_MIN_TOKENS and window is None and head_dim and page_size
+            and ops.attention_tc_fits(head_dim, page_size, group)):
+        return 128
     return 64
 
 
@@ -84,16 +92,21 @@ class GQAttention(Mixer):
                             ("v", self.n_kv_heads, self.head_dim)), self.window)
 
     # ------------------------------------------------------------------ step
-    def tile_rows(self, decode_only: bool) -> int:
-        return attention_tile_rows(self.env.dtype, decode_only, self.group)
+    def tile_rows(self, decode_only: bool, n_tokens: int = 0, page_size: int = 0) -> int:
+        return attention_tile_rows(self.env.dtype, decode_only, self.group, n_tokens, self.head_dim, page_size,
+                                   self.window)
 
-    def plan_key(self, decode_only: bool = False):
-        return ("attention", self.group, self.tile_rows(decode_only), self.window, self.n_kv_heads, self.head_dim)
+    def plan_key(self, decode_only: bool = False, n_tokens: int = 0, page_size: int = 0):
+        return ("attention", self.group, self.tile_rows(decode_only, n_tokens, page_size), self.window,
+                self.n_kv_heads, self.head_dim)
 
     def prepare(self, builder) -> None:
         """Ask the step for the work list this mixer's attention kernel runs from."""
-        builder.attention_plan(self.group, self.tile_rows(builder.decode_only), self.window, self.n_kv_heads,
-                               self.head_dim)
+        n_tokens = sum(q for q, _ in builder.seg_lens)
+        page_size = builder.engine.config.page_size if builder.engine is not None else 0
+        # forward() of the same step runs the kernel this work list was made for
+        self._step_plan = builder.attention_plan(self.group, self.tile_rows(builder.decode_only, n_tokens, page_size),
+                                                 self.window, self.n_kv_heads, self.head_dim)
 
     def forward(self, h: torch.Tensor, step: StepState, cache: Any, writes_cache: bool) -> torch.Tensor:
         T = h.shape[0]
@@ -115,11 +128,11 @@ class GQAttention(Mixer):
                                  slab=cache.slabs["v"], slot_map=cache.slot_map))
         ops.norm_rope_store(qkv, self.head_dim, self.rotary_dim, step.positions,
                             self.position.table(), self.eps, self.gemma, sections)
-        plan = step.attention_plans[self.plan_key(step.decode_only)]
+        plan = step.attention_plans[self._step_plan]
         o = ws.get("attn.o", (T, self.n_heads, self.head_dim), dt, (cap, self.n_heads, self.head_dim))
         ops.paged_attention(q, cache.slabs["k"], cache.slabs["v"], cache.block_table, step.seg_info,
                             len(step.segments), plan.items_dev, plan.n_items, plan.part_o, plan.part_ml,
-                            o, self.tile_rows(step.decode_only), self.scale, self.window)
+                            o, self._step_plan[2], self.scale, self.window)
         out = ws.get("attn.out", (T, self.hidden), dt, (cap, self.hidden))
         ops.linear(o.view(T, self.q_dim), self.params["o_proj.weight"], out)
         return out

@@ -17,7 +17,7 @@ from plain.m3_plain import PlainM3, sample_reference
 from tiny_configs import ALL
 
 pytestmark = pytest.mark.gpu
-PAGE = {"A": 4, "B": 8, "C": 16, "D": 4}
+PAGE = {"A": 4, "B": 8, "C": 16, "D": 4, "E": 16}
 CONFIGS = ["A", "B", "C", "D"]
 DTYPES = ["float32", "bfloat16"]
 
@@ -97,6 +97,28 @@ def test_long_decoding_and_first_tokens(dtype, world):
     for n in (1, 2, 3):
         check(replay_whole(eng, f"first{n}", toks[:n]), ref, dtype, margins, f"first {n} tokens")
     check(replay_cuts(eng, "ones", toks[:5], [1, 1, 1, 1, 1]), ref, dtype, margins, "from the first token on")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_steps_on_the_tensor_core_attention(dtype, world):
+    """Heads of 128 and pages of 16: steps of 128 tokens and more run the tcgen05 attention kernel in
+    bfloat16 (the other kernels otherwise).  Whole prompts, a prompt in two long portions, and long
+    portions beside decoded tokens of other requests, all against the plain model."""
+    _, plain, eng = world("E", dtype, pages=64, max_step=320)
+    V = plain.cfg.vocab
+    toks = tokens_for(V, 300, 77)
+    ref, margins = plain.logits(toks), plain.router_margins(toks)
+    check(replay_whole(eng, "w", toks), ref, dtype, margins, "300 tokens whole")
+    check(replay_cuts(eng, "c", toks, [170, 129]), ref, dtype, margins, "two long portions and one token")
+    seqs = {"a": tokens_for(V, 200, 78), "b": tokens_for(V, 150, 79), "c": tokens_for(V, 40, 80)}
+    sched = [{"c": 30}, {"a": 190, "c": 1}, {"b": 140, "c": 1, "a": 1}] + [{"a": 1, "b": 1, "c": 1}] * 10
+    got = replay_mixed(eng, seqs, sched)
+    for r, t in seqs.items():
+        check(got[r], plain.logits(t), dtype, plain.router_margins(t), f"mixed with long portions {r}")
+    if dtype == "bfloat16":
+        from freetoken_b200.kernels import ops
+
+        assert ops.attention_tc_fits(128, 16, 3) and ops.read_status() == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -219,6 +219,62 @@ def test_attention_mixed_batch(dtype, Hq, Hkv, D, P):
     torch.testing.assert_close(out.float(), want.float(), **attn_tol(dtype))
 
 
+@pytest.mark.parametrize("Hq,Hkv,P", [(12, 2, 16), (48, 8, 16), (5, 5, 32), (7, 1, 64), (16, 1, 16), (3, 1, 48)])
+def test_attention_tensor_core_kernel(Hq, Hkv, P):
+    """The tcgen05 kernel (tiles of 128 query rows, head size 128) on a mixed batch: whole prompts,
+    portions with earlier keys, single tokens, lengths on and off the edges of its 128-key tiles and
+    16-key boxes; every unwritten cache slot holds NaN."""
+    assert ops.attention_tc_fits(128, P, Hq // Hkv)
+    assert not ops.attention_tc_fits(64, P, Hq // Hkv) and not ops.attention_tc_fits(128, 8, 1)
+    segs = [(300, 300), (1, 1), (128, 128), (17, 273), (1, 130), (129, 257), (40, 40), (2, 64), (250, 1000), (1, 129)]
+    out, want, _ = run_attention(torch.bfloat16, Hq, Hkv, 128, P, segs, None, tile=128)
+    assert not torch.isnan(out).any()
+    torch.testing.assert_close(out.float(), want.float(), **attn_tol(torch.bfloat16))
+    assert ops.read_status() == 0
+
+
+def test_attention_tensor_core_kernel_split_keys():
+    """One long request alone: its tiles are split along the keys and merged."""
+    segs = [(140, 3000)]
+    out, want, plan = run_attention(torch.bfloat16, 12, 2, 128, 16, segs, None, force_split=True, tile=128)
+    assert plan.n_slots > 0
+    assert not torch.isnan(out).any()
+    torch.testing.assert_close(out.float(), want.float(), **attn_tol(torch.bfloat16))
+    assert ops.read_status() == 0
+
+
+def test_attention_tensor_core_kernel_finds_a_far_key():
+    """One key among two thousand carries the whole weight: scale one query and that key so that its
+    score stands out; the output must be that key's value row."""
+    torch.manual_seed(3)
+    Hq, Hkv, D, P, n = 6, 1, 128, 16, 2048
+    segs = [(n, n)]
+    G = Hq // Hkv
+    pages = n // P + 1
+    ks = torch.randn(pages, Hkv, P, D).mul(0.1)
+    vs = torch.randn(pages, Hkv, P, D)
+    q = torch.randn(n, Hq, D).mul(0.1)
+    far, tok = 37, 1900
+    direction = torch.randn(D)
+    direction = direction / direction.norm()
+    ks[1 + far // P, 0, far % P] = direction * 30
+    q[tok, :] = direction * 30
+    bt = torch.arange(1, pages, dtype=torch.int32).view(1, -1).to(DEV)
+    seg = torch.tensor([[0, n, n, 0]], dtype=torch.int32, device=DEV)
+    plan = build_plan(segs, G, 128, None, Hkv)
+    items = torch.from_numpy(plan.items).to(DEV)
+    q, ks, vs = q.to(torch.bfloat16).to(DEV), ks.to(torch.bfloat16).to(DEV), vs.to(torch.bfloat16).to(DEV)
+    out = torch.empty_like(q)
+    po = pm = None
+    if plan.n_slots:  # one request alone on the GPU: its tiles are split along the keys
+        po = torch.empty(plan.n_slots, Hkv, 128, D, dtype=torch.float32, device=DEV)
+        pm = torch.empty(plan.n_slots, Hkv, 128, 2, dtype=torch.float32, device=DEV)
+    ops.paged_attention(q, ks, vs, bt, seg, 1, items, plan.n_items, po, pm, out, 128, D ** -0.5, None)
+    want = vs[1 + far // P, 0, far % P].float()
+    for h in range(Hq):
+        torch.testing.assert_close(out[tok, h].float(), want, rtol=2e-2, atol=2e-2)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("fixed", [None, 5])
 def test_attention_split_keys(dtype, fixed):

@@ -8,6 +8,7 @@ C: the reference's real options on small sizes: swigluoai, one dense prefix laye
    expert, routed_scaling_factor 2, 7 q / 1 kv heads of 48 (no power of two anywhere).
 D: block-sparse attention layers after one full layer (index heads, 8-token blocks, top-3), two
    experts that every token uses.
+E: A with 6 q / 2 kv heads of 128 and pages of 16 tokens: long steps run the tensor-core attention.
 """
 
 from __future__ import annotations
@@ -66,4 +67,11 @@ TINY_D = dict(copy.deepcopy(TINY_A), **{
     },
 })
 
-ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+# E: heads of 128 with 3 query heads per KV head and pages of 16, the sizes the tensor-core attention
+# kernel takes; everything else small.
+TINY_E = dict(copy.deepcopy(TINY_A), **{
+    "hidden_size": 96, "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 128, "rotary_dim": 64,
+    "max_position_embeddings": 1024, "num_local_experts": 4, "num_experts_per_tok": 2, "intermediate_size": 48,
+})
+
+ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
