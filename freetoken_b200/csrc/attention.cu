@@ -890,8 +890,9 @@ extern "C" int ftk_paged_attention_tc(const void* q, const void* k_slab, const v
   FTK_REQUIRE(attention_tc_fits(head_dim, page_size, n_q_heads / n_kv_heads),
               "paged_attention_tc: head size %d, pages of %d, %d heads per KV head: takes head size 128, pages of a "
               "multiple of 16, at most 128 heads per KV head", head_dim, page_size, n_q_heads / n_kv_heads);
-  FTK_REQUIRE(n_tokens >= 1 && n_items >= 0 && n_segs >= 1 && num_pages >= 1 && bt_stride >= 1 && window >= 0,
+  FTK_REQUIRE(n_tokens >= 1 && n_items >= 0 && n_segs >= 1 && num_pages >= 1 && bt_stride >= 1,
               "paged_attention_tc: bad sizes");
+  FTK_REQUIRE(window == 0, "paged_attention_tc: layers with a window run on the other kernels");
   FTK_REQUIRE(n_slots == 0 || (part_o && part_ml), "paged_attention_tc: split tiles need scratch");
   FTK_REQUIRE((((uintptr_t)q | (uintptr_t)k_slab | (uintptr_t)v_slab | (uintptr_t)out) & 15) == 0,
               "paged_attention_tc: 16-byte aligned tensors only");

@@ -12,8 +12,8 @@
 //                    running maximum is only moved when it grew by more than 8 (a factor 256), so the
 //                    accumulator is rescaled a few times per row, not once per tile;
 //   O += P V         tcgen05.mma with V as the MN-major B operand (the page rows as they are), O in TMEM.
-// One CTA = 6 warps: warp 0 issues the TMA loads, warp 1 the MMAs, warps 2-5 are the softmax (and the
-// epilogue: O / l to the output, or the partial sums of a split tile for the merge kernel).
+// One CTA = 7 warps: warps 0 and 6 issue the TMA loads of keys and values, warp 1 the MMAs, warps 2-5 are the
+// softmax (and the epilogue: O / l to the output, or the partial sums of a split tile for the merge kernel).
 // Every wait is bounded; a timeout records a code in g_attn_status, lets copies land, frees TMEM, returns.
 // Key rows past the end of the request are never multiplied as they lie in memory (they may hold
 // anything): whole 16-key boxes past the end are not loaded (the stages start zeroed), and the rows
@@ -30,10 +30,10 @@ __device__ int g_attn_status[4];  // [0] first error code, [1] block; 0 = fine
 constexpr int kTcRows = 128;
 constexpr int kTcKeys = 128;
 constexpr int kTcD = 128;
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 224;
 constexpr int kTcHalf = 128 * 64 * 2;       // bytes of a [128 rows x 64 elements] swizzle-atom column
 constexpr int kTcTile = 2 * kTcHalf;        // a [128 x 128] bfloat16 tile
-constexpr int kTcSmem = 6 * kTcTile + 1024; // Q, K x2, V x2, P
+constexpr int kTcSmem = 7 * kTcTile + 1024; // Q, K x2, V x2, P x2
 
 __device__ __forceinline__ void tmem_ld32(uint32_t addr, float (&v)[32]) {
   uint32_t r[32];
@@ -99,7 +99,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   pdl_wait();
   pdl_trigger();
   extern __shared__ unsigned char dyn_smem[];
-  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, pv_done;
+  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2], pv_done[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -117,9 +117,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4);
+      mbar_init(&p_full[s], 4); mbar_init(&pv_done[s], 1);
     }
-    mbar_init(&p_full, 4);
-    mbar_init(&pv_done, 1);
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -140,40 +139,46 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     abort_flag = 1;
   };
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
-    if (lane == 0 && n_tiles > 0) {
-      mbar_expect_tx(&q_full, (uint32_t)(2 * 128 * G * (kTcRows / G)));  // two boxes of (64, group, tokens per tile)
-      for (int h = 0; h < 2; ++h)  // (d, head, token): rows land as token-major, head-minor
-        tma_load_3d(tiles + h * kTcHalf, &map_q, &q_full, h * 64, kvh * G, it.q_start + it.tok0);
+  if (warp == 0 || warp == 6) {
+    // ------------------------------------------------------------ TMA producers: warp 0 keys, warp 6 values
+    // One lane per box: lane = 2 * (16-key box of the tile) + (half of the head dimension), so one
+    // warp instruction issues a whole tile and every lane looks its own page up.  (One thread issuing
+    // the boxes of a tile one after the other took longer than the tile's products; keys and values in
+    // one warp made the keys wait for the value stage.)
+    if (n_tiles > 0 && lane < 16) {
+      const int kv = warp == 6, box = lane >> 1, h = lane & 1;
+      if (lane == 0 && !kv) {
+        mbar_expect_tx(&q_full, (uint32_t)(2 * 128 * G * (kTcRows / G)));  // two boxes of (64, group, tokens per tile)
+        for (int hh = 0; hh < 2; ++hh)  // (d, head, token): rows land as token-major, head-minor
+          tma_load_3d(tiles + hh * kTcHalf, &map_q, &q_full, hh * 64, kvh * G, it.q_start + it.tok0);
+      }
       const int32_t* bt = p.block_table + (size_t)it.bt_row * p.bt_stride;
-      for (int j = 0; j < n_tiles; ++j) {
+      const CUtensorMap* map = kv ? &map_v : &map_k;
+      uint64_t* full = kv ? v_full : k_full;
+      uint64_t* empty = kv ? v_empty : k_empty;
+      unsigned char* stage0 = tiles + (kv ? 3 : 1) * kTcTile + h * kTcHalf + box * 2048;
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j & 1;
         const uint32_t par = ((j >> 1) & 1) ^ 1;
         const int key0 = it.kb + j * kTcKeys;
         const int n_box = min(8, (it.ke - key0 + 15) >> 4);  // boxes of 16 keys that hold keys of the request
-        int rows[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int key = key0 + 16 * i;
-          int page = 0;
-          if (i < n_box) {
-            const int slot = key / p.P;
-            page = slot < p.bt_stride ? bt[slot] : 0;
-            if (page < 0 || page >= p.num_pages) page = 0;
-          }
-          rows[i] = (page * p.Hkv + kvh) * p.P + key % p.P;
+        const int key = key0 + 16 * box;
+        int page = 0;
+        if (box < n_box) {
+          const int slot = key / p.P;
+          page = slot < p.bt_stride ? bt[slot] : 0;
+          if (page < 0 || page >= p.num_pages) page = 0;
         }
-        if (!mbar_wait(&k_empty[st], par, abortp)) { fail(201); break; }
-        mbar_expect_tx(&k_full[st], (uint32_t)n_box * 2 * 2048);
-        for (int i = 0; i < n_box; ++i)
-          for (int h = 0; h < 2; ++h)
-            tma_load_2d(tiles + kTcTile + st * kTcTile + h * kTcHalf + i * 2048, &map_k, &k_full[st], h * 64, rows[i]);
-        if (!mbar_wait(&v_empty[st], par, abortp)) { fail(202); break; }
-        mbar_expect_tx(&v_full[st], (uint32_t)n_box * 2 * 2048);
-        for (int i = 0; i < n_box; ++i)
-          for (int h = 0; h < 2; ++h)
-            tma_load_2d(tiles + 3 * kTcTile + st * kTcTile + h * kTcHalf + i * 2048, &map_v, &v_full[st], h * 64, rows[i]);
+        const int row = (page * p.Hkv + kvh) * p.P + key % p.P;
+        if (!__all_sync(0x0000ffffu, mbar_wait(&empty[st], par, abortp))) {
+          if (lane == 0) fail(201 + kv);
+          ok = false;
+          break;
+        }
+        if (lane == 0) mbar_expect_tx(&full[st], (uint32_t)n_box * 2 * 2048);
+        __syncwarp(0x0000ffffu);
+        if (box < n_box) tma_load_2d(stage0 + st * kTcTile, map, &full[st], h * 64, row);
       }
     }
   } else if (warp == 1) {
@@ -210,7 +215,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       if (j >= 1) {
         const int i = j - 1, st = i & 1;
-        if (!mbar_wait(&p_full, (uint32_t)(i & 1), abortp) || !mbar_wait(&v_full[st], (uint32_t)((i >> 1) & 1), abortp)) {
+        if (!mbar_wait(&p_full[st], (uint32_t)((i >> 1) & 1), abortp) || !mbar_wait(&v_full[st], (uint32_t)((i >> 1) & 1), abortp)) {
           if (lane == 0) fail(205);
           ok = false;
           break;
@@ -233,12 +238,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           const uint32_t d = tmem + 2 * kTcKeys;
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {  // 16 keys per MMA
-            const uint64_t a = smem_desc(p_s + (kk >> 2) * kTcHalf) + 2 * (kk & 3);
+            const uint64_t a = smem_desc(p_s + st * kTcTile + (kk >> 2) * kTcHalf) + 2 * (kk & 3);
             const uint64_t b = smem_desc_mn(v_s + st * kTcTile + kk * 2048, kTcHalf);
             tc_mma(d, a, b, idesc_pv, (i | kk) != 0);
           }
           tc_commit(&v_empty[st]);
-          tc_commit(&pv_done);
+          tc_commit(&pv_done[st]);
         }
         __syncwarp();
       }
@@ -250,7 +255,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int R = it.ok ? it.ntok * G : 0;
     const int pos_base = it.kv_len - it.q_len + it.tok0;
     const int qpos = r < R ? pos_base + r / G : -1;
-    const int lo = p.window > 0 ? qpos - p.window + 1 : 0;
+    // last key this row may read; rows past the tile's last are never stored and must not hold the others up
+    const int hi = r < R ? min(it.ke - 1, qpos) : 0x7fffffff;
     const float sl2 = p.scale * 1.4426950408889634f;
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
     float m_used = -INFINITY, l = 0.f;
@@ -265,20 +271,30 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       tc_fence_after();
       const uint32_t s_addr = lane_addr + (uint32_t)(sb * kTcKeys);
       const int key0 = it.kb + j * kTcKeys;
-      // keys every row of the warp may read in full need no mask
-      const int hi = min(it.ke - 1, qpos);  // last key this row may read
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float v[32];
-        tmem_ld32(s_addr + c * 32, v);
-        const int k0 = key0 + c * 32;
+      // the row's 128 scores, in registers for both passes
+      float v0[32], v1[32], v2[32], v3[32];
+      tmem_ld32(s_addr, v0);
+      tmem_ld32(s_addr + 32, v1);
+      tmem_ld32(s_addr + 64, v2);
+      tmem_ld32(s_addr + 96, v3);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[sb]);  // the next product may overwrite this buffer
+      // a tile that every row of the warp reads in full needs no mask (most tiles of a long prompt)
+      const bool interior = __all_sync(0xffffffffu, key0 + kTcKeys - 1 <= hi);
+      if (!interior) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const bool valid = k0 + i <= hi && k0 + i >= lo;
-          mx = fmaxf(mx, valid ? v[i] * sl2 : -INFINITY);
+          if (key0 + i > hi) v0[i] = -INFINITY;
+          if (key0 + 32 + i > hi) v1[i] = -INFINITY;
+          if (key0 + 64 + i > hi) v2[i] = -INFINITY;
+          if (key0 + 96 + i > hi) v3[i] = -INFINITY;
         }
       }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) mx = fmaxf(fmaxf(mx, v0[i]), fmaxf(v1[i], fmaxf(v2[i], v3[i])));
+      mx *= sl2;  // the scale is positive: the largest score stays the largest
       // move the running maximum only when it grew by more than 8 (or is not set yet)
       float alpha = 1.f;
       if (mx > m_used + 8.f || (m_used == -INFINITY && mx > -INFINITY)) {
@@ -287,15 +303,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       l *= alpha;
       const bool rescale = __any_sync(0xffffffffu, alpha != 1.f) && j > 0;
-      if (j > 0) {  // the product before this one has read P and updated O
-        if (!__all_sync(0xffffffffu, mbar_wait(&pv_done, (uint32_t)((j - 1) & 1), abortp))) {
+      if (j >= 2) {  // the product two tiles back has read the P buffer this tile writes
+        if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[sb], (uint32_t)(((j - 2) >> 1) & 1), abortp))) {
           if (lane == 0) fail(207);
           ok = false;
           break;
         }
-        tc_fence_after();
       }
-      if (rescale) {
+      if (rescale) {  // O must hold every product so far before it is scaled
+        if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[sb ^ 1], (uint32_t)(((j - 1) >> 1) & 1), abortp))) {
+          if (lane == 0) fail(209);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           float o[32];
@@ -307,41 +328,39 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       const float mb = m_used == -INFINITY ? 0.f : m_used;
       float sum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float v[32];
-        tmem_ld32(s_addr + c * 32, v);
-        const int k0 = key0 + c * 32;
+      // probabilities as bfloat16 into row r of the A-operand layout: two [128 x 64]-key atoms, rows of
+      // 128 bytes in groups of eight, 16-byte chunks swizzled by the row
+      unsigned char* prow = tiles + (5 + sb) * kTcTile + (r >> 3) * 1024 + (r & 7) * 128;
+      auto emit = [&](float (&v)[32], int c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const bool v0 = k0 + i <= hi && k0 + i >= lo, v1 = k0 + i + 1 <= hi && k0 + i + 1 >= lo;
-          const float p0 = v0 ? tc_exp2(v[i] * sl2 - mb) : 0.f;
-          const float p1 = v1 ? tc_exp2(v[i + 1] * sl2 - mb) : 0.f;
+          const float p0 = tc_exp2(fmaf(v[i], sl2, -mb));      // exp2(-inf) = 0 for masked keys
+          const float p1 = tc_exp2(fmaf(v[i + 1], sl2, -mb));
           sum += p0 + p1;
           pk[i >> 1] = tc_pack(p0, p1);
         }
-        // row r of the [128 x 64]-key atom (c >> 1), 16-byte chunks (c & 1) * 4 .. + 3, swizzled by the row
-        unsigned char* prow = tiles + 5 * kTcTile + (c >> 1) * kTcHalf + (r >> 3) * 1024 + (r & 7) * 128;
+        unsigned char* dst = prow + (c >> 1) * kTcHalf;
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           const int chunk = (c & 1) * 4 + q4;
-          *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) =
+          *reinterpret_cast<uint4*>(dst + ((chunk ^ (r & 7)) << 4)) =
               make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
         }
-      }
+      };
+      emit(v0, 0);
+      emit(v1, 1);
+      emit(v2, 2);
+      emit(v3, 3);
       l += sum;
       fence_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&s_empty[sb]);
-        mbar_arrive(&p_full);
-      }
+      if (lane == 0) mbar_arrive(&p_full[sb]);
     }
     // ---- epilogue
     if (ok && n_tiles > 0) {
-      if (!__all_sync(0xffffffffu, mbar_wait(&pv_done, (uint32_t)((n_tiles - 1) & 1), abortp))) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[(n_tiles - 1) & 1], (uint32_t)(((n_tiles - 1) >> 1) & 1), abortp))) {
         if (lane == 0) fail(208);
         ok = false;
       }

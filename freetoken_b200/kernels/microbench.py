@@ -115,7 +115,7 @@ def bench_attention(a) -> dict:
     seg = torch.tensor(info, dtype=torch.int32, device=dev)
     q = torch.randn(q0, Hq, D, device=dev, generator=g).to(torch.bfloat16)
     fixed = None
-    tile = 64
+    tile = 128 if (a.prefill >= 128 and not a.no_tc and ops.attention_tc_fits(D, P, G)) else 64
     if not a.prefill:
         fixed = wave_splits(len(segs) * Hkv, 2 * 148, 16) if a.splits is None else a.splits
         tile = 16 if G <= 16 else 64
@@ -201,6 +201,7 @@ def main(argv=None) -> int:
             p.add_argument("--head-dim", type=int, default=128)
             p.add_argument("--page-size", type=int, default=16)
             p.add_argument("--splits", type=int, default=None)
+            p.add_argument("--no-tc", action="store_true", help="prefill on the mma.sync kernel instead of tcgen05")
         else:
             p.add_argument("--rows", type=int, default=8)
             p.add_argument("--vocab", type=int, default=200064)
