@@ -320,7 +320,7 @@ class Engine:
             return body()
         # one graph per batch size and metadata layout (the attention split count moves with the
         # longest request, which changes the size of the work list a few times over a long decode)
-        key = (S, tuple(arr.size for _, arr in builder.sections))
+        key = (S, tuple(arr.size for _, arr in builder.sections), tuple(sorted(map(repr, builder.plans))))
         if key not in self.graphs:
             body()  # warm-up: allocates work buffers and library workspaces outside the capture
             torch.cuda.synchronize(self.device)

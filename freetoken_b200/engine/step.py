@@ -101,23 +101,27 @@ class StepBuilder:
     def add(self, name: str, arr: np.ndarray) -> None:
         self.sections.append((name, np.ascontiguousarray(arr, dtype=np.int32)))
 
-    def fixed_splits(self, n_kv_heads: int) -> int:
-        """Splits per tile of a graph-replayed decode step: enough CTAs to fill the GPU at
-        this batch size, independent of the requests' lengths."""
-        b = max(1, len(self.seg_lens))
+    def longest_span(self) -> int:
+        """The longest request's length rounded up to a power of two: what a graph-replayed decode
+        step may let its kernel choice and split count depend on (it changes a handful of times as
+        requests grow)."""
         longest = max(kv for _, kv in self.seg_lens)
-        # the count may only depend on what a graph's replays share (the batch size), so the span is
-        # rounded up to a power of two: the split count then changes a handful of times as requests grow
-        span = 1 << max(6, (longest - 1).bit_length())
-        return wave_splits(b * n_kv_heads, 2 * self.sm_count, 16, span)
+        return 1 << max(6, (longest - 1).bit_length())
+
+    def fixed_splits(self, n_kv_heads: int, ctas_per_sm: int = 2) -> int:
+        """Splits per tile of a graph-replayed decode step: enough CTAs to fill the GPU at
+        this batch size, independent of the requests' exact lengths."""
+        b = max(1, len(self.seg_lens))
+        return wave_splits(b * n_kv_heads, ctas_per_sm * self.sm_count, 16, self.longest_span())
 
     def attention_plan(self, group: int, tile_rows: int, window: Optional[int], n_kv_heads: int,
                        head_dim: int) -> Any:
         key = ("attention", group, tile_rows, window, n_kv_heads, head_dim)
         if key not in self.plans:
+            per_sm = 1 if tile_rows == 128 else 2  # the 128-row kernel fills an SM with one CTA
             plan = build_plan(self.seg_lens, group, tile_rows, window, n_kv_heads,
-                              sm_count=self.sm_count,
-                              fixed_splits=self.fixed_splits(n_kv_heads) if self.fixed else None)
+                              sm_count=self.sm_count if per_sm == 2 else max(1, self.sm_count // 2),
+                              fixed_splits=self.fixed_splits(n_kv_heads, per_sm) if self.fixed else None)
             self.plans[key] = plan
             self.plan_dims[key] = (n_kv_heads, tile_rows, head_dim)
             self.add(f"plan.{len(self.plans) - 1}", plan.items)
@@ -143,7 +147,7 @@ class StepBuilder:
             n_kv, rows, dim = self.plan_dims[key]
             part_o = part_ml = None
             if plan.n_slots:
-                tag = f"attn.part.{i}.fixed{len(self.seg_lens)}x{plan.n_slots}" if self.fixed else f"attn.part.{i}"
+                tag = f"attn.part.{i}.fixed{len(self.seg_lens)}x{plan.n_slots}x{rows}" if self.fixed else f"attn.part.{i}"
                 part_o = workspace.get(tag + ".o", (plan.n_slots, n_kv, rows, dim), torch.float32)
                 part_ml = workspace.get(tag + ".ml", (plan.n_slots, n_kv, rows, 2), torch.float32)
             plans[key] = DevicePlan(tensors[f"plan.{i}"], plan.n_items, part_o, part_ml, plan)

@@ -117,8 +117,9 @@ def bench_attention(a) -> dict:
     fixed = None
     tile = 128 if (a.prefill >= 128 and not a.no_tc and ops.attention_tc_fits(D, P, G)) else 64
     if not a.prefill:
-        fixed = wave_splits(len(segs) * Hkv, 2 * 148, 16) if a.splits is None else a.splits
-        tile = 16 if G <= 16 else 64
+        tc = a.tc and ops.attention_tc_fits(D, P, G)
+        fixed = wave_splits(len(segs) * Hkv, 148 if tc else 2 * 148, 16) if a.splits is None else a.splits
+        tile = 128 if tc else (16 if G <= 16 else 64)
     plan = build_plan(segs, G, tile, None, Hkv, fixed_splits=fixed)
     items = torch.from_numpy(plan.items).to(dev)
     po = pm = None
@@ -202,6 +203,7 @@ def main(argv=None) -> int:
             p.add_argument("--page-size", type=int, default=16)
             p.add_argument("--splits", type=int, default=None)
             p.add_argument("--no-tc", action="store_true", help="prefill on the mma.sync kernel instead of tcgen05")
+            p.add_argument("--tc", action="store_true", help="decode on the tcgen05 kernel")
         else:
             p.add_argument("--rows", type=int, default=8)
             p.add_argument("--vocab", type=int, default=200064)

@@ -23,18 +23,26 @@ from .base import MIXERS, BuildEnv, Mixer, StepState
 from .rope import shared_position
 
 
-TC_MIN_TOKENS = 128  # shortest step that goes to the tcgen05 attention kernel
+TC_MIN_TOKENS = 128      # shortest step that goes to the tcgen05 attention kernel
+TC_MIN_DECODE_SPAN = 8192  # decode steps go there once the longest request is past half of this
 
 
 def attention_tile_rows(dtype: torch.dtype, decode_only: bool = False, group: int = 1, n_tokens: int = 0,
-                        head_dim: int = 0, page_size: int = 0, window: Optional[int] = None) -> int:
+                        head_dim: int = 0, page_size: int = 0, window: Optional[int] = None,
+                        longest_span: int = 0) -> int:
     """Query rows (tokens x group heads) one attention CTA handles: 16 in the 32-bit kernel and in
     the bfloat16 kernel for steps of single decoded tokens; 128 (the tcgen05 kernel) for long bfloat16
-    steps whose sizes it takes; 64 in the bfloat16 mma.sync kernel otherwise."""
-    if dtype != torch.bfloat16 or (decode_only and group <= 16):
+    steps whose sizes it takes, and for decode steps over long contexts (measured: the same time as the
+    16-row kernel at 2k tokens of context, 19 % less at 8k; ``longest_span`` is the longest request's
+    length rounded up to a power of two); 64 in the bfloat16 mma.sync kernel otherwise."""
+    if dtype != torch.bfloat16:
         return 16
-    if (not decode_only and n_tokens >= TC_MIN_TOKENS and window is None and head_dim and page_size
-            and ops.attention_tc_fits(head_dim, page_size, group)):
+    tc = bool(window is None and head_dim and page_size and ops.attention_tc_fits(head_dim, page_size, group))
+    if decode_only:
+        if tc and longest_span >= TC_MIN_DECODE_SPAN:
+            return 128
+        return 16 if group <= 16 else 64
+    if tc and n_tokens >= TC_MIN_TOKENS:
         return 128
     return 64
 
@@ -92,12 +100,12 @@ class GQAttention(Mixer):
                             ("v", self.n_kv_heads, self.head_dim)), self.window)
 
     # ------------------------------------------------------------------ step
-    def tile_rows(self, decode_only: bool, n_tokens: int = 0, page_size: int = 0) -> int:
+    def tile_rows(self, decode_only: bool, n_tokens: int = 0, page_size: int = 0, longest_span: int = 0) -> int:
         return attention_tile_rows(self.env.dtype, decode_only, self.group, n_tokens, self.head_dim, page_size,
-                                   self.window)
+                                   self.window, longest_span)
 
-    def plan_key(self, decode_only: bool = False, n_tokens: int = 0, page_size: int = 0):
-        return ("attention", self.group, self.tile_rows(decode_only, n_tokens, page_size), self.window,
+    def plan_key(self, decode_only: bool = False, n_tokens: int = 0, page_size: int = 0, longest_span: int = 0):
+        return ("attention", self.group, self.tile_rows(decode_only, n_tokens, page_size, longest_span), self.window,
                 self.n_kv_heads, self.head_dim)
 
     def prepare(self, builder) -> None:
@@ -105,8 +113,8 @@ class GQAttention(Mixer):
         n_tokens = sum(q for q, _ in builder.seg_lens)
         page_size = builder.engine.config.page_size if builder.engine is not None else 0
         # forward() of the same step runs the kernel this work list was made for
-        self._step_plan = builder.attention_plan(self.group, self.tile_rows(builder.decode_only, n_tokens, page_size),
-                                                 self.window, self.n_kv_heads, self.head_dim)
+        rows = self.tile_rows(builder.decode_only, n_tokens, page_size, builder.longest_span())
+        self._step_plan = builder.attention_plan(self.group, rows, self.window, self.n_kv_heads, self.head_dim)
 
     def forward(self, h: torch.Tensor, step: StepState, cache: Any, writes_cache: bool) -> torch.Tensor:
         T = h.shape[0]
