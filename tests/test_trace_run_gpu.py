@@ -128,3 +128,40 @@ def test_trace_run_reports_errors(tmp_path_factory, tmp_path):
                         "--out", str(tmp_path / "o"), "--max-tokens", "64"], input=too_many + "\n",
                        capture_output=True, text=True)
     assert p.returncode != 0 and "done 0" not in p.stdout
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_long_steps(dtype, tmp_path_factory, tmp_path):
+    """Steps of more than 128 tokens with heads of 128: in bfloat16 these run the tensor-core
+    attention kernel.  A request whole, the same in two long portions and ten single tokens, and a
+    long portion beside single tokens of another request."""
+    folder = model_folder(tmp_path_factory.getbasetemp(), "E", ALL["E"])
+    plain = PlainM3(folder)
+    V = plain.cfg.vocab
+    a, b = tokens_for(V, 300, 61), tokens_for(V, 180, 62)
+    steps = [
+        {"step": 0, "entries": [{"id": "w", "tokens": a, "want": list(range(300))}], "end": ["w"]},
+        {"step": 1, "entries": [{"id": "p", "tokens": a[:160], "want": [0, 159]}], "end": []},
+        {"step": 2, "entries": [{"id": "p", "tokens": a[160:290], "want": list(range(130))},
+                                {"id": "q", "tokens": b[:20], "want": [19]}], "end": []},
+    ]
+    for i in range(10):
+        steps.append({"step": 3 + i, "entries": [{"id": "p", "tokens": [a[290 + i]], "want": [0]},
+                                                 {"id": "q", "tokens": [b[20 + i]], "want": [0]}],
+                      "end": ["p"] if i == 9 else []})
+    steps.append({"step": 13, "entries": [{"id": "q", "tokens": b[30:], "want": list(range(150))}], "end": ["q"]})
+    out_dir = str(tmp_path / "out")
+    run_trace(folder, dtype, out_dir, 1024, steps)
+    ra, rb = plain.logits(a), plain.logits(b)
+    ma, mb = plain.router_margins(a), plain.router_margins(b)
+    check(read_logits(out_dir, 0, V), ra, dtype, ma, "300 tokens whole")
+    idx = torch.tensor([0, 159])
+    check(read_logits(out_dir, 1, V), ra[idx], dtype, ma[idx], "first portion")
+    got = read_logits(out_dir, 2, V)
+    check(got[:130], ra[160:290], dtype, ma[160:290], "second portion beside another request")
+    check(got[130:], rb[19:20], dtype, mb[19:20], "short portion beside a long one")
+    pa = torch.cat([read_logits(out_dir, 3 + i, V)[:1] for i in range(10)])
+    qb = torch.cat([read_logits(out_dir, 3 + i, V)[1:] for i in range(10)])
+    check(pa, ra[290:], dtype, ma[290:], "decoded after long portions")
+    check(qb, rb[20:30], dtype, mb[20:30], "decoded beside")
+    check(read_logits(out_dir, 13, V), rb[30:], dtype, mb[30:], "a long portion over earlier keys")
