@@ -3,8 +3,10 @@
 // sigmoid form (python/freetoken/models/minimax_m3/moe.py:71-81): s = sigmoid(logits); the experts
 // are chosen by s + bias, weighted by the unbiased s, divided by their sum (+1e-20) and multiplied by
 // the scaling factor.  softmax form (python/freetoken/moe/fused.py:27-31): s = softmax(logits).
-// The logits themselves are a library matrix product in float32, as in the reference (F.linear).
 // One warp per token; the largest choice goes first and the lower expert index wins a tie.
+// For long steps the logits are a library matrix product in float32, as in the reference (F.linear),
+// and router_topk_kernel takes them; for short steps moe_route_kernel computes them itself and also
+// sorts the routes by expert, all in one launch.
 #include "common.cuh"
 
 namespace ftk {

@@ -20,7 +20,16 @@ moe_gemm2              fused_moe.py:156-302 (route weight on the accumulator, :2
 moe_combine            fused_moe.py:111-153
 act_and_mul            activation.py:67-112
 sample                 python/freetoken/engine/sample.py:24-80, python/freetoken/kernel/triton/sampling.py
+moe_route              router product + router_topk + moe_permute in one launch (short steps)
+add_rmsnorm_routes     moe_combine + add_rmsnorm in one pass
+linear / dense_tc      python/freetoken/layers/linear.py:66-70 (library product, or the tcgen05
+                       kernel with k cut into slices for few tokens and few rows)
+copy_tokens            the sampled tokens of the step before, taken on the device
+                       (python/freetoken/scheduler/scheduler.py:194-256, overlapped scheduling)
 =====================  ==========================================================
+
+``paged_attention`` runs one of four kernels by ``tile_rows``: 16 (float32, or bfloat16 decode), 64
+(bfloat16 mma.sync), 128 (bfloat16 tcgen05: long steps, decode over long contexts).
 """
 
 from __future__ import annotations
