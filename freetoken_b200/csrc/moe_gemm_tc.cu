@@ -518,14 +518,15 @@ static int launch_tc_impl(const CUtensorMap& ma, const CUtensorMap& mb, const Tc
   return 0;
 }
 
-// Few tiles: shallow pipelines, two CTAs per SM.  Many tiles (several per SM): one deep pipeline per SM.
+// Few tiles: shallow pipelines, two CTAs per SM.  More than two tiles per SM: one deep pipeline per SM.
 template <int BN, bool GATED>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int max_tiles, int likely_tiles,
                      cudaStream_t s) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (likely_tiles > 3 * sms || !p.offsets) return launch_tc_impl<BN, GATED, true>(ma, mb, p, max_tiles, s);
+  // measured: 192 tiles (one token) are faster two CTAs to an SM, 384 (two tokens) already one deep pipeline per SM
+  if (likely_tiles > 2 * sms || !p.offsets) return launch_tc_impl<BN, GATED, true>(ma, mb, p, max_tiles, s);
   return launch_tc_impl<BN, GATED, false>(ma, mb, p, max_tiles, s);
 }
 
