@@ -243,8 +243,12 @@ def main():
         T = PROMPT
         flops = L * (2 * T * H * (qdim + 2 * kvdim) + 2 * T * qdim * H + 4 * (T * (T + 1) // 2) * qdim
                      + 2 * T * H * E + k * T * (2 * H * 2 * I + 2 * I * H)) + 2 * H * V
+        # what the step has to read at least: every expert's weights once (2 048 tokens x top-k reach all of
+        # them), the attention weights, the router and the head
+        pre_bytes = L * (2 * (H * (qdim + 2 * kvdim) + qdim * H) + 4 * E * H + E * 2 * (2 * I * H + H * I)) + 2 * H * V
         prefill = {"value": round(T / (ms / 1e3), 1), "tokens": T, "ms": round(ms, 3),
-                   "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+                   "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+                   "hbm_frac": round(pre_bytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
 
     # ------------------------------------------------------------------ decode
     def fill(batch, tag):
