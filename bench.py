@@ -17,6 +17,9 @@ of the whole batch.  It prints ONE JSON line:
 * ``points``: decode tokens/s at batch 1 and 64;
 * ``clocks``: SM clock and throttle reasons sampled during the timed region.
 
+``--workload long_contexts | chunked_prefill`` runs one of the larger workloads of
+freetoken_b200/workloads.py instead and prints that workload's own JSON line.
+
 Peaks come from MEASURED_PEAKS.json when the driver wrote it, else 6.65 TB/s and 1.59 PFLOP/s.
 More than one GPU is outside this engine: ``--gpus N`` with N > 1 prints one line and exits 2.
 """
@@ -163,6 +166,14 @@ def main():
     ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
                     help="run only that phase and bracket `--steps` steps of it with cudaProfilerStart/Stop "
                          "(for ncu --profile-from-start off); prints no bench line")
+    ap.add_argument("--workload", choices=["long_contexts", "chunked_prefill"], default=None,
+                    help="run one of the larger workloads of freetoken_b200/workloads.py instead (its own JSON line)")
+    ap.add_argument("--requests", type=int, default=None)
+    ap.add_argument("--max-prompt", type=int, default=None)
+    ap.add_argument("--new-tokens", type=int, default=None)
+    ap.add_argument("--prompt", type=int, default=None)
+    ap.add_argument("--chunk", type=int, default=None)
+    ap.add_argument("--decoders", type=int, default=None)
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is outside its scope")
@@ -171,6 +182,15 @@ def main():
         return reference_arm()
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload:
+        from freetoken_b200 import workloads
+
+        layers = args.layers if "--layers" in sys.argv else None
+        if args.workload == "long_contexts":
+            return workloads.run("long_contexts", HEADLINE, layers=layers, requests=args.requests,
+                                 max_prompt=args.max_prompt, new_tokens=args.new_tokens)
+        return workloads.run("chunked_prefill", HEADLINE, layers=layers, prompt=args.prompt, chunk=args.chunk,
+                             decoders=args.decoders)
 
     import numpy as np
     import torch

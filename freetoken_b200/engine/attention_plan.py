@@ -86,17 +86,26 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
             tiles.append((s, tok0, ntok, lo, hi))
     n_tiles = len(tiles)
     target = 2 * sm_count
+    # keys of all tiles together, per resident CTA: a tile that is long against that and against the
+    # other tiles would keep one SM busy long after the rest is done (a long portion beside many
+    # single tokens), so it is cut into pieces of half that share
+    all_keys = sum(hi - lo for _, _, _, lo, hi in tiles)
+    piece = max(all_keys * n_kv_heads / max(1, target) / 2, float(min_split_keys))
+    mean_span = all_keys / max(1, n_tiles)
     rows: List[List[int]] = []
     n_slots = 0
     for (s, tok0, ntok, lo, hi) in tiles:
         span = hi - lo
+        most = min(max_splits, max(1, span // min_split_keys))
         if fixed_splits is not None:
             want = fixed_splits
         elif n_tiles * n_kv_heads >= target:
             want = 1
+            if span > piece and span > 2 * mean_span:
+                want = max(1, min(most, int(-(-span // piece))))
         else:
             # splits that fill whole waves of resident CTAs, none shorter than min_split_keys
-            want = wave_splits(n_tiles * n_kv_heads, target, min(max_splits, max(1, span // min_split_keys)), span)
+            want = wave_splits(n_tiles * n_kv_heads, target, most, span)
         quanta = -(-span // SPLIT_QUANTUM)
         n_real = max(1, min(want, quanta))
         per = -(-quanta // n_real) * SPLIT_QUANTUM

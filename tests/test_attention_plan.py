@@ -1,0 +1,64 @@
+"""The attention work list (host side): every tile's key range is covered exactly once by its
+splits, long tiles beside many short ones are cut, even steps are not."""
+
+import numpy as np
+import pytest
+
+from freetoken_b200.engine.attention_plan import SPLIT_QUANTUM, build_plan, wave_splits
+
+
+def ranges_by_tile(plan):
+    tiles = {}
+    for seg, tok0, ntok, kb, ke, nsplit, split, base in plan.items.tolist():
+        tiles.setdefault((seg, tok0, ntok), []).append((split, kb, ke, nsplit, base))
+    return tiles
+
+
+@pytest.mark.parametrize("segs,group,tile,window", [
+    ([(1, 1), (1, 130), (17, 17), (5, 69), (2, 64), (33, 200), (1, 65)], 3, 16, None),
+    ([(300, 300), (1, 5000), (40, 1000)], 6, 128, None),
+    ([(7, 90), (1, 400)], 2, 64, 32),
+    ([(1, 40000)], 6, 16, None),
+])
+def test_splits_cover_each_tile_once(segs, group, tile, window):
+    plan = build_plan(segs, group, tile, window, n_kv_heads=2)
+    assert plan.n_items == plan.items.shape[0]
+    slots = []
+    for (seg, tok0, ntok), parts in ranges_by_tile(plan).items():
+        q_len, kv_len = segs[seg]
+        pos0 = kv_len - q_len
+        hi = pos0 + tok0 + ntok
+        lo = max(0, pos0 + tok0 - window + 1) if window else 0
+        parts.sort()
+        assert [p[0] for p in parts] == list(range(len(parts))) and all(p[3] == len(parts) for p in parts)
+        assert parts[0][1] == lo and parts[-1][2] == hi
+        for (_, _, e0, _, _), (_, b1, _, _, _) in zip(parts, parts[1:]):
+            assert e0 == b1 and (b1 - lo) % SPLIT_QUANTUM == 0
+        if len(parts) > 1:
+            slots += list(range(parts[0][4], parts[0][4] + len(parts)))
+    assert sorted(slots) == list(range(plan.n_slots)), "partial slots are used once each"
+
+
+def test_a_long_portion_beside_many_single_tokens_is_cut():
+    """63 decoded tokens over 2k contexts beside a 512-token portion over a 100k-token prefix: the long
+    tiles are split so that no SM is left alone with one of them; an even prefill is left whole."""
+    segs = [(1, 2000 + i) for i in range(63)] + [(512, 100_000)]
+    plan = build_plan(segs, 6, 128, None, n_kv_heads=8, sm_count=74)
+    long_tiles = [parts for (seg, _, _), parts in ranges_by_tile(plan).items() if seg == 63]
+    assert all(len(parts) >= 2 for parts in long_tiles)
+    longest = max(ke - kb for parts in long_tiles for _, kb, ke, _, _ in parts)
+    total = sum(ke - kb for _, _, _, kb, ke, _, _, _ in plan.items.tolist())
+    assert longest <= 0.75 * total * 8 / (2 * 74), "no piece near the fair share of an SM"
+    even = build_plan([(2048, 2048)], 6, 128, None, n_kv_heads=8, sm_count=74)
+    assert even.n_slots == 0
+    batch = build_plan([(1, 2048)] * 64, 6, 16, None, n_kv_heads=8)
+    assert batch.n_slots == 0, "64 equal requests fill the GPU as they are"
+    one_long = build_plan([(1, 2048)] * 63 + [(1, 100_000)], 6, 16, None, n_kv_heads=8)
+    assert one_long.n_slots >= 16, "the one long request is cut"
+
+
+def test_wave_splits_prefers_full_waves():
+    assert wave_splits(64, 296, 16, 2048) in (4, 5)  # 64 tiles on 296 slots: 4 or 5 splits fill a wave
+    assert wave_splits(512, 296, 16, 2048) == 1       # already more tiles than slots
+    assert wave_splits(8, 296, 1, 128) == 1           # the caller's limit (no piece under 256 keys) holds
+    assert wave_splits(8, 296, 16, 2048) == 16        # one request alone: as many pieces as allowed
