@@ -12,6 +12,11 @@ answered with an error instead of waiting forever (scheduler.py:489-519).  A por
 is never sampled (prefill.py:28-37).  A request finishes by length or by an EOS token id
 (scheduler.py:334-353) and its pages and state slot return to the free lists at once.
 
+Steps can be overlapped (``step_overlapped``, the default of ``run``): the next step is planned and
+launched while the device still computes the one before, whose sampled tokens stay on the device and
+are copied into the next step's token ids there; the host reads them one step late
+(scheduler.py:194-256 in the reference).  ``step`` launches and reads in one go.
+
 What happens when pages run out: they cannot, for admitted requests, because admission reserves
 the pages of the whole request (prompt + max_tokens) in every cache group.  A request that could
 not fit even in an empty cache is finished at once with ``finish_reason="error"``.
