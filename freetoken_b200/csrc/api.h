@@ -78,10 +78,6 @@ int ftk_sparse_select(const void* iq, const void* ik_slab, int dtype, const int3
                       int32_t* sel, void* stream);
 int ftk_router_topk(const float* logits, const float* bias, int n_tokens, int n_experts, int top_k,
                     int scoring, float scale, int32_t* ids, float* weights, void* stream);
-// out[T, n_out] = x[T, k] w[n_out, k]^T, bfloat16 with float32 accumulation, for steps of at most 64 tokens
-// (tcgen05, k cut into slices so that every SM streams a part of the weight).
-int ftk_dense_tc_fits(int n_tokens, int n_out, int k);
-int ftk_dense_tc(const void* x, const void* w, void* out, int n_tokens, int n_out, int k, void* stream);
 // Router logits (float32 x [T, hidden] times gate_w [E, hidden]), choice and sort of the routes in one
 // launch, for steps of at most 32 tokens (beyond that the
 // separate kernels are faster); ftk_moe_route_fits says whether the sizes are taken.

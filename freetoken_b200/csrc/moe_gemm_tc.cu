@@ -60,20 +60,7 @@ struct TcParams {
   float alpha, limit;
   __nv_bfloat16* out;
   int depth;                     // loads a CTA keeps in flight while every CTA has a tile (<= stages)
-  // one plain product instead of experts (offsets == nullptr): the rows are [0, dense_rows)
-  int dense_rows;
-  // k cut into k_splits slices, each a unit of work of its own: the slices of a tile leave float32
-  // partial sums in `partial` and the last of them to arrive (counted in `arrivals`) adds them in
-  // slice order and writes the tile
-  int k_splits;
-  float* partial;                // [tile][slice][BN][128]
-  unsigned int* arrivals;        // [tile][4 lane quadrants], zero between launches
 };
-
-constexpr int kPartialFloats = 2 * 1024 * 1024;  // 8 MB of partial sums
-constexpr int kArrivalSlots = 4096;
-__device__ float g_tc_partial[kPartialFloats];
-__device__ unsigned int g_tc_arrivals[kArrivalSlots];
 
 // DEEP: one CTA per SM (many tiles: each SM streams on its own, with a longer pipeline for the large
 // token tiles); otherwise two CTAs per SM (few tiles: more of them run at once).
@@ -132,7 +119,6 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  auto first_row = [&](int e) { return p.offsets ? p.offsets[e] : (e == 0 ? 0 : p.dense_rows); };
   if (warp == 1) tmem_alloc(&tmem_slot, S::kTmemCols);
   // token tiles per expert, prefix-summed by warp 0
   if (warp == 0) {
@@ -141,7 +127,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
     int local = 0;
     for (int i = 0; i < per; ++i) {
       const int e = lane * per + i;
-      if (e < E) local += (first_row(e + 1) - first_row(e) + BN - 1) / BN;
+      if (e < E) local += (p.offsets[e + 1] - p.offsets[e] + BN - 1) / BN;
     }
     int incl = local;
 #pragma unroll
@@ -154,7 +140,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
       const int e = lane * per + i;
       if (e < E) {
         tile_prefix[e] = run;
-        run += (first_row(e + 1) - first_row(e) + BN - 1) / BN;
+        run += (p.offsets[e + 1] - p.offsets[e] + BN - 1) / BN;
       }
     }
     if (lane == 31) tile_prefix[E] = incl;
@@ -166,9 +152,6 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
   const int m_units = (p.m_tiles + S::kMT - 1) / S::kMT;
   const int total_tiles = tile_prefix[p.n_experts] * m_units;
   const int k_blocks = (p.K + S::kAtoms * kBK - 1) / (S::kAtoms * kBK);  // k past the end reads as zero
-  const int n_splits = (S::kMT == 1 && p.k_splits > 1) ? p.k_splits : 1;
-  const int kb_per = (k_blocks + n_splits - 1) / n_splits;
-  const int total_units = total_tiles * n_splits;  // unit u: tile u / n_splits, k slice u % n_splits
   volatile int* abortp = &abort_flag;
 
   constexpr int kFeat = GATED ? 64 : 128;  // output features of one feature tile
@@ -182,7 +165,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
       if (tile_prefix[mid] <= g) lo = mid; else hi = mid - 1;
     }
     e = lo;
-    const int start = first_row(e), end = first_row(e + 1);
+    const int start = p.offsets[e], end = p.offsets[e + 1];
     row0 = start + (g - tile_prefix[e]) * BN;
     rows = min(BN, end - row0);
   };
@@ -196,8 +179,8 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
       // by the latency of its own loads.
       int i = 0;
       bool ok = true;
-      const int full_waves = total_units / (int)gridDim.x * (int)gridDim.x;
-      const bool thin_tail = 2 * (total_units - full_waves) <= (int)gridDim.x;
+      const int full_waves = total_tiles / (int)gridDim.x * (int)gridDim.x;
+      const bool thin_tail = 2 * (total_tiles - full_waves) <= (int)gridDim.x;
       const int depth_main = p.depth > 0 ? min(p.depth, S::kStages) : S::kDepth;
       auto stage_bytes = [&](int rows) {
         const int nb = (rows + S::kBBoxRows - 1) / S::kBBoxRows;
@@ -230,27 +213,25 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
       };
       // the weights of the first loads, while the kernel before this one may still be running
       int ahead = 0;
-      if ((int)blockIdx.x < total_units) {
+      if ((int)blockIdx.x < total_tiles) {
         int e, row0, rows, m0;
-        const int t = blockIdx.x / n_splits, kb0 = (blockIdx.x - t * n_splits) * kb_per;
-        locate(t, e, row0, rows, m0);
-        ahead = min(depth_main, min(k_blocks, kb0 + kb_per) - kb0);
-        for (int j = 0; j < ahead; ++j) {
-          mbar_expect_tx(&full_bar[j], stage_bytes(rows));
-          load_a(j, kb0 + j, m0, e);
+        locate(blockIdx.x, e, row0, rows, m0);
+        ahead = min(depth_main, k_blocks);
+        for (int kb = 0; kb < ahead; ++kb) {
+          mbar_expect_tx(&full_bar[kb], stage_bytes(rows));
+          load_a(kb, kb, m0, e);
         }
         pdl_wait();
-        for (int j = 0; j < ahead; ++j) load_b(j, kb0 + j, row0, rows);
+        for (int kb = 0; kb < ahead; ++kb) load_b(kb, kb, row0, rows);
       } else {
         pdl_wait();
       }
-      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         int e, row0, rows, m0;
-        const int t = u / n_splits, kb0 = (u - t * n_splits) * kb_per, kb1 = min(k_blocks, kb0 + kb_per);
         locate(t, e, row0, rows, m0);
-        const int depth = (u >= full_waves && thin_tail) ? S::kStages : depth_main;
-        for (int kb = kb0; kb < kb1; ++kb, ++i) {
-          if (u == (int)blockIdx.x && kb - kb0 < ahead) continue;  // already on its way
+        const int depth = (t >= full_waves && thin_tail) ? S::kStages : depth_main;
+        for (int kb = 0; kb < k_blocks; ++kb, ++i) {
+          if (t == (int)blockIdx.x && kb < ahead) continue;  // already on its way
           const int j = i - depth;  // the load whose stage must have been read before load i goes out
           if (j >= 0 && !mbar_wait(&empty_bar[j % S::kStages], (uint32_t)(j / S::kStages) & 1u, abortp)) {
             ok = false;
@@ -273,8 +254,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
       uint32_t acc_phase = 0;  // bit a: phase of accumulator buffer a
       int acc = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-        const int t = u / n_splits, kb0 = (u - t * n_splits) * kb_per, kb1 = min(k_blocks, kb0 + kb_per);
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         if (!mbar_wait(&acc_empty[acc], ((acc_phase >> acc) & 1u) ^ 1u, abortp)) {
           atomicCAS(&g_status[0], 0, 102);
           abort_flag = 1;
@@ -286,7 +266,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
         // only the columns of tokens that exist are computed (and only their boxes were loaded)
         const uint32_t idesc = instr_desc(min(BN, (rows + 15) & ~15));
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * S::kAccCols);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&full_bar[s], phase, abortp)) {
             ok = false;
             atomicCAS(&g_status[0], 0, 103);
@@ -303,7 +283,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
               const uint64_t a_desc = smem_desc(a_addr + (h * S::kMT + mt) * kABytes);
 #pragma unroll
               for (int k = 0; k < kBK / 16; ++k)  // 16 k elements = 32 bytes = 2 descriptor units
-                tc_mma(d_tmem + (uint32_t)(mt * BN), a_desc + 2 * k, b_desc + 2 * k, idesc, ((kb - kb0) | h | k) != 0);
+                tc_mma(d_tmem + (uint32_t)(mt * BN), a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | h | k) != 0);
             }
           }
           tc_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
@@ -324,9 +304,8 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
     uint32_t acc_phase = 0;
     int acc = 0;
     pdl_wait();  // nothing is stored while the kernel before this one runs; a block without tiles waits too
-    for (int u = blockIdx.x; u < total_units; u += gridDim.x) {
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       int e, row0, rows, m0;
-      const int t = u / n_splits, slice = u - t * n_splits;
       locate(t, e, row0, rows, m0);
       // the whole warp takes one decision: the loads below need all 32 lanes
       if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[acc], (acc_phase >> acc) & 1u, abortp))) {
@@ -337,37 +316,6 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
       tc_fence_after();
       const int c_end = min(BN, (rows + 15) & ~15);
       const int unit_m0 = m0;
-      bool from_tmem = true;
-      const int my_row = quad * 32 + lane;
-      if (n_splits > 1) {
-        // this slice's partial sums go to memory ([column][row]: a warp writes 32 consecutive floats)
-        float* mine = p.partial + (size_t)(t * n_splits + slice) * BN * 128;
-        const uint32_t t_addr0 = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * S::kAccCols);
-#pragma unroll 1
-        for (int c = 0; c < c_end; c += 16) {
-          float v[16];
-          tmem_ld16(t_addr0 + c, v);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) mine[(c + i) * 128 + my_row] = v[i];
-        }
-        tc_fence_before();
-        __threadfence();
-        __syncwarp();
-        unsigned int before = 0;
-        if (lane == 0) {
-          mbar_arrive(&acc_empty[acc]);
-          before = atomicAdd(&p.arrivals[t * 4 + quad], 1u);
-        }
-        before = __shfl_sync(0xffffffffu, before, 0);
-        if (before != (unsigned)n_splits - 1u) {  // another slice's warp will write these rows
-          acc_phase ^= 1u << acc;
-          acc ^= 1;
-          continue;
-        }
-        __threadfence();
-        if (lane == 0) p.arrivals[t * 4 + quad] = 0;  // every slice has arrived: ready for the next launch
-        from_tmem = false;
-      }
       int last_mt = 0;  // the last feature tile of the unit that exists
 #pragma unroll
       for (int mt = 1; mt < S::kMT; ++mt)
@@ -379,22 +327,11 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
 #pragma unroll 1
       for (int c = 0; c < c_end; c += 16) {
         float v[16];
-        if (from_tmem) {
-          tmem_ld16(t_addr + c, v);
-          if (mt == last_mt && c + 16 >= c_end) {  // last read of this accumulator buffer: hand it back to the MMA warp
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[acc]);
-          }
-        } else {  // the slices' partial sums, added in slice order
-          const float* part = p.partial + (size_t)t * n_splits * BN * 128 + (size_t)c * 128 + my_row;
-#pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = __ldcg(part + i * 128);
-          for (int sl = 1; sl < n_splits; ++sl) {
-            part += (size_t)BN * 128;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] += __ldcg(part + i * 128);
-          }
+        tmem_ld16(t_addr + c, v);
+        if (mt == last_mt && c + 16 >= c_end) {  // last read of this accumulator buffer: hand it back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[acc]);
         }
         float (*tb)[33] = turn[quad];
         if (GATED) {
@@ -428,12 +365,8 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
           // route weights of this chunk's 16 tokens: lanes 0-15 fetch one each
           float wl = 0.f;
           if (lane < 16 && c + lane < rows) {
-            if (p.sorted_routes) {
-              const int route = p.sorted_routes[row0 + c + lane];
-              wl = (route >= 0 && route < p.n_routes) ? p.route_weights[route] : 0.f;
-            } else {
-              wl = 1.f;  // a plain product
-            }
+            const int route = p.sorted_routes[row0 + c + lane];
+            wl = (route >= 0 && route < p.n_routes) ? p.route_weights[route] : 0.f;
           }
 #pragma unroll
           for (int i = 0; i < 16; ++i) tb[i][lane] = v[i] * __shfl_sync(0xffffffffu, wl, i);
@@ -526,7 +459,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   // measured: 192 tiles (one token) are faster two CTAs to an SM, 384 (two tokens) already one deep pipeline per SM
-  if (likely_tiles > 2 * sms || !p.offsets) return launch_tc_impl<BN, GATED, true>(ma, mb, p, max_tiles, s);
+  if (likely_tiles > 2 * sms) return launch_tc_impl<BN, GATED, true>(ma, mb, p, max_tiles, s);
   return launch_tc_impl<BN, GATED, false>(ma, mb, p, max_tiles, s);
 }
 
@@ -540,37 +473,12 @@ static int run_tc(const void* x, int x_cols, const void* w, int w_rows, const Tc
     depth_env = v ? atoi(v) : 0;
   }
   p.depth = depth_env;  // 0: the variant's own choice
-  if (p.k_splits < 1) p.k_splits = 1;
-  static float* partial = nullptr;
-  static unsigned int* arrivals = nullptr;
-  if (!partial) {
-    cudaGetSymbolAddress((void**)&partial, g_tc_partial);
-    cudaGetSymbolAddress((void**)&arrivals, g_tc_arrivals);
-  }
-  p.partial = partial;
-  p.arrivals = arrivals;
   // TMA needs 16-byte row strides; the epilogue stores 8 features at a time; the gate/up interleave
   // works on groups of 16 features
   if (x_cols % 8 != 0 || p.n_out % 8 != 0 || p.n_experts > kMaxExperts) return -1;
   if (GATED && p.n_out % 16 != 0) return -1;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -1;
-  const int bn = p.offsets ? pick_bn(p.n_routes, p.n_experts)
-                           : (p.dense_rows <= 16 ? 16 : (p.dense_rows <= 32 ? 32 : 64));
-  if (!p.offsets) {
-    // one plain product of a few rows: cut k so that every SM gets a unit of work
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int tiles = ((p.dense_rows + bn - 1) / bn) * p.m_tiles;
-    const int k_blocks = (x_cols + 2 * kBK - 1) / (2 * kBK);  // the one-CTA-per-SM variants take 128 of k per stage
-    int splits = tiles > 0 ? sms / tiles : 1;
-    if (splits > k_blocks / 2) splits = k_blocks / 2;  // at least two stages of work per slice
-    if (splits < 1) splits = 1;
-    const int per = (k_blocks + splits - 1) / splits;
-    splits = (k_blocks + per - 1) / per;  // no empty slice
-    if (bn > 64 || tiles * 4 > kArrivalSlots || (long long)tiles * splits * bn * 128 > kPartialFloats) splits = 1;
-    p.k_splits = splits;
-  }
+  const int bn = pick_bn(p.n_routes, p.n_experts);
   CUtensorMap ma, mb;
   const uint64_t K = (uint64_t)x_cols;
   if (GATED) {
@@ -602,7 +510,7 @@ static int run_tc(const void* x, int x_cols, const void* w, int w_rows, const Tc
       return 4;
     }
   }
-  const int max_tiles = ((p.n_routes + bn - 1) / bn + p.n_experts) * p.m_tiles * p.k_splits;
+  const int max_tiles = ((p.n_routes + bn - 1) / bn + p.n_experts) * p.m_tiles;
   // token tiles when the routes spread evenly: experts that got rows, each with its share of tiles
   const int busy = p.n_routes < p.n_experts ? p.n_routes : p.n_experts;
   const int per_expert = (p.n_routes / (busy > 0 ? busy : 1) + bn - 1) / bn;
@@ -633,27 +541,6 @@ static int g_tc_enabled = 1;
 extern "C" int ftk_set_moe_tensor_cores(int enabled) {
   g_tc_enabled = enabled ? 1 : 0;
   return 0;
-}
-
-// out[T, n_out] = x[T, k] w[n_out, k]^T for a step of a few tokens, on the grouped kernel as one expert
-// whose k is cut into slices.  Returns -1 where the sizes are not taken (the caller uses the library).
-extern "C" int ftk_dense_tc_fits(int n_tokens, int n_out, int k) {
-  return n_tokens >= 1 && n_tokens <= 64 && n_out >= 8 && n_out % 8 == 0 && k >= 8 && k % 8 == 0;
-}
-
-extern "C" int ftk_dense_tc(const void* x, const void* w, void* out, int n_tokens, int n_out, int k, void* stream) {
-  FTK_REQUIRE(ftk_dense_tc_fits(n_tokens, n_out, k),
-              "dense_tc: %d tokens, %d features, k = %d: takes 1 to 64 tokens, features and k multiples of 8", n_tokens,
-              n_out, k);
-  FTK_REQUIRE(x && w && out, "dense_tc: null pointer");
-  FTK_REQUIRE((((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) == 0, "dense_tc: 16-byte aligned tensors only");
-  TcParams p{};
-  p.offsets = nullptr; p.dense_rows = n_tokens; p.n_experts = 1; p.K = k; p.n_out = n_out;
-  p.m_tiles = (n_out + 127) / 128; p.n_routes = n_tokens;
-  p.sorted_routes = nullptr; p.route_weights = nullptr; p.out = (__nv_bfloat16*)out;
-  const int rc = run_tc<false>(x, k, w, n_out, p, (cudaStream_t)stream, "dense_tc (tcgen05)");
-  FTK_REQUIRE(rc >= 0, "dense_tc: the tensor-core kernel does not take these tensors");
-  return rc;
 }
 
 int ftk_moe_gemm1_act_tc(const void* x_sorted, const void* w1, const int32_t* expert_offsets, int n_experts,

@@ -4,7 +4,6 @@
     python -m freetoken_b200.kernels.microbench attention --batch 8 --context 2048
     python -m freetoken_b200.kernels.microbench attention --prefill 2048
     python -m freetoken_b200.kernels.microbench sample --rows 8 --vocab 200064
-    python -m freetoken_b200.kernels.microbench dense --tokens 8 --n 8192 --k 3072
 
 Each case allocates its inputs once (larger than L2 where the real workload is), warms up, then
 times ``--iters`` launches with CUDA events and prints one JSON line: time, the bytes the kernel has
@@ -136,31 +135,6 @@ def bench_attention(a) -> dict:
             "tensor_frac": round(flops / us / 1e6 / BF16_TFLOPS, 3)}
 
 
-def bench_dense(a) -> dict:
-    """The sliced tensor-core product against the library's, over several copies of the weight so
-    that none of it stays in L2 between launches."""
-    dev = "cuda"
-    T, N, K = a.tokens, a.n, a.k
-    copies = max(2, int(400e6 // (N * K * 2)) + 1)
-    g = torch.Generator(device=dev).manual_seed(0)
-    ws = [torch.empty(N, K, dtype=torch.bfloat16, device=dev).normal_(0, 0.02, generator=g) for _ in range(copies)]
-    x = torch.randn(T, K, device=dev, generator=g).to(torch.bfloat16)
-    out = torch.empty(T, N, dtype=torch.bfloat16, device=dev)
-    res = {}
-    for name, fn in (("kernel", lambda w: ops.dense_tc(x, w, out)), ("library", lambda w: torch.matmul(x, w.t(), out=out))):
-        if name == "kernel" and not ops.dense_tc_fits(T, N, K):
-            continue
-
-        def many():
-            for w in ws:
-                fn(w)
-
-        us = _time(many, a.iters, a.warmup, a.profile) / copies
-        res[name] = {"us": round(us, 2), "gbs": round(N * K * 2 / us / 1e3, 1), "hbm_frac": round(N * K * 2 / us / 1e3 / HBM_GBS, 3)}
-    res["status"] = ops.read_status()
-    return res
-
-
 def bench_sample(a) -> dict:
     dev = "cuda"
     logits = torch.randn(a.rows, a.vocab, device=dev)
@@ -177,7 +151,7 @@ def bench_sample(a) -> dict:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="microbench")
     sub = ap.add_subparsers(dest="case", required=True)
-    for name in ("moe", "attention", "sample", "dense"):
+    for name in ("moe", "attention", "sample"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=5)
@@ -189,10 +163,6 @@ def main(argv=None) -> int:
             p.add_argument("--inter", type=int, default=1536)
             p.add_argument("--top-k", type=int, default=8)
             p.add_argument("--only", choices=["gemm1", "gemm2"], default=None)
-        elif name == "dense":
-            p.add_argument("--tokens", type=int, default=8)
-            p.add_argument("--n", type=int, default=8192)
-            p.add_argument("--k", type=int, default=3072)
         elif name == "attention":
             p.add_argument("--batch", type=int, default=8)
             p.add_argument("--context", type=int, default=2048)
@@ -209,7 +179,7 @@ def main(argv=None) -> int:
             p.add_argument("--vocab", type=int, default=200064)
             p.add_argument("--temperature", type=float, default=0.0)
     a = ap.parse_args(argv)
-    res = {"moe": bench_moe, "attention": bench_attention, "sample": bench_sample, "dense": bench_dense}[a.case](a)
+    res = {"moe": bench_moe, "attention": bench_attention, "sample": bench_sample}[a.case](a)
     print(json.dumps({"case": a.case, **{k: v for k, v in vars(a).items() if k != "case"}, "result": res}))
     return 0
 

@@ -22,8 +22,7 @@ act_and_mul            activation.py:67-112
 sample                 python/freetoken/engine/sample.py:24-80, python/freetoken/kernel/triton/sampling.py
 moe_route              router product + router_topk + moe_permute in one launch (short steps)
 add_rmsnorm_routes     moe_combine + add_rmsnorm in one pass
-linear / dense_tc      python/freetoken/layers/linear.py:66-70 (library product, or the tcgen05
-                       kernel with k cut into slices for few tokens and few rows)
+linear                 python/freetoken/layers/linear.py:66-70 (the library product)
 copy_tokens            the sampled tokens of the step before, taken on the device
                        (python/freetoken/scheduler/scheduler.py:194-256, overlapped scheduling)
 =====================  ==========================================================
@@ -76,8 +75,6 @@ _SIGNATURES = {
     "ftk_sparse_select": [_vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "ftk_router_topk": [_vp, _vp, _i, _i, _i, _i, _f, _vp, _vp, _vp],
     "ftk_moe_permute": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp],
-    "ftk_dense_tc_fits": [_i, _i, _i],
-    "ftk_dense_tc": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "ftk_moe_route_fits": [_i, _i, _i, _i],
     "ftk_moe_route": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "ftk_moe_gather": [_vp, _i, _vp, _i, _i, _i, _vp, _vp],
@@ -457,48 +454,32 @@ def moe_permute(topk_ids: torch.Tensor, n_experts: int, expert_counts: torch.Ten
                                   _dev(route_pos, "route_pos", torch.int32), _stream()), "moe_permute", 2)
 
 
-# Where the sliced kernel beats the library product (measured on B200, bfloat16): steps of at most 32
-# tokens and weights of at most 32 tiles of 128 features, which leave the library with too few tiles
-# to fill the GPU (3072 x 6144: 14 against 16 to 18 microseconds; 8192 x 3072: 12 against 10).
-LINEAR_KERNEL_MAX_TOKENS = 32
-LINEAR_KERNEL_MAX_FEATURES = 32 * 128
+LINEAR_PAD_ROWS = 16
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """``out = x @ w^T`` (``x [T, K]``, ``w [N, K]``, ``out [T, N]``).
+    """``out = x @ w^T`` (``x [T, K]``, ``w [N, K]``, ``out [T, N]``) by the library, as in the reference
+    (python/freetoken/layers/linear.py:66-70).
 
-    Steps of a few tokens in bfloat16 whose weight has few rows and a long k run on this library's
-    tensor-core kernel, which cuts k into slices so that every SM streams a part of the weight;
-    everything else is the library matrix product, as in the reference
-    (python/freetoken/layers/linear.py:66-70)."""
+    For fewer than 16 rows of bfloat16 and a weight that is at least as long as it is tall, the
+    product is taken over 16 rows of the same buffers (the rows past ``T`` hold whatever the
+    buffers hold and their results are never read): measured on B200, the library's choice for 16
+    rows runs 3072 x 6144 in 10.9 microseconds, its choice for 8 rows in 16.6."""
     T, K = x.shape
     N = w.shape[0]
     if w.shape != (N, K) or out.shape != (T, N):
         raise KernelError("linear: shapes do not agree")
-    if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
-            and x.is_cuda and x.is_contiguous() and w.is_contiguous() and out.is_contiguous()
-            and (w.data_ptr() | x.data_ptr() | out.data_ptr()) % 16 == 0
-            and T <= LINEAR_KERNEL_MAX_TOKENS and N <= LINEAR_KERNEL_MAX_FEATURES and K >= 2 * N
-            and dense_tc_fits(T, N, K)):
-        dense_tc(x, w, out)
+    P = LINEAR_PAD_ROWS
+    if (T < P and K >= N and x.dtype == torch.bfloat16 and x.is_cuda and x.is_contiguous() and out.is_contiguous()
+            and _room(x) >= P * K and _room(out) >= P * N):
+        torch.matmul(x.as_strided((P, K), (K, 1)), w.t(), out=out.as_strided((P, N), (N, 1)))
     else:
         torch.matmul(x, w.t(), out=out)
 
 
-def dense_tc_fits(n_tokens: int, n_out: int, k: int) -> bool:
-    return bool(_lib().ftk_dense_tc_fits(n_tokens, n_out, k))
-
-
-def dense_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """``out = x @ w^T`` in bfloat16 with float32 accumulation for at most 64 tokens."""
-    T, K = x.shape
-    N = w.shape[0]
-    if w.shape != (N, K) or out.shape != (T, N):
-        raise KernelError("dense_tc: shapes do not agree")
-    for name, t in (("x", x), ("w", w), ("out", out)):
-        if t.dtype != torch.bfloat16 or not t.is_contiguous():
-            raise KernelError(f"dense_tc: {name} must be contiguous bfloat16")
-    _check(_lib().ftk_dense_tc(_dev(x, "x"), _dev(w, "w"), _dev(out, "out"), T, N, K, _stream()), "dense_tc")
+def _room(t: torch.Tensor) -> int:
+    """Elements from the tensor's first one to the end of its storage."""
+    return t.untyped_storage().nbytes() // t.element_size() - t.storage_offset()
 
 
 def moe_route_fits(n_tokens: int, hidden: int, n_experts: int, top_k: int) -> bool:

@@ -185,16 +185,12 @@ def moe_permute(topk_ids, n_experts, expert_counts, expert_offsets, sorted_route
     route_pos[order] = torch.arange(flat.numel(), dtype=torch.int32, device=flat.device)
 
 
+def linear(x, w, out):
+    out.copy_((x.float() @ w.float().T).to(out.dtype))
+
+
 def attention_tc_fits(head_dim, page_size, group):
     return False  # the CPU tests plan for the other kernels
-
-
-def dense_tc_fits(n_tokens, n_out, k):
-    return False  # the CPU tests take the library product
-
-
-def dense_tc(x, w, out):
-    out.copy_((x.float() @ w.float().T).to(out.dtype))
 
 
 def moe_route_fits(n_tokens, hidden, n_experts, top_k):
@@ -271,7 +267,7 @@ def sample(logits, temperature, top_k, top_p, u, out):
 
 
 ALL = ["copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "add_rmsnorm_routes", "act_and_mul", "cast", "table_update", "norm_rope_store",
-       "paged_attention", "router_topk", "moe_permute", "moe_route", "moe_route_fits", "dense_tc", "dense_tc_fits", "attention_tc_fits", "moe_gather", "moe_gemm1_act", "moe_gemm2",
+       "paged_attention", "router_topk", "moe_permute", "moe_route", "moe_route_fits", "linear", "attention_tc_fits", "moe_gather", "moe_gemm1_act", "moe_gemm2",
        "moe_combine", "sample"]
 
 

@@ -414,31 +414,23 @@ def test_router_topk(scoring, bias, T, E, k):
     torch.testing.assert_close(w, w2, rtol=1e-5, atol=1e-7)
 
 
-@pytest.mark.parametrize("T,N,K", [(1, 48, 64), (8, 8192, 3072), (13, 104, 200), (32, 3072, 6144), (5, 24, 40),
-                                   (16, 520, 1000), (3, 9000, 72), (64, 384, 2048), (40, 3072, 6144)])
-def test_dense_tc_matches_the_plain_product(T, N, K):
-    """The sliced tensor-core product for steps of a few tokens: feature counts and k that are
-    multiples of 8; run twice so that the arrival counters are seen to come back to zero; a token's
-    result is the same bits whatever else is in the step."""
-    assert ops.dense_tc_fits(T, N, K) and not ops.dense_tc_fits(65, N, K) and not ops.dense_tc_fits(T, N, K + 4)
-    x = rnd(T, K, dtype=torch.bfloat16)
-    w = rnd(N, K, dtype=torch.bfloat16, scale=K ** -0.5, seed=3)
-    want = x.float() @ w.float().T
-    for _ in range(2):
-        out = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
-        ops.dense_tc(x, w, out)
-        torch.testing.assert_close(out.float(), want, rtol=1e-2, atol=2e-3)
-    assert ops.read_status() == 0
-    alone = torch.empty(1, N, dtype=torch.bfloat16, device=DEV)
-    ops.dense_tc(x[-1:].contiguous(), w, alone)
-    assert torch.equal(alone[0], out[-1])
-    via = torch.empty_like(out)
-    ops.linear(x, w, via)  # the dispatcher: this kernel or the library product, by the sizes
-    torch.testing.assert_close(via.float(), want, rtol=1e-2, atol=2e-3)
-    big = rnd(70, K, dtype=torch.bfloat16, seed=9)  # more tokens than the kernel takes: the library product
-    out_big = torch.empty(70, N, dtype=torch.bfloat16, device=DEV)
-    ops.linear(big, w, out_big)
-    torch.testing.assert_close(out_big.float(), big.float() @ w.float().T, rtol=2e-2, atol=4e-3)
+@pytest.mark.parametrize("T,N,K,dtype", [(8, 96, 192, torch.bfloat16), (1, 64, 64, torch.bfloat16), (8, 192, 96, torch.bfloat16),
+                                         (20, 96, 192, torch.bfloat16), (5, 96, 192, torch.float32)])
+def test_linear_pads_few_rows_inside_its_buffers(T, N, K, dtype):
+    """Few bfloat16 rows against a long weight are multiplied as 16 rows of the same buffers: the rows
+    past T may hold anything (NaN here) and what lies behind the output rows is only overwritten where
+    the buffer has room; without room the product is taken as it is."""
+    w = rnd(N, K, dtype=dtype, scale=K ** -0.5, seed=3)
+    xbuf = torch.full((64, K), float("nan"), dtype=dtype, device=DEV)
+    obuf = torch.zeros(64, N, dtype=dtype, device=DEV)
+    xbuf[:T] = rnd(T, K, dtype=dtype)
+    ops.linear(xbuf[:T], w, obuf[:T])
+    want = xbuf[:T].float() @ w.float().T
+    torch.testing.assert_close(obuf[:T].float(), want, **tol(dtype))
+    assert not torch.isnan(obuf[:T]).any() and (obuf[max(16, T):] == 0).all()
+    tight_x, tight_o = xbuf[:T].clone(), torch.empty(T, N, dtype=dtype, device=DEV)  # no room to pad
+    ops.linear(tight_x, w, tight_o)
+    torch.testing.assert_close(tight_o.float(), want, **tol(dtype))
 
 
 @pytest.mark.parametrize("scoring,bias", [("sigmoid", True), ("softmax", False)])
