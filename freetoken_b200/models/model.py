@@ -38,7 +38,7 @@ def head_matmul(y: torch.Tensor, w: torch.Tensor, logits: torch.Tensor) -> None:
     if y.dtype == torch.float32:
         torch.matmul(y, w.t(), out=logits)
     else:
-        logits.copy_(torch.mm(y, w.t(), out_dtype=torch.float32))
+        torch.mm(y, w.t(), out=logits, out_dtype=torch.float32)
 
 
 class Model:
