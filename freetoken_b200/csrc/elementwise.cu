@@ -92,14 +92,23 @@ __global__ void add_rmsnorm_kernel(const XT* __restrict__ x, float* __restrict__
       if (residual) Vec4<float>::load(residual + src + i, z);
       if (x && route_pos) {
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int j = 0; j < top_k; ++j) {
-          const int p = __ldg(route_pos + (size_t)src_row * top_k + j);
-          if (p >= 0 && p < n_routes) {
-            float xv[4];
-            Vec4<XT>::load(x + (size_t)p * hidden + i, xv);
+        for (int j0 = 0; j0 < top_k; j0 += 8) {  // eight rows' loads in flight before the first is added
+          int ps[8];
+          float xv[8][4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) acc[q] += xv[q];
+          for (int u = 0; u < 8; ++u) ps[u] = j0 + u < top_k ? __ldg(route_pos + (size_t)src_row * top_k + j0 + u) : -1;
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            if (ps[u] >= 0 && ps[u] < n_routes) {
+              Vec4<XT>::load(x + (size_t)ps[u] * hidden + i, xv[u]);
+            } else {
+              xv[u][0] = xv[u][1] = xv[u][2] = xv[u][3] = 0.f;
+            }
           }
+#pragma unroll
+          for (int u = 0; u < 8; ++u)  // route order
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc[q] += xv[u][q];
         }
         if (shared) {
           float xv[4];
@@ -282,7 +291,9 @@ static int launch_norm(const void* x, float* residual, const float* weight, void
                        const int32_t* route_pos = nullptr, int top_k = 0, int n_routes = 0, const void* shared = nullptr) {
   const bool vec = hidden % 4 == 0 && aligned16(x) && aligned16(residual) && aligned16(weight) &&
                    aligned16(out) && aligned16(out_f32) && (hidden % 8 == 0) && aligned16(shared);
-  const int threads = hidden >= 2048 ? 256 : 128;
+  int threads = hidden >= 2048 ? 256 : 128;
+  // few rows: a thread per four elements, so that every load of a row is in flight at once
+  if (n_rows <= 64 && vec) threads = hidden / 4 >= 1024 ? 1024 : (hidden / 4 + 31) / 32 * 32 > threads ? (hidden / 4 + 31) / 32 * 32 : threads;
   const size_t smem = (size_t)hidden * sizeof(float);
   auto kv = add_rmsnorm_kernel<XT, OT, true>;
   auto ks = add_rmsnorm_kernel<XT, OT, false>;
