@@ -15,9 +15,9 @@
 // One CTA = 7 warps: warps 0 and 6 issue the TMA loads of keys and values, warp 1 the MMAs, warps 2-5 are the
 // softmax (and the epilogue: O / l to the output, or the partial sums of a split tile for the merge kernel).
 // Every wait is bounded; a timeout records a code in g_attn_status, lets copies land, frees TMEM, returns.
-// Key rows past the end of the request are never multiplied as they lie in memory (they may hold
-// anything): whole 16-key boxes past the end are not loaded (the stages start zeroed), and the rows
-// past the end inside the last box are zeroed in shared memory before the product.
+// Value rows past the end of the request are never multiplied as they lie in memory (they may hold
+// anything): whole 16-key boxes past the end are not loaded, and all rows of the stage past the end
+// are zeroed in shared memory before the product.
 //
 // The reference's prefill attention is a Triton kernel (python/freetoken/kernel/triton/attention.py:469-880).
 #pragma once
@@ -123,10 +123,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(&tmem_slot, 512);
-  // the value stages start zeroed: boxes past the end of the request are not loaded
-  for (int i = threadIdx.x; i < 2 * kTcTile / 16; i += blockDim.x)
-    reinterpret_cast<uint4*>(tiles + 3 * kTcTile)[i] = make_uint4(0u, 0u, 0u, 0u);
-  fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -222,11 +218,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         const int key0 = it.kb + i * kTcKeys;
         const int live = it.ke - key0;  // keys of the request in this tile
-        if (live < kTcKeys && (live & 15)) {
-          // the rows past the end inside the last loaded box: zero, whatever the page holds there
-          const int r0 = live, r1 = (live + 15) & ~15;
-          for (int x = lane; x < (r1 - r0) * 2 * 8; x += 32) {
-            const int r = r0 + x / 16, h = (x / 8) & 1, c = x & 7;
+        if (live < kTcKeys) {
+          // the value rows past the end of the request: zero, whatever the page holds there (the rest of
+          // the last loaded box) and whatever the stage held before (boxes that were not loaded)
+          for (int x = lane; x < (kTcKeys - live) * 16; x += 32) {
+            const int r = live + x / 16, h = (x / 8) & 1, c = x & 7;
             *reinterpret_cast<uint4*>(tiles + 3 * kTcTile + st * kTcTile + h * kTcHalf + r * 128 + c * 16) =
                 make_uint4(0u, 0u, 0u, 0u);
           }
