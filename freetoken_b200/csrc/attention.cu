@@ -220,59 +220,79 @@ __global__ void __launch_bounds__(kF32Rows * 32) attention_f32_kernel(AttnParams
 
 // ================================================================= merge of split tiles
 // out = sum_i acc_i e^(m_i - M) / sum_i l_i e^(m_i - M), splits taken in order.  The CTA of split s
-// merges the tile's rows s, s + n_splits, ...; a thread owns output columns and fetches the splits'
-// values eight at a time, so a row costs a few memory round trips however many splits there are.
+// merges the tile's rows s, s + n_splits, ...: a warp takes a row, a lane four output columns, and the
+// splits' values are fetched eight at a time, so a row costs a few memory round trips however many
+// splits there are.
 template <typename T>
 __global__ void attention_merge_kernel(AttnParams p) {
+  const Item it = load_item(p, blockIdx.x);  // the work list was made on the host before the step
   pdl_wait();
   pdl_trigger();
-  const Item it = load_item(p, blockIdx.x);
   if (!it.ok || it.nsplit <= 1) return;
   const int kvh = blockIdx.y;
   const int D = p.D, G = p.G;
   const int R = it.ntok * G;
   const int lane = threadIdx.x & 31;
   const size_t slot_step = (size_t)p.Hkv * p.tile_rows;
-  for (int r = it.split; r < R; r += it.nsplit) {
+  // a row per warp at a time (the rows of a block are independent, and each is three dependent trips
+  // to memory), four output elements per lane
+  const int warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  for (int r = it.split + warp * it.nsplit; r < R; r += it.nsplit * n_warps) {
     const size_t slot0 = ((size_t)it.base * p.Hkv + kvh) * p.tile_rows + r;
-    // weights of the splits, spread over the lanes of every warp (each warp computes them itself)
+    // weights of the splits, spread over the lanes
     float wgt[kMaxMergeSplits / 32];
+    float lsum[kMaxMergeSplits / 32];
     float M = -INFINITY;
 #pragma unroll
     for (int j = 0; j < kMaxMergeSplits / 32; ++j) {
       const int i = lane + 32 * j;
-      wgt[j] = i < it.nsplit ? p.part_ml[(slot0 + i * slot_step) * 2] : -INFINITY;
-      M = fmaxf(M, wgt[j]);
+      const float2 ml = i < it.nsplit ? *reinterpret_cast<const float2*>(p.part_ml + (slot0 + i * slot_step) * 2)
+                                      : make_float2(-INFINITY, 0.f);
+      wgt[j] = ml.x;
+      lsum[j] = ml.y;
+      M = fmaxf(M, ml.x);
     }
     M = warp_max(M);
     float L = 0.f;
 #pragma unroll
     for (int j = 0; j < kMaxMergeSplits / 32; ++j) {
-      const int i = lane + 32 * j;
-      const float w = (i < it.nsplit && wgt[j] != -INFINITY) ? expf(wgt[j] - M) : 0.f;
+      const float w = wgt[j] != -INFINITY ? expf(wgt[j] - M) : 0.f;
       wgt[j] = w;
-      if (i < it.nsplit) L += p.part_ml[(slot0 + i * slot_step) * 2 + 1] * w;
+      L += lsum[j] * w;
     }
     L = warp_sum(L);
     const float inv = L > 0.f ? 1.f / L : 0.f;
     const int tok = it.q_start + it.tok0 + r / G;
     T* o = (T*)p.out + ((size_t)tok * p.Hq + kvh * G + r % G) * D;
-    for (int d0 = 0; d0 < D; d0 += blockDim.x) {
-      const int d = d0 + threadIdx.x;
-      float acc = 0.f;
+    for (int d0 = 0; d0 < D; d0 += 128) {
+      const int d = d0 + 4 * lane;  // D is a multiple of 16: a lane's four elements exist together or not at all
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int i0 = 0; i0 < it.nsplit; i0 += 8) {  // eight loads in flight before the first use
-        float x[8], w[8];
+        float4 x[8];
+        float w[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
           const int i = i0 + u;
           const float wsrc = (i >> 5) ? wgt[1] : wgt[0];
           w[u] = __shfl_sync(0xffffffffu, wsrc, i & 31);
-          x[u] = (i < it.nsplit && d < D && w[u] != 0.f) ? p.part_o[(slot0 + i * slot_step) * D + d] : 0.f;
+          x[u] = (i < it.nsplit && d < D && w[u] != 0.f)
+                     ? *reinterpret_cast<const float4*>(p.part_o + (slot0 + i * slot_step) * D + d)
+                     : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
-        for (int u = 0; u < 8; ++u) acc += x[u] * w[u];
+        for (int u = 0; u < 8; ++u) {
+          acc.x += x[u].x * w[u];
+          acc.y += x[u].y * w[u];
+          acc.z += x[u].z * w[u];
+          acc.w += x[u].w * w[u];
+        }
       }
-      if (d < D) o[d] = from_float<T>(acc * inv);
+      if (d < D) {
+        o[d] = from_float<T>(acc.x * inv);
+        o[d + 1] = from_float<T>(acc.y * inv);
+        o[d + 2] = from_float<T>(acc.z * inv);
+        o[d + 3] = from_float<T>(acc.w * inv);
+      }
     }
   }
 }

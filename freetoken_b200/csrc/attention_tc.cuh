@@ -96,8 +96,6 @@ __device__ __forceinline__ uint32_t tc_pack(float lo, float hi) {
 __global__ void __launch_bounds__(kTcThreads)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, AttnParams p) {
-  pdl_wait();
-  pdl_trigger();
   extern __shared__ unsigned char dyn_smem[];
   __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2], pv_done[2];
   __shared__ uint32_t tmem_slot;
@@ -126,6 +124,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // barriers, TMEM and the work item (made on the host before the step) are set up while the kernel
+  // before this one still runs; what it wrote (queries, the new keys and values) is read from here on
+  pdl_wait();
+  pdl_trigger();
   const uint32_t tmem = tmem_slot;
   volatile int* abortp = &abort_flag;
   const int n_tiles = it.ok ? (it.ke - it.kb + kTcKeys - 1) / kTcKeys : 0;
