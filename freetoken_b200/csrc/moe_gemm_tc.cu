@@ -59,20 +59,15 @@ struct TcParams {
   int act;
   float alpha, limit;
   __nv_bfloat16* out;
-  int depth;                     // loads a CTA keeps in flight while every CTA has a tile (<= stages)
 };
 
 // DEEP: one CTA per SM (many tiles: each SM streams on its own, with a longer pipeline for the large
 // token tiles); otherwise two CTAs per SM (few tiles: more of them run at once).
 template <int BN, bool DEEP>
 struct Smem {
-  // Feature tiles per unit of work; with 2 they share every token tile that comes in.  Measured at 64
-  // to 256 tokens per expert: no faster than 1 (the weights, read once from memory, are what the time
-  // goes to), so 1 it is.
-  static constexpr int kMT = 1;
   // 64-element pieces of k per stage.  Two of them make every row of a weight tile a 256-byte read,
   // which the memory serves faster than twice 128 bytes (measured: 6.7 against 6.1 TB/s).
-  static constexpr int kAtoms = (DEEP && kMT == 1) ? 2 : 1;
+  static constexpr int kAtoms = DEEP ? 2 : 1;
   static constexpr int kStages = DEEP ? (BN <= 16 ? 5 : (BN <= 32 ? 4 : (BN <= 64 ? 4 : (BN <= 128 ? 3 : 2))))
                                       : (BN <= 16 ? 5 : (BN <= 128 ? 4 : 3));
   // loads kept in flight while every CTA streams (measured for the small token tiles: 144 KB per SM
@@ -80,8 +75,8 @@ struct Smem {
   static constexpr int kDepth = (DEEP && BN <= 16) ? 4 : kStages;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kBBoxRows = BN < 32 ? BN : 32;  // token rows per TMA box: only boxes with rows are loaded
-  static constexpr int kStageBytes = kAtoms * (kMT * kABytes + kBBytes);
-  static constexpr int kAccCols = kMT * BN;            // TMEM columns of one accumulator buffer
+  static constexpr int kStageBytes = kAtoms * (kABytes + kBBytes);
+  static constexpr int kAccCols = BN;                  // TMEM columns of one accumulator buffer
   static constexpr int kTmemCols = 2 * kAccCols < 32 ? 32 : 2 * kAccCols;
   static constexpr int kDynamic = kStages * kStageBytes + 1024;
 };
@@ -149,16 +144,15 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
-  const int m_units = (p.m_tiles + S::kMT - 1) / S::kMT;
-  const int total_tiles = tile_prefix[p.n_experts] * m_units;
+  const int total_tiles = tile_prefix[p.n_experts] * p.m_tiles;
   const int k_blocks = (p.K + S::kAtoms * kBK - 1) / (S::kAtoms * kBK);  // k past the end reads as zero
   volatile int* abortp = &abort_flag;
 
   constexpr int kFeat = GATED ? 64 : 128;  // output features of one feature tile
-  // unit of work -> expert, token tile, first feature
+  // tile -> expert, token tile, first feature
   auto locate = [&](int t, int& e, int& row0, int& rows, int& m0) {
-    const int g = t / m_units;
-    m0 = (t % m_units) * S::kMT * kFeat;
+    const int g = t / p.m_tiles;
+    m0 = (t % p.m_tiles) * kFeat;
     int lo = 0, hi = p.n_experts - 1;  // last e with tile_prefix[e] <= g
     while (lo < hi) {
       const int mid = (lo + hi + 1) >> 1;
@@ -181,29 +175,26 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
       bool ok = true;
       const int full_waves = total_tiles / (int)gridDim.x * (int)gridDim.x;
       const bool thin_tail = 2 * (total_tiles - full_waves) <= (int)gridDim.x;
-      const int depth_main = p.depth > 0 ? min(p.depth, S::kStages) : S::kDepth;
+      const int depth_main = S::kDepth;
       auto stage_bytes = [&](int rows) {
         const int nb = (rows + S::kBBoxRows - 1) / S::kBBoxRows;
-        return (uint32_t)(S::kAtoms * (S::kMT * kABytes + nb * S::kBBoxRows * kBK * 2));
+        return (uint32_t)(S::kAtoms * (kABytes + nb * S::kBBoxRows * kBK * 2));
       };
       auto load_a = [&](int s, int kb, int m0, int e) {
         unsigned char* a = tiles + s * S::kStageBytes;
 #pragma unroll
         for (int h = 0; h < S::kAtoms; ++h) {
           const int k0 = (kb * S::kAtoms + h) * kBK;
-#pragma unroll
-          for (int mt = 0; mt < S::kMT; ++mt) {  // a feature tile past the end reads as zero
-            unsigned char* dst = a + (h * S::kMT + mt) * kABytes;
-            if (GATED) {  // (k, row in group, gate|up, group of 16 features, expert)
-              tma_load_5d(dst, &map_a, &full_bar[s], k0, 0, 0, (m0 + mt * kFeat) >> 4, e);
-            } else {
-              tma_load_3d(dst, &map_a, &full_bar[s], k0, m0 + mt * kFeat, e);
-            }
+          unsigned char* dst = a + h * kABytes;  // weight rows past the expert's last read as zero
+          if (GATED) {  // (k, row in group, gate|up, group of 16 features, expert)
+            tma_load_5d(dst, &map_a, &full_bar[s], k0, 0, 0, m0 >> 4, e);
+          } else {
+            tma_load_3d(dst, &map_a, &full_bar[s], k0, m0, e);
           }
         }
       };
       auto load_b = [&](int s, int kb, int row0, int rows) {
-        unsigned char* b = tiles + s * S::kStageBytes + S::kAtoms * S::kMT * kABytes;
+        unsigned char* b = tiles + s * S::kStageBytes + S::kAtoms * kABytes;
         const int nb = (rows + S::kBBoxRows - 1) / S::kBBoxRows;
 #pragma unroll
         for (int h = 0; h < S::kAtoms; ++h)
@@ -277,14 +268,11 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
           const uint32_t a_addr = tiles_base + s * S::kStageBytes;
 #pragma unroll
           for (int h = 0; h < S::kAtoms; ++h) {
-            const uint64_t b_desc = smem_desc(a_addr + S::kAtoms * S::kMT * kABytes + h * S::kBBytes);
+            const uint64_t b_desc = smem_desc(a_addr + S::kAtoms * kABytes + h * S::kBBytes);
+            const uint64_t a_desc = smem_desc(a_addr + h * kABytes);
 #pragma unroll
-            for (int mt = 0; mt < S::kMT; ++mt) {
-              const uint64_t a_desc = smem_desc(a_addr + (h * S::kMT + mt) * kABytes);
-#pragma unroll
-              for (int k = 0; k < kBK / 16; ++k)  // 16 k elements = 32 bytes = 2 descriptor units
-                tc_mma(d_tmem + (uint32_t)(mt * BN), a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | h | k) != 0);
-            }
+            for (int k = 0; k < kBK / 16; ++k)  // 16 k elements = 32 bytes = 2 descriptor units
+              tc_mma(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | h | k) != 0);
           }
           tc_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
           if (++s == S::kStages) {
@@ -315,20 +303,12 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
       }
       tc_fence_after();
       const int c_end = min(BN, (rows + 15) & ~15);
-      const int unit_m0 = m0;
-      int last_mt = 0;  // the last feature tile of the unit that exists
-#pragma unroll
-      for (int mt = 1; mt < S::kMT; ++mt)
-        if (unit_m0 + mt * kFeat < p.n_out) last_mt = mt;
-#pragma unroll 1
-      for (int mt = 0; mt <= last_mt; ++mt) {
-      m0 = unit_m0 + mt * kFeat;
-      const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * S::kAccCols + mt * BN);
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * S::kAccCols);
 #pragma unroll 1
       for (int c = 0; c < c_end; c += 16) {
         float v[16];
         tmem_ld16(t_addr + c, v);
-        if (mt == last_mt && c + 16 >= c_end) {  // last read of this accumulator buffer: hand it back to the MMA warp
+        if (c + 16 >= c_end) {  // last read of this accumulator buffer: hand it back to the MMA warp
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -391,7 +371,6 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
           }
           __syncwarp();
         }
-      }
       }
       acc_phase ^= 1u << acc;
       acc ^= 1;
@@ -464,15 +443,8 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
 }
 
 template <bool GATED>
-static int run_tc(const void* x, int x_cols, const void* w, int w_rows, const TcParams& p0, cudaStream_t s,
+static int run_tc(const void* x, int x_cols, const void* w, int w_rows, const TcParams& p, cudaStream_t s,
                   const char* name) {
-  TcParams p = p0;
-  static int depth_env = -1;
-  if (depth_env < 0) {
-    const char* v = getenv("FTK_TC_DEPTH");
-    depth_env = v ? atoi(v) : 0;
-  }
-  p.depth = depth_env;  // 0: the variant's own choice
   // TMA needs 16-byte row strides; the epilogue stores 8 features at a time; the gate/up interleave
   // works on groups of 16 features
   if (x_cols % 8 != 0 || p.n_out % 8 != 0 || p.n_experts > kMaxExperts) return -1;
