@@ -145,6 +145,19 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
   const int total_tiles = tile_prefix[p.n_experts] * p.m_tiles;
+  // Tiles are dealt out in turns.  A last turn with a tile for only a few CTAs costs about two thirds of
+  // a whole turn (a lone SM streams a tile at about 70 GB/s, not much faster than its share when all
+  // SMs stream).  Where that costs more than it, only as many CTAs take part as fill every turn: with
+  // 1,344 tiles on 148 SMs, 135 CTAs take ten tiles each instead of 148 taking nine and twelve of them
+  // a tenth.  The others leave at once.  Costs are counted in tile times of a full turn.
+  const int all = (int)gridDim.x;
+  const int turns = (total_tiles + all - 1) / all;
+  const int even = turns > 0 ? (total_tiles + turns - 1) / turns : 1;
+  const int rest = total_tiles % all;
+  const int cost_all = total_tiles - rest + (rest ? max(rest, 2 * all / 3) : 0);
+  // (one CTA per SM and the small token tiles only: that is where it was measured)
+  const int G = (DEEP && BN <= 32 && turns * even < cost_all) ? even : all;
+  const int t_first = (int)blockIdx.x < G ? (int)blockIdx.x : total_tiles;
   const int k_blocks = (p.K + S::kAtoms * kBK - 1) / (S::kAtoms * kBK);  // k past the end reads as zero
   volatile int* abortp = &abort_flag;
 
@@ -173,8 +186,8 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
       // by the latency of its own loads.
       int i = 0;
       bool ok = true;
-      const int full_waves = total_tiles / (int)gridDim.x * (int)gridDim.x;
-      const bool thin_tail = 2 * (total_tiles - full_waves) <= (int)gridDim.x;
+      const int full_waves = total_tiles / G * G;
+      const bool thin_tail = 2 * (total_tiles - full_waves) <= G;
       const int depth_main = S::kDepth;
       auto stage_bytes = [&](int rows) {
         const int nb = (rows + S::kBBoxRows - 1) / S::kBBoxRows;
@@ -204,9 +217,9 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
       };
       // the weights of the first loads, while the kernel before this one may still be running
       int ahead = 0;
-      if ((int)blockIdx.x < total_tiles) {
+      if (t_first < total_tiles) {
         int e, row0, rows, m0;
-        locate(blockIdx.x, e, row0, rows, m0);
+        locate(t_first, e, row0, rows, m0);
         ahead = min(depth_main, k_blocks);
         for (int kb = 0; kb < ahead; ++kb) {
           mbar_expect_tx(&full_bar[kb], stage_bytes(rows));
@@ -217,12 +230,12 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
       } else {
         pdl_wait();
       }
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = t_first; t < total_tiles && ok; t += G) {
         int e, row0, rows, m0;
         locate(t, e, row0, rows, m0);
         const int depth = (t >= full_waves && thin_tail) ? S::kStages : depth_main;
         for (int kb = 0; kb < k_blocks; ++kb, ++i) {
-          if (t == (int)blockIdx.x && kb < ahead) continue;  // already on its way
+          if (t == t_first && kb < ahead) continue;  // already on its way
           const int j = i - depth;  // the load whose stage must have been read before load i goes out
           if (j >= 0 && !mbar_wait(&empty_bar[j % S::kStages], (uint32_t)(j / S::kStages) & 1u, abortp)) {
             ok = false;
@@ -245,7 +258,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
       uint32_t acc_phase = 0;  // bit a: phase of accumulator buffer a
       int acc = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = t_first; t < total_tiles && ok; t += G) {
         if (!mbar_wait(&acc_empty[acc], ((acc_phase >> acc) & 1u) ^ 1u, abortp)) {
           atomicCAS(&g_status[0], 0, 102);
           abort_flag = 1;
@@ -292,7 +305,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
     uint32_t acc_phase = 0;
     int acc = 0;
     pdl_wait();  // nothing is stored while the kernel before this one runs; a block without tiles waits too
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    for (int t = t_first; t < total_tiles; t += G) {
       int e, row0, rows, m0;
       locate(t, e, row0, rows, m0);
       // the whole warp takes one decision: the loads below need all 32 lanes
