@@ -133,6 +133,28 @@ norm_rope_store_vec_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, in
     if (slot < 0 || slot >= (long long)S.num_pages * S.page_size) store = false;  // not stored
   }
   const __nv_bfloat16* src = x + (size_t)t * row_elems + (size_t)(S.first_head + hl) * kHeadDim + l * 8;
+  // everything this thread reads is asked for before the first use: the row, the norm weight, and the
+  // two runs of eight table entries of its rotation (cos | sin halves of the position's row)
+  const int half = rotary_dim >> 1;
+  const bool rot = S.rotate && rotary_dim > 0;
+  const bool low = l * 8 < half, in = l * 8 < rotary_dim;
+  float w[8], ca[8], cb[8];
+  if (S.norm_weight) {
+    *reinterpret_cast<float4*>(w) = *reinterpret_cast<const float4*>(S.norm_weight + l * 8);
+    *reinterpret_cast<float4*>(w + 4) = *reinterpret_cast<const float4*>(S.norm_weight + l * 8 + 4);
+  }
+  if (rot && in) {
+    int pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float* cs = rope_table + (size_t)pos * rotary_dim;
+    const int d0 = l * 8;
+    const float* a = low ? cs + d0 : cs + d0 - half;  // cos of this element's pair
+    const float* b = low ? cs + half + d0 : cs + d0;  // sin of this element's pair
+    *reinterpret_cast<float4*>(ca) = *reinterpret_cast<const float4*>(a);
+    *reinterpret_cast<float4*>(ca + 4) = *reinterpret_cast<const float4*>(a + 4);
+    *reinterpret_cast<float4*>(cb) = *reinterpret_cast<const float4*>(b);
+    *reinterpret_cast<float4*>(cb + 4) = *reinterpret_cast<const float4*>(b + 4);
+  }
   float v[8];
   {
     uint4 raw = make_uint4(0u, 0u, 0u, 0u);
@@ -156,18 +178,13 @@ norm_rope_store_vec_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, in
     if (S.norm_weight) {
       const float inv = rsqrtf(ss / (float)kHeadDim + eps);
       const float one = gemma ? 1.f : 0.f;
-      float w[8];
-      *reinterpret_cast<float4*>(w) = *reinterpret_cast<const float4*>(S.norm_weight + l * 8);
-      *reinterpret_cast<float4*>(w + 4) = *reinterpret_cast<const float4*>(S.norm_weight + l * 8 + 4);
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = v[j] * inv * (w[j] + one);
     }
   }
   {
     // rotation partners: the lane half a rotary span away, on either side
-    const int half = rotary_dim >> 1, hop = half >> 3;  // lanes per half span
-    const bool rot = S.rotate && rotary_dim > 0;
-    const bool low = l * 8 < half, in = l * 8 < rotary_dim;
+    const int hop = half >> 3;  // lanes per half span
     float partner[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -176,16 +193,8 @@ norm_rope_store_vec_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, in
       partner[j] = low ? up : dn;
     }
     if (rot && in) {
-      int pos = positions[t];
-      pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
-      const float* cs = rope_table + (size_t)pos * rotary_dim;
-      const int d0 = l * 8;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int d = d0 + j;
-        if (low) v[j] = v[j] * cs[d] - partner[j] * cs[half + d];
-        else v[j] = v[j] * cs[d - half] + partner[j] * cs[d];
-      }
+      for (int j = 0; j < 8; ++j) v[j] = low ? v[j] * ca[j] - partner[j] * cb[j] : v[j] * ca[j] + partner[j] * cb[j];
     }
   }
   if (!store) return;
