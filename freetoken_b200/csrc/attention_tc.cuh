@@ -97,20 +97,31 @@ __global__ void __launch_bounds__(kTcThreads)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, AttnParams p) {
   extern __shared__ unsigned char dyn_smem[];
-  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2], pv_done[2];
+  __shared__ uint64_t q_full, q_empty, o_free, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2],
+      p_full[2], pv_done[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // long tiles first: the grid runs in block order and the tiles of a segment grow with the token index
-  const Item it = load_item(p, (int)gridDim.x - 1 - (int)blockIdx.x);
-  const int kvh = blockIdx.y;
+  // A CTA works through one piece of work of every round of gridDim.x pieces: piece w is the tile
+  // (or part of a tile) n_items - 1 - w / Hkv (long tiles first: they grow with the token index) for
+  // KV head w % Hkv.  The three roles below run through the same pieces on their own, held together
+  // only by the barriers, so the loads and the first product of a piece run under the end of the one before.
+  // Rounds run to and fro over the CTAs (the work is sorted by length, so the CTA that gets the longest
+  // piece of one round gets the shortest of the next).
+  const int n_work = p.n_items * p.Hkv;
+  const int n_rounds = (n_work + (int)gridDim.x - 1) / (int)gridDim.x;
+  auto piece = [&](int i) {
+    return i * (int)gridDim.x + ((i & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
+  };
   const uint32_t base = (smem_addr(dyn_smem) + 1023u) & ~1023u;
   unsigned char* tiles = dyn_smem + (base - smem_addr(dyn_smem));
   const uint32_t q_s = base, k_s = base + kTcTile, v_s = base + 3 * kTcTile, p_s = base + 5 * kTcTile;
 
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
+    mbar_init(&q_empty, 1);
+    mbar_init(&o_free, 4);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
@@ -130,8 +141,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   pdl_trigger();
   const uint32_t tmem = tmem_slot;
   volatile int* abortp = &abort_flag;
-  const int n_tiles = it.ok ? (it.ke - it.kb + kTcKeys - 1) / kTcKeys : 0;
   const int G = p.G;
+  auto tiles_of = [](const Item& it) { return it.ok ? (it.ke - it.kb + kTcKeys - 1) / kTcKeys : 0; };
   auto fail = [&](int code) {
     atomicCAS(&g_attn_status[0], 0, code);
     abort_flag = 1;
@@ -143,125 +154,165 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // warp instruction issues a whole tile and every lane looks its own page up.  (One thread issuing
     // the boxes of a tile one after the other took longer than the tile's products; keys and values in
     // one warp made the keys wait for the value stage.)
-    if (n_tiles > 0 && lane < 16) {
+    if (lane < 16) {
       const int kv = warp == 6, box = lane >> 1, h = lane & 1;
-      if (lane == 0 && !kv) {
-        mbar_expect_tx(&q_full, (uint32_t)(2 * 128 * G * (kTcRows / G)));  // two boxes of (64, group, tokens per tile)
-        for (int hh = 0; hh < 2; ++hh)  // (d, head, token): rows land as token-major, head-minor
-          tma_load_3d(tiles + hh * kTcHalf, &map_q, &q_full, hh * 64, kvh * G, it.q_start + it.tok0);
-      }
-      const int32_t* bt = p.block_table + (size_t)it.bt_row * p.bt_stride;
       const CUtensorMap* map = kv ? &map_v : &map_k;
       uint64_t* full = kv ? v_full : k_full;
       uint64_t* empty = kv ? v_empty : k_empty;
       unsigned char* stage0 = tiles + (kv ? 3 : 1) * kTcTile + h * kTcHalf + box * 2048;
       bool ok = true;
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t par = ((j >> 1) & 1) ^ 1;
-        const int key0 = it.kb + j * kTcKeys;
-        const int n_box = min(8, (it.ke - key0 + 15) >> 4);  // boxes of 16 keys that hold keys of the request
-        const int key = key0 + 16 * box;
-        int page = 0;
-        if (box < n_box) {
-          const int slot = key / p.P;
-          page = slot < p.bt_stride ? bt[slot] : 0;
-          if (page < 0 || page >= p.num_pages) page = 0;
+      int g = 0;   // tiles of all pieces so far: stage g & 1
+      int qi = 0;  // pieces with tiles so far
+      for (int i_round = 0; i_round < n_rounds && ok; ++i_round) {
+      const int w = piece(i_round);
+      if (w >= n_work) continue;
+        const Item it = load_item(p, p.n_items - 1 - w / p.Hkv);
+        const int kvh = w % p.Hkv;
+        const int n_tiles = tiles_of(it);
+        if (n_tiles == 0) continue;
+        if (!kv) {  // the queries, once the products of the piece before have read theirs
+          if (!__all_sync(0x0000ffffu, mbar_wait(&q_empty, (uint32_t)(qi & 1) ^ 1u, abortp))) {
+            if (lane == 0) fail(210);
+            ok = false;
+            break;
+          }
+          if (lane == 0) {
+            mbar_expect_tx(&q_full, (uint32_t)(2 * 128 * G * (kTcRows / G)));  // two boxes of (64, group, tokens per tile)
+            for (int hh = 0; hh < 2; ++hh)  // (d, head, token): rows land as token-major, head-minor
+              tma_load_3d(tiles + hh * kTcHalf, &map_q, &q_full, hh * 64, kvh * G, it.q_start + it.tok0);
+          }
         }
-        const int row = (page * p.Hkv + kvh) * p.P + key % p.P;
-        if (!__all_sync(0x0000ffffu, mbar_wait(&empty[st], par, abortp))) {
-          if (lane == 0) fail(201 + kv);
-          ok = false;
-          break;
+        ++qi;
+        const int32_t* bt = p.block_table + (size_t)it.bt_row * p.bt_stride;
+        for (int j = 0; j < n_tiles && ok; ++j, ++g) {
+          const int st = g & 1;
+          const uint32_t par = ((g >> 1) & 1) ^ 1;
+          const int key0 = it.kb + j * kTcKeys;
+          const int n_box = min(8, (it.ke - key0 + 15) >> 4);  // boxes of 16 keys that hold keys of the request
+          const int key = key0 + 16 * box;
+          int page = 0;
+          if (box < n_box) {
+            const int slot = key / p.P;
+            page = slot < p.bt_stride ? bt[slot] : 0;
+            if (page < 0 || page >= p.num_pages) page = 0;
+          }
+          const int row = (page * p.Hkv + kvh) * p.P + key % p.P;
+          if (!__all_sync(0x0000ffffu, mbar_wait(&empty[st], par, abortp))) {
+            if (lane == 0) fail(201 + kv);
+            ok = false;
+            break;
+          }
+          if (lane == 0) mbar_expect_tx(&full[st], (uint32_t)n_box * 2 * 2048);
+          __syncwarp(0x0000ffffu);
+          if (box < n_box) tma_load_2d(stage0 + st * kTcTile, map, &full[st], h * 64, row);
         }
-        if (lane == 0) mbar_expect_tx(&full[st], (uint32_t)n_box * 2 * 2048);
-        __syncwarp(0x0000ffffu);
-        if (box < n_box) tma_load_2d(stage0 + st * kTcTile, map, &full[st], h * 64, row);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (lane 0); the warp zeroes value rows past the end
     constexpr uint32_t idesc_qk = instr_desc(kTcKeys);
     constexpr uint32_t idesc_pv = instr_desc(kTcD) | (1u << 16);  // B (values) MN-major
-    bool ok = n_tiles > 0;
-    if (ok && !mbar_wait(&q_full, 0, abortp)) {
-      if (lane == 0) fail(203);
-      ok = false;
-    }
-    for (int j = 0; j <= n_tiles && ok; ++j) {
-      if (j < n_tiles) {
-        const int st = j & 1;
-        const uint32_t par = (j >> 1) & 1;
-        if (!mbar_wait(&k_full[st], par, abortp) || !mbar_wait(&s_empty[st], par ^ 1, abortp)) {
-          if (lane == 0) fail(204);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        if (lane == 0) {
-          const uint32_t d = tmem + (uint32_t)(st * kTcKeys);
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {  // 16 elements of the head dimension per MMA
-            const uint64_t a = smem_desc(q_s + (kk >> 2) * kTcHalf) + 2 * (kk & 3);
-            const uint64_t b = smem_desc(k_s + st * kTcTile + (kk >> 2) * kTcHalf) + 2 * (kk & 3);
-            tc_mma(d, a, b, idesc_qk, kk != 0);
-          }
-          tc_commit(&k_empty[st]);
-          tc_commit(&s_full[st]);
-        }
-        __syncwarp();
+    bool ok = true;
+    int g0 = 0;  // tiles of the pieces before this one
+    int qi = 0;  // pieces with tiles before this one
+    for (int i_round = 0; i_round < n_rounds && ok; ++i_round) {
+      const int w = piece(i_round);
+      if (w >= n_work) continue;
+      const Item it = load_item(p, p.n_items - 1 - w / p.Hkv);
+      const int n_tiles = tiles_of(it);
+      if (n_tiles == 0) continue;
+      if (!mbar_wait(&q_full, (uint32_t)(qi & 1), abortp)) {
+        if (lane == 0) fail(203);
+        ok = false;
+        break;
       }
-      if (j >= 1) {
-        const int i = j - 1, st = i & 1;
-        if (!mbar_wait(&p_full[st], (uint32_t)((i >> 1) & 1), abortp) || !mbar_wait(&v_full[st], (uint32_t)((i >> 1) & 1), abortp)) {
-          if (lane == 0) fail(205);
-          ok = false;
-          break;
-        }
-        const int key0 = it.kb + i * kTcKeys;
-        const int live = it.ke - key0;  // keys of the request in this tile
-        if (live < kTcKeys) {
-          // the value rows past the end of the request: zero, whatever the page holds there (the rest of
-          // the last loaded box) and whatever the stage held before (boxes that were not loaded)
-          for (int x = lane; x < (kTcKeys - live) * 16; x += 32) {
-            const int r = live + x / 16, h = (x / 8) & 1, c = x & 7;
-            *reinterpret_cast<uint4*>(tiles + 3 * kTcTile + st * kTcTile + h * kTcHalf + r * 128 + c * 16) =
-                make_uint4(0u, 0u, 0u, 0u);
+      for (int j = 0; j <= n_tiles && ok; ++j) {
+        if (j < n_tiles) {
+          const int g = g0 + j, st = g & 1;
+          const uint32_t par = (g >> 1) & 1;
+          if (!mbar_wait(&k_full[st], par, abortp) || !mbar_wait(&s_empty[st], par ^ 1, abortp)) {
+            if (lane == 0) fail(204);
+            ok = false;
+            break;
           }
-          fence_async_smem();
-        }
-        __syncwarp();
-        tc_fence_after();
-        if (lane == 0) {
-          const uint32_t d = tmem + 2 * kTcKeys;
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t d = tmem + (uint32_t)(st * kTcKeys);
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {  // 16 keys per MMA
-            const uint64_t a = smem_desc(p_s + st * kTcTile + (kk >> 2) * kTcHalf) + 2 * (kk & 3);
-            const uint64_t b = smem_desc_mn(v_s + st * kTcTile + kk * 2048, kTcHalf);
-            tc_mma(d, a, b, idesc_pv, (i | kk) != 0);
+            for (int kk = 0; kk < 8; ++kk) {  // 16 elements of the head dimension per MMA
+              const uint64_t a = smem_desc(q_s + (kk >> 2) * kTcHalf) + 2 * (kk & 3);
+              const uint64_t b = smem_desc(k_s + st * kTcTile + (kk >> 2) * kTcHalf) + 2 * (kk & 3);
+              tc_mma(d, a, b, idesc_qk, kk != 0);
+            }
+            tc_commit(&k_empty[st]);
+            tc_commit(&s_full[st]);
+            if (j == n_tiles - 1) tc_commit(&q_empty);  // the next piece's queries may come
           }
-          tc_commit(&v_empty[st]);
-          tc_commit(&pv_done[st]);
+          __syncwarp();
         }
-        __syncwarp();
+        if (j >= 1) {
+          const int i = j - 1, g = g0 + i, st = g & 1;
+          const uint32_t par = (g >> 1) & 1;
+          if (!mbar_wait(&p_full[st], par, abortp) || !mbar_wait(&v_full[st], par, abortp) ||
+              (i == 0 && !mbar_wait(&o_free, (uint32_t)(qi & 1) ^ 1u, abortp))) {  // the piece before has read its output
+            if (lane == 0) fail(205);
+            ok = false;
+            break;
+          }
+          const int key0 = it.kb + i * kTcKeys;
+          const int live = it.ke - key0;  // keys of the request in this tile
+          if (live < kTcKeys) {
+            // the value rows past the end of the request: zero, whatever the page holds there (the rest of
+            // the last loaded box) and whatever the stage held before (boxes that were not loaded)
+            for (int x = lane; x < (kTcKeys - live) * 16; x += 32) {
+              const int r = live + x / 16, h = (x / 8) & 1, c = x & 7;
+              *reinterpret_cast<uint4*>(tiles + 3 * kTcTile + st * kTcTile + h * kTcHalf + r * 128 + c * 16) =
+                  make_uint4(0u, 0u, 0u, 0u);
+            }
+            fence_async_smem();
+          }
+          __syncwarp();
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t d = tmem + 2 * kTcKeys;
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {  // 16 keys per MMA
+              const uint64_t a = smem_desc(p_s + st * kTcTile + (kk >> 2) * kTcHalf) + 2 * (kk & 3);
+              const uint64_t b = smem_desc_mn(v_s + st * kTcTile + kk * 2048, kTcHalf);
+              tc_mma(d, a, b, idesc_pv, (i | kk) != 0);
+            }
+            tc_commit(&v_empty[st]);
+            tc_commit(&pv_done[st]);
+          }
+          __syncwarp();
+        }
       }
+      g0 += n_tiles;
+      ++qi;
     }
   } else {
     // ------------------------------------------------------------ softmax and epilogue (warps 2..5), one row per thread
     const int quad = warp & 3;
     const int r = quad * 32 + lane;           // row of the tile = TMEM lane
+    const float sl2 = p.scale * 1.4426950408889634f;
+    const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
+    bool ok = true;
+    int g0 = 0;  // tiles of the pieces before this one
+    for (int i_round = 0; i_round < n_rounds && ok; ++i_round) {
+      const int w = piece(i_round);
+      if (w >= n_work) continue;
+    const Item it = load_item(p, p.n_items - 1 - w / p.Hkv);
+    const int kvh = w % p.Hkv;
+    const int n_tiles = tiles_of(it);
     const int R = it.ok ? it.ntok * G : 0;
     const int pos_base = it.kv_len - it.q_len + it.tok0;
     const int qpos = r < R ? pos_base + r / G : -1;
     // last key this row may read; rows past the tile's last are never stored and must not hold the others up
     const int hi = r < R ? min(it.ke - 1, qpos) : 0x7fffffff;
-    const float sl2 = p.scale * 1.4426950408889634f;
-    const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
     float m_used = -INFINITY, l = 0.f;
-    bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int sb = j & 1;
-      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb], (uint32_t)((j >> 1) & 1), abortp))) {
+      const int g = g0 + j, sb = g & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb], (uint32_t)((g >> 1) & 1), abortp))) {
         if (lane == 0) fail(206);
         ok = false;
         break;
@@ -301,15 +352,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       l *= alpha;
       const bool rescale = __any_sync(0xffffffffu, alpha != 1.f) && j > 0;
-      if (j >= 2) {  // the product two tiles back has read the P buffer this tile writes
-        if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[sb], (uint32_t)(((j - 2) >> 1) & 1), abortp))) {
+      if (g >= 2) {  // the product two tiles back has read the P buffer this tile writes
+        if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[sb], (uint32_t)(((g - 2) >> 1) & 1), abortp))) {
           if (lane == 0) fail(207);
           ok = false;
           break;
         }
       }
       if (rescale) {  // O must hold every product so far before it is scaled
-        if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[sb ^ 1], (uint32_t)(((j - 1) >> 1) & 1), abortp))) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[sb ^ 1], (uint32_t)(((g - 1) >> 1) & 1), abortp))) {
           if (lane == 0) fail(209);
           ok = false;
           break;
@@ -358,7 +409,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
     // ---- epilogue
     if (ok && n_tiles > 0) {
-      if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[(n_tiles - 1) & 1], (uint32_t)(((n_tiles - 1) >> 1) & 1), abortp))) {
+      const int gl = g0 + n_tiles - 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[gl & 1], (uint32_t)((gl >> 1) & 1), abortp))) {
         if (lane == 0) fail(208);
         ok = false;
       }
@@ -405,6 +457,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
       }
     }
+    if (n_tiles > 0) {  // the output accumulator has been read: the next piece's first product may overwrite it
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&o_free);
+    }
+    g0 += n_tiles;
+    }
   }
   // ---------------------------------------------------------------- teardown
   if (abort_flag) {
@@ -447,7 +506,14 @@ inline int launch_attention_tc(const AttnParams& p, int n_tokens, cudaStream_t s
     const uint32_t box[2] = {64, 16};
     if (!make_map(&mk, p.k, 2, dims, strides, box) || !make_map(&mv, p.v, 2, dims, strides, box)) return 4;
   }
-  dim3 grid(p.n_items, p.Hkv);
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 1;
+  }
+  const long long n_work = (long long)p.n_items * p.Hkv;  // one CTA per SM, each takes every sms-th piece of work
+  const int grid = (int)(n_work < sms ? n_work : sms);
   FTK_LAUNCH(attention_tc_kernel, grid, kTcThreads, kTcSmem, s, mq, mk, mv, p);
   return 0;
 }
