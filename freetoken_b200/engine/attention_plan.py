@@ -22,7 +22,7 @@ from typing import List, Optional, Sequence, Tuple
 import numpy as np
 
 ITEM_INTS = 8
-SPLIT_QUANTUM = 64  # split boundaries are multiples of this many keys
+SPLIT_QUANTUM = 64  # split boundaries are multiples of this many keys (of 128 for the kernel with 128-key tiles)
 
 
 @dataclass
@@ -106,9 +106,10 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
         else:
             # splits that fill whole waves of resident CTAs, none shorter than min_split_keys
             want = wave_splits(n_tiles * n_kv_heads, target, most, span)
-        quanta = -(-span // SPLIT_QUANTUM)
+        quantum = 128 if tile_rows == 128 else SPLIT_QUANTUM  # a piece that ends inside a key tile pays for all of it
+        quanta = -(-span // quantum)
         n_real = max(1, min(want, quanta))
-        per = -(-quanta // n_real) * SPLIT_QUANTUM
+        per = -(-quanta // n_real) * quantum
         n_real = max(1, -(-span // per)) if span > 0 else 1
         n_rows = fixed_splits if fixed_splits is not None else n_real
         base = n_slots if n_rows > 1 else 0
