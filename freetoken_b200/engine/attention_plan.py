@@ -119,6 +119,10 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
             rows.append([s, tok0, ntok, b, e, n_rows, i, base])
         if n_rows > 1:
             n_slots += n_rows
+    if tile_rows == 128 and fixed_splits is None:
+        # the 128-row kernel deals the list out from its end, to and fro over its CTAs: longest pieces last
+        # here (their place in the list means nothing else: partial results are found by base + split)
+        rows.sort(key=lambda r: r[4] - r[3])
     items = np.asarray(rows, dtype=np.int32).reshape(-1, ITEM_INTS)
     return AttentionPlan(items=items, n_items=items.shape[0], n_slots=n_slots,
                          tokens_per_tile=tpt, max_splits=max_splits)
