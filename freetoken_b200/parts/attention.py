@@ -30,12 +30,13 @@ TC_MIN_DECODE_SPAN = 0   # decode steps go there from this length of the longest
 def attention_tile_rows(dtype: torch.dtype, decode_only: bool = False, group: int = 1, n_tokens: int = 0,
                         head_dim: int = 0, page_size: int = 0, window: Optional[int] = None,
                         longest_span: int = 0) -> int:
-    """Query rows (tokens x group heads) one attention CTA handles: 16 in the 32-bit kernel and in
-    the bfloat16 kernel for steps of single decoded tokens; 128 (the tcgen05 kernel) for long bfloat16
-    steps whose sizes it takes, and for decode steps (measured at 2k tokens of context: 12 against
-    13 microseconds at batch 1, 31 against 42 at batch 16, the same at batch 64; 19 % less at 8k
-    tokens; ``longest_span`` is the longest request's length rounded up to a power of two); 64 in the
-    bfloat16 mma.sync kernel otherwise."""
+    """Query rows (tokens x group heads) one attention CTA handles: 16 in the 32-bit kernel; 128 (the
+    tcgen05 kernel) for bfloat16 steps whose sizes it takes, long ones (``TC_MIN_TOKENS`` tokens and
+    more) and decode steps alike (measured at 2k tokens of context against the 16-row kernel: 11
+    against 13 microseconds at batch 1, 21 against 26 at batch 8, 105 against 133 at batch 64);
+    ``longest_span`` is the longest request's length rounded up to a power of two, from which on decode
+    steps go there (``TC_MIN_DECODE_SPAN``); otherwise 16 rows for decode steps of small groups and 64
+    in the bfloat16 mma.sync kernel."""
     if dtype != torch.bfloat16:
         return 16
     tc = bool(window is None and head_dim and page_size and ops.attention_tc_fits(head_dim, page_size, group))
