@@ -33,7 +33,8 @@ constexpr int kTcD = 128;
 constexpr int kTcThreads = 224;
 constexpr int kTcHalf = 128 * 64 * 2;       // bytes of a [128 rows x 64 elements] swizzle-atom column
 constexpr int kTcTile = 2 * kTcHalf;        // a [128 x 128] bfloat16 tile
-constexpr int kTcSmem = 7 * kTcTile + 1024; // Q, K x2, V x2, P x2
+constexpr int kTcSmem = 5 * kTcTile + 1024; // Q, K x2, V x2
+constexpr int kTcPCol = 3 * kTcKeys;        // tensor memory: S x2 (128 columns each), O (128), P x2 (64 each)
 
 __device__ __forceinline__ void tmem_ld32(uint32_t addr, float (&v)[32]) {
   uint32_t r[32];
@@ -68,6 +69,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t addr, const float (&v)[32]) {
       : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+// sixteen 32-bit words of this thread's row into columns [addr, addr + 16); completed by tmem_st_wait()
+__device__ __forceinline__ void tmem_st16u(uint32_t addr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // Shared-memory descriptor of an MN-major operand with 128-byte swizzle: 64 elements of the MN side
@@ -116,7 +126,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   };
   const uint32_t base = (smem_addr(dyn_smem) + 1023u) & ~1023u;
   unsigned char* tiles = dyn_smem + (base - smem_addr(dyn_smem));
-  const uint32_t q_s = base, k_s = base + kTcTile, v_s = base + 3 * kTcTile, p_s = base + 5 * kTcTile;
+  const uint32_t q_s = base, k_s = base + kTcTile, v_s = base + 3 * kTcTile;
 
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
@@ -277,9 +287,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const uint32_t d = tmem + 2 * kTcKeys;
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) {  // 16 keys per MMA
-              const uint64_t a = smem_desc(p_s + st * kTcTile + (kk >> 2) * kTcHalf) + 2 * (kk & 3);
+              const uint32_t a = tmem + (uint32_t)(kTcPCol + st * (kTcKeys / 2) + kk * 8);
               const uint64_t b = smem_desc_mn(v_s + st * kTcTile + kk * 2048, kTcHalf);
-              tc_mma(d, a, b, idesc_pv, (i | kk) != 0);
+              tc_mma_ts(d, a, b, idesc_pv, (i | kk) != 0);
             }
             tc_commit(&v_empty[st]);
             tc_commit(&pv_done[st]);
@@ -377,9 +387,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       const float mb = m_used == -INFINITY ? 0.f : m_used;
       float sum = 0.f;
-      // probabilities as bfloat16 into row r of the A-operand layout: two [128 x 64]-key atoms, rows of
-      // 128 bytes in groups of eight, 16-byte chunks swizzled by the row
-      unsigned char* prow = tiles + (5 + sb) * kTcTile + (r >> 3) * 1024 + (r & 7) * 128;
+      // probabilities as bfloat16 into this row of the A operand in tensor memory: two keys per 32-bit
+      // column, 64 columns per buffer behind the output accumulator
+      const uint32_t p_addr = lane_addr + (uint32_t)(kTcPCol + sb * (kTcKeys / 2));
       auto emit = [&](float (&v)[32], int c) {
         uint32_t pk[16];
 #pragma unroll
@@ -389,20 +399,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           sum += p0 + p1;
           pk[i >> 1] = tc_pack(p0, p1);
         }
-        unsigned char* dst = prow + (c >> 1) * kTcHalf;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = (c & 1) * 4 + q4;
-          *reinterpret_cast<uint4*>(dst + ((chunk ^ (r & 7)) << 4)) =
-              make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
-        }
+        tmem_st16u(p_addr + (uint32_t)(c * 16), pk);
       };
       emit(v0, 0);
       emit(v1, 1);
       emit(v2, 2);
       emit(v3, 3);
       l += sum;
-      fence_async_smem();
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[sb]);
