@@ -33,7 +33,8 @@ constexpr int kTcD = 128;
 constexpr int kTcThreads = 224;
 constexpr int kTcHalf = 128 * 64 * 2;       // bytes of a [128 rows x 64 elements] swizzle-atom column
 constexpr int kTcTile = 2 * kTcHalf;        // a [128 x 128] bfloat16 tile
-constexpr int kTcSmem = 5 * kTcTile + 1024; // Q, K x2, V x2
+constexpr int kTcStages = 3;                // key and value tiles in flight
+constexpr int kTcSmem = (1 + 2 * kTcStages) * kTcTile + 1024;  // Q, K and V stages
 constexpr int kTcPCol = 3 * kTcKeys;        // tensor memory: S x2 (128 columns each), O (128), P x2 (64 each)
 
 __device__ __forceinline__ void tmem_ld32(uint32_t addr, float (&v)[32]) {
@@ -107,7 +108,7 @@ __global__ void __launch_bounds__(kTcThreads)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, AttnParams p) {
   extern __shared__ unsigned char dyn_smem[];
-  __shared__ uint64_t q_full, q_empty, o_free, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2],
+  __shared__ uint64_t q_full, q_empty, o_free, k_full[kTcStages], k_empty[kTcStages], v_full[kTcStages], v_empty[kTcStages], s_full[2], s_empty[2],
       p_full[2], pv_done[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
@@ -126,15 +127,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   };
   const uint32_t base = (smem_addr(dyn_smem) + 1023u) & ~1023u;
   unsigned char* tiles = dyn_smem + (base - smem_addr(dyn_smem));
-  const uint32_t q_s = base, k_s = base + kTcTile, v_s = base + 3 * kTcTile;
+  const uint32_t q_s = base, k_s = base + kTcTile, v_s = base + (1 + kTcStages) * kTcTile;
 
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
     mbar_init(&q_empty, 1);
     mbar_init(&o_free, 4);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kTcStages; ++s) {
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4);
       mbar_init(&p_full[s], 4); mbar_init(&pv_done[s], 1);
     }
@@ -169,7 +172,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const CUtensorMap* map = kv ? &map_v : &map_k;
       uint64_t* full = kv ? v_full : k_full;
       uint64_t* empty = kv ? v_empty : k_empty;
-      unsigned char* stage0 = tiles + (kv ? 3 : 1) * kTcTile + h * kTcHalf + box * 2048;
+      unsigned char* stage0 = tiles + (kv ? 1 + kTcStages : 1) * kTcTile + h * kTcHalf + box * 2048;
       bool ok = true;
       int g = 0;   // tiles of all pieces so far: stage g & 1
       int qi = 0;  // pieces with tiles so far
@@ -195,8 +198,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         ++qi;
         const int32_t* bt = p.block_table + (size_t)it.bt_row * p.bt_stride;
         for (int j = 0; j < n_tiles && ok; ++j, ++g) {
-          const int st = g & 1;
-          const uint32_t par = ((g >> 1) & 1) ^ 1;
+          const int st = g % kTcStages;
+          const uint32_t par = ((g / kTcStages) & 1) ^ 1;
           const int key0 = it.kb + j * kTcKeys;
           const int n_box = min(8, (it.ke - key0 + 15) >> 4);  // boxes of 16 keys that hold keys of the request
           const int key = key0 + 16 * box;
@@ -238,9 +241,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       for (int j = 0; j <= n_tiles && ok; ++j) {
         if (j < n_tiles) {
-          const int g = g0 + j, st = g & 1;
+          const int g = g0 + j, st = g & 1, ks = g % kTcStages;  // score buffer, key stage
           const uint32_t par = (g >> 1) & 1;
-          if (!mbar_wait(&k_full[st], par, abortp) || !mbar_wait(&s_empty[st], par ^ 1, abortp)) {
+          if (!mbar_wait(&k_full[ks], (uint32_t)(g / kTcStages) & 1u, abortp) || !mbar_wait(&s_empty[st], par ^ 1, abortp)) {
             if (lane == 0) fail(204);
             ok = false;
             break;
@@ -251,19 +254,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) {  // 16 elements of the head dimension per MMA
               const uint64_t a = smem_desc(q_s + (kk >> 2) * kTcHalf) + 2 * (kk & 3);
-              const uint64_t b = smem_desc(k_s + st * kTcTile + (kk >> 2) * kTcHalf) + 2 * (kk & 3);
+              const uint64_t b = smem_desc(k_s + ks * kTcTile + (kk >> 2) * kTcHalf) + 2 * (kk & 3);
               tc_mma(d, a, b, idesc_qk, kk != 0);
             }
-            tc_commit(&k_empty[st]);
+            tc_commit(&k_empty[ks]);
             tc_commit(&s_full[st]);
             if (j == n_tiles - 1) tc_commit(&q_empty);  // the next piece's queries may come
           }
           __syncwarp();
         }
         if (j >= 1) {
-          const int i = j - 1, g = g0 + i, st = g & 1;
+          const int i = j - 1, g = g0 + i, st = g & 1, vs = g % kTcStages;  // probability buffer, value stage
           const uint32_t par = (g >> 1) & 1;
-          if (!mbar_wait(&p_full[st], par, abortp) || !mbar_wait(&v_full[st], par, abortp) ||
+          if (!mbar_wait(&p_full[st], par, abortp) || !mbar_wait(&v_full[vs], (uint32_t)(g / kTcStages) & 1u, abortp) ||
               (i == 0 && !mbar_wait(&o_free, (uint32_t)(qi & 1) ^ 1u, abortp))) {  // the piece before has read its output
             if (lane == 0) fail(205);
             ok = false;
@@ -276,7 +279,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             // the last loaded box) and whatever the stage held before (boxes that were not loaded)
             for (int x = lane; x < (kTcKeys - live) * 16; x += 32) {
               const int r = live + x / 16, h = (x / 8) & 1, c = x & 7;
-              *reinterpret_cast<uint4*>(tiles + 3 * kTcTile + st * kTcTile + h * kTcHalf + r * 128 + c * 16) =
+              *reinterpret_cast<uint4*>(tiles + (1 + kTcStages + vs) * kTcTile + h * kTcHalf + r * 128 + c * 16) =
                   make_uint4(0u, 0u, 0u, 0u);
             }
             fence_async_smem();
@@ -288,10 +291,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) {  // 16 keys per MMA
               const uint32_t a = tmem + (uint32_t)(kTcPCol + st * (kTcKeys / 2) + kk * 8);
-              const uint64_t b = smem_desc_mn(v_s + st * kTcTile + kk * 2048, kTcHalf);
+              const uint64_t b = smem_desc_mn(v_s + vs * kTcTile + kk * 2048, kTcHalf);
               tc_mma_ts(d, a, b, idesc_pv, (i | kk) != 0);
             }
-            tc_commit(&v_empty[st]);
+            tc_commit(&v_empty[vs]);
             tc_commit(&pv_done[st]);
           }
           __syncwarp();
