@@ -62,3 +62,19 @@ def test_wave_splits_prefers_full_waves():
     assert wave_splits(512, 296, 16, 2048) == 1       # already more tiles than slots
     assert wave_splits(8, 296, 1, 128) == 1           # the caller's limit (no piece under 256 keys) holds
     assert wave_splits(8, 296, 16, 2048) == 16        # one request alone: as many pieces as allowed
+
+
+def test_the_128_row_kernel_gets_pieces_on_tile_boundaries_sorted_by_length():
+    # one long portion beside single tokens of other requests, as the 128-row kernel gets it
+    segs = [(512, 20000)] + [(1, 100 + 37 * i) for i in range(20)]
+    plan = build_plan(segs, 6, 128, None, n_kv_heads=8, sm_count=74)
+    spans = [ke - kb for _, _, _, kb, ke, _, _, _ in plan.items.tolist()]
+    assert spans == sorted(spans), "the kernel deals the list out from its end: longest pieces last"
+    for (seg, tok0, ntok), parts in ranges_by_tile(plan).items():
+        parts.sort()
+        lo = parts[0][1]
+        for (_, _, e0, _, _) in parts[:-1]:
+            assert (e0 - lo) % 128 == 0, "a piece ends where a 128-key tile ends"
+    # with a fixed number of splits (graph replay) the list keeps its order: tile after tile
+    fixed = build_plan([(1, 3000), (1, 500)], 6, 128, None, n_kv_heads=8, fixed_splits=3)
+    assert [r[0] for r in fixed.items.tolist()] == [0, 0, 0, 1, 1, 1]
