@@ -1,19 +1,22 @@
-// Paged causal attention for long steps on the 5th-generation tensor cores (tcgen05), bfloat16,
-// head size 128.  Included by attention.cu after AttnParams / Item / load_item.
+// Paged causal attention on the 5th-generation tensor cores (tcgen05), bfloat16, head size 128: long
+// steps and decode steps.  Included by attention.cu after AttnParams / Item / load_item.
 //
 // A tile is 128 query rows: the `group` query heads of one KV head for 128 / group consecutive tokens
-// of one segment, so a key/value tile is read once for all the heads that share it.  Keys come in
-// tiles of 128.  Per key tile:
+// of one segment, so a key/value tile is read once for all the heads that share it (a decode step
+// fills only the first `group` rows).  Keys come in tiles of 128.  Per key tile:
 //   S = Q K^T        tcgen05.mma, Q [128 x 128] and K [128 keys x 128] K-major in shared memory
 //                    (TMA, 128-byte swizzle; K straight from the pages, 16 keys per box), S in TMEM
 //                    (two buffers, so the next tile's product runs under this tile's softmax);
 //   softmax          one thread per row (its TMEM lane): scale, mask, running maximum, exp2, sum; the
-//                    probabilities go to shared memory as bfloat16 in the A-operand layout.  The
+//                    probabilities go back to TMEM as bfloat16 (two buffers of 64 columns).  The
 //                    running maximum is only moved when it grew by more than 8 (a factor 256), so the
 //                    accumulator is rescaled a few times per row, not once per tile;
-//   O += P V         tcgen05.mma with V as the MN-major B operand (the page rows as they are), O in TMEM.
-// One CTA = 7 warps: warps 0 and 6 issue the TMA loads of keys and values, warp 1 the MMAs, warps 2-5 are the
-// softmax (and the epilogue: O / l to the output, or the partial sums of a split tile for the merge kernel).
+//   O += P V         tcgen05.mma with P as the A operand in TMEM and V as the MN-major B operand (the
+//                    page rows as they are, three stages like the keys), O in TMEM.
+// One CTA per SM = 7 warps: warps 0 and 6 issue the TMA loads of keys and values, warp 1 the MMAs, warps
+// 2-5 are the softmax (and the epilogue: O / l to the output, or the partial sums of a split tile for
+// the merge kernel).  A CTA works through its share of the work list; the three roles run through it on
+// their own, so the loads and the first product of a piece run under the end of the piece before.
 // Every wait is bounded; a timeout records a code in g_attn_status, lets copies land, frees TMEM, returns.
 // Value rows past the end of the request are never multiplied as they lie in memory (they may hold
 // anything): whole 16-key boxes past the end are not loaded, and all rows of the stage past the end
