@@ -876,6 +876,7 @@ static int launch_bf16(const AttnParams& p, cudaStream_t s) {
 }  // namespace ftk
 
 #include "attention_tc.cuh"
+#include "attention_tc2.cuh"
 
 using namespace ftk;
 
@@ -896,14 +897,15 @@ extern "C" int ftk_attention_tc_fits(int head_dim, int page_size, int group) {
   return attention_tc_fits(head_dim, page_size, group) ? 1 : 0;
 }
 
-// Long steps in bfloat16 on the tensor-core kernel: tiles of 128 query rows (`items` planned for
-// tile_rows = 128); `n_tokens` is the number of rows of q.
-extern "C" int ftk_paged_attention_tc(const void* q, const void* k_slab, const void* v_slab,
-                                      const int32_t* block_table, int bt_stride, const int32_t* seg_info,
-                                      int n_segs, const int32_t* items, int n_items, float* part_o, float* part_ml,
-                                      int n_slots, void* out, int n_tokens, int n_q_heads, int n_kv_heads,
-                                      int head_dim, int page_size, int num_pages, float scale, int window,
-                                      void* stream) {
+// bfloat16 steps on the tensor-core kernels: tiles of 128 query rows (`items` planned for tile_rows =
+// 128), or pieces of two such tiles (`pair`, planned for tile_rows = 256); `n_tokens` is the number of
+// rows of q.
+static int paged_attention_tc_impl(const void* q, const void* k_slab, const void* v_slab,
+                                   const int32_t* block_table, int bt_stride, const int32_t* seg_info,
+                                   int n_segs, const int32_t* items, int n_items, float* part_o, float* part_ml,
+                                   int n_slots, void* out, int n_tokens, int n_q_heads, int n_kv_heads,
+                                   int head_dim, int page_size, int num_pages, float scale, int window,
+                                   void* stream, bool pair) {
   FTK_REQUIRE(q && k_slab && v_slab && block_table && seg_info && items && out, "paged_attention_tc: null pointer");
   FTK_REQUIRE(n_q_heads >= 1 && n_kv_heads >= 1 && n_q_heads % n_kv_heads == 0, "paged_attention_tc: %d query heads, %d KV heads",
               n_q_heads, n_kv_heads);
@@ -923,10 +925,10 @@ extern "C" int ftk_paged_attention_tc(const void* q, const void* k_slab, const v
   p.seg_info = seg_info; p.n_segs = n_segs; p.items = items; p.n_items = n_items;
   p.part_o = part_o; p.part_ml = part_ml; p.n_slots = n_slots;
   p.Hq = n_q_heads; p.Hkv = n_kv_heads; p.G = n_q_heads / n_kv_heads; p.D = head_dim; p.P = page_size;
-  p.num_pages = num_pages; p.tile_rows = kTcRows; p.scale = scale; p.window = window;
+  p.num_pages = num_pages; p.tile_rows = pair ? 2 * kTcRows : kTcRows; p.scale = scale; p.window = window;
   p.sel = nullptr; p.sel_stride = 0; p.block_size = 0; p.arrivals = nullptr;
   cudaStream_t s = (cudaStream_t)stream;
-  const int rc = launch_attention_tc(p, n_tokens, s);
+  const int rc = pair ? launch_attention_tc2(p, n_tokens, s) : launch_attention_tc(p, n_tokens, s);
   FTK_REQUIRE(rc == 0, "paged_attention_tc: cannot set up the kernel (%d)", rc);
   FTK_LAUNCH_CHECK("paged_attention_tc");
   if (n_slots > 0) {
@@ -935,6 +937,28 @@ extern "C" int ftk_paged_attention_tc(const void* q, const void* k_slab, const v
     FTK_LAUNCH_CHECK("paged_attention_tc merge");
   }
   return 0;
+}
+
+extern "C" int ftk_paged_attention_tc(const void* q, const void* k_slab, const void* v_slab,
+                                      const int32_t* block_table, int bt_stride, const int32_t* seg_info,
+                                      int n_segs, const int32_t* items, int n_items, float* part_o, float* part_ml,
+                                      int n_slots, void* out, int n_tokens, int n_q_heads, int n_kv_heads,
+                                      int head_dim, int page_size, int num_pages, float scale, int window,
+                                      void* stream) {
+  return paged_attention_tc_impl(q, k_slab, v_slab, block_table, bt_stride, seg_info, n_segs, items, n_items, part_o,
+                                 part_ml, n_slots, out, n_tokens, n_q_heads, n_kv_heads, head_dim, page_size, num_pages,
+                                 scale, window, stream, false);
+}
+
+extern "C" int ftk_paged_attention_tc_pair(const void* q, const void* k_slab, const void* v_slab,
+                                           const int32_t* block_table, int bt_stride, const int32_t* seg_info,
+                                           int n_segs, const int32_t* items, int n_items, float* part_o,
+                                           float* part_ml, int n_slots, void* out, int n_tokens, int n_q_heads,
+                                           int n_kv_heads, int head_dim, int page_size, int num_pages, float scale,
+                                           int window, void* stream) {
+  return paged_attention_tc_impl(q, k_slab, v_slab, block_table, bt_stride, seg_info, n_segs, items, n_items, part_o,
+                                 part_ml, n_slots, out, n_tokens, n_q_heads, n_kv_heads, head_dim, page_size, num_pages,
+                                 scale, window, stream, true);
 }
 
 static int paged_attention_impl(const void* q, const void* k_slab, const void* v_slab, int dtype,

@@ -53,6 +53,8 @@ def wave_splits(base_ctas: int, slots: int, limit: int, span: int = 2048) -> int
 
 
 def tokens_per_tile(tile_rows: int, group: int) -> int:
+    if tile_rows == 256:  # two tiles of 128 rows, each with whole tokens
+        return 2 * max(1, 128 // group)
     return max(1, tile_rows // group)
 
 
@@ -106,7 +108,7 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
         else:
             # splits that fill whole waves of resident CTAs, none shorter than min_split_keys
             want = wave_splits(n_tiles * n_kv_heads, target, most, span)
-        quantum = 128 if tile_rows == 128 else SPLIT_QUANTUM  # a piece that ends inside a key tile pays for all of it
+        quantum = 128 if tile_rows >= 128 else SPLIT_QUANTUM  # a piece that ends inside a key tile pays for all of it
         quanta = -(-span // quantum)
         n_real = max(1, min(want, quanta))
         per = -(-quanta // n_real) * quantum
@@ -119,8 +121,8 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
             rows.append([s, tok0, ntok, b, e, n_rows, i, base])
         if n_rows > 1:
             n_slots += n_rows
-    if tile_rows == 128 and fixed_splits is None:
-        # the 128-row kernel deals the list out from its end, to and fro over its CTAs: longest pieces last
+    if tile_rows >= 128 and fixed_splits is None:
+        # the tcgen05 kernels deal the list out from its end, to and fro over its CTAs: longest pieces last
         # here (their place in the list means nothing else: partial results are found by base + split)
         rows.sort(key=lambda r: r[4] - r[3])
     items = np.asarray(rows, dtype=np.int32).reshape(-1, ITEM_INTS)

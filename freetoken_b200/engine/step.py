@@ -118,7 +118,7 @@ class StepBuilder:
                        head_dim: int) -> Any:
         key = ("attention", group, tile_rows, window, n_kv_heads, head_dim)
         if key not in self.plans:
-            per_sm = 1 if tile_rows == 128 else 2  # the 128-row kernel fills an SM with one CTA
+            per_sm = 1 if tile_rows >= 128 else 2  # the tcgen05 kernels fill an SM with one CTA
             plan = build_plan(self.seg_lens, group, tile_rows, window, n_kv_heads,
                               sm_count=self.sm_count if per_sm == 2 else max(1, self.sm_count // 2),
                               fixed_splits=self.fixed_splits(n_kv_heads, per_sm) if self.fixed else None)

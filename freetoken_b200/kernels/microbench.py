@@ -115,6 +115,8 @@ def bench_attention(a) -> dict:
     q = torch.randn(q0, Hq, D, device=dev, generator=g).to(torch.bfloat16)
     fixed = None
     tile = 128 if (a.prefill >= 128 and not a.no_tc and ops.attention_tc_fits(D, P, G)) else 64
+    if tile == 128 and a.pair:
+        tile = 256  # two query tiles per CTA
     if not a.prefill:
         tc = a.tc and ops.attention_tc_fits(D, P, G)
         fixed = wave_splits(len(segs) * Hkv, 148 if tc else 2 * 148, 16) if a.splits is None else a.splits
@@ -174,6 +176,7 @@ def main(argv=None) -> int:
             p.add_argument("--splits", type=int, default=None)
             p.add_argument("--no-tc", action="store_true", help="prefill on the mma.sync kernel instead of tcgen05")
             p.add_argument("--tc", action="store_true", help="decode on the tcgen05 kernel")
+            p.add_argument("--pair", action="store_true", help="prefill on the tcgen05 kernel with two query tiles per CTA")
         else:
             p.add_argument("--rows", type=int, default=8)
             p.add_argument("--vocab", type=int, default=200064)

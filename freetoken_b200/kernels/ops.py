@@ -27,8 +27,9 @@ copy_tokens            the sampled tokens of the step before, taken on the devic
                        (python/freetoken/scheduler/scheduler.py:194-256, overlapped scheduling)
 =====================  ==========================================================
 
-``paged_attention`` runs one of four kernels by ``tile_rows``: 16 (float32, or bfloat16 decode), 64
-(bfloat16 mma.sync), 128 (bfloat16 tcgen05: long steps, decode over long contexts).
+``paged_attention`` runs one of five kernels by ``tile_rows``: 16 (float32, or bfloat16 steps of single
+tokens where the tcgen05 kernel does not take the sizes), 64 (bfloat16 mma.sync), 128 (bfloat16 tcgen05:
+long steps and decode steps), 256 (the same with two query tiles per CTA: very long steps).
 """
 
 from __future__ import annotations
@@ -70,6 +71,8 @@ _SIGNATURES = {
     "ftk_attention_tc_fits": [_i, _i, _i],
     "ftk_paged_attention_tc": [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
                                _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "ftk_paged_attention_tc_pair": [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
+                                    _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "ftk_paged_attention_sparse": [_vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
                                    _i, _i, _i, _i, _i, _i, _f, _vp, _i, _i, _vp],
     "ftk_sparse_select": [_vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
@@ -351,10 +354,11 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
     if part_o is not None and (part_o.shape[1:] != (Hkv, tile_rows, D) or part_ml is None
                                or part_ml.shape != (n_slots, Hkv, tile_rows, 2)):
         raise KernelError("paged_attention: scratch shapes do not match tile_rows / heads")
-    if tile_rows == 128:  # long bfloat16 steps: the tcgen05 kernel
+    if tile_rows in (128, 256):  # bfloat16 steps on the tcgen05 kernels: one query tile per CTA, or a pair of them
         if sel is not None or window or q.dtype != torch.bfloat16:
             raise KernelError("paged_attention: 128-row tiles take bfloat16 without window or block selection")
-        _check(_lib().ftk_paged_attention_tc(
+        fn = _lib().ftk_paged_attention_tc_pair if tile_rows == 256 else _lib().ftk_paged_attention_tc
+        _check(fn(
             _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"),
             _dev(block_table, "block_table", torch.int32), block_table.shape[1],
             _dev(seg_info, "seg_info", torch.int32), n_segs,

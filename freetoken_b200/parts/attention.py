@@ -24,6 +24,7 @@ from .rope import shared_position
 
 
 TC_MIN_TOKENS = 128      # shortest step that goes to the tcgen05 attention kernel
+TC_PAIR_MIN_TOKENS = 1024  # from this many tokens on, a step goes to the kernel with two query tiles per CTA
 TC_MIN_DECODE_SPAN = 0   # decode steps go there from this length of the longest request (rounded up to 2^n) on
 
 
@@ -32,7 +33,7 @@ def attention_tile_rows(dtype: torch.dtype, decode_only: bool = False, group: in
                         longest_span: int = 0) -> int:
     """Query rows (tokens x group heads) one attention CTA handles: 16 in the 32-bit kernel; 128 (the
     tcgen05 kernel) for bfloat16 steps whose sizes it takes, long ones (``TC_MIN_TOKENS`` tokens and
-    more) and decode steps alike (measured at 2k tokens of context against the 16-row kernel: 11
+    more; 256, two such tiles per CTA, from ``TC_PAIR_MIN_TOKENS`` tokens on) and decode steps alike (measured at 2k tokens of context against the 16-row kernel: 11
     against 13 microseconds at batch 1, 21 against 26 at batch 8, 105 against 133 at batch 64);
     ``longest_span`` is the longest request's length rounded up to a power of two, from which on decode
     steps go there (``TC_MIN_DECODE_SPAN``); otherwise 16 rows for decode steps of small groups and 64
@@ -44,6 +45,8 @@ def attention_tile_rows(dtype: torch.dtype, decode_only: bool = False, group: in
         if tc and longest_span >= TC_MIN_DECODE_SPAN:
             return 128
         return 16 if group <= 16 else 64
+    if tc and n_tokens >= TC_PAIR_MIN_TOKENS:
+        return 256
     if tc and n_tokens >= TC_MIN_TOKENS:
         return 128
     return 64

@@ -121,6 +121,29 @@ def test_long_steps_on_the_tensor_core_attention(dtype, world):
         assert ops.attention_tc_fits(128, 16, 3) and ops.read_status() == 0
 
 
+def test_long_steps_on_the_attention_kernel_with_two_query_tiles(world, monkeypatch):
+    """The same long steps on the tcgen05 kernel that gives a CTA two query tiles (the engine sends steps
+    of a thousand tokens and more there; here every long step): whole, in portions, beside decoded tokens."""
+    import freetoken_b200.parts.attention as attention
+
+    monkeypatch.setattr(attention, "TC_PAIR_MIN_TOKENS", 128)
+    _, plain, eng = world("E", "bfloat16", pages=64, max_step=320)
+    V = plain.cfg.vocab
+    toks = tokens_for(V, 300, 77)
+    ref, margins = plain.logits(toks), plain.router_margins(toks)
+    check(replay_whole(eng, "w", toks), ref, "bfloat16", margins, "300 tokens whole")
+    check(replay_cuts(eng, "c", toks, [170, 129]), ref, "bfloat16", margins, "two long portions and one token")
+    seqs = {"a": tokens_for(V, 200, 78), "b": tokens_for(V, 150, 79), "c": tokens_for(V, 40, 80)}
+    sched = [{"c": 30}, {"a": 190, "c": 1}, {"b": 140, "c": 1, "a": 1}] + [{"a": 1, "b": 1, "c": 1}] * 10
+    got = replay_mixed(eng, seqs, sched)
+    for r, t in seqs.items():
+        check(got[r], plain.logits(t), "bfloat16", plain.router_margins(t), f"mixed with long portions {r}")
+    from freetoken_b200.kernels import ops
+
+    assert ops.read_status() == 0
+    assert attention.attention_tile_rows(torch.bfloat16, False, 3, 300, 128, 16) == 256
+
+
 def test_decode_over_a_long_context_on_the_tensor_core_attention(world, monkeypatch):
     """Decode steps run the 16-row kernel below a length of the longest request and the tcgen05
     kernel above it (the threshold is 0 by default: always the tcgen05 kernel where it fits; it is

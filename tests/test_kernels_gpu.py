@@ -219,24 +219,26 @@ def test_attention_mixed_batch(dtype, Hq, Hkv, D, P):
     torch.testing.assert_close(out.float(), want.float(), **attn_tol(dtype))
 
 
+@pytest.mark.parametrize("tile", [128, 256])
 @pytest.mark.parametrize("Hq,Hkv,P", [(12, 2, 16), (48, 8, 16), (5, 5, 32), (7, 1, 64), (16, 1, 16), (3, 1, 48)])
-def test_attention_tensor_core_kernel(Hq, Hkv, P):
-    """The tcgen05 kernel (tiles of 128 query rows, head size 128) on a mixed batch: whole prompts,
+def test_attention_tensor_core_kernel(Hq, Hkv, P, tile):
+    """The tcgen05 kernels (tiles of 128 query rows, one or two to a CTA, head size 128) on a mixed batch: whole prompts,
     portions with earlier keys, single tokens, lengths on and off the edges of its 128-key tiles and
     16-key boxes; every unwritten cache slot holds NaN."""
     assert ops.attention_tc_fits(128, P, Hq // Hkv)
     assert not ops.attention_tc_fits(64, P, Hq // Hkv) and not ops.attention_tc_fits(128, 8, 1)
     segs = [(300, 300), (1, 1), (128, 128), (17, 273), (1, 130), (129, 257), (40, 40), (2, 64), (250, 1000), (1, 129)]
-    out, want, _ = run_attention(torch.bfloat16, Hq, Hkv, 128, P, segs, None, tile=128)
+    out, want, _ = run_attention(torch.bfloat16, Hq, Hkv, 128, P, segs, None, tile=tile)
     assert not torch.isnan(out).any()
     torch.testing.assert_close(out.float(), want.float(), **attn_tol(torch.bfloat16))
     assert ops.read_status() == 0
 
 
-def test_attention_tensor_core_kernel_split_keys():
+@pytest.mark.parametrize("tile", [128, 256])
+def test_attention_tensor_core_kernel_split_keys(tile):
     """One long request alone: its tiles are split along the keys and merged."""
     segs = [(140, 3000)]
-    out, want, plan = run_attention(torch.bfloat16, 12, 2, 128, 16, segs, None, force_split=True, tile=128)
+    out, want, plan = run_attention(torch.bfloat16, 12, 2, 128, 16, segs, None, force_split=True, tile=tile)
     assert plan.n_slots > 0
     assert not torch.isnan(out).any()
     torch.testing.assert_close(out.float(), want.float(), **attn_tol(torch.bfloat16))
