@@ -114,23 +114,57 @@ moe_seg_scan_kernel(int n_segs, int n_experts, int* __restrict__ seg_counts, int
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) carry = 0;
   __syncthreads();
-  for (int e0 = 0; e0 < n_experts; e0 += blockDim.x) {
-    const int e = e0 + threadIdx.x;
-    int run = 0;
-    if (e < n_experts) {
-      for (int sg0 = 0; sg0 < n_segs; sg0 += 16) {  // sixteen loads in flight, then their running sums
+  // An expert's segments are shared by the `parts` threads el, el + round, ...: each adds up its
+  // stretch of segments, the stretches' totals are exchanged through shared memory, and each writes the
+  // running sums of its stretch (one thread per expert walked all segments, sixteen loads at a time:
+  // eight trips to memory for 128 segments).
+  __shared__ int part_tot[1024];
+  const int round = min((int)blockDim.x, (n_experts + 31) & ~31);  // experts per pass over the block
+  const int parts = (int)blockDim.x / round;
+  const int el = (int)threadIdx.x % round, q = (int)threadIdx.x / round;
+  const int per = (n_segs + parts - 1) / parts;
+  const int sg_lo = min(n_segs, q * per), sg_hi = min(n_segs, sg_lo + per);
+  for (int e0 = 0; e0 < n_experts; e0 += round) {
+    const int e = e0 + el;
+    const bool active = e < n_experts && q < parts;
+    int sum = 0;
+    if (active) {
+      for (int sg0 = sg_lo; sg0 < sg_hi; sg0 += 16) {  // sixteen loads in flight
         int v[16];
 #pragma unroll
         for (int u = 0; u < 16; ++u)
-          v[u] = sg0 + u < n_segs ? __ldcg(seg_counts + (size_t)(sg0 + u) * n_experts + e) : 0;
+          v[u] = sg0 + u < sg_hi ? __ldcg(seg_counts + (size_t)(sg0 + u) * n_experts + e) : 0;
+#pragma unroll
+        for (int u = 0; u < 16; ++u) sum += v[u];
+      }
+    }
+    part_tot[threadIdx.x] = active ? sum : 0;
+    __syncthreads();
+    int run = 0;  // the expert's total, in the thread of its first stretch; 0 in the others
+    if (active) {
+      int before = 0, total = 0;
+      for (int q2 = 0; q2 < parts; ++q2) {
+        const int v = part_tot[q2 * round + el];
+        if (q2 < q) before += v;
+        total += v;
+      }
+      for (int sg0 = sg_lo; sg0 < sg_hi; sg0 += 16) {
+        int v[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u)
+          v[u] = sg0 + u < sg_hi ? __ldcg(seg_counts + (size_t)(sg0 + u) * n_experts + e) : 0;
 #pragma unroll
         for (int u = 0; u < 16; ++u) {
-          if (sg0 + u < n_segs) seg_counts[(size_t)(sg0 + u) * n_experts + e] = run;
-          run += v[u];
+          if (sg0 + u < sg_hi) seg_counts[(size_t)(sg0 + u) * n_experts + e] = before;
+          before += v[u];
         }
       }
-      counts[e] = run;
+      if (q == 0) {
+        run = total;
+        counts[e] = total;
+      }
     }
+    const bool owner = active && q == 0;
     // exclusive scan of this round's totals over the block, on top of the rounds before
     int incl = run;
 #pragma unroll
@@ -153,7 +187,7 @@ moe_seg_scan_kernel(int n_segs, int n_experts, int* __restrict__ seg_counts, int
       if (lane == 31) warp_tot[32] = ti;  // this round's total
     }
     __syncthreads();
-    if (e < n_experts) offsets[e] = carry + warp_tot[warp] + incl - run;
+    if (owner) offsets[e] = carry + warp_tot[warp] + incl - run;
     __syncthreads();
     if (threadIdx.x == 0) carry += warp_tot[32];
     __syncthreads();
