@@ -37,6 +37,7 @@ from .build import build_model, load_weights, random_weights
 from .step import StepBuffers, StepBuilder
 
 _TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+STATUS_CHECK_EVERY = 1024  # steps between two looks at the kernels' status words (a look waits for the device)
 
 
 @dataclass
@@ -241,7 +242,16 @@ class Engine:
         if self.config.check_cache:
             self.cache.check()
         self.steps_run += 1
+        if self.steps_run == 1 or self.steps_run % STATUS_CHECK_EVERY == 0:
+            self.check_kernels()
         return StepOutput(logits=logits, rows=rows)
+
+    def check_kernels(self) -> None:
+        """Raise if a kernel gave up a bounded wait since the last check (its results are not valid).
+        Reading the status words waits for the device, so steps do it only now and then; whoever reads a
+        result on the host anyway (trace replay, the end of a generation) calls this as well."""
+        if self.device.type == "cuda":
+            ops.check_status()
 
     def _run(self, entries, plan, token_ids: np.ndarray, logit_rows: List[int]) -> torch.Tensor:
         S = len(entries)

@@ -56,6 +56,7 @@ class LLM:
             sched.add_request(self._ids(p), sp, rid=i)
         off = os.environ.get("FREETOKEN_DISABLE_OVERLAP_SCHEDULING", "").lower() in ("1", "true", "yes", "on")
         sched.run(overlap=self.config.overlap_scheduling and not off)
+        self.engine.check_kernels()
         results = []
         for i in range(len(prompts)):
             req = sched.done[i]

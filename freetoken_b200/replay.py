@@ -88,6 +88,7 @@ def main(argv: Optional[List[str]] = None) -> int:
                     tmp = os.path.join(args.out, f".{step}.f32.tmp")
                     arr.tofile(tmp)
                     os.replace(tmp, os.path.join(args.out, f"{step}.f32"))
+                    engine.check_kernels()  # the logits were just read: the device is idle anyway
             for rid in rec.get("end", []):
                 if engine.is_open(rid):
                     engine.close(rid)
