@@ -117,7 +117,9 @@ def reference_arm():
     ref = os.path.join(ROOT, "baseline", "_ref")
     why = None
     if not os.path.isdir(os.path.join(ref, "freetoken")):
-        why = "baseline/_ref is not installed (pip install --no-deps of the reference was not run on this box)"
+        why = ("baseline/_ref is absent: the reference installs offline only with --no-deps, its package then fails to "
+               "import (flashlib is not installable offline), its MiniMax-M3 loader takes NVFP4 expert banks only, and "
+               "its installed tree names a CUDA call that is closed on this pool, so it was taken out again")
     else:
         p = subprocess.run([sys.executable, "-c",
                             f"import sys; sys.path.insert(0, {ref!r}); import freetoken.layers"],
