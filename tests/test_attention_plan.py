@@ -78,3 +78,22 @@ def test_the_128_row_kernel_gets_pieces_on_tile_boundaries_sorted_by_length():
     # with a fixed number of splits (graph replay) the list keeps its order: tile after tile
     fixed = build_plan([(1, 3000), (1, 500)], 6, 128, None, n_kv_heads=8, fixed_splits=3)
     assert [r[0] for r in fixed.items.tolist()] == [0, 0, 0, 1, 1, 1]
+
+
+def test_which_attention_kernel_a_step_gets():
+    """The rows per CTA name the kernel: 16 float32 / small bfloat16 tiles, 64 mma.sync, 128 tcgen05 with
+    one query tile, 256 with two (steps of a thousand tokens and more)."""
+    import torch
+
+    from freetoken_b200.parts.attention import TC_MIN_TOKENS, TC_PAIR_MIN_TOKENS, attention_tile_rows as rows
+
+    bf, f32 = torch.bfloat16, torch.float32
+    assert rows(f32, False, 6, 4096, 128, 16) == 16 and rows(f32, True, 6, 8, 128, 16) == 16
+    assert rows(bf, True, 6, 8, 128, 16, None, 4096) == 128          # decode on the tcgen05 kernel
+    assert rows(bf, True, 6, 8, 64, 16, None, 4096) == 16            # head size it does not take
+    assert rows(bf, True, 6, 8, 128, 16, 512, 4096) == 16            # a window
+    assert rows(bf, True, 6, 8, 128, 8, None, 4096) == 16            # pages of 8 tokens
+    assert rows(bf, False, 6, TC_MIN_TOKENS - 1, 128, 16) == 64
+    assert rows(bf, False, 6, TC_MIN_TOKENS, 128, 16) == 128
+    assert rows(bf, False, 6, TC_PAIR_MIN_TOKENS, 128, 16) == 256
+    assert rows(bf, False, 6, 4096, 80, 16) == 64
