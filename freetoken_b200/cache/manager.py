@@ -156,6 +156,7 @@ class CacheManager:
             by_key.setdefault(need.group_key(), []).append(entry)
             need_of[need.group_key()] = need
         step = max_step_tokens or max_seq_len
+        self.max_step_tokens = step
         for key, entries in by_key.items():
             need = need_of[key]
             if isinstance(need, PagedKVNeed):
@@ -230,13 +231,21 @@ class CacheManager:
         want = -(-(length + new_tokens) // self.page_size)
         return max(0, want - max(have, first_live))
 
-    def pages_to_admit(self, total_tokens: int) -> List[int]:
-        """Pages per paged group that a request reaching ``total_tokens`` holds at its peak."""
+    def pages_to_admit(self, total_tokens: int, step_tokens: Optional[int] = None) -> List[int]:
+        """Pages per paged group that a request reaching ``total_tokens`` holds at its peak.
+
+        ``step_tokens``: the most tokens of the request one step carries (default: the engine's
+        step size).  A windowed group holds, while a step of ``n`` tokens runs on top of ``L``
+        cached ones, the blocks from the first one a query of the step before could still read,
+        ``(L - window + 1) // P``, to the last one the step writes, ``ceil((L + n) / P)``: at most
+        ``ceil((window - 1 + n) / P) + 1`` pages, whatever ``L`` is."""
+        P = self.page_size
+        n_step = min(step_tokens or self.max_step_tokens, self.max_step_tokens, max(1, total_tokens))
         out = []
         for g in self.paged:
-            n = -(-total_tokens // self.page_size)
+            n = -(-total_tokens // P)
             if g.need.window is not None:
-                n = min(n, -(-(g.need.window + 1) // self.page_size) + 1)
+                n = min(n, -(-(g.need.window - 1 + n_step) // P) + 1)
             out.append(n)
         return out
 

@@ -1,4 +1,4 @@
-"""Command line: ``python -m freetoken_b200 <command>`` (console script ``ft``).
+"""Command line: ``python -m freetoken_b200 <command>`` (console scripts ``freetoken`` and ``ft``).
 
 Commands are looked up in a name -> function table and imported lazily, like the reference's
 dispatcher (python/freetoken/cli.py:93-126).  Engine options carry the reference's names
@@ -22,6 +22,7 @@ def add_engine_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--model-path", "--model", dest="model_path", required=True,
                    help="folder with config.json and the safetensors files")
     p.add_argument("--dtype", default="auto", choices=["auto", "bfloat16", "float32"])
+    p.add_argument("--device", default="cuda:0", help="the CUDA device the engine runs on")
     p.add_argument("--max-running-requests", type=int, default=4)
     p.add_argument("--max-seq-len-override", type=int, default=None)
     p.add_argument("--memory-ratio", type=float, default=0.9)
@@ -39,7 +40,7 @@ def add_engine_args(p: argparse.ArgumentParser) -> None:
 
 
 def engine_kwargs(a: argparse.Namespace) -> Dict:
-    return dict(dtype=a.dtype, max_running_req=a.max_running_requests,
+    return dict(dtype=a.dtype, device=a.device, max_running_req=a.max_running_requests,
                 max_seq_len_override=a.max_seq_len_override, memory_ratio=a.memory_ratio,
                 use_dummy_weight=a.dummy_weight, max_extend_tokens=a.max_extend_tokens,
                 max_step_tokens=a.max_step_tokens, num_page_override=a.num_pages,

@@ -24,6 +24,7 @@ from dataclasses import asdict, dataclass, field
 from typing import Any, Dict, List, Mapping, Optional, Tuple
 
 from ..errors import ConfigError
+from .reader import read_config_json
 
 ARCHITECTURES = ("MiniMaxM3SparseForCausalLM", "MiniMaxM3SparseForConditionalGeneration")
 
@@ -349,14 +350,3 @@ class MiniMaxM3Config:
     @property
     def group_size(self) -> int:
         return self.num_attention_heads // self.num_key_value_heads
-
-
-def read_config_json(folder: str) -> Dict[str, Any]:
-    path = os.path.join(folder, "config.json")
-    if not os.path.isfile(path):
-        raise ConfigError(f"{path}: no config.json in the model folder")
-    with open(path, "r", encoding="utf-8") as f:
-        try:
-            return json.load(f)
-        except json.JSONDecodeError as e:
-            raise ConfigError(f"{path}: not valid JSON ({e})") from e

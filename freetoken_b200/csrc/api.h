@@ -101,6 +101,9 @@ int ftk_moe_combine(const void* y, int dtype, const int32_t* route_pos, int n_to
 // Status words of the kernels' bounded waits: out[0] = first code since the last call (0 = none),
 // out[1] = block that recorded it.  Synchronises with the device and clears the words.
 int ftk_read_status(int* out);
+// Writes `code` into a status word from the host (unit 0: grouped GEMM, 1: attention), so that a caller's
+// handling of a given-up wait can be tested without any wait running out on the device.
+int ftk_debug_set_status(int unit, int code);
 // 0 sends bfloat16 grouped expert products to the CUDA-core kernels; default 1 (tcgen05).
 int ftk_set_moe_tensor_cores(int enabled);
 int ftk_sample(const float* logits, int n_rows, int vocab, const float* temperature,

@@ -893,6 +893,11 @@ int ftk_attention_tc_status(int* out) {
   return 0;
 }
 
+int ftk_attention_tc_set_status(int code) {
+  int host[4] = {code, -1, 0, 0};
+  return cudaMemcpyToSymbol(g_attn_status, host, sizeof(host)) == cudaSuccess ? 0 : 2;
+}
+
 extern "C" int ftk_attention_tc_fits(int head_dim, int page_size, int group) {
   return attention_tc_fits(head_dim, page_size, group) ? 1 : 0;
 }

@@ -552,7 +552,31 @@ int ftk_moe_gemm2_tc(const void* a, const void* w2, const int32_t* expert_offset
 
 // Status of the bounded waits: out[0] = first code recorded since the last call (0 = none),
 // out[1] = block, then cleared.  Synchronises with the device.
-int ftk_attention_tc_status(int* out);  // attention.cu
+int ftk_attention_tc_status(int* out);       // attention.cu
+int ftk_attention_tc_set_status(int code);  // attention.cu
+
+// Writes a code into a status word from the host, as a kernel whose wait ran out would: unit 0 = the
+// grouped GEMM's word, 1 = the attention kernel's.  It exists so that the path from a status word to the
+// caller's error can be exercised without making any wait on the device run out.
+extern "C" int ftk_debug_set_status(int unit, int code) {
+  if (unit == 1) {
+    if (ftk_attention_tc_set_status(code) != 0) {
+      set_error("debug_set_status: cannot write the attention status word");
+      return 2;
+    }
+    return 0;
+  }
+  if (unit != 0) {
+    set_error("debug_set_status: unit must be 0 (grouped GEMM) or 1 (attention), got %d", unit);
+    return 1;
+  }
+  int host[4] = {code, -1, 0, 0};
+  if (cudaMemcpyToSymbol(g_status, host, sizeof(host)) != cudaSuccess) {
+    set_error("debug_set_status: cannot write the status words");
+    return 2;
+  }
+  return 0;
+}
 
 extern "C" int ftk_read_status(int* out) {
   int attn[2] = {0, 0};

@@ -11,7 +11,6 @@ from typing import Any, Dict, Mapping, Optional, Tuple
 
 import torch
 
-from ..config.minimax_m3 import read_config_json
 from ..config.spec import ModelSpec, ParamSpec
 from ..models.model import Model
 from ..parts import BuildEnv, Workspace

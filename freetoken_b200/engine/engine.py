@@ -27,11 +27,11 @@ import torch
 
 from ..cache.manager import CacheManager, PagedCacheView
 from ..config.engine_config import EngineConfig, normalize_dtype
-from ..config.minimax_m3 import read_config_json
-from ..config.spec import ModelSpec
+from ..config.reader import read_config_json
+from ..config.spec import ModelSpec, PagedKVNeed
 from ..errors import CacheError, ConfigError, SchedulerError
 from ..kernels import ops
-from ..parts import BuildEnv, Segment, StepState, Workspace
+from ..parts import BuildEnv, PositionEncoding, Segment, StepState, Workspace
 from ..registry import architecture_of
 from .build import build_model, load_weights, random_weights
 from .step import StepBuffers, StepBuilder
@@ -100,21 +100,28 @@ class Engine:
             raise ConfigError(
                 f"max_seq_len_override={config.max_seq_len_override} exceeds the model's "
                 f"max_position_embeddings={spec.max_position}")
-        if config.num_page_override is not None:
-            limit = min(limit, config.num_page_override * config.page_size)
-        self.max_seq_len = limit
         self.max_step_tokens = int(config.max_step_tokens)
         self.workspace = Workspace(self.device)
-        self.env = BuildEnv(dtype=self.dtype, device=self.device, max_seq_len=self.max_seq_len,
+        self.env = BuildEnv(dtype=self.dtype, device=self.device, max_seq_len=limit,
                             max_step_tokens=self.max_step_tokens, workspace=self.workspace,
                             max_decode_rows=config.max_running_req)
         self.model = build_model(spec, self.env)
+        needs = self.model.cache_needs()
+        # a cache given in pages bounds the longest sequence, unless every mixer that keeps pages has
+        # a window (then a sequence never holds more than its window and a step's tokens)
+        keeps_all = any(isinstance(n, PagedKVNeed) and n.window is None for _, n in needs)
+        if config.num_page_override is not None and keeps_all:
+            limit = min(limit, config.num_page_override * config.page_size)
+        self.max_seq_len = self.env.max_seq_len = limit
         if config.use_dummy_weight:
             random_weights(self.model, config.seed)
         else:
             load_weights(self.model, self.arch, self.typed, config.model_path)
+        for part in self.model.parts():  # position tables: made now, so that the cache is sized after them
+            table = getattr(part, "table", None)
+            if callable(table) and isinstance(part, PositionEncoding):
+                table()
 
-        needs = self.model.cache_needs()
         itemsize = 4 if self.dtype == torch.float32 else 2
         if config.num_page_override is not None:
             num_pages = config.num_page_override
@@ -156,17 +163,10 @@ class Engine:
         return torch.cuda.mem_get_info(self.device)[0]
 
     def _activation_reserve(self) -> int:
-        """Room for the step's work buffers, which are allocated at the first steps."""
-        T = self.max_step_tokens
-        H = self.spec.hidden_size
-        widest = 0
-        for ls in self.spec.layers:
-            p = ls.ffn.params
-            k = int(p.get("top_k", 1) or 1)
-            widest = max(widest, k * (H * 2 + int(p.get("inter", 0))) + 2 * int(p.get("inter", 0)))
-            m = ls.mixer.params
-            widest = max(widest, 3 * int(m.get("n_heads", 0)) * int(m.get("head_dim", 0)))
-        return T * (widest + 6 * H) * 4 + (1 << 28)
+        """Room for the step's work buffers, which are allocated at the first steps: what the model
+        and its parts report for the largest step (:meth:`Part.workspace_bytes`), and some slack for
+        the library's own work areas."""
+        return self.model.workspace_bytes(self.max_step_tokens) + (1 << 28)
 
     def _metadata_capacity(self) -> int:
         """int32 elements the packed metadata of the largest step can take."""
@@ -229,14 +229,23 @@ class Engine:
                 rows.append((e.request_id, int(w)))
                 logit_rows.append(t0 + int(w))
             t0 += n
-        for e in entries:
-            if not self.cache.is_open(e.request_id):
-                self.cache.open(e.request_id)
-        plan = self.cache.begin_step([(e.request_id, len(e.tokens)) for e in entries])
+        opened: List[Hashable] = []  # requests this call opened: closed again if the step is refused
+        try:
+            for e in entries:
+                if not self.cache.is_open(e.request_id) and e.request_id not in opened:
+                    self.cache.open(e.request_id)
+                    opened.append(e.request_id)
+            plan = self.cache.begin_step([(e.request_id, len(e.tokens)) for e in entries])
+        except Exception:
+            for rid in opened:
+                self.cache.close(rid)
+            raise
         try:
             logits = self._run(entries, plan, token_ids, logit_rows)
         except Exception:
             self.cache.abort_step()
+            for rid in opened:
+                self.cache.close(rid)
             raise
         self.cache.end_step()
         if self.config.check_cache:

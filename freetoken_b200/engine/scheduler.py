@@ -108,7 +108,8 @@ class Scheduler:
             return self._reject(req, f"prompt of {len(prompt)} tokens does not fit the longest "
                                      f"sequence of {self.max_seq_len}")
         req.max_tokens = min(params.max_tokens, self.max_seq_len - len(prompt))
-        need = self.engine.cache.pages_to_admit(len(prompt) + req.max_tokens)
+        need = self.engine.cache.pages_to_admit(len(prompt) + req.max_tokens,
+                                                  min(self.max_step_tokens, self.max_extend))
         if any(n > p for n, p in zip(need, self.pool_pages)):
             return self._reject(req, f"needs {need} pages, the cache has {self.pool_pages}")
         req.reserved = need

@@ -91,6 +91,7 @@ _SIGNATURES = {
     "ftk_copy_tokens": [_vp, _i, _vp, _vp, _i, _i, _i, _vp],
     "ftk_read_status": [ctypes.POINTER(ctypes.c_int)],
     "ftk_set_moe_tensor_cores": [_i],
+    "ftk_debug_set_status": [_i, _i],
 }
 _bound = False
 _launches = 0
@@ -165,6 +166,12 @@ def check_status() -> None:
     code = read_status()
     if code:
         raise KernelError(f"a kernel gave up waiting (status {code}); its results are not valid")
+
+
+def debug_set_status(unit: int, code: int) -> None:
+    """Write ``code`` into a status word from the host (``unit`` 0: grouped GEMM, 1: attention), as a
+    kernel whose bounded wait ran out would have.  For tests of the error path; nothing waits."""
+    _check(_lib().ftk_debug_set_status(int(unit), int(code)), "debug_set_status", 0)
 
 
 def set_moe_tensor_cores(enabled: bool) -> None:

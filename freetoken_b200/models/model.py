@@ -3,24 +3,26 @@
 The class knows no architecture: layers come from the part registries, their order from
 ``spec.schedule``.  Parameter names are the dotted paths of the part tree
 (``model.layers.3.self_attn.qkv_proj.weight``), which is how the reference names its state
-dict (python/freetoken/layers/base.py:15-53, python/freetoken/models/minimax_m3/model.py:25-97).
+dict (python/freetoken/layers/base.py:15-53).
 
-Forward (model.py:75-80,96-97; python/freetoken/layers/embedding.py:40-57,103-113): gather
-embedding rows (no scaling) into the 32-bit residual stream, run the schedule, add the last
-layer's output and apply the final norm at the rows whose logits are wanted only, multiply
-by the head matrix (the embedding table when tied) into float32 logits.
+Forward (the order every model class of the reference follows, e.g. its M3 ``model.py:75-80,96-97``;
+python/freetoken/layers/embedding.py:40-57,103-113): the
+embedding part fills the 32-bit residual stream, the schedule runs, the last layer's output is
+added and the final norm applied at the rows whose logits are wanted only, and the head part
+turns those rows into float32 logits.  Embedding and head come from registries like every other
+part (``spec.embedding.kind``, ``spec.head.kind``); the model hands them its vocabulary and width
+as default parameters.
 """
 
 from __future__ import annotations
 
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Any, Dict, List, Tuple
 
 import torch
 
-from ..config.spec import ModelSpec, ParamSpec
+from ..config.spec import ModelSpec, ParamSpec, PartSpec
 from ..errors import ConfigError
-from ..kernels import ops
-from ..parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, BuildEnv, Part, StepState
+from ..parts import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, BuildEnv, Part, StepState
 from ..parts.base import as_rows
 
 
@@ -31,16 +33,6 @@ def _walk(prefix: str, part: Part, out: Dict[str, Tuple[Part, str, ParamSpec]]) 
         _walk(f"{prefix}.{name}", child, out)
 
 
-def head_matmul(y: torch.Tensor, w: torch.Tensor, logits: torch.Tensor) -> None:
-    """``logits = y @ w^T`` as float32.  bfloat16 operands keep their 32-bit accumulator
-    (the reference rounds the logits to bfloat16 and widens them again for sampling,
-    python/freetoken/layers/embedding.py:113, python/freetoken/engine/sample.py:80)."""
-    if y.dtype == torch.float32:
-        torch.matmul(y, w.t(), out=logits)
-    else:
-        torch.mm(y, w.t(), out=logits, out_dtype=torch.float32)
-
-
 class Model:
     def __init__(self, spec: ModelSpec, env: BuildEnv):
         spec.validate()
@@ -48,7 +40,10 @@ class Model:
         self.env = env
         self.hidden = spec.hidden_size
         self.vocab = spec.vocab_size
-        self.tied = bool(spec.head.get("tied", False))
+        ends = dict(vocab=self.vocab, hidden=self.hidden)
+        self.embedding = EMBEDDINGS.build(PartSpec(spec.embedding.kind, {**ends, **spec.embedding.params}), env)
+        self.head = HEADS.build(PartSpec(spec.head.kind, {**ends, **spec.head.params}), env)
+        self.tied = bool(self.head.tied)
         self.blocks = []
         for ls in spec.layers:
             mixer = MIXERS.build(ls.mixer, env)
@@ -56,12 +51,9 @@ class Model:
             self.blocks.append(BLOCKS.build(ls.block, env, mixer=mixer, ffn=ffn,
                                             mixer_name=ls.mixer_name, ffn_name=ls.ffn_name))
         self.final_norm = NORMS.build(spec.final_norm, env)
-        self.embed_weight: Optional[torch.Tensor] = None
-        self.head_weight: Optional[torch.Tensor] = None
-        self._index: Dict[str, Tuple[Optional[Part], str, ParamSpec]] = {}
-        self._index[f"{spec.embedding_name}.weight"] = (None, "embed", ParamSpec((self.vocab, self.hidden)))
-        if not self.tied:
-            self._index[f"{spec.head_name}.weight"] = (None, "head", ParamSpec((self.vocab, self.hidden)))
+        self._index: Dict[str, Tuple[Part, str, ParamSpec]] = {}
+        _walk(spec.embedding_name, self.embedding, self._index)
+        _walk(spec.head_name, self.head, self._index)
         for ls, block in zip(spec.layers, self.blocks):
             _walk(ls.name, block, self._index)
         _walk(spec.final_norm_name, self.final_norm, self._index)
@@ -84,17 +76,11 @@ class Model:
             if tuple(t.shape) != tuple(ps.shape) or t.dtype != self.param_dtype(ps):
                 raise ConfigError(f"bind: tensor '{name}' is {tuple(t.shape)} {t.dtype}, "
                                   f"expected {tuple(ps.shape)} {self.param_dtype(ps)}")
-            if part is None:
-                if local == "embed":
-                    self.embed_weight = t
-                else:
-                    self.head_weight = t
-            else:
-                per_part.setdefault(id(part), (part, {}))[1][local] = t
+            per_part.setdefault(id(part), (part, {}))[1][local] = t
         for part, ts in per_part.values():
             part.bind(ts)
         if self.tied:
-            self.head_weight = self.embed_weight
+            self.head.tie(self.embedding)
 
     def cache_needs(self) -> List[Tuple[int, Any]]:
         """(schedule entry, need) for every entry that owns a cache."""
@@ -109,6 +95,36 @@ class Model:
     def mixers(self):
         return [b.mixer for b in self.blocks]
 
+    def parts(self) -> List[Part]:
+        """Every part of the model, each once (parts shared through ``env.shared`` included)."""
+        seen: Dict[int, Part] = {}
+
+        def visit(p: Part) -> None:
+            if id(p) in seen:
+                return
+            seen[id(p)] = p
+            for c in p.children().values():
+                visit(c)
+
+        for p in (self.embedding, *self.blocks, self.final_norm, self.head):
+            visit(p)
+        for p in self.env.shared.values():
+            if isinstance(p, Part):
+                visit(p)
+        return list(seen.values())
+
+    def workspace_bytes(self, n_tokens: int) -> int:
+        """Work buffers of a step of ``n_tokens`` tokens: the model's own (residual stream, final
+        rows, logits for ``env.max_decode_rows`` rows) and what its parts report.  Parts of equal
+        kind and parameters share their buffers (they are named by the part, not by the layer),
+        so each distinct one counts once."""
+        own = n_tokens * self.hidden * (4 + 4) + self.env.max_decode_rows * self.vocab * 4
+        distinct: Dict[Any, int] = {}
+        for p in self.parts():
+            distinct[(type(p), p.spec.key())] = max(distinct.get((type(p), p.spec.key()), 0),
+                                                    int(p.workspace_bytes(n_tokens)))
+        return own + sum(distinct.values())
+
     # ------------------------------------------------------------------ forward
     def forward(self, step: StepState, cache_views: List[Any]) -> torch.Tensor:
         """Run the step's tokens; return float32 logits ``[n_logit_rows, vocab]``.
@@ -119,7 +135,7 @@ class Model:
         env = self.env
         ws, dt, cap = env.workspace, env.dtype, env.max_step_tokens
         residual = ws.get("model.residual", (T, self.hidden), torch.float32, (cap, self.hidden))
-        ops.embedding_gather(self.embed_weight, step.token_ids, residual)
+        self.embedding.forward(step.token_ids, residual)
         x = None
         for i, e in enumerate(self.spec.schedule):
             x = self.blocks[e.layer].forward(x, residual, step, cache_views[i], e.cache_from is None)
@@ -133,5 +149,5 @@ class Model:
             logits = ws.get("model.logits", (R, self.vocab), torch.float32)
         y = ws.get("model.final", (R, self.hidden), dt, (cap, self.hidden))
         self.final_norm.add_forward(as_rows(x, self.final_norm), residual, y, rows=step.logit_rows)
-        head_matmul(y, self.head_weight, logits)
+        self.head.forward(y, logits)
         return logits

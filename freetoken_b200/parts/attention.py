@@ -104,6 +104,13 @@ class GQAttention(Mixer):
         return PagedKVNeed((("k", self.n_kv_heads, self.head_dim),
                             ("v", self.n_kv_heads, self.head_dim)), self.window)
 
+    def workspace_bytes(self, n_tokens: int) -> int:
+        item = 4 if self.env.dtype == torch.float32 else 2
+        # qkv, q, o, out; and the 32-bit partial results of tiles split along the keys (two CTAs'
+        # worth of slots per SM, 128 rows each at most)
+        rows = n_tokens * (3 * self.q_dim + 2 * self.kv_dim + self.hidden) * item
+        return rows + 2 * 148 * 128 * (self.head_dim + 2) * 4 * 2
+
     # ------------------------------------------------------------------ step
     def tile_rows(self, decode_only: bool, n_tokens: int = 0, page_size: int = 0, longest_span: int = 0) -> int:
         return attention_tile_rows(self.env.dtype, decode_only, self.group, n_tokens, self.head_dim, page_size,

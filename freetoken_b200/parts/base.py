@@ -1,8 +1,8 @@
 """Interfaces of the parts a layer is put together from, and their registries.
 
-Five kinds of part exist: mixer (attention, or anything else that mixes tokens),
-feed-forward, norm, position encoding, and block (the arrangement of the other four
-in a layer).  A part is built from a :class:`PartSpec` (its sizes and constants) and a
+Seven kinds of part exist: mixer (attention, or anything else that mixes tokens),
+feed-forward, norm, position encoding, block (the arrangement of those four in a layer),
+and the model's two ends, embedding and head.  A part is built from a :class:`PartSpec` (its sizes and constants) and a
 :class:`BuildEnv`; it declares the tensors it owns (:meth:`Part.param_specs`), gets
 them bound by name (:meth:`Part.bind`), and runs on the tokens of one step.  No part
 looks at the model it is in.
@@ -66,6 +66,8 @@ FEED_FORWARDS: PartRegistry = PartRegistry("feed-forward")
 NORMS: PartRegistry = PartRegistry("norm")
 POSITIONS: PartRegistry = PartRegistry("position encoding")
 BLOCKS: PartRegistry = PartRegistry("block")
+EMBEDDINGS: PartRegistry = PartRegistry("embedding")
+HEADS: PartRegistry = PartRegistry("head")
 
 
 @dataclass
@@ -74,7 +76,8 @@ class BuildEnv:
 
     dtype: torch.dtype  # compute dtype: torch.bfloat16 or torch.float32
     device: torch.device
-    max_seq_len: int  # longest sequence a request may reach (sizes position tables)
+    max_seq_len: int  # longest sequence a request may reach (sizes position tables); an upper bound while
+    # parts are built, final (it may have shrunk to what the cache holds) before the first step
     max_step_tokens: int  # most tokens one step carries (sizes work buffers)
     workspace: "Workspace"
     max_decode_rows: int = 64  # most rows of logits a decode-only step asks for
@@ -134,6 +137,12 @@ class Part:
     def children(self) -> Dict[str, "Part"]:
         """Sub-parts by local name (their parameters are prefixed with ``name.``)."""
         return {}
+
+    def workspace_bytes(self, n_tokens: int) -> int:
+        """Bytes of work buffers this part (without its children) asks the :class:`Workspace` for
+        in a step of ``n_tokens`` tokens.  The engine sets that much memory aside before it sizes
+        the cache, because the buffers are only allocated at the first steps."""
+        return 0
 
 
 class RouteSum:
@@ -206,6 +215,31 @@ class FeedForward(Part):
     # call it when it exists and hand the result to :func:`as_rows` before any consumer but a norm.
 
     wants_f32_input: bool = False  # ask the preceding norm for a 32-bit copy of its output
+
+
+class Embedding(Part):
+    """Token ids to rows of the 32-bit residual stream."""
+
+    def forward(self, token_ids: torch.Tensor, residual: torch.Tensor) -> None:
+        """``residual[t] = float32(row of token_ids[t])`` for the step's tokens (``residual [T, hidden]``)."""
+        raise NotImplementedError
+
+    def table(self) -> torch.Tensor:
+        """The ``[vocab, hidden]`` table, for a head that is tied to it."""
+        raise NotImplementedError
+
+
+class Head(Part):
+    """Normed rows to float32 logits."""
+
+    tied: bool = False  # the head owns no matrix and is given the embedding by :meth:`tie`
+
+    def tie(self, embedding: Embedding) -> None:
+        raise NotImplementedError
+
+    def forward(self, y: torch.Tensor, logits: torch.Tensor) -> None:
+        """``logits [R, vocab]`` (float32, preallocated) from ``y [R, hidden]``."""
+        raise NotImplementedError
 
 
 class Block(Part):

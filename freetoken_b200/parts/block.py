@@ -34,6 +34,10 @@ class PreNormResidualBlock(Block):
         return {self.input_norm_name: self.input_norm, self.mixer_name: self.mixer,
                 self.post_norm_name: self.post_norm, self.ffn_name: self.ffn}
 
+    def workspace_bytes(self, n_tokens: int) -> int:
+        item = 4 if self.env.dtype == torch.float32 else 2
+        return n_tokens * self.hidden * (2 * item + 4)
+
     def forward(self, x: Optional[torch.Tensor], residual: torch.Tensor, step: StepState,
                 cache: Any, writes_cache: bool) -> torch.Tensor:
         T = residual.shape[0]

@@ -41,6 +41,10 @@ class GatedMLP(FeedForward):
             "down_proj.weight": ParamSpec((self.hidden, self.inter)),
         }
 
+    def workspace_bytes(self, n_tokens: int) -> int:
+        item = 4 if self.env.dtype == torch.float32 else 2
+        return n_tokens * (3 * self.inter + self.hidden) * item
+
     def forward(self, h: torch.Tensor, step: StepState, h_f32: Optional[torch.Tensor] = None) -> torch.Tensor:
         T = h.shape[0]
         ws, dt, cap = self.env.workspace, self.env.dtype, self.env.max_step_tokens

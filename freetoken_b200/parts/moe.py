@@ -71,6 +71,12 @@ class MoE(FeedForward):
     def children(self) -> Dict[str, Part]:
         return {"shared_experts": self.shared} if self.shared is not None else {}
 
+    def workspace_bytes(self, n_tokens: int) -> int:
+        item = 4 if self.env.dtype == torch.float32 else 2
+        T, k, H, I, E = n_tokens, self.top_k, self.hidden, self.inter, self.n_experts
+        routed = T * k * ((2 * H + I) * item + 4 * 4)  # expert-ordered input, activation, output; ids, weights, sort
+        return routed + T * (H * (4 + item) + E * 4) + (2 * E + 1) * 4
+
     def forward(self, h: torch.Tensor, step: StepState, h_f32: Optional[torch.Tensor] = None) -> torch.Tensor:
         return self.forward_lazy(h, step, h_f32).rows()
 

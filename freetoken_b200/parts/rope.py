@@ -34,14 +34,17 @@ class NeoxRope(PositionEncoding):
         if self.rotary_dim % 2 or self.rotary_dim < 0:
             raise ConfigError(f"rope_neox: rotary_dim={self.rotary_dim} must be even and >= 0")
         self._table: Optional[torch.Tensor] = None
-        if self.rotary_dim:
-            rd = self.rotary_dim
-            inv_freq = 1.0 / (self.theta ** (torch.arange(0, rd, 2, dtype=torch.float) / rd))
-            t = torch.arange(env.max_seq_len, dtype=torch.float)
-            freqs = torch.einsum("i,j -> ij", t, inv_freq)
-            self._table = torch.cat((freqs.cos(), freqs.sin()), dim=-1).contiguous().to(env.device)
 
     def table(self) -> Optional[torch.Tensor]:
+        """Built at the first call: by then the engine has settled its longest sequence
+        (``env.max_seq_len`` may shrink between a part's construction and the first step, once
+        the cache has been sized)."""
+        if self._table is None and self.rotary_dim:
+            rd = self.rotary_dim
+            inv_freq = 1.0 / (self.theta ** (torch.arange(0, rd, 2, dtype=torch.float) / rd))
+            t = torch.arange(self.env.max_seq_len, dtype=torch.float)
+            freqs = torch.einsum("i,j -> ij", t, inv_freq)
+            self._table = torch.cat((freqs.cos(), freqs.sin()), dim=-1).contiguous().to(self.env.device)
         return self._table
 
 

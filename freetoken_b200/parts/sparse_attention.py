@@ -61,6 +61,11 @@ class BlockSparseAttention(GQAttention):
 
     graph_safe = True
 
+    def workspace_bytes(self, n_tokens: int) -> int:
+        item = 4 if self.env.dtype == torch.float32 else 2
+        index = n_tokens * ((2 * self.n_index_heads + 1) * self.index_dim * item + self.n_kv_heads * self.topk_blocks * 4)
+        return super().workspace_bytes(n_tokens) + index
+
     def plan_key(self, decode_only: bool = False):
         return ("sparse_attention", self.group, 16, self.n_kv_heads, self.head_dim, self.block_size,
                 self.topk_blocks)

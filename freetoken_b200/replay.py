@@ -35,6 +35,7 @@ def build_parser() -> argparse.ArgumentParser:
                    help="most tokens that live requests hold at any time (each rounded up to 64)")
     p.add_argument("--page-size", type=int, default=PAGE_SIZE, help=argparse.SUPPRESS)
     p.add_argument("--no-cuda-graph", action="store_true", help=argparse.SUPPRESS)
+    p.add_argument("--device", default="cuda:0", help=argparse.SUPPRESS)
     return p
 
 
@@ -49,19 +50,19 @@ def main(argv: Optional[List[str]] = None) -> int:
     import torch
 
     from .config.engine_config import EngineConfig
-    from .config.minimax_m3 import read_config_json
+    from .config.reader import read_config_json
     from .engine.engine import Engine, StepEntry
     from .errors import FreeTokenError
+    from .registry import architecture_of
 
     page = args.page_size
     n_pages = -(-args.max_tokens // page)
     try:
         raw = read_config_json(args.model)
-        text = raw.get("text_config", raw)
-        max_pos = int(text.get("max_position_embeddings", args.max_tokens))
-        seq = min(max_pos, n_pages * page)
+        arch = architecture_of(raw)  # the architecture says how long its sequences may get
+        seq = min(int(arch.build_spec(arch.parse_config(raw)).max_position), n_pages * page)
         engine = Engine(EngineConfig(
-            model_path=args.model, dtype=args.dtype, page_size=page, num_page_override=n_pages,
+            model_path=args.model, dtype=args.dtype, device=args.device, page_size=page, num_page_override=n_pages,
             max_running_req=MAX_LIVE, max_seq_len_override=seq, max_extend_tokens=seq,
             max_step_tokens=max(seq, MAX_LIVE), cuda_graph=not args.no_cuda_graph))
     except FreeTokenError as e:

@@ -284,20 +284,14 @@ def router_margin(h: torch.Tensor, w_gate: torch.Tensor, bias: Optional[torch.Te
     return gap / slope.clamp_min(1e-12)
 
 
-def moe_block(h, W, prefix: str, cfg: PlainConfig, rounding, margins: Optional[list] = None):
-    """Routed experts: ``sum_j (act(h W1^T) W2^T) w_j`` with the weight applied to the
-    unrounded product and the sum over routes in route order
-    (python/freetoken/moe/fused_nvfp4.py:317-344; python/freetoken/kernel/triton/fused_moe.py:287-296,142-152),
-    plus the shared expert on the same input (moe.py:87-88)."""
-    bias = W.get(prefix + "e_score_correction_bias") if cfg.bias else None
-    w, ids = router(h, W[prefix + "gate.weight"], bias, cfg)
-    if margins is not None:
-        margins.append((router_margin(h, W[prefix + "gate.weight"], bias, cfg),
-                        h.float() @ W[prefix + "gate.weight"].float().T))
+def routed_experts(h, ids, w, W, prefix: str, cfg: PlainConfig, rounding):
+    """``out_t = sum_j (act(h_t W1[e]^T) W2[e]^T) w[t, j]`` with ``e = ids[t, j]``: the weight multiplies
+    the unrounded product, the sum runs over the routes in route order
+    (python/freetoken/moe/fused_nvfp4.py:317-344; python/freetoken/kernel/triton/fused_moe.py:287-296,142-152)."""
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         acc = torch.zeros(h.shape[1], dtype=h.dtype)
-        for j in range(cfg.top_k):
+        for j in range(ids.shape[1]):
             e = int(ids[t, j])
             x = h[t: t + 1]
             g = _rnd(x @ W[f"{prefix}experts.{e}.w1.weight"].T, rounding)
@@ -306,6 +300,18 @@ def moe_block(h, W, prefix: str, cfg: PlainConfig, rounding, margins: Optional[l
             y = _rnd((a @ W[f"{prefix}experts.{e}.w2.weight"].T) * w[t, j].to(h.dtype), rounding)
             acc = acc + y[0]
         out[t] = _rnd(acc, rounding)
+    return out
+
+
+def moe_block(h, W, prefix: str, cfg: PlainConfig, rounding, margins: Optional[list] = None):
+    """Router, routed experts (:func:`routed_experts`), plus the shared expert on the same input
+    (python/freetoken/models/minimax_m3/moe.py:83-88)."""
+    bias = W.get(prefix + "e_score_correction_bias") if cfg.bias else None
+    w, ids = router(h, W[prefix + "gate.weight"], bias, cfg)
+    if margins is not None:
+        margins.append((router_margin(h, W[prefix + "gate.weight"], bias, cfg),
+                        h.float() @ W[prefix + "gate.weight"].float().T))
+    out = routed_experts(h, ids, w, W, prefix, cfg, rounding)
     if cfg.n_shared > 0:
         sh = gated_mlp(h, W[prefix + "shared_experts.gate_proj.weight"],
                        W[prefix + "shared_experts.up_proj.weight"],

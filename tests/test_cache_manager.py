@@ -181,3 +181,42 @@ def test_close_is_refused_during_a_step_and_state_slots_are_fresh_once():
         m.open(r)
     with pytest.raises(CacheError, match="no request slot"):
         m.open("e")
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_admission_reserves_what_a_windowed_request_holds_at_its_peak(seed):
+    """``pages_to_admit`` is a bound on what a request ever holds while a step runs, for full and
+    windowed groups, whatever the portions are; and it is reached (the bound is not loose by more
+    than a page for the windowed group)."""
+    rng = random.Random(seed)
+    page = rng.choice([2, 4, 8])
+    window = rng.choice([1, 3, 8, 10, 17])
+    step = rng.choice([1, 2, 5, 16, 64])
+    total = rng.randint(1, 200)
+    need = PagedKVNeed((("k", 1, 16), ("v", 1, 16)), window=window)
+    m = CacheManager([(0, FULL), (1, need)], page, 200, 2, 256, torch.float32, CPU, max_step_tokens=step)
+    bound = m.pages_to_admit(total)
+    assert bound[0] == -(-total // page)
+    m.open("a")
+    peak, fed = [0, 0], 0
+    while fed < total:
+        n = min(step if rng.random() < 0.5 else rng.randint(1, step), total - fed)
+        m.begin_step([("a", n)])
+        for i, g in enumerate(m.paged):
+            peak[i] = max(peak[i], g.pool.num_pages - g.pool.free_count)
+        m.end_step()
+        fed += n
+    assert peak[0] == bound[0]
+    assert peak[1] <= bound[1], (page, window, step, total, peak, bound)
+    # with whole steps every time the bound is tight within one page
+    m.close("a")
+    m.open("b")
+    peak_b, fed = 0, 0
+    while fed < total:
+        n = min(step, total - fed)
+        m.begin_step([("b", n)])
+        peak_b = max(peak_b, m.paged[1].pool.num_pages - m.paged[1].pool.free_count)
+        m.end_step()
+        fed += n
+    assert bound[1] - peak_b <= 2
+    assert m.pages_to_admit(total, step_tokens=1)[1] <= bound[1]

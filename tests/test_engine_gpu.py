@@ -200,8 +200,8 @@ def test_step_refuses_bad_input_and_leaks_nothing(world):
     out = eng.step([StepEntry("x", [5], [0])])  # the engine still works after the refusal
     assert out.logits.shape == (1, 256)
     eng.close("x")
-    if eng.is_open("y"):
-        eng.close("y")
+    assert not eng.is_open("y")  # the refused step undid the open it had done
+    assert eng.cache.free_request_slots() == eng.config.max_running_req
     assert eng.cache.paged[0].pool.free_count == 6
 
 
@@ -258,3 +258,30 @@ def test_kernels_ran_and_the_library_is_loaded(world):
     assert path and path.endswith(".so")
     with open("/proc/self/maps") as f:
         assert any(path in line for line in f)
+
+
+@pytest.mark.parametrize("unit,code", [(0, 103), (1, 7)])
+def test_a_given_up_wait_reaches_the_caller_as_an_error(unit, code, world):
+    """The tensor-core kernels bound every wait and leave a code in a status word when one runs out.
+    Here the word is written from the host (no wait is made to run out): the engine's check raises
+    ``KernelError`` naming the code, the word is cleared by the read, and the engine goes on working."""
+    from freetoken_b200.errors import KernelError
+    from freetoken_b200.kernels import ops
+
+    _, plain, eng = world("A", "bfloat16")
+    eng.check_kernels()  # clean to begin with
+    ops.debug_set_status(unit, code)
+    with pytest.raises(KernelError, match=f"status {code}"):
+        eng.check_kernels()
+    eng.check_kernels()  # reading cleared it
+    assert ops.read_status() == 0
+    # the first step of a fresh engine looks at the word as well
+    fresh = make_engine(world("A")[0], "bfloat16", "cuda:0", 4, 16)
+    ops.debug_set_status(unit, code)
+    with pytest.raises(KernelError, match="gave up waiting"):
+        fresh.step([StepEntry("s", [1, 2, 3], [2])])
+    out = fresh.step([StepEntry("s", [4], [0])])
+    assert torch.isfinite(out.logits).all()
+    fresh.close("s")
+    with pytest.raises(KernelError, match="unit must be"):
+        ops.debug_set_status(5, 1)

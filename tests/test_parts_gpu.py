@@ -22,7 +22,7 @@ from freetoken_b200.engine.engine import Engine, StepEntry
 from freetoken_b200.engine.step import StepBuffers, StepBuilder
 from freetoken_b200.parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, BuildEnv, Mixer, Segment,
                                   StepState, Workspace)
-from freetoken_b200.parts.base import FeedForward, Norm, PositionEncoding
+from freetoken_b200.parts.base import EMBEDDINGS, HEADS, Embedding, FeedForward, Head, Norm, PositionEncoding
 from freetoken_b200.registry import Architecture, register_architecture, unregister_architecture
 from freetoken_b200.weights.random_init import random_tensors_cpu, write_model_folder
 from helpers import F32_TOL
@@ -342,8 +342,9 @@ def test_a_schedule_may_repeat_a_layer_and_share_a_cache(tmp_path):
 
 
 # ---------------------------------------------------------------------------------------------
-# A toy norm, a toy position encoding and a toy feed-forward with routing, defined here, beside the
-# framework's attention and its mixture of experts, in one toy architecture.
+# A toy norm, a toy position encoding, a toy feed-forward with routing, a scaled embedding and a head
+# with bias and soft cap, defined here, beside the framework's attention and its mixture of experts,
+# in one toy architecture.
 class ToyCenteredNorm(Norm):
     """``(x - mean) * rsqrt(var + eps) * w``; takes no sum-over-routes, so a mixture of experts
     before it hands its output over as plain rows."""
@@ -421,11 +422,44 @@ class ToySwitchFFN(FeedForward):
         return torch.einsum("tni,nhi,tn->th", mid, self.params["w_out"], keep).contiguous()
 
 
+class ToyScaledEmbedding(Embedding):
+    """Rows of the table times ``sqrt(hidden)``, as some model families scale their embeddings."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.vocab, self.hidden = int(spec["vocab"]), int(spec["hidden"])
+
+    def param_specs(self):
+        return {"weight": ParamSpec((self.vocab, self.hidden))}
+
+    def forward(self, token_ids, residual):
+        residual.copy_(self.params["weight"][token_ids.long()].float() * self.hidden ** 0.5)
+
+    def table(self):
+        return self.params["weight"]
+
+
+class ToySoftcapHead(Head):
+    """``cap * tanh((y W^T + b) / cap)``: a bias and a soft cap, neither of which the framework's head has."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.vocab, self.hidden, self.cap = int(spec["vocab"]), int(spec["hidden"]), float(spec["cap"])
+
+    def param_specs(self):
+        return {"weight": ParamSpec((self.vocab, self.hidden), init=("normal", 0.0, 0.2)),
+                "bias": ParamSpec((self.vocab,), "float32", ("normal", 0.0, 0.5))}
+
+    def forward(self, y, logits):
+        z = y.float() @ self.params["weight"].float().T + self.params["bias"]
+        logits.copy_(self.cap * torch.tanh(z / self.cap))
+
+
 def toy_routed_reference(W, tokens, cfg):
     """Plain statement of the toy model below; also returns, per token, the smallest gap between the
     two largest router values of either routed layer (a token with a small gap may go elsewhere in
     reduced precision)."""
-    r = W["model.embed_tokens.weight"][torch.as_tensor(tokens)]
+    r = W["model.embed_tokens.weight"][torch.as_tensor(tokens)] * cfg["hidden"] ** 0.5
     T = r.shape[0]
     tab = ToyAngles.angles(cfg["rotary"], cfg["step"], T)
     cos, sin = tab[:, : cfg["rotary"] // 2], tab[:, cfg["rotary"] // 2:]
@@ -462,7 +496,7 @@ def toy_routed_reference(W, tokens, cfg):
                     f[t] += (dn[ex] @ act) * wts[t, j]
         r = r + f
     y = ToyCenteredNorm.apply(r, W["model.norm.weight"], 1e-5)
-    return y @ W["lm_head.weight"].T, gaps
+    return cfg["cap"] * torch.tanh((y @ W["lm_head.weight"].T + W["lm_head.bias"]) / cfg["cap"]), gaps
 
 
 @pytest.fixture
@@ -470,6 +504,8 @@ def toy_routed_architecture():
     NORMS.register("toy_centered")(ToyCenteredNorm)
     POSITIONS.register("toy_angles")(ToyAngles)
     FEED_FORWARDS.register("toy_switch")(ToySwitchFFN)
+    EMBEDDINGS.register("toy_scaled")(ToyScaledEmbedding)
+    HEADS.register("toy_softcap")(ToySoftcapHead)
 
     def parse(raw, num_layers=None):
         return types.SimpleNamespace(**raw)
@@ -486,13 +522,14 @@ def toy_routed_architecture():
         layers = tuple(LayerSpec(name=f"model.layers.{l}", block=block, mixer=attn, ffn=ffns[l], mixer_name="attn",
                                  ffn_name="ffn") for l in range(2))
         return ModelSpec(architecture="ToyRoutedLM", vocab_size=c.vocab, hidden_size=c.hidden, layers=layers,
-                         schedule=(ScheduleEntry(0), ScheduleEntry(1)), embedding=PartSpec("token_embedding"),
-                         final_norm=norm, head=PartSpec("linear_head", dict(tied=False)), max_position=256)
+                         schedule=(ScheduleEntry(0), ScheduleEntry(1)), embedding=PartSpec("toy_scaled"),
+                         final_norm=norm, head=PartSpec("toy_softcap", dict(cap=c.cap)), max_position=256)
 
     register_architecture(Architecture(names=("ToyRoutedLM",), parse_config=parse, build_spec=build_spec))
     yield
     unregister_architecture("ToyRoutedLM")
-    for reg, kind in ((NORMS, "toy_centered"), (POSITIONS, "toy_angles"), (FEED_FORWARDS, "toy_switch")):
+    for reg, kind in ((NORMS, "toy_centered"), (POSITIONS, "toy_angles"), (FEED_FORWARDS, "toy_switch"),
+                      (EMBEDDINGS, "toy_scaled"), (HEADS, "toy_softcap")):
         reg.unregister(kind)
 
 
@@ -505,7 +542,7 @@ def test_toy_norm_position_and_routed_ffn_beside_the_frameworks_parts(dtype, toy
     from safetensors.torch import load_file
 
     cfg = {"architectures": ["ToyRoutedLM"], "vocab": 131, "hidden": 64, "inter": 48, "heads": 4, "kv_heads": 2,
-           "head_dim": 32, "rotary": 16, "step": 0.013}
+           "head_dim": 32, "rotary": 16, "step": 0.013, "cap": 3.0}
     folder = write_model_folder(cfg, str(tmp_path / "toyr"), seed=6)
     W = {k: v.float() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
     eng = Engine(EngineConfig(model_path=folder, dtype=dtype, page_size=4, num_page_override=40, max_running_req=3,

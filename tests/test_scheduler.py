@@ -168,3 +168,48 @@ def test_sampling_params_follow_the_reference():
     assert SamplingParams().max_tokens == 1024 and SamplingParams().top_k == -1
     assert 0.0 <= uniform_for(1, "a", 3) < 1.0 and uniform_for(1, "a", 3) == uniform_for(1, "a", 3)
     assert uniform_for(1, "a", 3) != uniform_for(1, "a", 4)
+
+
+def test_windowed_groups_are_reserved_at_their_peak(setup, tmp_path_factory):
+    """A mixer with a window keeps few pages between steps but needs those of a whole portion while
+    a step runs: admission reserves that peak, so admitted requests never meet "out of pages", with
+    portions longer than a token and a pool that holds barely more than one request."""
+    import dataclasses
+
+    from freetoken_b200.config.engine_config import EngineConfig
+    from freetoken_b200.config.spec import PartSpec
+    from freetoken_b200.engine.engine import Engine
+
+    sched0, plain = setup()
+    base = sched0.engine
+    folder = base.config.model_path
+    layers = tuple(dataclasses.replace(ls, mixer=PartSpec(ls.mixer.kind, dict(ls.mixer.params, window=8)))
+                   for ls in base.spec.layers)
+    spec = dataclasses.replace(base.spec, layers=layers)
+
+    def run(pages, max_step, prompts):
+        cfg = EngineConfig(model_path=folder, dtype="float32", device="cpu", page_size=4, num_page_override=pages,
+                           max_step_tokens=max_step, max_extend_tokens=max_step, max_running_req=3, check_cache=True)
+        eng = Engine(cfg, spec=spec)
+        s = Scheduler(eng, Sampler(eng.device, eng.spec.vocab_size, 3))
+        ids = [s.add_request(p, SamplingParams(max_tokens=12)) for p in prompts]
+        live = 0
+        while not s.idle:
+            s.step()
+            live = max(live, len(s.running))
+            eng.cache.check()
+            assert all(x <= p for x, p in zip(s.reserved, s.pool_pages))
+        assert all(g.pool.free_count == g.pool.num_pages for g in eng.cache.paged)
+        return [s.done[i] for i in ids], live, s
+
+    V = plain.cfg.vocab
+    prompts = [tokens_for(V, n, 70 + n) for n in (100, 61, 33)]
+    roomy, live_roomy, _ = run(pages=200, max_step=8, prompts=prompts)
+    tight, live_tight, s = run(pages=6, max_step=8, prompts=prompts)  # ceil((7 + 8) / 4) + 1 = 5 pages a request
+    assert [r.finish_reason for r in tight] == ["length"] * 3
+    assert [r.output for r in tight] == [r.output for r in roomy]  # same tokens, only later
+    assert live_roomy == 3 and live_tight == 1
+    assert s.engine.cache.pages_to_admit(112, 8) == [5]
+    # a step size whose peak the pool cannot hold is answered with an error, not admitted to fail later
+    refused, _, _ = run(pages=6, max_step=64, prompts=prompts[:1])
+    assert refused[0].finish_reason == "error" and "pages" in refused[0].error

@@ -12,7 +12,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import F32_TOL, assert_bf16_close, mixed_schedule, model_folder, tokens_for
+from helpers import BF16_TOL, F32_TOL, assert_bf16_close, clear_tokens, mixed_schedule, model_folder, tokens_for
 from plain.m3_plain import PlainM3
 from tiny_configs import ALL
 
@@ -21,10 +21,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 TRACE_RUN = os.path.join(ROOT, "bin", "trace_run")
 
 
-def run_trace(folder, dtype, out_dir, max_tokens, steps):
+def run_trace(folder, dtype, out_dir, max_tokens, steps, extra=()):
     lines = "".join(json.dumps(s) + "\n" for s in steps)
     p = subprocess.run([sys.executable, TRACE_RUN, "--model", folder, "--dtype", dtype, "--out", out_dir,
-                        "--max-tokens", str(max_tokens)], input=lines, capture_output=True, text=True, timeout=600)
+                        "--max-tokens", str(max_tokens), *extra], input=lines, capture_output=True, text=True,
+                       timeout=600)
     assert p.returncode == 0, p.stderr[-2000:]
     done = [l for l in p.stdout.splitlines() if l.startswith("done ")]
     assert done == [f"done {s['step']}" for s in steps]
@@ -36,21 +37,28 @@ def read_logits(out_dir, step, vocab):
     return torch.from_numpy(a.reshape(-1, vocab).copy())
 
 
-def check(got, ref, dtype, margins, what):
+def check(got, ref, dtype, margins, what, prefix_only=False):
     if dtype == "float32":
         torch.testing.assert_close(got, ref[: got.shape[0]], **F32_TOL, msg=lambda m: f"{what}: {m}")
+    elif prefix_only and got.shape[0] < 24:
+        # a few rows out of a sequence with block-sparse layers: strict where every earlier choice was clear
+        sure = margins[: got.shape[0]] > 0
+        torch.testing.assert_close(got[sure], ref[: got.shape[0]][sure], **BF16_TOL, msg=lambda m: f"{what}: {m}")
     else:
-        assert_bf16_close(got, ref, margins, what)
+        assert_bf16_close(got, ref, margins, what, prefix_only=prefix_only)
 
 
-@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("A", "bfloat16"), ("C", "float32"), ("C", "bfloat16"),
-                                        ("D", "float32")])
+# B (tied head, softmax router, no QK norm) runs with its own pages of 8 tokens; D has block-sparse layers,
+# where bfloat16 is compared before the first near-tie of a sequence only.
+@pytest.mark.parametrize("name,dtype", [(n, d) for n in "ABCD" for d in ("float32", "bfloat16")])
 def test_trace_replay(name, dtype, tmp_path_factory, tmp_path):
     folder = model_folder(tmp_path_factory.getbasetemp(), name, ALL[name])
     plain = PlainM3(folder)
     V = plain.cfg.vocab
+    sparse = name == "D"
     lengths = {"a": 70, "b": 100, "c": 45, "d": 64, "e": 90, "f": 33}
-    seqs = {r: tokens_for(V, n, 50 + i) for i, (r, n) in enumerate(lengths.items())}
+    seqs = {r: (clear_tokens(plain, n, 50 + 40 * i, 30) if sparse else tokens_for(V, n, 50 + i))
+            for i, (r, n) in enumerate(lengths.items())}
     steps, where = [], {}  # where[(request, mode)] = list of (step, rows, first position)
     n = 0
 
@@ -90,13 +98,21 @@ def test_trace_replay(name, dtype, tmp_path_factory, tmp_path):
             if fed[r] == lengths[r]:
                 steps[-1]["end"].append("m" + r)
     out_dir = str(tmp_path / "out")
-    run_trace(folder, dtype, out_dir, 4 * 128, steps)
+    run_trace(folder, dtype, out_dir, 4 * 128, steps, extra=("--page-size", "8") if name == "B" else ())
 
     ref = {r: plain.logits(t) for r, t in seqs.items()}
     marg = {r: plain.router_margins(t) for r, t in seqs.items()}
-    check(read_logits(out_dir, where["whole"][0][0], V), ref["a"], dtype, marg["a"], "whole")
+    if sparse:  # a flip spreads to later tokens: everything after the first near-tie counts as unsure
+        for r, m in marg.items():
+            unsure = m <= 0
+            if unsure.any():
+                m[int(unsure.float().argmax()):] = 0
+    check(read_logits(out_dir, where["whole"][0][0], V), ref["a"], dtype, marg["a"], "whole", sparse)
     tail = torch.cat([read_logits(out_dir, s, V) for s, _, _ in where["tail"]])
-    check(tail, ref["a"][38:], dtype, marg["a"][38:], "tail")
+    if not (sparse and dtype == "bfloat16"):  # (a tail of a sparse sequence lies behind its first near-tie)
+        check(tail, ref["a"][38:], dtype, marg["a"][38:], "tail")
+    else:
+        assert torch.isfinite(tail).all() and (tail - ref["a"][38:]).abs().max() < 0.5
     assert not os.path.exists(os.path.join(out_dir, "1.f32"))  # nothing was wanted in that step
     rows, places = [], []
     for s, c, i in where["cuts"]:
@@ -105,7 +121,11 @@ def test_trace_replay(name, dtype, tmp_path_factory, tmp_path):
         rows.append(got)
         places += [i, i + c - 1]
     idx = torch.tensor(places)
-    check(torch.cat(rows), ref["a"][idx], dtype, marg["a"][idx], "portions of changing size")
+    if sparse and dtype == "bfloat16":
+        keep = marg["a"][idx] > 0
+        torch.testing.assert_close(torch.cat(rows)[keep], ref["a"][idx][keep], **BF16_TOL)
+    else:
+        check(torch.cat(rows), ref["a"][idx], dtype, marg["a"][idx], "portions of changing size")
     files = {}
     for r in seqs:
         rows = []
@@ -115,7 +135,7 @@ def test_trace_replay(name, dtype, tmp_path_factory, tmp_path):
             entry_ids = [e["id"] for e in steps[s]["entries"]]
             off = sum(len(e["want"]) for e in steps[s]["entries"][: entry_ids.index("m" + r)])
             rows.append(files[s][off:off + k])
-        check(torch.cat(rows), ref[r], dtype, marg[r], f"mixed {r}")
+        check(torch.cat(rows), ref[r], dtype, marg[r], f"mixed {r}", sparse)
 
 
 def test_trace_run_reports_errors(tmp_path_factory, tmp_path):
