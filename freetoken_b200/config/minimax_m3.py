@@ -10,8 +10,9 @@ variant the reference asserts on becomes a :class:`ConfigError` naming the key.
 
 Options that the reference pins but this engine takes from config.json:
 ``use_qk_norm`` (false skips the per-head norms), ``use_gemma_norm`` (false multiplies
-by ``w`` instead of ``1+w``), ``hidden_act`` (``"silu"`` is plain SwiGLU,
-``"swigluoai"`` the clamped form), ``scoring_func`` (``"sigmoid"`` or ``"softmax"``),
+by ``w`` instead of ``1+w``), ``hidden_act`` (``"swigluoai"`` is the clamped form; ``"silu"`` is
+plain SwiGLU unless ``swiglu_alpha`` / ``swiglu_limit`` stand beside it, which is how the native
+key shape spells the clamped form), ``scoring_func`` (``"sigmoid"`` or ``"softmax"``),
 ``use_routing_bias``, ``n_shared_experts`` (0 means no shared expert) and
 ``attn_type_list`` as an alias for a per-layer mixer choice (0 = full attention).
 """
@@ -145,6 +146,10 @@ class MiniMaxM3Config:
         act = text.get("hidden_act", "swigluoai")
         if act not in ("swigluoai", "silu"):  # config.py:132-135
             raise ConfigError(f"config.json: hidden_act={act!r} is not supported (swigluoai or silu)")
+        if act == "silu" and ("swiglu_alpha" in text or "swiglu_limit" in text):
+            # the native key shape spells the clamped activation "silu" but keeps its constants; the
+            # reference runs swigluoai for it (config.py:128-145).  "silu" without them is plain SwiGLU.
+            act = "swigluoai"
         scoring = text.get("scoring_func", "sigmoid")
         if scoring not in ("sigmoid", "softmax"):
             raise ConfigError(f"config.json: scoring_func={scoring!r} is not supported (sigmoid or softmax)")
@@ -316,8 +321,6 @@ class MiniMaxM3Config:
             "use_gemma_norm": self.use_gemma_norm,
             "tie_word_embeddings": self.tie_word_embeddings,
             "hidden_act": self.hidden_act,
-            "swiglu_alpha": self.swiglu_alpha,
-            "swiglu_limit": self.swiglu_limit,
             "num_local_experts": self.num_local_experts,
             "num_experts_per_tok": self.num_experts_per_tok,
             "intermediate_size": self.intermediate_size,
@@ -328,6 +331,9 @@ class MiniMaxM3Config:
             "use_routing_bias": self.use_routing_bias,
             "scoring_func": self.scoring_func,
             "moe_layer_freq": [1 if t == FFN_MOE else 0 for t in self.ffn_types],
+            # (only beside the clamped activation: next to "silu" they would turn it into swigluoai)
+            **({"swiglu_alpha": self.swiglu_alpha, "swiglu_limit": self.swiglu_limit}
+               if self.hidden_act == "swigluoai" else {}),
             "torch_dtype": self.torch_dtype or "bfloat16",
         }
         if self.eos_token_ids:

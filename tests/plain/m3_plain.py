@@ -3,9 +3,12 @@
 Written from the reference's formulas (file:line cited in each function; paths are
 relative to the reference project).  The reference's own model code cannot run a
 forward pass on a CPU (its norm, rope, attention and expert kernels are Triton or
-library CUDA code), so this file rests on the formulas; the pieces of the reference
-that do run on a CPU (router, rope table) are compared once in
-``tests/golden/make_golden.py``.
+library CUDA code), so the whole model rests on the formulas; part by part it is
+compared with what of the reference does run on a CPU (its router and rope table,
+its tests' PyTorch oracles for paged attention, block-sparse attention and fused
+experts, and its Triton norm, rope and activation kernels under Triton's CPU
+interpreter) in ``tests/golden/make_golden.py``, whose recorded outputs
+``tests/test_plain.py`` checks again without the reference.
 
 It shares no code with ``freetoken_b200``: it parses config.json and reads the
 safetensors file (through the ``safetensors`` package) itself.
@@ -86,6 +89,9 @@ def read_config(folder: str) -> PlainConfig:
         sf = sp.get("sparse_attention_freq")
         sparse_layers = [bool(f) for f in sf[:layers]] if sf else [True] * layers
     inter = c["intermediate_size"]
+    act = c.get("hidden_act", "swigluoai")
+    if act == "silu" and ("swiglu_alpha" in c or "swiglu_limit" in c):
+        act = "swigluoai"  # the native key shape's spelling of the clamped form (config.py:128-145)
     return PlainConfig(
         vocab=c["vocab_size"],
         hidden=c["hidden_size"],
@@ -99,7 +105,7 @@ def read_config(folder: str) -> PlainConfig:
         qk_norm=bool(c.get("use_qk_norm", True)),
         gemma=bool(c.get("use_gemma_norm", True)),
         tied=bool(c.get("tie_word_embeddings", False)),
-        act=c.get("hidden_act", "swigluoai"),
+        act=act,
         alpha=float(c.get("swiglu_alpha", 1.702)),
         limit=float(c.get("swiglu_limit", 7.0)),
         experts=experts,
