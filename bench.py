@@ -14,7 +14,9 @@ of the whole batch.  It prints ONE JSON line:
 * ``prefill``: one 2048-token prompt in one step: tokens/s, ms, and flops / time / bf16 peak;
 * ``roofline``: bytes the decode step has to read (every weight it uses once, plus the cache of the
   live requests) / its time, against the measured HBM copy bandwidth;
-* ``points``: decode tokens/s at batch 1 and 64;
+* ``points``: decode tokens/s at batch 1 and 64, at longer contexts (batch 8 at 8k and 32k tokens, batch 64
+  at 8k), and the two larger workloads of freetoken_b200/workloads.py (``--no-long-points`` and
+  ``--no-workloads`` leave them out); ``points_hbm_frac``: bytes read / time / HBM peak of the decode points;
 * ``clocks``: SM clock and throttle reasons sampled during the timed region.
 
 ``--workload long_contexts | chunked_prefill`` runs one of the larger workloads of
@@ -51,6 +53,9 @@ HEADLINE = {
 }
 PROMPT = 2048
 CONTEXT = 4096
+# further decode points on the same engine: (batch, context) with their own roofline fractions
+LONG_POINTS = ((8, 8192), (8, 32768), (64, 8192))
+MAX_POSITION = 32768 + 256
 
 
 def peaks():
@@ -165,6 +170,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--no-long-points", action="store_true", help="skip the decode points at 8k and 32k tokens of context")
+    ap.add_argument("--no-workloads", action="store_true", help="skip the long_contexts and chunked_prefill workloads")
     ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
                     help="run only that phase and bracket `--steps` steps of it with cudaProfilerStart/Stop "
                          "(for ncu --profile-from-start off); prints no bench line")
@@ -204,12 +211,16 @@ def main():
     from freetoken_b200.sampling import Sampler, SamplingParams
 
     pk = peaks()
-    raw = dict(HEADLINE, num_hidden_layers=args.layers)
+    long_points = [] if (args.no_points or args.no_long_points) else list(LONG_POINTS)
+    raw = dict(HEADLINE, num_hidden_layers=args.layers,
+               max_position_embeddings=MAX_POSITION if long_points else HEADLINE["max_position_embeddings"])
     max_b = max(args.batch, 1 if args.no_points else 64)
+    pool_tokens = max([max_b * CONTEXT] + [b * (ctx + 256) for b, ctx in long_points])
+    max_seq = max([CONTEXT] + [ctx + 256 for _, ctx in long_points])
     t0 = time.time()
     engine = Engine(EngineConfig(model_path="", dtype="bfloat16", use_dummy_weight=True, seed=0, page_size=16,
-                                 max_running_req=max_b, num_token_override=max_b * CONTEXT,
-                                 max_seq_len_override=CONTEXT, max_extend_tokens=PROMPT, max_step_tokens=PROMPT),
+                                 max_running_req=max_b, num_token_override=pool_tokens,
+                                 max_seq_len_override=max_seq, max_extend_tokens=PROMPT, max_step_tokens=PROMPT),
                     raw_config=raw)
     torch.cuda.synchronize()
     build_s = time.time() - t0
@@ -273,12 +284,25 @@ def main():
                    "hbm_frac": round(pre_bytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
 
     # ------------------------------------------------------------------ decode
-    def fill(batch, tag):
-        """Give `batch` requests a real 2048-token prompt each; return their ids."""
-        rids = [(tag, i) for i in range(batch)]
+    def fill(batch, tag, context=PROMPT, rids=None):
+        """Give `batch` requests a real prompt of `context` tokens each (in portions of 2048 tokens, a
+        request's next portion at a time; requests in `rids` are grown to that length); return their ids."""
+        rids = rids or [(tag, i) for i in range(batch)]
         for r in rids:
-            engine.step([StepEntry(r, rng.integers(0, V, PROMPT).tolist(), [])])
+            have = engine.length(r) if engine.is_open(r) else 0
+            while have < context:
+                n = min(PROMPT, context - have)
+                engine.step([StepEntry(r, rng.integers(0, V, n).tolist(), [])])
+                have += n
         return rids
+
+    def step_bytes_of(rids):
+        """Bytes a decode step of these requests has to read: every weight it uses once (the experts it
+        touches counted on a real step) and the cache of the live requests."""
+        distinct = expert_bytes_read(engine, lambda: [StepEntry(r, [int(rng.integers(0, V))], [0]) for r in rids])
+        kv = sum(engine.length(r) for r in rids) * L * 2 * kvdim * 2
+        weights = L * 2 * (H * (qdim + 2 * kvdim) + qdim * H) + L * 4 * E * H + distinct * 2 * (2 * I * H + H * I) + 2 * H * V
+        return weights + kv, distinct
 
     def decode_tokens_per_s(rids, steps, warmup, sample=True):
         B = len(rids)
@@ -306,14 +330,7 @@ def main():
     with ClockSampler() as clocks:
         value, ms_step, launches = decode_tokens_per_s(rids, args.steps, args.warmup)
     # bytes the step had to read
-    distinct = expert_bytes_read(engine, lambda: [StepEntry(r, [int(rng.integers(0, V))], [0]) for r in rids])
-    kv_len = engine.length(rids[0])
-    w_attn = L * 2 * (H * (qdim + 2 * kvdim) + qdim * H)
-    w_router = L * 4 * E * H
-    w_experts = distinct * 2 * (2 * I * H + H * I)
-    w_head = 2 * H * V
-    kv_bytes = args.batch * kv_len * L * 2 * kvdim * 2
-    step_bytes = w_attn + w_router + w_experts + w_head + kv_bytes
+    step_bytes, distinct = step_bytes_of(rids)
     achieved = step_bytes / (ms_step / 1e3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                 "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes),
@@ -352,14 +369,32 @@ def main():
         sched.abort(r.rid)
 
     # ------------------------------------------------------------------ batch 1 and 64
-    points = {}
+    points, fracs = {}, {}
     if not args.no_points:
+        n_steps = max(8, args.steps // 2)
+
+        def point(name, rr):
+            v, ms, _ = decode_tokens_per_s(rr, n_steps, args.warmup)
+            nbytes, _ = step_bytes_of(rr)
+            points[name] = round(v, 1)
+            fracs[name] = round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+
         for B in (1, 64):
             rr = fill(B, f"b{B}")
-            v, _, _ = decode_tokens_per_s(rr, max(8, args.steps // 2), args.warmup)
-            points[f"decode_b{B}"] = round(v, 1)
+            point(f"decode_b{B}", rr)
             for r in rr:
                 engine.close(r)
+        rr, last_b = [], None
+        for B, ctx in long_points:  # (batch 8 grows from 8k to 32k tokens: the same requests go on)
+            if B != last_b:
+                for r in rr:
+                    engine.close(r)
+                rr = None
+            rr = fill(B, f"c{B}", context=ctx, rids=rr)
+            last_b = B
+            point(f"decode_b{B}_ctx{ctx // 1024}k", rr)
+        for r in rr or []:
+            engine.close(r)
 
     line = {
         "metric": "decode tok/s at batch 8, context 4096 (2048 prompt + decode), MiniMax-M3 layer sizes",
@@ -373,8 +408,29 @@ def main():
                    "prompt_len": PROMPT, "page_size": 16, "parallelism": "none (1 GPU)",
                    "l2": "inputs larger than L2 (a step reads >20 GB of weights)", "cuda_graph": engine.use_graphs},
         "e2e": e2e, "gpu_launches": int(launches), "prefill": prefill, "roofline": roofline, "points": points,
-        "clocks": clocks.summary(), "build_seconds": round(build_s, 1),
+        "points_hbm_frac": fracs, "clocks": clocks.summary(), "build_seconds": round(build_s, 1),
     }
+    if not (args.no_points or args.no_workloads):
+        # the two larger workloads need engines of their own (16 and 4 layers): this one goes first
+        import gc
+
+        from freetoken_b200 import workloads
+
+        del sched, sampler, engine
+        gc.collect()
+        torch.cuda.empty_cache()
+        with ClockSampler() as wl_clocks:
+            for name, keys in (("long_contexts", ("prefill_tokens_per_s", "decode_tokens_per_s")),
+                               ("chunked_prefill", ("tokens_per_s",))):
+                try:
+                    res = getattr(workloads, name)(HEADLINE)
+                    for key in keys:
+                        points[f"{name}_{key}"] = res[key]
+                except Exception as e:  # a workload that does not fit must not cost the headline its line
+                    points[f"{name}_error"] = f"{type(e).__name__}: {e}"[:200]
+                gc.collect()
+                torch.cuda.empty_cache()
+        line["workload_clocks"] = wl_clocks.summary()
     print(json.dumps(line))
     return 0
 

@@ -84,7 +84,15 @@ int ftk_router_topk(const float* logits, const float* bias, int n_tokens, int n_
 int ftk_moe_route_fits(int n_tokens, int hidden, int n_experts, int top_k);
 int ftk_moe_route(const float* x, const float* gate_w, const float* bias, int n_tokens, int hidden, int n_experts,
                   int top_k, int scoring, float scale, float* logits, int32_t* ids, float* weights,
-                  int32_t* counts, int32_t* offsets, int32_t* routes, int32_t* pos, void* stream);
+                  int32_t* counts, int32_t* offsets, int32_t* routes, int32_t* pos, int do_sort, void* stream);
+// Products of very few tokens (bfloat16): the weights are streamed once by warps of every SM (gemv.cu).
+int ftk_small_linear_fits(int n_tokens, int n_out, int k);
+int ftk_small_linear(const void* x, const void* w, void* out, int n_tokens, int n_out, int k, void* stream);
+int ftk_moe_small_fits(int n_tokens, int hidden, int inter, int top_k);
+int ftk_moe_small_gate_up(const void* h, const int32_t* ids, const void* w1, void* a, int n_tokens, int top_k,
+                          int n_experts, int hidden, int inter, int act, float alpha, float limit, void* stream);
+int ftk_moe_small_down(const void* a, const int32_t* ids, const float* weights, const void* w2, void* y, int n_tokens,
+                       int top_k, int n_experts, int hidden, int inter, void* stream);
 int ftk_moe_permute(const int32_t* topk_ids, int n_tokens, int top_k, int n_experts,
                     int32_t* expert_counts, int32_t* expert_offsets, int32_t* sorted_routes,
                     int32_t* route_pos, void* stream);
@@ -100,6 +108,8 @@ int ftk_moe_combine(const void* y, int dtype, const int32_t* route_pos, int n_to
                     int hidden, const void* shared, void* out, void* stream);
 // Status words of the kernels' bounded waits: out[0] = first code since the last call (0 = none),
 // out[1] = block that recorded it.  Synchronises with the device and clears the words.
+// Kernel forms launched so far, as "name<TAB>count" lines (see ftk::note_variant); returns the bytes needed.
+int ftk_variant_counts(char* buf, int cap, int reset);
 int ftk_read_status(int* out);
 // Writes `code` into a status word from the host (unit 0: grouped GEMM, 1: attention), so that a caller's
 // handling of a given-up wait can be tested without any wait running out on the device.

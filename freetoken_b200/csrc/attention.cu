@@ -933,6 +933,7 @@ static int paged_attention_tc_impl(const void* q, const void* k_slab, const void
   p.num_pages = num_pages; p.tile_rows = pair ? 2 * kTcRows : kTcRows; p.scale = scale; p.window = window;
   p.sel = nullptr; p.sel_stride = 0; p.block_size = 0; p.arrivals = nullptr;
   cudaStream_t s = (cudaStream_t)stream;
+  note_variant(pair ? "attention: tcgen05, two 128-row query tiles per CTA" : "attention: tcgen05, 128-row query tiles");
   const int rc = pair ? launch_attention_tc2(p, n_tokens, s) : launch_attention_tc(p, n_tokens, s);
   FTK_REQUIRE(rc == 0, "paged_attention_tc: cannot set up the kernel (%d)", rc);
   FTK_LAUNCH_CHECK("paged_attention_tc");
@@ -1005,6 +1006,7 @@ static int paged_attention_impl(const void* q, const void* k_slab, const void* v
                 kF32Rows, tile_rows);
     FTK_REQUIRE(p.G <= kF32Rows, "paged_attention: %d query heads per KV head exceed the %d-row tile", p.G, kF32Rows);
     const size_t smem = ((size_t)kF32Rows * head_dim + (size_t)kF32Chunk * (2 * head_dim + 1)) * sizeof(float);
+    note_variant(sel ? "attention: float32, block-sparse" : "attention: float32, warp per row");
     auto kern = attention_f32_kernel<float>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     FTK_LAUNCH(kern, grid, kF32Rows * 32, smem, s, p);
@@ -1021,15 +1023,26 @@ static int paged_attention_impl(const void* q, const void* k_slab, const void* v
     bool merged = false;
     if (tile_rows == kDecRows) {
       if (n_slots > 0 && (long long)n_slots * p.Hkv <= kAttnArrivalSlots && p.D % 4 == 0) {
-        static unsigned int* arrivals = nullptr;
-        if (!arrivals) cudaGetSymbolAddress((void**)&arrivals, g_attn_arrivals);
-        p.arrivals = arrivals;
+        // the counters live in this device's copy of the array: look the address up once per device
+        static unsigned int* arrivals[64] = {};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        FTK_REQUIRE(dev >= 0 && dev < 64, "paged_attention: device index %d out of range", dev);
+        if (!arrivals[dev]) {
+          FTK_REQUIRE(cudaGetSymbolAddress((void**)&arrivals[dev], g_attn_arrivals) == cudaSuccess,
+                      "paged_attention: cannot find the arrival counters on device %d", dev);
+        }
+        p.arrivals = arrivals[dev];
         merged = true;
       }
+      note_variant(sel ? "attention: bfloat16 mma.sync, 16-row tiles, block-sparse"
+                       : merged ? "attention: bfloat16 mma.sync, 16-row tiles, last split merges"
+                                : "attention: bfloat16 mma.sync, 16-row tiles");
       if (head_dim <= 64) launch_decode_bf16<64>(p, s);
       else if (head_dim <= 128) launch_decode_bf16<128>(p, s);
       else launch_decode_bf16<256>(p, s);
     } else {
+      note_variant("attention: bfloat16 mma.sync, 64-row tiles");
       if (head_dim <= 64) launch_bf16<64>(p, s);
       else if (head_dim <= 128) launch_bf16<128>(p, s);
       else launch_bf16<256>(p, s);
@@ -1105,12 +1118,21 @@ extern "C" int ftk_paged_attention_static_scratch(const void* q, const void* k_s
                                                   void* stream) {
   FTK_REQUIRE(n_items >= 0, "paged_attention_static_scratch: bad item count");
   FTK_REQUIRE(n_items == 0 || items_host_copy, "paged_attention_static_scratch: the host copy of the work list is needed to size the scratch");
-  FTK_REQUIRE(n_kv_heads >= 1 && tile_rows >= 1 && head_dim >= 1, "paged_attention_static_scratch: bad sizes");
+  // bounded before anything is multiplied, so that the size below cannot wrap
+  FTK_REQUIRE(n_kv_heads >= 1 && n_kv_heads <= 65535 && tile_rows >= 1 && tile_rows <= 256 && head_dim >= 1 &&
+                  head_dim <= 256,
+              "paged_attention_static_scratch: %d KV heads, tiles of %d rows, heads of %d: at most 65535, 256 and 256",
+              n_kv_heads, tile_rows, head_dim);
   // slots the work list uses: a split tile owns slots [base, base + n_splits)
+  const long long max_slots = FTK_STATIC_SCRATCH_BYTES / 8;  // a slot holds 8 bytes at the very least
   long long n_slots = 0;
   for (int i = 0; i < n_items; ++i) {
     const int32_t* w = items_host_copy + (size_t)i * 8;
-    if (w[5] > 1 && (long long)w[7] + w[5] > n_slots) n_slots = (long long)w[7] + w[5];
+    if (w[5] <= 1) continue;
+    FTK_REQUIRE(w[5] <= 64 && w[7] >= 0 && (long long)w[7] + w[5] <= max_slots,
+                "paged_attention_static_scratch: work item %d is split %d ways from slot %d: at most 64 splits, slots in "
+                "[0, %lld)", i, w[5], w[7], max_slots);
+    if ((long long)w[7] + w[5] > n_slots) n_slots = (long long)w[7] + w[5];
   }
   const long long rows = n_slots * n_kv_heads * tile_rows;
   const long long need = rows * (head_dim + 2) * (long long)sizeof(float);

@@ -15,6 +15,9 @@
 namespace ftk {
 
 void set_error(const char* fmt, ...);
+// Counts a launch under the name of the kernel form it took (`name` must be a string literal);
+// ftk_variant_counts() reports the counts.
+void note_variant(const char* name);
 
 #define FTK_REQUIRE(cond, ...)        \
   do {                                \

@@ -146,6 +146,7 @@ extern "C" int ftk_moe_gemm1_act(const void* x_sorted, const void* w1, int dtype
   const int tiles = (n_routes + kBM - 1) / kBM + n_experts;
   FTK_REQUIRE(tiles <= 65535, "moe_gemm1_act: too many row tiles (%d)", tiles);
   dim3 grid((inter + kBN - 1) / kBN, tiles);
+  note_variant(dtype == FTK_F32 ? "expert gate/up product: float32 on CUDA cores" : "expert gate/up product: bfloat16 on CUDA cores");
   if (dtype == FTK_F32)
     FTK_LAUNCH((moe_gemm_kernel<float, true>), grid, 256, 0, s, (const float*)x_sorted, (const float*)w1, expert_offsets, n_experts,
                                                       hidden, inter, 2 * inter, nullptr, nullptr, n_routes, act, alpha,
@@ -174,6 +175,7 @@ extern "C" int ftk_moe_gemm2(const void* a, const void* w2, int dtype, const int
   const int tiles = (n_routes + kBM - 1) / kBM + n_experts;
   FTK_REQUIRE(tiles <= 65535, "moe_gemm2: too many row tiles (%d)", tiles);
   dim3 grid((hidden + kBN - 1) / kBN, tiles);
+  note_variant(dtype == FTK_F32 ? "expert down product: float32 on CUDA cores" : "expert down product: bfloat16 on CUDA cores");
   if (dtype == FTK_F32)
     FTK_LAUNCH((moe_gemm_kernel<float, false>), grid, 256, 0, s, (const float*)a, (const float*)w2, expert_offsets, n_experts, inter,
                                                        hidden, hidden, sorted_routes, topk_weights, n_routes, 0, 0.f, 0.f,

@@ -436,6 +436,22 @@ static int launch_tc_impl(const CUtensorMap& ma, const CUtensorMap& mb, const Tc
     if (ctas_per_sm > 2) ctas_per_sm = 2;
     if (DEEP) ctas_per_sm = 1;
   }
+  {
+    static const char* const names[2][2][5] = {
+        {{"expert down product: tcgen05, 16 tokens a tile", "expert down product: tcgen05, 32 tokens a tile",
+          "expert down product: tcgen05, 64 tokens a tile", "expert down product: tcgen05, 128 tokens a tile",
+          "expert down product: tcgen05, 256 tokens a tile"},
+         {"expert down product: tcgen05, 16 tokens a tile, deep pipeline", "expert down product: tcgen05, 32 tokens a tile, deep pipeline",
+          "expert down product: tcgen05, 64 tokens a tile, deep pipeline", "expert down product: tcgen05, 128 tokens a tile, deep pipeline",
+          "expert down product: tcgen05, 256 tokens a tile, deep pipeline"}},
+        {{"expert gate/up product: tcgen05, 16 tokens a tile", "expert gate/up product: tcgen05, 32 tokens a tile",
+          "expert gate/up product: tcgen05, 64 tokens a tile", "expert gate/up product: tcgen05, 128 tokens a tile",
+          "expert gate/up product: tcgen05, 256 tokens a tile"},
+         {"expert gate/up product: tcgen05, 16 tokens a tile, deep pipeline", "expert gate/up product: tcgen05, 32 tokens a tile, deep pipeline",
+          "expert gate/up product: tcgen05, 64 tokens a tile, deep pipeline", "expert gate/up product: tcgen05, 128 tokens a tile, deep pipeline",
+          "expert gate/up product: tcgen05, 256 tokens a tile, deep pipeline"}}};
+    note_variant(names[GATED ? 1 : 0][DEEP ? 1 : 0][BN == 16 ? 0 : BN == 32 ? 1 : BN == 64 ? 2 : BN == 128 ? 3 : 4]);
+  }
   int grid = sms * ctas_per_sm;
   if (grid > max_tiles) grid = max_tiles;
   if (grid < 1) grid = 1;

@@ -255,8 +255,16 @@ extern "C" int ftk_moe_permute(const int32_t* topk_ids, int n_tokens, int top_k,
   const int n_segs = (n_routes + kSegRoutes - 1) / kSegRoutes;
   const size_t seg_smem = (size_t)kSegWarps * n_experts * sizeof(int);
   if (n_routes > 2048 && (long long)n_segs * n_experts <= kSegScratchInts && seg_smem <= 48 * 1024) {
-    static int* seg_counts = nullptr;
-    if (!seg_counts) cudaGetSymbolAddress((void**)&seg_counts, g_seg_counts);
+    static int* seg_counts_of[64] = {};  // the scratch lives in each device's copy of the array
+    int dev = 0;
+    cudaGetDevice(&dev);
+    FTK_REQUIRE(dev >= 0 && dev < 64, "moe_permute: device index %d out of range", dev);
+    if (!seg_counts_of[dev]) {
+      FTK_REQUIRE(cudaGetSymbolAddress((void**)&seg_counts_of[dev], g_seg_counts) == cudaSuccess,
+                  "moe_permute: cannot find the segment counters on device %d", dev);
+    }
+    int* seg_counts = seg_counts_of[dev];
+    note_variant("route sort: three passes over 128-route segments");
     const int blocks = (n_segs + kSegWarps - 1) / kSegWarps;
     FTK_LAUNCH(moe_seg_count_kernel, blocks, kSegWarps * 32, seg_smem, s, topk_ids, n_routes, n_experts, seg_counts);
     FTK_LAUNCH_CHECK("moe_permute (segment counts)");
@@ -267,6 +275,7 @@ extern "C" int ftk_moe_permute(const int32_t* topk_ids, int n_tokens, int top_k,
     FTK_LAUNCH_CHECK("moe_permute (segment place)");
     return 0;
   }
+  note_variant("route sort: one block per expert");
   FTK_LAUNCH(moe_count_kernel, n_experts, kPermThreads, 0, s, topk_ids, n_routes, expert_counts);
   FTK_LAUNCH_CHECK("moe_permute (count)");
   FTK_LAUNCH(moe_place_kernel, n_experts, kPermThreads, 0, s, topk_ids, n_routes, n_experts, expert_counts, expert_offsets,

@@ -199,8 +199,7 @@ moe_route_kernel(const float* __restrict__ x, const float* __restrict__ w, const
                  int n_tokens, int hidden, int n_experts, int top_k, int scoring, float scale,
                  float* __restrict__ logits, int32_t* __restrict__ ids, float* __restrict__ weights,
                  int32_t* __restrict__ counts, int32_t* __restrict__ offsets, int32_t* __restrict__ routes,
-                 int32_t* __restrict__ pos) {
-  pdl_wait();
+                 int32_t* __restrict__ pos, int do_sort) {
   extern __shared__ float sm[];
   __shared__ float part[kRouteExperts][kRouteTokens][kRouteWarps + 1];
   __shared__ bool last;
@@ -209,6 +208,13 @@ moe_route_kernel(const float* __restrict__ x, const float* __restrict__ w, const
   const int h4 = hidden >> 2;
   const float4* w4 = reinterpret_cast<const float4*>(w);
   const float4* x4 = reinterpret_cast<const float4*>(x);
+  // the router's weights never depend on the kernel before: a thread's first pieces of them are on
+  // their way before the wait
+  float4 w_first[kRouteExperts];
+#pragma unroll
+  for (int j = 0; j < kRouteExperts; ++j)
+    w_first[j] = tid < h4 ? __ldg(w4 + (size_t)min(e0 + j, n_experts - 1) * h4 + tid) : make_float4(0.f, 0.f, 0.f, 0.f);
+  pdl_wait();
   // every block fetches the bias now, under the matrix product, so that the one that turns out to
   // be last does not wait for it
   float* sbias = sm + (size_t)kRouteWarps * 2 * n_experts;
@@ -225,9 +231,11 @@ moe_route_kernel(const float* __restrict__ x, const float* __restrict__ w, const
     for (int i = tid; i < h4; i += kRouteWarps * 32) {
       float4 wv[kRouteExperts], xv[kRouteTokens];
 #pragma unroll
-      for (int j = 0; j < kRouteExperts; ++j) wv[j] = __ldg(w4 + (size_t)min(e0 + j, n_experts - 1) * h4 + i);
+      for (int j = 0; j < kRouteExperts; ++j)
+        wv[j] = i == tid ? w_first[j] : __ldg(w4 + (size_t)min(e0 + j, n_experts - 1) * h4 + i);
 #pragma unroll
-      for (int u = 0; u < kRouteTokens; ++u) xv[u] = __ldg(x4 + (size_t)min(t0 + u, n_tokens - 1) * h4 + i);
+      for (int u = 0; u < kRouteTokens; ++u)  // (rows past the step's tokens are never stored: no load for them)
+        xv[u] = u < nt ? __ldg(x4 + (size_t)(t0 + u) * h4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
       for (int j = 0; j < kRouteExperts; ++j)
 #pragma unroll
@@ -271,7 +279,11 @@ moe_route_kernel(const float* __restrict__ x, const float* __restrict__ w, const
   float* s = sm + (size_t)warp * 2 * n_experts;
   for (int t = warp; t < n_tokens; t += kRouteWarps)
     route_one(logits + (size_t)t * n_experts, bias ? sbias : nullptr, n_experts, top_k, scoring, scale, s,
-              ids + (size_t)t * top_k, weights + (size_t)t * top_k, sid + (size_t)t * top_k);
+              ids + (size_t)t * top_k, weights + (size_t)t * top_k, do_sort ? sid + (size_t)t * top_k : nullptr);
+  if (!do_sort) {  // the caller's kernels take the routes in token order
+    if (tid == 0) g_route_arrivals = 0;
+    return;
+  }
   for (int i = tid; i < n_experts; i += blockDim.x) cnt[i] = 0;
   __syncthreads();
   // ---- counting sort of the routes by expert; rows of one expert keep the order of the routes
@@ -329,6 +341,7 @@ extern "C" int ftk_router_topk(const float* logits, const float* bias, int n_tok
   FTK_REQUIRE(smem <= 200 * 1024, "router_topk: %d experts exceed what one block can hold (6400)", n_experts);
   if (smem > 48 * 1024) cudaFuncSetAttribute(router_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   const int blocks = (n_tokens + kRouterWarps - 1) / kRouterWarps;
+  note_variant("routing: expert choice from given logits");
   FTK_LAUNCH(router_topk_kernel, blocks, kRouterWarps * 32, smem, (cudaStream_t)stream, logits, bias, n_tokens, n_experts, top_k,
                                                                                scoring, scale, ids, weights);
   FTK_LAUNCH_CHECK("router_topk");
@@ -347,19 +360,22 @@ extern "C" int ftk_moe_route_fits(int n_tokens, int hidden, int n_experts, int t
 extern "C" int ftk_moe_route(const float* x, const float* gate_w, const float* bias, int n_tokens, int hidden,
                              int n_experts, int top_k, int scoring, float scale, float* logits, int32_t* ids,
                              float* weights, int32_t* counts, int32_t* offsets, int32_t* routes, int32_t* pos,
-                             void* stream) {
+                             int do_sort, void* stream) {
   FTK_REQUIRE(scoring == FTK_SCORE_SIGMOID || scoring == FTK_SCORE_SOFTMAX, "moe_route: unknown scoring %d", scoring);
   FTK_REQUIRE(ftk_moe_route_fits(n_tokens, hidden, n_experts, top_k),
               "moe_route: %d tokens, width %d, %d experts, top %d do not fit the one-launch routing (at most 32 tokens, "
               "a width that is a multiple of 4); use the matrix product + router_topk + moe_permute",
               n_tokens, hidden, n_experts, top_k);
-  FTK_REQUIRE(x && gate_w && logits && ids && weights && counts && offsets && routes && pos, "moe_route: null pointer");
+  FTK_REQUIRE(x && gate_w && logits && ids && weights, "moe_route: null pointer");
+  FTK_REQUIRE(!do_sort || (counts && offsets && routes && pos), "moe_route: the sort needs its four outputs");
   FTK_REQUIRE(((uintptr_t)x | (uintptr_t)gate_w) % 16 == 0, "moe_route: x and the gate weight must be 16-byte aligned");
   const size_t smem = route_smem(n_tokens, n_experts, top_k);
   if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   const int blocks = (n_experts + kRouteExperts - 1) / kRouteExperts;
+  note_variant(do_sort ? "routing: product, choice and sort in one launch" : "routing: product and choice in one launch");
   FTK_LAUNCH(moe_route_kernel, blocks, kRouteWarps * 32, smem, (cudaStream_t)stream, 
-      x, gate_w, bias, n_tokens, hidden, n_experts, top_k, scoring, scale, logits, ids, weights, counts, offsets, routes, pos);
+      x, gate_w, bias, n_tokens, hidden, n_experts, top_k, scoring, scale, logits, ids, weights, counts, offsets, routes, pos,
+      do_sort);
   FTK_LAUNCH_CHECK("moe_route");
   return 0;
 }

@@ -4,6 +4,8 @@
     python -m freetoken_b200.kernels.microbench attention --batch 8 --context 2048
     python -m freetoken_b200.kernels.microbench attention --prefill 2048
     python -m freetoken_b200.kernels.microbench sample --rows 8 --vocab 200064
+    python -m freetoken_b200.kernels.microbench sparse --batch 8 --context 32768
+    python -m freetoken_b200.kernels.microbench sparse --prefill 2048 --context 32768
 
 Each case allocates its inputs once (larger than L2 where the real workload is), warms up, then
 times ``--iters`` launches with CUDA events and prints one JSON line: time, the bytes the kernel has
@@ -16,6 +18,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 
 import torch
@@ -23,8 +26,17 @@ import torch
 from ..engine.attention_plan import build_plan, wave_splits
 from . import ops
 
-HBM_GBS = 6650.0
+HBM_GBS = 6650.0  # used when no measured peaks are on file
 BF16_TFLOPS = 1590.0
+_PEAKS = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "MEASURED_PEAKS.json")
+if os.path.isfile(_PEAKS):  # the copy rate and library product rate measured on this machine's GPUs
+    try:
+        with open(_PEAKS) as _f:
+            _m = json.load(_f)
+        HBM_GBS = float(_m.get("hbm_gbs", HBM_GBS))
+        BF16_TFLOPS = float(_m.get("bf16_tflops", BF16_TFLOPS))
+    except (OSError, ValueError):
+        pass
 
 
 def _time(fn, iters: int, warmup: int, profile: bool) -> float:
@@ -137,6 +149,59 @@ def bench_attention(a) -> dict:
             "tensor_frac": round(flops / us / 1e6 / BF16_TFLOPS, 3)}
 
 
+def bench_sparse(a) -> dict:
+    """The block-sparse layer kind at its real geometry (the reference's M3: blocks of 128 keys, 16 chosen
+    blocks, 64 query heads on 4 KV heads of 128, one shared index key of 128 per token): block selection
+    (index scores, forced blocks, top-k) and attention over the chosen blocks, for single tokens of
+    ``--batch`` requests at ``--context`` tokens, or for a ``--prefill`` portion at the end of one request of
+    ``--context`` tokens.  Bytes: the visible index keys once per request and step; the chosen keys and values
+    per token and KV head."""
+    dev = "cuda"
+    Hq, Hkv, D, P, Di = a.q_heads, a.kv_heads, a.head_dim, a.page_size, a.head_dim
+    block, topk = a.block, a.topk
+    segs = [(a.prefill, a.context)] if a.prefill else [(1, a.context)] * a.batch
+    n_pages = sum(-(-kv // P) for _, kv in segs) + 1
+    g = torch.Generator(device=dev).manual_seed(0)
+    ks = torch.empty(n_pages, Hkv, P, D, dtype=torch.bfloat16, device=dev).normal_(0, 1, generator=g)
+    vs = torch.empty(n_pages, Hkv, P, D, dtype=torch.bfloat16, device=dev).normal_(0, 1, generator=g)
+    iks = torch.empty(n_pages, 1, P, Di, dtype=torch.bfloat16, device=dev).normal_(0, 1, generator=g)
+    width = max(-(-kv // P) for _, kv in segs)
+    bt = torch.zeros(len(segs), width, dtype=torch.int32)
+    info, q0, page = [], 0, 1
+    for row, (ql, kv) in enumerate(segs):
+        n = -(-kv // P)
+        bt[row, :n] = torch.arange(page, page + n)
+        page += n
+        info.append([q0, ql, kv, row])
+        q0 += ql
+    bt, T = bt.to(dev), q0
+    seg = torch.tensor(info, dtype=torch.int32, device=dev)
+    q = torch.randn(T, Hq, D, device=dev, generator=g).to(torch.bfloat16)
+    iq = torch.randn(T, Hkv, Di, device=dev, generator=g).to(torch.bfloat16)
+    sel = torch.empty(T, Hkv, topk, dtype=torch.int32, device=dev)
+    max_blocks = -(-a.context // block)
+    out = {}
+    us = _time(lambda: ops.sparse_select(iq, iks, bt, seg, len(segs), block, a.local, a.init, max_blocks, sel),
+               a.iters, a.warmup, a.profile)
+    index_bytes = sum(kv for _, kv in segs) * Di * 2
+    flops = sum(2 * (ql * kv - ql * (ql - 1) // 2) * Hkv * Di for ql, kv in segs)
+    out["select"] = {"us": round(us, 2), "index_key_bytes": index_bytes, "gbs": round(index_bytes / us / 1e3, 1),
+                     "hbm_frac": round(index_bytes / us / 1e3 / HBM_GBS, 3), "tflops": round(flops / us / 1e6, 2)}
+    plan = build_plan(segs, Hq // Hkv, 16, None, Hkv, sparse=(block, topk))
+    items = torch.from_numpy(plan.items).to(dev)
+    po = pm = None
+    if plan.n_slots:
+        po = torch.empty(plan.n_slots, Hkv, 16, D, dtype=torch.float32, device=dev)
+        pm = torch.empty(plan.n_slots, Hkv, 16, 2, dtype=torch.float32, device=dev)
+    o = torch.empty_like(q)
+    us = _time(lambda: ops.paged_attention(q, ks, vs, bt, seg, len(segs), items, plan.n_items, po, pm, o, 16, D ** -0.5,
+                                           None, sel=sel, block_size=block), a.iters, a.warmup, a.profile)
+    kv_bytes = sum(min(topk * block, kv - ql + t + 1) for ql, kv in segs for t in range(ql)) * Hkv * D * 2 * 2
+    out["attend"] = {"us": round(us, 2), "items": plan.n_items, "kv_bytes": kv_bytes, "gbs": round(kv_bytes / us / 1e3, 1),
+                     "hbm_frac": round(kv_bytes / us / 1e3 / HBM_GBS, 3)}
+    return out
+
+
 def bench_sample(a) -> dict:
     dev = "cuda"
     logits = torch.randn(a.rows, a.vocab, device=dev)
@@ -153,7 +218,7 @@ def bench_sample(a) -> dict:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="microbench")
     sub = ap.add_subparsers(dest="case", required=True)
-    for name in ("moe", "attention", "sample"):
+    for name in ("moe", "attention", "sample", "sparse"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=5)
@@ -177,12 +242,24 @@ def main(argv=None) -> int:
             p.add_argument("--no-tc", action="store_true", help="prefill on the mma.sync kernel instead of tcgen05")
             p.add_argument("--tc", action="store_true", help="decode on the tcgen05 kernel")
             p.add_argument("--pair", action="store_true", help="prefill on the tcgen05 kernel with two query tiles per CTA")
+        elif name == "sparse":
+            p.add_argument("--batch", type=int, default=8)
+            p.add_argument("--context", type=int, default=32768)
+            p.add_argument("--prefill", type=int, default=0)
+            p.add_argument("--q-heads", type=int, default=64)
+            p.add_argument("--kv-heads", type=int, default=4)
+            p.add_argument("--head-dim", type=int, default=128)
+            p.add_argument("--page-size", type=int, default=16)
+            p.add_argument("--block", type=int, default=128)
+            p.add_argument("--topk", type=int, default=16)
+            p.add_argument("--local", type=int, default=1)
+            p.add_argument("--init", type=int, default=0)
         else:
             p.add_argument("--rows", type=int, default=8)
             p.add_argument("--vocab", type=int, default=200064)
             p.add_argument("--temperature", type=float, default=0.0)
     a = ap.parse_args(argv)
-    res = {"moe": bench_moe, "attention": bench_attention, "sample": bench_sample}[a.case](a)
+    res = {"moe": bench_moe, "attention": bench_attention, "sample": bench_sample, "sparse": bench_sparse}[a.case](a)
     print(json.dumps({"case": a.case, **{k: v for k, v in vars(a).items() if k != "case"}, "result": res}))
     return 0
 

@@ -79,7 +79,12 @@ _SIGNATURES = {
     "ftk_router_topk": [_vp, _vp, _i, _i, _i, _i, _f, _vp, _vp, _vp],
     "ftk_moe_permute": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp],
     "ftk_moe_route_fits": [_i, _i, _i, _i],
-    "ftk_moe_route": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    "ftk_moe_route": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp],
+    "ftk_small_linear_fits": [_i, _i, _i],
+    "ftk_small_linear": [_vp, _vp, _vp, _i, _i, _i, _vp],
+    "ftk_moe_small_fits": [_i, _i, _i, _i],
+    "ftk_moe_small_gate_up": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp],
+    "ftk_moe_small_down": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ftk_moe_gather": [_vp, _i, _vp, _i, _i, _i, _vp, _vp],
     "ftk_moe_gemm1_act": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _f, _f, _vp, _vp],
     "ftk_moe_gemm2": [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
@@ -92,6 +97,7 @@ _SIGNATURES = {
     "ftk_read_status": [ctypes.POINTER(ctypes.c_int)],
     "ftk_set_moe_tensor_cores": [_i],
     "ftk_debug_set_status": [_i, _i],
+    "ftk_variant_counts": [ctypes.c_char_p, _i, _i],
 }
 _bound = False
 _launches = 0
@@ -166,6 +172,22 @@ def check_status() -> None:
     code = read_status()
     if code:
         raise KernelError(f"a kernel gave up waiting (status {code}); its results are not valid")
+
+
+def variant_counts(reset: bool = False) -> dict:
+    """Launches so far by the form of kernel they took (``"attention: tcgen05, 128-row query tiles"``,
+    ``"expert gate/up product: tcgen05, 64 tokens a tile, deep pipeline"``, ``"route sort: three passes over
+    128-route segments"`` ...): what a step really ran, for tests and measurements.  Launches replayed from
+    a CUDA graph were counted when the graph was recorded."""
+    lib = _lib()
+    need = lib.ftk_variant_counts(None, 0, 0)
+    buf = ctypes.create_string_buffer(need + 256)
+    lib.ftk_variant_counts(buf, len(buf), 1 if reset else 0)
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, _, n = line.rpartition("\t")
+        out[name] = int(n)
+    return out
 
 
 def debug_set_status(unit: int, code: int) -> None:
@@ -468,9 +490,33 @@ def moe_permute(topk_ids: torch.Tensor, n_experts: int, expert_counts: torch.Ten
 LINEAR_PAD_ROWS = 16
 
 
+# Steps of this many tokens stream the weights with this library's own kernel (0 switches it off).  The
+# kernel takes up to four rows, but measured on B200 (3072 x 8192 and 6144 x 3072, inside a decode step) it
+# wins against the library's 16-row product only for one: 10.2 / 9.3 against 11.2 / 11.1 microseconds; at
+# two rows 12.9 / 14.5, at four 17 / 19.6 (the lanes run out of issue slots, not of bandwidth).
+SMALL_LINEAR_MAX_TOKENS = 1
+
+
+def small_linear_fits(n_tokens: int, n_out: int, k: int) -> bool:
+    return bool(_lib().ftk_small_linear_fits(n_tokens, n_out, k))
+
+
+def small_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """``out = x @ w^T`` in bfloat16 for one to four rows of ``x``: every SM streams its share of the
+    weight rows once, 32-bit sums (``csrc/gemv.cu``)."""
+    T, K = x.shape
+    N = w.shape[0]
+    if w.shape != (N, K) or out.shape != (T, N) or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 \
+            or out.dtype != torch.bfloat16:
+        raise KernelError("small_linear: bfloat16 x [T, K], w [N, K], out [T, N] expected")
+    _check(_lib().ftk_small_linear(_dev(x, "x"), _dev(w, "w"), _dev(out, "out"), T, N, K, _stream()), "small_linear")
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """``out = x @ w^T`` (``x [T, K]``, ``w [N, K]``, ``out [T, N]``) by the library, as in the reference
-    (python/freetoken/layers/linear.py:66-70).
+    """``out = x @ w^T`` (``x [T, K]``, ``w [N, K]``, ``out [T, N]``): by the library, as in the reference
+    (python/freetoken/layers/linear.py:66-70), except for bfloat16 steps of up to four tokens, whose
+    product is a stream over the weights that :func:`small_linear` does faster than the library's choice
+    of tile (measured on B200, 3072 x 8192 for one token: see the design notes).
 
     For fewer than 16 rows of bfloat16 and a weight that is at least as long as it is tall, the
     product is taken over 16 rows of the same buffers (the rows past ``T`` hold whatever the
@@ -480,6 +526,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     N = w.shape[0]
     if w.shape != (N, K) or out.shape != (T, N):
         raise KernelError("linear: shapes do not agree")
+    if (T <= SMALL_LINEAR_MAX_TOKENS and x.dtype == torch.bfloat16 and x.is_cuda and x.is_contiguous()
+            and w.is_contiguous() and out.is_contiguous() and small_linear_fits(T, N, K)):
+        small_linear(x, w, out)
+        return
     P = LINEAR_PAD_ROWS
     if (T < P and K >= N and x.dtype == torch.bfloat16 and x.is_cuda and x.is_contiguous() and out.is_contiguous()
             and _room(x) >= P * K and _room(out) >= P * N):
@@ -500,15 +550,20 @@ def moe_route_fits(n_tokens: int, hidden: int, n_experts: int, top_k: int) -> bo
 
 def moe_route(x: torch.Tensor, gate_w: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, scoring: str,
               scale: float, logits: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-              expert_counts: torch.Tensor, expert_offsets: torch.Tensor, sorted_routes: torch.Tensor,
-              route_pos: torch.Tensor) -> None:
-    """``logits = x @ gate_w^T`` in float32, then :func:`router_topk` and :func:`moe_permute`, in one launch."""
+              expert_counts: Optional[torch.Tensor] = None, expert_offsets: Optional[torch.Tensor] = None,
+              sorted_routes: Optional[torch.Tensor] = None, route_pos: Optional[torch.Tensor] = None) -> None:
+    """``logits = x @ gate_w^T`` in float32, then :func:`router_topk` and :func:`moe_permute`, in one launch.
+    Without the four outputs of the sort only ids and weights are made (the few-token expert kernels take
+    the routes in token order)."""
     T, H = x.shape
     E = gate_w.shape[0]
     if gate_w.shape != (E, H) or logits.shape != (T, E) or ids.shape != (T, top_k) or weights.shape != (T, top_k):
         raise KernelError("moe_route: shapes do not agree")
-    if expert_offsets.shape != (E + 1,) or expert_counts.shape != (E,) or sorted_routes.numel() != T * top_k \
-            or route_pos.numel() != T * top_k:
+    sort = expert_counts is not None
+    if sort and (expert_offsets is None or sorted_routes is None or route_pos is None):
+        raise KernelError("moe_route: give all four outputs of the sort, or none")
+    if sort and (expert_offsets.shape != (E + 1,) or expert_counts.shape != (E,) or sorted_routes.numel() != T * top_k
+                 or route_pos.numel() != T * top_k):
         raise KernelError("moe_route: output shapes are wrong")
     if bias is not None and bias.shape != (E,):
         raise KernelError("moe_route: bias must be [E]")
@@ -519,7 +574,40 @@ def moe_route(x: torch.Tensor, gate_w: torch.Tensor, bias: Optional[torch.Tensor
                                 _dev(expert_counts, "expert_counts", torch.int32),
                                 _dev(expert_offsets, "expert_offsets", torch.int32),
                                 _dev(sorted_routes, "sorted_routes", torch.int32),
-                                _dev(route_pos, "route_pos", torch.int32), _stream()), "moe_route")
+                                _dev(route_pos, "route_pos", torch.int32), 1 if sort else 0, _stream()), "moe_route")
+
+
+def moe_small_fits(n_tokens: int, hidden: int, inter: int, top_k: int) -> bool:
+    """Whether the few-token expert kernels (:func:`moe_small_gate_up`, :func:`moe_small_down`) take a step."""
+    return bool(_lib().ftk_moe_small_fits(n_tokens, hidden, inter, top_k))
+
+
+def moe_small_gate_up(h: torch.Tensor, ids: torch.Tensor, w1: torch.Tensor, act: str, alpha: float, limit: float,
+                      out: torch.Tensor) -> None:
+    """``out[t*k + j] = act(h[t] W1[ids[t, j]]^T)`` for a step of up to four tokens: routes in token order,
+    no sort, no gathered copy; ``w1 [E, 2I, H]`` rows gate then up, bfloat16."""
+    T, H = h.shape
+    k = ids.shape[1]
+    E, two_i, H2 = w1.shape
+    if H2 != H or ids.shape != (T, k) or out.shape != (T * k, two_i // 2) or h.dtype != torch.bfloat16 \
+            or w1.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("moe_small_gate_up: shapes or dtypes do not agree")
+    _check(_lib().ftk_moe_small_gate_up(_dev(h, "h"), _dev(ids, "ids", torch.int32), _dev(w1, "w1"), _dev(out, "out"),
+                                        T, k, E, H, two_i // 2, ACT_CODES[act], float(alpha), float(limit), _stream()),
+           "moe_small_gate_up")
+
+
+def moe_small_down(a: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w2: torch.Tensor,
+                   out: torch.Tensor) -> None:
+    """``out[r] = (a[r] W2[ids.flat[r]]^T) * weights.flat[r]`` for the routes of up to four tokens."""
+    R, I = a.shape
+    E, H, I2 = w2.shape
+    T, k = ids.shape
+    if I2 != I or R != T * k or weights.numel() != R or out.shape != (R, H) or a.dtype != torch.bfloat16 \
+            or w2.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("moe_small_down: shapes or dtypes do not agree")
+    _check(_lib().ftk_moe_small_down(_dev(a, "a"), _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32),
+                                     _dev(w2, "w2"), _dev(out, "out"), T, k, E, H, I, _stream()), "moe_small_down")
 
 
 def moe_gather(h: torch.Tensor, sorted_routes: torch.Tensor, top_k: int, out: torch.Tensor) -> None:

@@ -80,6 +80,27 @@ class MoE(FeedForward):
     def forward(self, h: torch.Tensor, step: StepState, h_f32: Optional[torch.Tensor] = None) -> torch.Tensor:
         return self.forward_lazy(h, step, h_f32).rows()
 
+    def _few_tokens(self, h, h_f32, step, logits, ids, wts, bias) -> RouteSum:
+        """Steps of up to four tokens: the routes stay in token order (no sort, no gathered copy of the
+        activations) and each route's expert rows are streamed by the few-token kernels."""
+        T = h.shape[0]
+        ws, dt, cap = self.env.workspace, self.env.dtype, self.env.max_step_tokens
+        k, R = self.top_k, T * self.top_k
+        ops.moe_route(h_f32, self.params["gate.weight"], bias, k, self.scoring, self.scale, logits, ids, wts)
+        record = self.env.shared.get("record_expert_counts")
+        if record is not None:
+            record.append(torch.bincount(ids.view(-1).long(), minlength=self.n_experts).to(torch.int32))
+        if "moe.pos.identity" not in self.env.shared:
+            self.env.shared["moe.pos.identity"] = torch.arange(64 * 64, dtype=torch.int32, device=self.env.device)
+        pos = self.env.shared["moe.pos.identity"][:R]
+        a = ws.get("moe.act", (R, self.inter), dt, (cap * k, self.inter))
+        ops.moe_small_gate_up(h, ids, self.params["experts.gate_up_proj"], self.act, self.alpha, self.limit, a)
+        y = ws.get("moe.y", (R, self.hidden), dt, (cap * k, self.hidden))
+        ops.moe_small_down(a, ids, wts, self.params["experts.down_proj"], y)
+        shared = self.shared.forward(h, step) if self.shared is not None else None
+        out = ws.get("moe.out", (T, self.hidden), dt, (cap, self.hidden))
+        return RouteSum(y, pos, k, shared, T, out)
+
     def forward_lazy(self, h: torch.Tensor, step: StepState, h_f32: Optional[torch.Tensor] = None) -> RouteSum:
         """The experts' rows and where each token's routes lie among them; the sum over a token's routes
         is left to the consumer (the next norm takes it together with the residual sum)."""
@@ -100,6 +121,9 @@ class MoE(FeedForward):
         routes = ws.get("moe.routes", (R,), torch.int32, (cap * k,))
         pos = ws.get("moe.pos", (R,), torch.int32, (cap * k,))
         bias = self.params.get("e_score_correction_bias")
+        if (dt == torch.bfloat16 and ops.moe_small_fits(T, self.hidden, self.inter, k)
+                and ops.moe_route_fits(T, self.hidden, E, k)):
+            return self._few_tokens(h, h_f32, step, logits, ids, wts, bias)
         if ops.moe_route_fits(T, self.hidden, E, k):  # small steps: logits, choice and sort in one launch
             ops.moe_route(h_f32, self.params["gate.weight"], bias, k, self.scoring, self.scale, logits, ids, wts,
                           counts, offsets, routes, pos)

@@ -51,12 +51,13 @@ def _draw(ps: ParamSpec, gen: torch.Generator, device, dtype: torch.dtype) -> to
     raise ValueError(f"unknown init {ps.init!r}")
 
 
-def random_tensors_cpu(expected: Mapping[str, ParamSpec], seed: int) -> Dict[str, torch.Tensor]:
-    """Every expected tensor in its storage dtype, drawn in float32 and rounded."""
+def random_tensors_cpu(expected: Mapping[str, ParamSpec], seed: int, device: str = "cpu") -> Dict[str, torch.Tensor]:
+    """Every expected tensor in its storage dtype, drawn in float32 and rounded.  ``device`` may name
+    a CUDA device to draw there (large models; the values then differ from the CPU's draws)."""
     out = {}
     for name, ps in expected.items():
-        gen = torch.Generator(device="cpu").manual_seed(tensor_seed(seed, name))
-        t = _draw(ps, gen, "cpu", torch.float32 if ps.dtype != "int32" else torch.int32)
+        gen = torch.Generator(device=device).manual_seed(tensor_seed(seed, name))
+        t = _draw(ps, gen, device, torch.float32 if ps.dtype != "int32" else torch.int32)
         out[name] = t.to(_STORE[ps.storage_dtype()])
     return out
 
@@ -70,19 +71,22 @@ def random_tensors_on_device(expected: Mapping[str, ParamSpec], seed: int, compu
     return out
 
 
-def write_model_folder(config: Mapping[str, Any], folder: str, seed: int, fused_names: bool = False) -> str:
+def write_model_folder(config: Mapping[str, Any], folder: str, seed: int, fused_names: bool = False,
+                       device: str = "cpu") -> str:
     """Write ``config.json`` and ``model.safetensors`` for the architecture ``config`` names.
 
     ``config`` is the config.json content.  Tensors carry the checkpoint's per-part names
-    (``q_proj``, ``experts.3.w1`` ...) unless ``fused_names`` asks for the model's own."""
+    (``q_proj``, ``experts.3.w1`` ...) unless ``fused_names`` asks for the model's own.  ``device``:
+    where the values are drawn (a CUDA device makes gigabytes of weights in seconds; the file is the
+    reference either way, whoever reads it)."""
     from ..engine.build import describe_model  # late import: engine imports weights
 
     arch, typed, spec, expected = describe_model(config)
-    tensors = random_tensors_cpu(expected, seed)
+    tensors = random_tensors_cpu(expected, seed, device)
     if not fused_names:
         for rule in arch.fusion_rules(typed):
             if rule.target in tensors:
-                tensors.update({k: v.contiguous() for k, v in unfuse(rule, tensors.pop(rule.target)).items()})
+                tensors.update(unfuse(rule, tensors.pop(rule.target)))  # views: the writer copies tensor by tensor
     os.makedirs(folder, exist_ok=True)
     with open(os.path.join(folder, "config.json"), "w", encoding="utf-8") as f:
         json.dump(dict(config), f, indent=1)

@@ -170,6 +170,5 @@ def write_safetensors(path: str, tensors: Mapping[str, torch.Tensor],
         for name in order:
             t = tensors[name].detach().cpu().contiguous()
             if t.numel():
-                f.write(t.view(torch.uint8).numpy().tobytes() if t.dim() else
-                        t.reshape(1).view(torch.uint8).numpy().tobytes())
+                f.write((t if t.dim() else t.reshape(1)).view(torch.uint8).numpy().data)
     os.replace(tmp, path)

@@ -19,14 +19,25 @@ _FOLDERS: Dict[Tuple[str, int], str] = {}
 # run may legitimately choose otherwise, which changes its logits by more than rounding; bfloat16
 # comparisons check those tokens only loosely and require them to be a minority.
 NEAR_TIE = 0.0
-# bfloat16 logits against the 32-bit plain model: the bound the reference uses for its own
-# bfloat16 kernels (tests/kernels/test_minimax_m3_sparse.py:275-276) is 3e-2 max-abs.
-BF16_TOL = dict(rtol=3e-2, atol=2e-2)
+# bfloat16 logits against the 32-bit plain model.  Measured on the tiny configurations (whole prompts and
+# portions, six sequences each, positions clear of near-ties): the engine's largest error is 0.0049 (A),
+# 0.0046 (B), 0.0030 (D), 0.0045 (E), which is also what the plain model's own bfloat16 emulation makes
+# (0.0049 / 0.0044 / 0.0031 / 0.0052), on logits that spread by 0.16 to 0.21; C, whose experts' output is
+# doubled (routed_scaling_factor 2) and joined by a shared expert, reaches 0.0126.  The bound is about twice
+# that: it is far below the reference's own bound for its bfloat16 kernels (3e-2 max-abs,
+# tests/kernels/test_minimax_m3_sparse.py:275-276), so that a fault the size of the noise shows.
+BF16_TOL = dict(rtol=2e-2, atol=8e-3)
+BF16_NOISE = {"C": 2.0}  # configurations whose bfloat16 noise is a multiple of the others'
 F32_TOL = dict(rtol=1e-4, atol=2e-5)
 
 
+def bf16_tol(name: str = "") -> dict:
+    f = BF16_NOISE.get(name, 1.0)
+    return dict(rtol=BF16_TOL["rtol"], atol=BF16_TOL["atol"] * f)
+
+
 def assert_bf16_close(got: torch.Tensor, ref: torch.Tensor, margins: torch.Tensor, what: str = "",
-                      prefix_only: bool = False) -> None:
+                      prefix_only: bool = False, name: str = "") -> None:
     """``got`` (bfloat16 engine) against ``ref`` (32-bit plain) at every position whose router
     gaps are clear of bfloat16 noise; the others are checked loosely.  ``prefix_only`` (models
     with block-sparse layers, where a flip spreads to later tokens) compares strictly only the
@@ -38,7 +49,7 @@ def assert_bf16_close(got: torch.Tensor, ref: torch.Tensor, margins: torch.Tenso
         assert first >= min(24, sure.numel()), f"{what}: the first near-tie comes at {first}, too early to compare"
     else:
         assert sure.float().mean() > 0.5, f"{what}: too many near-ties for a meaningful comparison"
-    torch.testing.assert_close(got[sure], ref[: got.shape[0]][sure], **BF16_TOL, msg=lambda m: f"{what}: {m}")
+    torch.testing.assert_close(got[sure], ref[: got.shape[0]][sure], **bf16_tol(name), msg=lambda m: f"{what}: {m}")
     assert torch.isfinite(got).all()
     assert (got - ref[: got.shape[0]]).abs().max() < 0.5, what
 

@@ -193,6 +193,10 @@ def attention_tc_fits(head_dim, page_size, group):
     return False  # the CPU tests plan for the other kernels
 
 
+def moe_small_fits(n_tokens, hidden, inter, top_k):
+    return False  # the few-token kernels are a second route to the same result; the CPU stand-ins take the general one
+
+
 def moe_route_fits(n_tokens, hidden, n_experts, top_k):
     return 1 <= n_tokens <= 32 and hidden % 4 == 0
 
@@ -266,7 +270,7 @@ def sample(logits, temperature, top_k, top_p, u, out):
         out[r] = idx
 
 
-ALL = ["copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "add_rmsnorm_routes", "act_and_mul", "cast", "table_update", "norm_rope_store",
+ALL = ["moe_small_fits", "copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "add_rmsnorm_routes", "act_and_mul", "cast", "table_update", "norm_rope_store",
        "paged_attention", "router_topk", "moe_permute", "moe_route", "moe_route_fits", "linear", "attention_tc_fits", "moe_gather", "moe_gemm1_act", "moe_gemm2",
        "moe_combine", "sample"]
 

@@ -126,16 +126,35 @@ def read_config(folder: str) -> PlainConfig:
     )
 
 
-def read_weights(folder: str, dtype: torch.dtype) -> Dict[str, torch.Tensor]:
+class _WidenOnRead(dict):
+    """Tensors kept as the file stores them and widened to the working dtype when read: for models
+    whose weights would not fit twice into memory."""
+
+    def __init__(self, dtype: torch.dtype):
+        super().__init__()
+        self.dtype = dtype
+
+    def __getitem__(self, name):
+        return super().__getitem__(name).to(self.dtype)
+
+    def get(self, name, default=None):
+        return self[name] if name in self else default
+
+
+def read_weights(folder: str, dtype: torch.dtype, lazy: bool = False) -> Dict[str, torch.Tensor]:
     """Tensors by checkpoint name (python/freetoken/models/minimax_m3/weight.py:182-246);
-    the ``language_model.`` prefix is dropped."""
+    the ``language_model.`` prefix is dropped.  ``lazy`` widens a tensor each time it is read instead
+    of once for all."""
     from safetensors.torch import load_file
 
-    out = {}
+    out = _WidenOnRead(dtype) if lazy else {}
     for name, t in load_file(os.path.join(folder, "model.safetensors")).items():
         if name.startswith("language_model."):
             name = name[len("language_model."):]
-        out[name] = t.to(dtype)
+        if lazy:
+            dict.__setitem__(out, name, t)
+        else:
+            out[name] = t.to(dtype)
     return out
 
 
@@ -355,9 +374,10 @@ def attention_layer(h, W, prefix: str, cfg: PlainConfig, cos, sin, sparse: bool,
 
 # --------------------------------------------------------------------------- model
 class PlainM3:
-    def __init__(self, folder: str, dtype: torch.dtype = torch.float32, rounding: Optional[str] = None):
+    def __init__(self, folder: str, dtype: torch.dtype = torch.float32, rounding: Optional[str] = None,
+                 lazy: bool = False):
         self.cfg = read_config(folder)
-        self.W = read_weights(folder, dtype)
+        self.W = read_weights(folder, dtype, lazy)
         self.dtype = dtype
         self.rounding = rounding
 

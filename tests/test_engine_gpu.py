@@ -50,7 +50,7 @@ def check(got, ref, dtype, margins, what, name=""):
     if dtype == "float32":
         torch.testing.assert_close(got, ref[: got.shape[0]], **F32_TOL, msg=lambda m: f"{what}: {m}")
     else:
-        assert_bf16_close(got, ref, margins, what, prefix_only=name in SPARSE)
+        assert_bf16_close(got, ref, margins, what, prefix_only=name in SPARSE, name=name)
 
 
 def sequence(plain, name, n, seed):

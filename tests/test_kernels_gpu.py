@@ -32,6 +32,12 @@ def attn_tol(dtype):
 
 
 def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    n = 1
+    for d in shape:
+        n *= d
+    if n > 50_000_000:  # (gigabytes of expert weights: drawn on the device, the CPU takes a quarter of a minute)
+        g = torch.Generator(device=DEV).manual_seed(seed + sum(shape))
+        return (torch.randn(*shape, generator=g, device=DEV) * scale).to(dtype)
     g = torch.Generator(device="cpu").manual_seed(seed + sum(shape))
     return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
 
@@ -139,8 +145,9 @@ def make_rope(max_pos, rd, theta=10000.0):
     (7, 1, 48, 24, 4, True, True), (6, 3, 32, 32, 8, False, False), (48, 8, 128, 64, 16, True, True),
     (5, 5, 80, 16, 3, True, True), (2, 2, 256, 128, 16, False, True), (5, 3, 64, 16, 5, True, True),
     (7, 3, 128, 0, 4, True, True), (5, 1, 128, 128, 8, False, True), (3, 2, 64, 64, 4, True, False)])
-def test_norm_rope_store(dtype, Hq, Hkv, D, rd, P, gemma, norm):
-    T, pages = 21, 12
+@pytest.mark.parametrize("T", [21, 150])  # (from 64 tokens on, bfloat16 heads of 64/128/256 take the block-per-token kernel)
+def test_norm_rope_store(dtype, Hq, Hkv, D, rd, P, gemma, norm, T):
+    pages = -(-T // P) + 9
     x = rnd(T, (Hq + 2 * Hkv) * D, dtype=dtype)
     pos = torch.randint(0, 100, (T,), dtype=torch.int32, device=DEV)
     table = make_rope(100, rd) if rd else None
@@ -163,7 +170,8 @@ def test_norm_rope_store(dtype, Hq, Hkv, D, rd, P, gemma, norm):
         torch.testing.assert_close(torch.nan_to_num(a.float()), torch.nan_to_num(b.float()), **tol(dtype))
 
 
-def run_attention(dtype, Hq, Hkv, D, P, segs, window, fixed_splits=None, force_split=False, seed=0, tile=None):
+def run_attention(dtype, Hq, Hkv, D, P, segs, window, fixed_splits=None, force_split=False, seed=0, tile=None,
+                  spoil_reference=None):
     """segs: list of (q_len, kv_len).  Builds a shuffled page layout with NaN in every unwritten
     slot, runs kernel and reference, returns both outputs."""
     G = Hq // Hkv
@@ -204,6 +212,13 @@ def run_attention(dtype, Hq, Hkv, D, P, segs, window, fixed_splits=None, force_s
     scale = D ** -0.5
     ops.paged_attention(q, ks, vs, bt, seg, len(segs), items, plan.n_items, part_o, part_ml, out, tile,
                         scale, window)
+    if spoil_reference is not None:  # (segment, position): the reference is made blind to that key
+        si, kpos = spoil_reference
+        page = int(bt[rows[si], kpos // P])
+        ks, vs = ks.clone(), vs.clone()
+        qs = q[seg_info[si][0]: seg_info[si][0] + seg_info[si][1]].float().view(-1, Hkv, G, D).mean((0, 2))
+        ks[page, :, kpos % P] = (-30.0 * qs / qs.norm(dim=-1, keepdim=True)).to(dtype)  # score far below the rest
+        vs[page, :, kpos % P] = 0
     ref.paged_attention(q, ks, vs, bt, seg, len(segs), items, plan.n_items, None, None, want, tile, scale,
                         window)
     return out, want, plan
@@ -399,6 +414,136 @@ def test_attention_far_key_stands_out(dtype):
     ops.paged_attention(q, ks, vs, bt, seg, 1, items, plan.n_items, po, pm, out, tile, D ** -0.5, None)
     for h in range(Hkv):
         torch.testing.assert_close(out[0, h * G].float(), vs[1, h, 3].float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("T", [1, 2, 3, 4])
+@pytest.mark.parametrize("N,K", [(8192, 3072), (3072, 6144), (100, 72), (7, 8), (1000, 520), (33, 24576)])
+def test_few_token_product_streams_the_weights(T, N, K, monkeypatch):
+    """``ops.linear`` sends products of few bfloat16 rows to this library's own kernel (by default of one row;
+    here of up to four, which the kernel takes as well); other sizes go to the library."""
+    x = rnd(T, K, dtype=torch.bfloat16)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.05)
+    out = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    name = "few-token product: weights streamed by warps"
+    before = ops.variant_counts().get(name, 0)
+    ops.linear(x, w, out)
+    assert ops.variant_counts().get(name, 0) - before == (1 if T <= ops.SMALL_LINEAR_MAX_TOKENS else 0)
+    monkeypatch.setattr(ops, "SMALL_LINEAR_MAX_TOKENS", 4)
+    before = ops.variant_counts().get(name, 0)
+    ops.linear(x, w, out)
+    took = ops.variant_counts().get(name, 0) - before
+    assert took == (1 if ops.small_linear_fits(T, N, K) else 0)
+    if not ops.small_linear_fits(T, N, K):  # three and four rows of 24,576 do not fit its shared memory: the library's
+        assert K == 24576 and T > 2
+        return
+    want = x.float() @ w.float().T
+    # (sums of thousands of terms near zero: the bound is on the size of the row's results, not of each)
+    torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-3 * float(want.abs().mean() + 1))
+    assert not ops.small_linear_fits(5, N, K) and not ops.small_linear_fits(1, N, 12)
+
+
+@pytest.mark.parametrize("act", ["silu", "swigluoai"])
+@pytest.mark.parametrize("T,k,E,H,I", [(1, 8, 256, 3072, 1536), (4, 8, 256, 3072, 1536), (3, 2, 5, 64, 40), (2, 3, 7, 520, 8),
+                                       (4, 4, 4, 48, 104)])
+def test_few_token_expert_products(T, k, E, H, I, act):
+    """The routed few-token kernels against the plain statement, routes in token order, several routes to
+    one expert, and a route that names no expert (its rows are zero)."""
+    g = torch.Generator().manual_seed(T * 100 + E)
+    h = rnd(T, H, dtype=torch.bfloat16)
+    w1 = rnd(E, 2 * I, H, dtype=torch.bfloat16, scale=0.05)
+    w2 = rnd(E, H, I, dtype=torch.bfloat16, scale=0.05)
+    ids = torch.stack([torch.randperm(E, generator=g)[:k] if k <= E else torch.randint(0, E, (k,), generator=g)
+                       for _ in range(T)]).to(torch.int32)
+    if T > 1:
+        ids[1, 0] = ids[0, 0]  # two tokens at one expert
+    if T > 2:
+        ids[2, k - 1] = -1
+    ids = ids.to(DEV)
+    wts = torch.rand(T, k, device=DEV) + 0.5
+    assert ops.moe_small_fits(T, H, I, k) and not ops.moe_small_fits(5, H, I, k) and not ops.moe_small_fits(1, H + 4, I, k)
+    a = torch.full((T * k, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    y = torch.full((T * k, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.moe_small_gate_up(h, ids, w1, act, 1.702, 7.0, a)
+    a_in = rnd(T * k, I, dtype=torch.bfloat16, seed=5)
+    ops.moe_small_down(a_in, ids, wts, w2, y)
+    want_a, want_y = torch.zeros(T * k, I, device=DEV), torch.zeros(T * k, H, device=DEV)
+    for r in range(T * k):
+        e = int(ids.view(-1)[r])
+        if e < 0:
+            continue
+        gu = (h[r // k].float() @ w1[e].float().T).to(torch.bfloat16).float()
+        want_a[r] = ref.gated(gu[:I], gu[I:], act, 1.702, 7.0) if hasattr(ref, "gated") else _gated(gu[:I], gu[I:], act)
+        want_y[r] = (a_in[r].float() @ w2[e].float().T) * wts.view(-1)[r]
+    assert not torch.isnan(a.float()).any() and not torch.isnan(y.float()).any()
+    # (gate and up are rounded to bfloat16 before the activation: a last-bit difference there is amplified by (u + 1))
+    torch.testing.assert_close(a.float(), want_a, rtol=3e-2, atol=4e-3)
+    torch.testing.assert_close(y.float(), want_y, **tol(torch.bfloat16))
+
+
+def _gated(g, u, act, alpha=1.702, limit=7.0):
+    if act == "silu":
+        return g * torch.sigmoid(g) * u
+    g = g.clamp(max=limit)
+    u = u.clamp(-limit, limit)
+    return g * torch.sigmoid(alpha * g) * (u + 1)
+
+
+# ---------------------------------------------------------------------------------------------
+# Negative controls: the tolerances above must be able to fail.  Each bfloat16 kernel's output is
+# compared, with the same bound as its test, against a reference that was given a slightly wrong
+# problem (one key of one request missing; one row counted to the neighbouring expert): the
+# comparison has to raise.
+@pytest.mark.parametrize("tile", [16, 64, 128, 256])
+def test_attention_bound_notices_one_missing_key(tile):
+    segs = [(40, 40), (1, 36)] if tile != 16 else [(1, 40), (1, 36)]
+    Hq, Hkv, D, P = 12, 2, 128, 16
+    out, want, _ = run_attention(torch.bfloat16, Hq, Hkv, D, P, segs, None, tile=tile)
+    torch.testing.assert_close(out.float(), want.float(), **attn_tol(torch.bfloat16))
+    # the same problem, but the reference does not see key 20 of the first request (its score is made
+    # hopeless by turning the key against every query, its value is zeroed)
+    out2, wrong, _ = run_attention(torch.bfloat16, Hq, Hkv, D, P, segs, None, tile=tile, spoil_reference=(0, 20))
+    assert torch.equal(out, out2)
+    with pytest.raises(AssertionError):
+        torch.testing.assert_close(out.float(), wrong.float(), **attn_tol(torch.bfloat16))
+    # (a small fault, not a gross one: the rows of the other request are untouched, and in the spoilt
+    # request the typical output moves by a few hundredths)
+    diff = (want.float() - wrong.float()).abs()
+    n_first = 40 if tile != 16 else 1
+    assert diff[n_first:].max() == 0 and diff[:n_first].median() < 0.05
+
+
+@pytest.mark.parametrize("tc", [True, False])
+def test_expert_product_bounds_notice_one_row_at_the_wrong_expert(tc):
+    E, H, I = 8, 256, 128
+    counts = [5, 0, 9, 3, 40, 1, 0, 6]
+    R = sum(counts)
+    off = torch.tensor([0] + list(np.cumsum(counts)), dtype=torch.int32, device=DEV)
+    wrong_off = off.clone()
+    wrong_off[3] += 1  # the first row of expert 3 is counted to expert 2
+    x = rnd(R, H, dtype=torch.bfloat16)
+    w1 = rnd(E, 2 * I, H, dtype=torch.bfloat16, scale=0.1)
+    w2 = rnd(E, H, I, dtype=torch.bfloat16, scale=0.1)
+    routes = torch.randperm(R).to(torch.int32).to(DEV)
+    wts = torch.rand(R, device=DEV) + 0.5
+    ops.set_moe_tensor_cores(tc)
+    try:
+        a, y = torch.empty(R, I, dtype=torch.bfloat16, device=DEV), torch.empty(R, H, dtype=torch.bfloat16, device=DEV)
+        ops.moe_gemm1_act(x, w1, off, "silu", 1.702, 7.0, a)
+        a_in = rnd(R, I, dtype=torch.bfloat16, seed=3)
+        ops.moe_gemm2(a_in, w2, off, routes, wts, y)
+    finally:
+        ops.set_moe_tensor_cores(True)
+    for offsets, ok in ((off, True), (wrong_off, False)):
+        a2, y2 = torch.empty_like(a), torch.empty_like(y)
+        ref.moe_gemm1_act(x, w1, offsets, "silu", 1.702, 7.0, a2)
+        ref.moe_gemm2(a_in, w2, offsets, routes, wts, y2)
+        for got, want in ((a, a2), (y, y2)):
+            if ok:
+                torch.testing.assert_close(got.float(), want.float(), **tol(torch.bfloat16))
+            else:
+                with pytest.raises(AssertionError):
+                    torch.testing.assert_close(got.float(), want.float(), **tol(torch.bfloat16))
+                assert ((got.float() - want.float()).abs().amax(-1) > 0.1).sum() == 1  # exactly that row
 
 
 @pytest.mark.parametrize("scoring,bias", [("sigmoid", True), ("sigmoid", False), ("softmax", False), ("softmax", True)])

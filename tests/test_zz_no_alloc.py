@@ -26,10 +26,10 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def problem(dtype, seed, segs, Hq=12, Hkv=2, D=64, P=16):
+def problem(dtype, seed, segs, Hq=12, Hkv=2, D=64, P=16, tile=None):
     g = torch.Generator().manual_seed(seed)
     G = Hq // Hkv
-    tile = 64 if dtype == torch.bfloat16 else 16
+    tile = tile or (64 if dtype == torch.bfloat16 else 16)
     n_pages = sum(-(-kv // P) for _, kv in segs) + 2
     perm = (torch.randperm(n_pages - 1, generator=g) + 1).tolist()
     bt = torch.zeros(len(segs), max(-(-kv // P) for _, kv in segs), dtype=torch.int32)
@@ -77,12 +77,15 @@ def static_scratch(lib, pr):
     return rc, out
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_static_scratch_matches_the_ordinary_entry_point_twice_in_a_row(dtype):
+@pytest.mark.parametrize("dtype,tile", [(torch.float32, 16), (torch.bfloat16, 64), (torch.bfloat16, 16)])
+def test_static_scratch_matches_the_ordinary_entry_point_twice_in_a_row(dtype, tile):
+    """16-row bfloat16 tiles are the decode kernel, whose splits are merged by the split that arrives last
+    (single tokens only); 64-row tiles and float32 use the separate merge."""
     lib = library.load()
     tol = dict(rtol=2e-5, atol=2e-6) if dtype == torch.float32 else dict(rtol=2e-2, atol=1.5e-2)
-    first = problem(dtype, 1, [(1, 900), (2, 300), (1, 64)])
-    second = problem(dtype, 2, [(1, 450), (1, 777), (3, 129), (1, 20)])
+    single = dtype == torch.bfloat16 and tile == 16
+    first = problem(dtype, 1, [(1, 900), (1 if single else 2, 300), (1, 64)], tile=tile)
+    second = problem(dtype, 2, [(1, 450), (1, 777), (1 if single else 3, 129), (1, 20)], tile=tile)
     for pr in (first, second):  # the second call finds the first call's partial results in the array
         want = ordinary(pr)
         rc, got = static_scratch(lib, pr)
@@ -103,3 +106,9 @@ def test_static_scratch_refuses_what_does_not_fit():
     rc, _ = static_scratch(lib, pr)
     assert rc != 0
     assert b"static array holds" in lib.ftk_last_error()
+    # a work list whose numbers make no sense is refused too, before any size is computed from it
+    bad = pr["plan"].items.copy()
+    bad[0, 5], bad[0, 7] = 3, -5
+    pr["plan"].items[:] = bad
+    rc, _ = static_scratch(lib, pr)
+    assert rc != 0 and b"split" in lib.ftk_last_error()
