@@ -37,6 +37,8 @@ def add_engine_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--cuda-graph-max-bs", type=int, default=None)
     p.add_argument("--disable-cuda-graph", action="store_true")
+    p.add_argument("--decode-log-interval", type=int, default=0,
+                   help="log a status line every so many decode steps (0: none)")
 
 
 def engine_kwargs(a: argparse.Namespace) -> Dict:
@@ -45,7 +47,8 @@ def engine_kwargs(a: argparse.Namespace) -> Dict:
                 use_dummy_weight=a.dummy_weight, max_extend_tokens=a.max_extend_tokens,
                 max_step_tokens=a.max_step_tokens, num_page_override=a.num_pages,
                 num_token_override=a.num_tokens, page_size=a.page_size, num_layers=a.num_layers,
-                seed=a.seed, cuda_graph=not a.disable_cuda_graph, cuda_graph_max_bs=a.cuda_graph_max_bs)
+                seed=a.seed, cuda_graph=not a.disable_cuda_graph, cuda_graph_max_bs=a.cuda_graph_max_bs,
+                decode_log_interval=a.decode_log_interval)
 
 
 def cmd_generate(argv: List[str]) -> int:
@@ -70,6 +73,10 @@ def cmd_generate(argv: List[str]) -> int:
     from .sampling.params import SamplingParams
 
     kw = engine_kwargs(a)
+    if a.decode_log_interval > 0:
+        import logging
+
+        logging.basicConfig(level=logging.INFO, format="[%(asctime)s] %(message)s", stream=sys.stderr)
     dtype = kw.pop("dtype")
     llm = LLM(a.model_path, dtype=dtype, **kw)
     sp = SamplingParams(temperature=a.temperature, top_k=a.top_k, top_p=a.top_p,

@@ -55,6 +55,7 @@ class EngineConfig:
     # launch step N+1 before step N's tokens are read; the reference's switch is the environment
     # variable FREETOKEN_DISABLE_OVERLAP_SCHEDULING (python/freetoken/env.py:72), honoured here too
     overlap_scheduling: bool = True
+    decode_log_interval: int = 0  # a status line every so many decode steps (the reference's server: 40); 0 = none
 
     def __post_init__(self) -> None:
         if self.dtype != "auto":

@@ -75,7 +75,10 @@ int ftk_paged_attention_sparse(const void* q, const void* k_slab, const void* v_
 int ftk_sparse_select(const void* iq, const void* ik_slab, int dtype, const int32_t* block_table, int bt_stride,
                       const int32_t* seg_info, int n_segs, int n_tokens, int n_heads, int dim, int page_size,
                       int num_pages, int block_size, int topk, int local_blocks, int init_blocks, int max_blocks,
-                      int32_t* sel, void* stream);
+                      int live_blocks, int32_t* sel, float* scores, void* stream);
+// Whether bfloat16 block scores of these sizes can be taken on the tensor cores (`scores [T, n_heads, max_blocks]`
+// float32 scratch must then be given to ftk_sparse_select).
+int ftk_sparse_score_fits(int n_heads, int dim, int block_size);
 int ftk_router_topk(const float* logits, const float* bias, int n_tokens, int n_experts, int top_k,
                     int scoring, float scale, int32_t* ids, float* weights, void* stream);
 // Router logits (float32 x [T, hidden] times gate_w [E, hidden]), choice and sort of the routes in one

@@ -106,6 +106,9 @@ __global__ void norm_rope_store_kernel(const T* __restrict__ x, int n_tokens, in
 // The same for bfloat16 heads of 64, 128 or 256 elements with 16-byte accesses: a head is spread over
 // LPH = head_dim / 8 lanes (8 consecutive elements each), a warp takes 32 / LPH heads at once, and a
 // lane gets its rotation partners from the lane half a rotary span away (rotary_dim a multiple of 16).
+// (Measured at 2,048 tokens of 64 heads: 25.6 microseconds.  A block per token whose warps walk the token's
+// heads with eight loads in flight per lane and the token's table rows read once took 30 to 37; four
+// tokens per thread took 29.)
 template <int LPH>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 norm_rope_store_vec_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int row_elems, int rotary_dim,
@@ -212,130 +215,6 @@ norm_rope_store_vec_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, in
   *reinterpret_cast<uint4*>(dst + l * 8) = pk;
 }
 
-// The same for steps of many tokens: a block takes one token and its four warps walk the token's heads in
-// turns of kTokenTurns, every load of a turn issued before the first is used (eight 16-byte loads in flight
-// per lane instead of one), and what belongs to the token rather than to a head (its position, its rows of
-// the rotation table, its cache slots) is read once.  The per-head kernel above keeps one load in flight per
-// thread behind two dependent ones (position, then table) and reached 2.6 TB/s at 2,048 tokens.
-constexpr int kTokenTurns = 8;
-constexpr int kTokenKernelMin = 64;  // steps of this many tokens and more take the block-per-token kernel
-
-template <int LPH>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
-norm_rope_store_token_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int row_elems, int rotary_dim,
-                             const int32_t* __restrict__ positions, const float* __restrict__ rope_table, int max_pos,
-                             float eps, int gemma, Sections sec) {
-  pdl_wait();
-  pdl_trigger();
-  constexpr int kHeadDim = LPH * 8;
-  constexpr int kHeadsPerWarp = 32 / LPH;
-  constexpr int kHeadsPerTurn = kWarpsPerBlock * kHeadsPerWarp;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x;
-  const int sub = lane / LPH, l = lane % LPH;
-  const int half = rotary_dim >> 1;
-  const bool low = l * 8 < half, in = l * 8 < rotary_dim;
-  float ca[8], cb[8];
-  if (rotary_dim > 0 && in) {
-    int pos = positions[t];
-    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
-    const float* cs = rope_table + (size_t)pos * rotary_dim;
-    const int d0 = l * 8;
-    const float* a = low ? cs + d0 : cs + d0 - half;
-    const float* b = low ? cs + half + d0 : cs + d0;
-    *reinterpret_cast<float4*>(ca) = *reinterpret_cast<const float4*>(a);
-    *reinterpret_cast<float4*>(ca + 4) = *reinterpret_cast<const float4*>(a + 4);
-    *reinterpret_cast<float4*>(cb) = *reinterpret_cast<const float4*>(b);
-    *reinterpret_cast<float4*>(cb + 4) = *reinterpret_cast<const float4*>(b + 4);
-  }
-  long long slots[kMaxSections];
-#pragma unroll
-  for (int i = 0; i < kMaxSections; ++i) {
-    slots[i] = -1;
-    if (i < sec.n && sec.s[i].slab) {
-      const long long sl = sec.s[i].slot_map[t];
-      if (sl >= 0 && sl < (long long)sec.s[i].num_pages * sec.s[i].page_size) slots[i] = sl;
-    }
-  }
-  const __nv_bfloat16* row = x + (size_t)t * row_elems;
-  const float one = gemma ? 1.f : 0.f;
-  const int hop = half >> 3;  // lanes per half rotary span
-  for (int h0 = 0; h0 < sec.total_heads; h0 += kTokenTurns * kHeadsPerTurn) {
-    uint4 raw[kTokenTurns];
-    int sec_of[kTokenTurns], head_of[kTokenTurns];
-#pragma unroll
-    for (int it = 0; it < kTokenTurns; ++it) {
-      const int hs = h0 + (it * kWarpsPerBlock + warp) * kHeadsPerWarp + sub;
-      int si = 0, hl = hs < sec.total_heads ? hs : 0;
-      while (si < sec.n - 1 && hl >= sec.s[si].n_heads) {
-        hl -= sec.s[si].n_heads;
-        ++si;
-      }
-      sec_of[it] = hs < sec.total_heads ? si : -1;
-      head_of[it] = hl;
-      raw[it] = make_uint4(0u, 0u, 0u, 0u);
-      if (hs < sec.total_heads)
-        raw[it] = *reinterpret_cast<const uint4*>(row + (size_t)(sec.s[si].first_head + hl) * kHeadDim + l * 8);
-    }
-#pragma unroll
-    for (int it = 0; it < kTokenTurns; ++it) {
-      const int si = sec_of[it] < 0 ? 0 : sec_of[it];
-      const FtkSection& S = sec.s[si];
-      float v[8];
-      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[it]);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __bfloat1622float2(h2[j]);
-        v[2 * j] = f.x;
-        v[2 * j + 1] = f.y;
-      }
-      float ss = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
-#pragma unroll
-      for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      if (S.norm_weight) {
-        float w[8];
-        *reinterpret_cast<float4*>(w) = *reinterpret_cast<const float4*>(S.norm_weight + l * 8);
-        *reinterpret_cast<float4*>(w + 4) = *reinterpret_cast<const float4*>(S.norm_weight + l * 8 + 4);
-        const float inv = rsqrtf(ss / (float)kHeadDim + eps);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = v[j] * inv * (w[j] + one);
-      }
-      float partner[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float up = __shfl_down_sync(0xffffffffu, v[j], hop & 31);
-        const float dn = __shfl_up_sync(0xffffffffu, v[j], hop & 31);
-        partner[j] = low ? up : dn;
-      }
-      if (S.rotate && rotary_dim > 0 && in) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = low ? v[j] * ca[j] - partner[j] * cb[j] : v[j] * ca[j] + partner[j] * cb[j];
-      }
-      if (sec_of[it] < 0) continue;
-      const int hl = head_of[it];
-      __nv_bfloat16* dst;
-      if (S.slab) {
-        long long slot = -1;
-#pragma unroll
-        for (int i = 0; i < kMaxSections; ++i)
-          if (i == si) slot = slots[i];
-        if (slot < 0) continue;  // not stored
-        const long long page = slot / S.page_size, off = slot % S.page_size;
-        dst = (__nv_bfloat16*)S.slab + (((size_t)page * S.n_heads + hl) * S.page_size + off) * kHeadDim;
-      } else {
-        dst = (__nv_bfloat16*)S.dense_out + ((size_t)t * S.n_heads + hl) * kHeadDim;
-      }
-      uint4 pk;
-      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-      *reinterpret_cast<uint4*>(dst + l * 8) = pk;
-    }
-  }
-}
-
 }  // namespace ftk
 
 using namespace ftk;
@@ -389,21 +268,7 @@ extern "C" int ftk_norm_rope_store(const void* x, int dtype, int n_tokens, int r
       if (part.s[i].slot_map) part.s[i].slot_map += t0;
     }
     dim3 grid(bx, nt);
-    if (vec && nt >= kTokenKernelMin) {
-      const int lph = head_dim / 8;
-      const __nv_bfloat16* xs = (const __nv_bfloat16*)x + (size_t)t0 * row_elems;
-      const int32_t* ps = positions ? positions + t0 : nullptr;
-      note_variant("head norm + rotation + cache write: a block per token");
-      if (lph == 8)
-        FTK_LAUNCH(norm_rope_store_token_kernel<8>, nt, kWarpsPerBlock * 32, 0, s, xs, nt, row_elems, rotary_dim, ps,
-                   rope_table, max_pos, eps, gemma, part);
-      else if (lph == 16)
-        FTK_LAUNCH(norm_rope_store_token_kernel<16>, nt, kWarpsPerBlock * 32, 0, s, xs, nt, row_elems, rotary_dim, ps,
-                   rope_table, max_pos, eps, gemma, part);
-      else
-        FTK_LAUNCH(norm_rope_store_token_kernel<32>, nt, kWarpsPerBlock * 32, 0, s, xs, nt, row_elems, rotary_dim, ps,
-                   rope_table, max_pos, eps, gemma, part);
-    } else if (vec) {
+    if (vec) {
       note_variant("head norm + rotation + cache write: a warp per head, 16-byte accesses");
       const int lph = head_dim / 8, per_block = kWarpsPerBlock * (32 / lph);
       dim3 vgrid((sec.total_heads + per_block - 1) / per_block, nt);

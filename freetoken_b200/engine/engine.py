@@ -339,7 +339,8 @@ class Engine:
             return body()
         # one graph per batch size and metadata layout (the attention split count moves with the
         # longest request, which changes the size of the work list a few times over a long decode)
-        key = (S, tuple(arr.size for _, arr in builder.sections), tuple(sorted(map(repr, builder.plans))))
+        key = (S, tuple(arr.size for _, arr in builder.sections), tuple(sorted(map(repr, builder.plans))),
+               builder.longest_span())
         if key not in self.graphs:
             body()  # warm-up: allocates work buffers and library workspaces outside the capture
             torch.cuda.synchronize(self.device)

@@ -18,6 +18,7 @@ from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .engine import Engine
 from .scheduler import Scheduler
+from .status import StatusLine
 
 
 class LLM:
@@ -51,7 +52,8 @@ class LLM:
             sampling_params = [sampling_params] * len(prompts)
         if len(sampling_params) != len(prompts):
             raise ConfigError("one SamplingParams per prompt, or a single one for all")
-        sched = Scheduler(self.engine, self.sampler, self.eos_token_ids)
+        status = StatusLine(self.config.decode_log_interval) if self.config.decode_log_interval > 0 else None
+        sched = Scheduler(self.engine, self.sampler, self.eos_token_ids, status=status)
         for i, (p, sp) in enumerate(zip(prompts, sampling_params)):
             sched.add_request(self._ids(p), sp, rid=i)
         off = os.environ.get("FREETOKEN_DISABLE_OVERLAP_SCHEDULING", "").lower() in ("1", "true", "yes", "on")

@@ -75,9 +75,11 @@ class Flight:
 
 
 class Scheduler:
-    def __init__(self, engine, sampler, eos_token_ids: Sequence[int] = ()):
+    def __init__(self, engine, sampler, eos_token_ids: Sequence[int] = (), status=None):
+        """``status``: a :class:`freetoken_b200.engine.status.StatusLine` that is told of every resolved step."""
         self.engine = engine
         self.sampler = sampler
+        self.status = status
         self.eos = set(int(e) for e in eos_token_ids)
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []
@@ -202,7 +204,10 @@ class Scheduler:
                 for i, n in enumerate(req.reserved):
                     self.reserved[i] -= n
                 self.done[req.rid] = req
-        return StepReport(flight.entries, sampled, finished, flight.admitted)
+        report = StepReport(flight.entries, sampled, finished, flight.admitted)
+        if self.status is not None:
+            self.status.step(report, self)
+        return report
 
     def step(self) -> StepReport:
         """One step, launched and resolved (nothing stays in flight)."""

@@ -4,6 +4,7 @@
     python -m freetoken_b200.kernels.microbench attention --batch 8 --context 2048
     python -m freetoken_b200.kernels.microbench attention --prefill 2048
     python -m freetoken_b200.kernels.microbench sample --rows 8 --vocab 200064
+    python -m freetoken_b200.kernels.microbench few --tokens 1
     python -m freetoken_b200.kernels.microbench sparse --batch 8 --context 32768
     python -m freetoken_b200.kernels.microbench sparse --prefill 2048 --context 32768
 
@@ -149,6 +150,48 @@ def bench_attention(a) -> dict:
             "tensor_frac": round(flops / us / 1e6 / BF16_TFLOPS, 3)}
 
 
+def bench_few(a) -> dict:
+    """The few-token kernels (``csrc/gemv.cu``) at the headline sizes: the qkv and output projections of
+    ``--tokens`` tokens, and the routed gate/up and down products of their routes.  Six copies of the dense
+    weights and other experts every launch, so that every launch reads its weights from memory."""
+    dev = "cuda"
+    H, I, E, k, T = a.hidden, a.inter, a.experts, a.top_k, a.tokens
+    q_dim, kv_dim, copies = a.q_heads * a.head_dim, a.kv_heads * a.head_dim, 6
+    g = torch.Generator(device=dev).manual_seed(0)
+    wq = torch.empty(copies, q_dim + 2 * kv_dim, H, dtype=torch.bfloat16, device=dev).normal_(0, 0.02, generator=g)
+    wo = torch.empty(copies, H, q_dim, dtype=torch.bfloat16, device=dev).normal_(0, 0.02, generator=g)
+    w1 = torch.empty(E, 2 * I, H, dtype=torch.bfloat16, device=dev).normal_(0, 0.02, generator=g)
+    w2 = torch.empty(E, H, I, dtype=torch.bfloat16, device=dev).normal_(0, 0.02, generator=g)
+    x = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+    xo = torch.randn(T, q_dim, device=dev, generator=g).to(torch.bfloat16)
+    qkv = torch.empty(T, q_dim + 2 * kv_dim, dtype=torch.bfloat16, device=dev)
+    o = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    ids = [torch.stack([(torch.randperm(E, device=dev, generator=g)[:k]) for _ in range(T)]).to(torch.int32)
+           for _ in range(copies)]
+    wts = torch.rand(T, k, device=dev)
+    act = torch.empty(T * k, I, dtype=torch.bfloat16, device=dev)
+    y = torch.empty(T * k, H, dtype=torch.bfloat16, device=dev)
+    turn = [0]
+
+    def nxt():
+        turn[0] = (turn[0] + 1) % copies
+        return turn[0]
+
+    cases = (
+        ("qkv", lambda: ops.small_linear(x, wq[nxt()], qkv), (q_dim + 2 * kv_dim) * H * 2),
+        ("out_proj", lambda: ops.small_linear(xo, wo[nxt()], o), H * q_dim * 2),
+        ("gate_up", lambda: ops.moe_small_gate_up(x, ids[nxt()], w1, "silu", 1.702, 7.0, act), T * k * 2 * I * H * 2),
+        ("down", lambda: ops.moe_small_down(act, ids[nxt()], wts, w2, y), T * k * H * I * 2))
+    out = {}
+    for name, fn, nbytes in cases:
+        if a.only and a.only != name:
+            continue
+        us = _time(fn, a.iters, a.warmup, a.profile)
+        out[name] = {"us": round(us, 2), "weight_bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1),
+                     "hbm_frac": round(nbytes / us / 1e3 / HBM_GBS, 3)}
+    return out
+
+
 def bench_sparse(a) -> dict:
     """The block-sparse layer kind at its real geometry (the reference's M3: blocks of 128 keys, 16 chosen
     blocks, 64 query heads on 4 KV heads of 128, one shared index key of 128 per token): block selection
@@ -181,7 +224,11 @@ def bench_sparse(a) -> dict:
     sel = torch.empty(T, Hkv, topk, dtype=torch.int32, device=dev)
     max_blocks = -(-a.context // block)
     out = {}
-    us = _time(lambda: ops.sparse_select(iq, iks, bt, seg, len(segs), block, a.local, a.init, max_blocks, sel),
+    scores = None
+    if not a.no_tc and ops.sparse_score_fits(Hkv, Di, block):
+        scores = torch.empty(T, Hkv, max_blocks, dtype=torch.float32, device=dev)
+    us = _time(lambda: ops.sparse_select(iq, iks, bt, seg, len(segs), block, a.local, a.init, max_blocks, sel, scores,
+                                         live_blocks=-(-a.context // block)),
                a.iters, a.warmup, a.profile)
     index_bytes = sum(kv for _, kv in segs) * Di * 2
     flops = sum(2 * (ql * kv - ql * (ql - 1) // 2) * Hkv * Di for ql, kv in segs)
@@ -218,7 +265,7 @@ def bench_sample(a) -> dict:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="microbench")
     sub = ap.add_subparsers(dest="case", required=True)
-    for name in ("moe", "attention", "sample", "sparse"):
+    for name in ("moe", "attention", "sample", "sparse", "few"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=5)
@@ -242,6 +289,16 @@ def main(argv=None) -> int:
             p.add_argument("--no-tc", action="store_true", help="prefill on the mma.sync kernel instead of tcgen05")
             p.add_argument("--tc", action="store_true", help="decode on the tcgen05 kernel")
             p.add_argument("--pair", action="store_true", help="prefill on the tcgen05 kernel with two query tiles per CTA")
+        elif name == "few":
+            p.add_argument("--tokens", type=int, default=1)
+            p.add_argument("--hidden", type=int, default=3072)
+            p.add_argument("--inter", type=int, default=1536)
+            p.add_argument("--experts", type=int, default=256)
+            p.add_argument("--top-k", type=int, default=8)
+            p.add_argument("--q-heads", type=int, default=48)
+            p.add_argument("--kv-heads", type=int, default=8)
+            p.add_argument("--head-dim", type=int, default=128)
+            p.add_argument("--only", choices=["qkv", "out_proj", "gate_up", "down"], default=None)
         elif name == "sparse":
             p.add_argument("--batch", type=int, default=8)
             p.add_argument("--context", type=int, default=32768)
@@ -254,12 +311,13 @@ def main(argv=None) -> int:
             p.add_argument("--topk", type=int, default=16)
             p.add_argument("--local", type=int, default=1)
             p.add_argument("--init", type=int, default=0)
+            p.add_argument("--no-tc", action="store_true", help="block scores by a CTA per token and head instead of mma.sync")
         else:
             p.add_argument("--rows", type=int, default=8)
             p.add_argument("--vocab", type=int, default=200064)
             p.add_argument("--temperature", type=float, default=0.0)
     a = ap.parse_args(argv)
-    res = {"moe": bench_moe, "attention": bench_attention, "sample": bench_sample, "sparse": bench_sparse}[a.case](a)
+    res = {"moe": bench_moe, "attention": bench_attention, "sample": bench_sample, "sparse": bench_sparse, "few": bench_few}[a.case](a)
     print(json.dumps({"case": a.case, **{k: v for k, v in vars(a).items() if k != "case"}, "result": res}))
     return 0
 

@@ -75,7 +75,8 @@ _SIGNATURES = {
                                     _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "ftk_paged_attention_sparse": [_vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
                                    _i, _i, _i, _i, _i, _i, _f, _vp, _i, _i, _vp],
-    "ftk_sparse_select": [_vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "ftk_sparse_select": [_vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
+    "ftk_sparse_score_fits": [_i, _i, _i],
     "ftk_router_topk": [_vp, _vp, _i, _i, _i, _i, _f, _vp, _vp, _vp],
     "ftk_moe_permute": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp],
     "ftk_moe_route_fits": [_i, _i, _i, _i],
@@ -424,27 +425,40 @@ def attention_tc_fits(head_dim: int, page_size: int, group: int) -> bool:
     return bool(_lib().ftk_attention_tc_fits(head_dim, page_size, group))
 
 
+def sparse_score_fits(n_heads: int, dim: int, block_size: int) -> bool:
+    """Whether bfloat16 block scores of these sizes are taken on the tensor cores (given a ``scores`` scratch)."""
+    return bool(_lib().ftk_sparse_score_fits(n_heads, dim, block_size))
+
+
 def sparse_select(iq: torch.Tensor, ik_slab: torch.Tensor, block_table: torch.Tensor, seg_info: torch.Tensor,
                   n_segs: int, block_size: int, local_blocks: int, init_blocks: int, max_blocks: int,
-                  sel: torch.Tensor) -> None:
+                  sel: torch.Tensor, scores: Optional[torch.Tensor] = None, live_blocks: int = 0) -> None:
     """Key blocks each new token of a block-sparse layer attends to.
 
     ``iq [T, Hi, Di]`` index queries, ``ik_slab [pages, 1, page_size, Di]`` cached index keys.  A
     block's score is the largest ``iq . ik`` over its visible positions; the first ``init_blocks``
     and the newest ``local_blocks`` blocks are always taken; the ``min(topk, visible)`` best go to
     ``sel [T, Hi, topk]`` in ascending order, padded with -1.  ``max_blocks`` bounds the blocks of
-    the longest request (sizes the kernel's shared memory)."""
+    the longest request (sizes the kernel's shared memory).  ``scores [T, Hi, max_blocks]`` float32 scratch lets
+    bfloat16 scores be contracted on the tensor cores (:func:`sparse_score_fits`), every key read once per
+    tile of tokens; without it a CTA per token and head walks the blocks.  ``live_blocks`` (0 = ``max_blocks``):
+    blocks that the longest request of this step can hold, which bounds the launch; a step replayed from a
+    CUDA graph must give a bound that holds for every replay."""
     T, Hi, Di = iq.shape
     pages, one, P, Di2 = ik_slab.shape
     if one != 1 or Di2 != Di or ik_slab.dtype != iq.dtype:
         raise KernelError("sparse_select: ik_slab must be [pages, 1, page_size, Di] of iq's dtype")
     if sel.dim() != 3 or sel.shape[0] < T or sel.shape[1] != Hi:
         raise KernelError("sparse_select: sel must be [T, Hi, topk]")
+    if scores is not None and (scores.dtype != torch.float32 or scores.numel() < T * Hi * max_blocks):
+        raise KernelError("sparse_select: scores must hold [T, Hi, max_blocks] float32")
     _check(_lib().ftk_sparse_select(_dev(iq, "iq"), _dev(ik_slab, "ik_slab"), _code(iq, "iq"),
                                     _dev(block_table, "block_table", torch.int32), block_table.shape[1],
                                     _dev(seg_info, "seg_info", torch.int32), n_segs, T, Hi, Di, P, pages,
                                     int(block_size), sel.shape[2], int(local_blocks), int(init_blocks),
-                                    int(max_blocks), _dev(sel, "sel", torch.int32), _stream()), "sparse_select")
+                                    int(max_blocks), int(live_blocks), _dev(sel, "sel", torch.int32),
+                                    _dev(scores, "scores", torch.float32), _stream()), "sparse_select",
+           2 if scores is not None else 1)
 
 
 # --------------------------------------------------------------------------- experts

@@ -23,7 +23,7 @@ import torch
 from ..config.spec import ModelSpec, ParamSpec, PartSpec
 from ..errors import ConfigError
 from ..parts import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, BuildEnv, Part, StepState
-from ..parts.base import as_rows
+from ..parts.base import as_rows, nvtx_range
 
 
 def _walk(prefix: str, part: Part, out: Dict[str, Tuple[Part, str, ParamSpec]]) -> None:
@@ -138,7 +138,8 @@ class Model:
         self.embedding.forward(step.token_ids, residual)
         x = None
         for i, e in enumerate(self.spec.schedule):
-            x = self.blocks[e.layer].forward(x, residual, step, cache_views[i], e.cache_from is None)
+            with nvtx_range(f"layer {e.layer}"):
+                x = self.blocks[e.layer].forward(x, residual, step, cache_views[i], e.cache_from is None)
         R = step.n_logit_rows
         if R == 0:
             return torch.empty((0, self.vocab), dtype=torch.float32, device=env.device)
@@ -148,6 +149,7 @@ class Model:
         else:  # grows with the largest request for logits seen so far
             logits = ws.get("model.logits", (R, self.vocab), torch.float32)
         y = ws.get("model.final", (R, self.hidden), dt, (cap, self.hidden))
-        self.final_norm.add_forward(as_rows(x, self.final_norm), residual, y, rows=step.logit_rows)
-        self.head.forward(y, logits)
+        with nvtx_range("final norm + head"):
+            self.final_norm.add_forward(as_rows(x, self.final_norm), residual, y, rows=step.logit_rows)
+            self.head.forward(y, logits)
         return logits

@@ -61,6 +61,33 @@ class PartRegistry(Generic[T]):
         return sorted(self._classes)
 
 
+_NVTX: Optional[bool] = None
+
+
+class nvtx_range:
+    """``with nvtx_range("layer 3"):`` marks a stretch of host work (and the launches it makes) for a
+    profiler's timeline when ``FREETOKEN_NVTX=1`` is set, and does nothing otherwise.  The reference marks
+    its layers the same way (python/freetoken/utils/torch_utils.py:23-37)."""
+
+    def __init__(self, name: str):
+        global _NVTX
+        if _NVTX is None:
+            import os
+
+            _NVTX = os.environ.get("FREETOKEN_NVTX", "").lower() in ("1", "true", "yes", "on") and torch.cuda.is_available()
+        self.name = name if _NVTX else None
+
+    def __enter__(self):
+        if self.name is not None:
+            torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        if self.name is not None:
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
 MIXERS: PartRegistry = PartRegistry("mixer")
 FEED_FORWARDS: PartRegistry = PartRegistry("feed-forward")
 NORMS: PartRegistry = PartRegistry("norm")

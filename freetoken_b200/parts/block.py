@@ -13,7 +13,7 @@ from typing import Any, Dict, Optional
 import torch
 
 from ..config.spec import PartSpec
-from .base import BLOCKS, NORMS, Block, BuildEnv, FeedForward, Mixer, Part, StepState, as_rows
+from .base import BLOCKS, NORMS, Block, BuildEnv, FeedForward, Mixer, Part, StepState, as_rows, nvtx_range
 
 
 @BLOCKS.register("prenorm_residual")
@@ -44,11 +44,13 @@ class PreNormResidualBlock(Block):
         ws, dt, cap = self.env.workspace, self.env.dtype, self.env.max_step_tokens
         h = ws.get("block.h", (T, self.hidden), dt, (cap, self.hidden))
         self.input_norm.add_forward(as_rows(x, self.input_norm), residual, h)
-        a = self.mixer.forward(h, step, cache, writes_cache)
+        with nvtx_range(f"mixer {self.mixer.kind}"):
+            a = self.mixer.forward(h, step, cache, writes_cache)
         h2 = ws.get("block.h2", (T, self.hidden), dt, (cap, self.hidden))
         h32 = None
         if self.ffn.wants_f32_input and dt != torch.float32:
             h32 = ws.get("block.h2_f32", (T, self.hidden), torch.float32, (cap, self.hidden))
         self.post_norm.add_forward(a, residual, h2, out_f32=h32)
         lazy = getattr(self.ffn, "forward_lazy", None)
-        return lazy(h2, step, h_f32=h32) if lazy is not None else self.ffn.forward(h2, step, h_f32=h32)
+        with nvtx_range(f"feed-forward {self.ffn.kind}"):
+            return lazy(h2, step, h_f32=h32) if lazy is not None else self.ffn.forward(h2, step, h_f32=h32)

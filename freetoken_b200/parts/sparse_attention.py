@@ -63,7 +63,8 @@ class BlockSparseAttention(GQAttention):
 
     def workspace_bytes(self, n_tokens: int) -> int:
         item = 4 if self.env.dtype == torch.float32 else 2
-        index = n_tokens * ((2 * self.n_index_heads + 1) * self.index_dim * item + self.n_kv_heads * self.topk_blocks * 4)
+        index = n_tokens * ((2 * self.n_index_heads + 1) * self.index_dim * item + self.n_kv_heads * self.topk_blocks * 4
+                            + self.n_index_heads * -(-self.env.max_seq_len // self.block_size) * 4)  # (+ block scores)
         return super().workspace_bytes(n_tokens) + index
 
     def plan_key(self, decode_only: bool = False):
@@ -71,6 +72,9 @@ class BlockSparseAttention(GQAttention):
                 self.topk_blocks)
 
     def prepare(self, builder) -> None:
+        # the longest request's length rounded up to a power of two: what a step replayed from a graph may
+        # depend on (the engine records a new graph when it changes)
+        self._span = builder.longest_span()
         builder.sparse_attention_plan(self.group, 16, self.n_kv_heads, self.head_dim, self.block_size,
                                       self.topk_blocks)
 
@@ -109,8 +113,12 @@ class BlockSparseAttention(GQAttention):
         # which key blocks each token reads, then attention over those
         sel = ws.get("attn.sel", (T, Hkv, self.topk_blocks), torch.int32, (cap, Hkv, self.topk_blocks))
         max_blocks = -(-self.env.max_seq_len // self.block_size)
+        scores = None
+        if dt == torch.bfloat16 and ops.sparse_score_fits(Hi, self.index_dim, self.block_size):
+            scores = ws.get("attn.block_scores", (T, Hi, max_blocks), torch.float32, (cap, Hi, max_blocks))
         ops.sparse_select(iq, cache.slabs["index_k"], cache.block_table, step.seg_info, len(step.segments),
-                          self.block_size, self.local_blocks, self.init_blocks, max_blocks, sel)
+                          self.block_size, self.local_blocks, self.init_blocks, max_blocks, sel, scores,
+                          live_blocks=min(max_blocks, -(-self._span // self.block_size)))
         plan = step.attention_plans[self.plan_key()]
         o = ws.get("attn.o", (T, Hq, D), dt, (cap, Hq, D))
         ops.paged_attention(q, cache.slabs["k"], cache.slabs["v"], cache.block_table, step.seg_info,

@@ -136,7 +136,12 @@ def paged_attention(q, k_slab, v_slab, block_table, seg_info, n_segs, items, n_i
             out[q_start + t] = o.reshape(Hq, D).to(out.dtype)
 
 
-def sparse_select(iq, ik_slab, block_table, seg_info, n_segs, block_size, local_blocks, init_blocks, max_blocks, sel):
+def sparse_score_fits(n_heads, dim, block_size):
+    return False
+
+
+def sparse_select(iq, ik_slab, block_table, seg_info, n_segs, block_size, local_blocks, init_blocks, max_blocks, sel,
+                  scores=None, live_blocks=0):
     T, Hi, Di = iq.shape
     P = ik_slab.shape[2]
     topk = sel.shape[2]
@@ -270,7 +275,7 @@ def sample(logits, temperature, top_k, top_p, u, out):
         out[r] = idx
 
 
-ALL = ["moe_small_fits", "copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "add_rmsnorm_routes", "act_and_mul", "cast", "table_update", "norm_rope_store",
+ALL = ["sparse_score_fits", "moe_small_fits", "copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "add_rmsnorm_routes", "act_and_mul", "cast", "table_update", "norm_rope_store",
        "paged_attention", "router_topk", "moe_permute", "moe_route", "moe_route_fits", "linear", "attention_tc_fits", "moe_gather", "moe_gemm1_act", "moe_gemm2",
        "moe_combine", "sample"]
 

@@ -145,7 +145,7 @@ def make_rope(max_pos, rd, theta=10000.0):
     (7, 1, 48, 24, 4, True, True), (6, 3, 32, 32, 8, False, False), (48, 8, 128, 64, 16, True, True),
     (5, 5, 80, 16, 3, True, True), (2, 2, 256, 128, 16, False, True), (5, 3, 64, 16, 5, True, True),
     (7, 3, 128, 0, 4, True, True), (5, 1, 128, 128, 8, False, True), (3, 2, 64, 64, 4, True, False)])
-@pytest.mark.parametrize("T", [21, 150])  # (from 64 tokens on, bfloat16 heads of 64/128/256 take the block-per-token kernel)
+@pytest.mark.parametrize("T", [21, 150])
 def test_norm_rope_store(dtype, Hq, Hkv, D, rd, P, gemma, norm, T):
     pages = -(-T // P) + 9
     x = rnd(T, (Hq + 2 * Hkv) * D, dtype=dtype)

@@ -213,3 +213,27 @@ def test_windowed_groups_are_reserved_at_their_peak(setup, tmp_path_factory):
     # a step size whose peak the pool cannot hold is answered with an error, not admitted to fail later
     refused, _, _ = run(pages=6, max_step=64, prompts=prompts[:1])
     assert refused[0].finish_reason == "error" and "pages" in refused[0].error
+
+
+def test_status_lines_in_the_references_words(setup):
+    """A line per step that reads prompt tokens, and one every ``decode_log_interval`` decode steps."""
+    from freetoken_b200.engine.status import StatusLine
+
+    sched, plain = setup(max_step=16)
+    lines, t = [], [0.0]
+
+    def clock():
+        t[0] += 0.5
+        return t[0]
+
+    sched.status = StatusLine(decode_log_interval=3, log=lines.append, clock=clock)
+    V = plain.cfg.vocab
+    for n in (5, 30):
+        sched.add_request(tokens_for(V, n, n), SamplingParams(max_tokens=7))
+    sched.run(overlap=False)
+    prefill = [l for l in lines if l.startswith("Prefill batch")]
+    decode = [l for l in lines if l.startswith("Decode batch")]
+    assert len(prefill) == 3 and "#new-token: 16" in prefill[0] and "#new-seq: 2" in prefill[0]  # 5 + 11, then 15, then 4
+    assert "#queue-req: 0" in prefill[0] and "input throughput (token/s):" in prefill[0]
+    assert len(decode) >= 2 and "gen throughput (token/s):" in decode[0] and "#running-req:" in decode[0]
+    assert "token usage: 0." in decode[0]
