@@ -409,7 +409,8 @@ extern "C" int ftk_sparse_select(const void* iq, const void* ik_slab, int dtype,
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     int bpc = (int)(((long long)tiles * live + 3LL * sms - 1) / (3LL * sms));
-    bpc = bpc < kScoreBlocksMin ? kScoreBlocksMin : (bpc > 64 ? 64 : bpc);
+    // (much work, as in a long portion of a prompt, is better cut finely: its CTAs then even out by themselves)
+    bpc = bpc < kScoreBlocksMin || bpc > 16 ? kScoreBlocksMin : bpc;
     dim3 sgrid((live + bpc - 1) / bpc, tiles);
     const size_t ssmem = (size_t)2 * block_size * (dim + 8) * sizeof(__nv_bfloat16);
     note_variant("block scores: mma.sync contraction, a block of keys per turn");
