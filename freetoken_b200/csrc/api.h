@@ -66,6 +66,15 @@ int ftk_paged_attention_tc(const void* q, const void* k_slab, const void* v_slab
                            float* part_o, float* part_ml, int n_slots, void* out, int n_tokens, int n_q_heads,
                            int n_kv_heads, int head_dim, int page_size, int num_pages, float scale, int window,
                            void* stream);
+// Decode steps in bfloat16 on the same kernel with tiles of at most 16 query rows (plan the items with
+// tile_rows = 16 and key pieces that are multiples of 128; at most 16 query heads per KV head): one
+// warp takes the softmax of the tile's rows.  part_o [slots, Hkv, 16, 128], part_ml [slots, Hkv, 16, 2].
+int ftk_attention_tc_few_fits(int head_dim, int page_size, int group);
+int ftk_paged_attention_tc_few(const void* q, const void* k_slab, const void* v_slab, const int32_t* block_table,
+                               int bt_stride, const int32_t* seg_info, int n_segs, const int32_t* items, int n_items,
+                               float* part_o, float* part_ml, int n_slots, void* out, int n_tokens, int n_q_heads,
+                               int n_kv_heads, int head_dim, int page_size, int num_pages, float scale, int window,
+                               void* stream);
 int ftk_paged_attention_sparse(const void* q, const void* k_slab, const void* v_slab, int dtype,
                                const int32_t* block_table, int bt_stride, const int32_t* seg_info, int n_segs,
                                const int32_t* items, int n_items, float* part_o, float* part_ml, int n_slots,

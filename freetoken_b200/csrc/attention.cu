@@ -902,21 +902,31 @@ extern "C" int ftk_attention_tc_fits(int head_dim, int page_size, int group) {
   return attention_tc_fits(head_dim, page_size, group) ? 1 : 0;
 }
 
+extern "C" int ftk_attention_tc_few_fits(int head_dim, int page_size, int group) {
+  return attention_tc_few_fits(head_dim, page_size, group) ? 1 : 0;
+}
+
+enum TcForm { kTcSingle = 0, kTcPair = 1, kTcFew = 2 };
+
 // bfloat16 steps on the tensor-core kernels: tiles of 128 query rows (`items` planned for tile_rows =
-// 128), or pieces of two such tiles (`pair`, planned for tile_rows = 256); `n_tokens` is the number of
-// rows of q.
+// 128), pieces of two such tiles (planned for tile_rows = 256), or tiles of at most 16 rows (decode
+// steps; planned for tile_rows = 16 and key pieces that are multiples of 128); `n_tokens` is the number
+// of rows of q.
 static int paged_attention_tc_impl(const void* q, const void* k_slab, const void* v_slab,
                                    const int32_t* block_table, int bt_stride, const int32_t* seg_info,
                                    int n_segs, const int32_t* items, int n_items, float* part_o, float* part_ml,
                                    int n_slots, void* out, int n_tokens, int n_q_heads, int n_kv_heads,
                                    int head_dim, int page_size, int num_pages, float scale, int window,
-                                   void* stream, bool pair) {
+                                   void* stream, TcForm form) {
+  const bool pair = form == kTcPair, few = form == kTcFew;
   FTK_REQUIRE(q && k_slab && v_slab && block_table && seg_info && items && out, "paged_attention_tc: null pointer");
   FTK_REQUIRE(n_q_heads >= 1 && n_kv_heads >= 1 && n_q_heads % n_kv_heads == 0, "paged_attention_tc: %d query heads, %d KV heads",
               n_q_heads, n_kv_heads);
   FTK_REQUIRE(attention_tc_fits(head_dim, page_size, n_q_heads / n_kv_heads),
               "paged_attention_tc: head size %d, pages of %d, %d heads per KV head: takes head size 128, pages of a "
               "multiple of 16, at most 128 heads per KV head", head_dim, page_size, n_q_heads / n_kv_heads);
+  FTK_REQUIRE(!few || attention_tc_few_fits(head_dim, page_size, n_q_heads / n_kv_heads),
+              "paged_attention_tc: tiles of 16 rows take at most 16 heads per KV head, got %d", n_q_heads / n_kv_heads);
   FTK_REQUIRE(n_tokens >= 1 && n_items >= 0 && n_segs >= 1 && num_pages >= 1 && bt_stride >= 1,
               "paged_attention_tc: bad sizes");
   FTK_REQUIRE(window == 0, "paged_attention_tc: layers with a window run on the other kernels");
@@ -930,10 +940,12 @@ static int paged_attention_tc_impl(const void* q, const void* k_slab, const void
   p.seg_info = seg_info; p.n_segs = n_segs; p.items = items; p.n_items = n_items;
   p.part_o = part_o; p.part_ml = part_ml; p.n_slots = n_slots;
   p.Hq = n_q_heads; p.Hkv = n_kv_heads; p.G = n_q_heads / n_kv_heads; p.D = head_dim; p.P = page_size;
-  p.num_pages = num_pages; p.tile_rows = pair ? 2 * kTcRows : kTcRows; p.scale = scale; p.window = window;
+  p.num_pages = num_pages; p.tile_rows = pair ? 2 * kTcRows : few ? kTcFewRows : kTcRows; p.scale = scale; p.window = window;
   p.sel = nullptr; p.sel_stride = 0; p.block_size = 0; p.arrivals = nullptr;
   cudaStream_t s = (cudaStream_t)stream;
-  note_variant(pair ? "attention: tcgen05, two 128-row query tiles per CTA" : "attention: tcgen05, 128-row query tiles");
+  note_variant(pair ? "attention: tcgen05, two 128-row query tiles per CTA"
+               : few ? "attention: tcgen05, tiles of at most 16 rows, one softmax warp"
+                     : "attention: tcgen05, 128-row query tiles");
   const int rc = pair ? launch_attention_tc2(p, n_tokens, s) : launch_attention_tc(p, n_tokens, s);
   FTK_REQUIRE(rc == 0, "paged_attention_tc: cannot set up the kernel (%d)", rc);
   FTK_LAUNCH_CHECK("paged_attention_tc");
@@ -953,7 +965,7 @@ extern "C" int ftk_paged_attention_tc(const void* q, const void* k_slab, const v
                                       void* stream) {
   return paged_attention_tc_impl(q, k_slab, v_slab, block_table, bt_stride, seg_info, n_segs, items, n_items, part_o,
                                  part_ml, n_slots, out, n_tokens, n_q_heads, n_kv_heads, head_dim, page_size, num_pages,
-                                 scale, window, stream, false);
+                                 scale, window, stream, kTcSingle);
 }
 
 extern "C" int ftk_paged_attention_tc_pair(const void* q, const void* k_slab, const void* v_slab,
@@ -964,7 +976,18 @@ extern "C" int ftk_paged_attention_tc_pair(const void* q, const void* k_slab, co
                                            int window, void* stream) {
   return paged_attention_tc_impl(q, k_slab, v_slab, block_table, bt_stride, seg_info, n_segs, items, n_items, part_o,
                                  part_ml, n_slots, out, n_tokens, n_q_heads, n_kv_heads, head_dim, page_size, num_pages,
-                                 scale, window, stream, true);
+                                 scale, window, stream, kTcPair);
+}
+
+extern "C" int ftk_paged_attention_tc_few(const void* q, const void* k_slab, const void* v_slab,
+                                          const int32_t* block_table, int bt_stride, const int32_t* seg_info,
+                                          int n_segs, const int32_t* items, int n_items, float* part_o, float* part_ml,
+                                          int n_slots, void* out, int n_tokens, int n_q_heads, int n_kv_heads,
+                                          int head_dim, int page_size, int num_pages, float scale, int window,
+                                          void* stream) {
+  return paged_attention_tc_impl(q, k_slab, v_slab, block_table, bt_stride, seg_info, n_segs, items, n_items, part_o,
+                                 part_ml, n_slots, out, n_tokens, n_q_heads, n_kv_heads, head_dim, page_size, num_pages,
+                                 scale, window, stream, kTcFew);
 }
 
 static int paged_attention_impl(const void* q, const void* k_slab, const void* v_slab, int dtype,

@@ -17,6 +17,11 @@
 // 2-5 are the softmax (and the epilogue: O / l to the output, or the partial sums of a split tile for
 // the merge kernel).  A CTA works through its share of the work list; the three roles run through it on
 // their own, so the loads and the first product of a piece run under the end of the piece before.
+// Decode steps (FEW = true) have at most 16 live rows in a tile: `group` query heads of one or a few
+// tokens.  A row per thread would leave one thread per live row with 128 exponentials a key tile, which
+// then sets the pace (1.5 us a tile, 45 GB/s per SM).  There, ONE warp takes rows 0-15 with the
+// 16-lane shapes of tcgen05.ld / st, which spread a row's columns over four threads (the layout of an
+// mma.sync accumulator fragment); the other three softmax warps have nothing to do.
 // Every wait is bounded; a timeout records a code in g_attn_status, lets copies land, frees TMEM, returns.
 // Value rows past the end of the request are never multiplied as they lie in memory (they may hold
 // anything): whole 16-key boxes past the end are not loaded, and all rows of the stage past the end
@@ -81,6 +86,37 @@ __device__ __forceinline__ void tmem_st16u(uint32_t addr, const uint32_t (&v)[16
         "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
       : "memory");
 }
+// Rows 0-15 of the warp's quadrant, 32 columns from `addr`: thread t gets rows t / 4 and t / 4 + 8; of the
+// i-th group of 8 columns it holds columns 8 i + 2 (t % 4) and the next one: r[4 i], r[4 i + 1] of its
+// first row and r[4 i + 2], r[4 i + 3] of its second.  Completed by tmem_ld_wait().
+__device__ __forceinline__ void tmem_ld_16rows_32cols(uint32_t addr, float* r) {
+  uint32_t u[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]),
+        "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
+      : "r"(addr) : "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) r[i] = __uint_as_float(u[i]);
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st_16rows_32cols(uint32_t addr, const float* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(addr), "r"(__float_as_uint(r[0])), "r"(__float_as_uint(r[1])), "r"(__float_as_uint(r[2])),
+        "r"(__float_as_uint(r[3])), "r"(__float_as_uint(r[4])), "r"(__float_as_uint(r[5])), "r"(__float_as_uint(r[6])),
+        "r"(__float_as_uint(r[7])), "r"(__float_as_uint(r[8])), "r"(__float_as_uint(r[9])), "r"(__float_as_uint(r[10])),
+        "r"(__float_as_uint(r[11])), "r"(__float_as_uint(r[12])), "r"(__float_as_uint(r[13])),
+        "r"(__float_as_uint(r[14])), "r"(__float_as_uint(r[15]))
+      : "memory");
+}
+// The same rows, sixteen 32-bit columns from `addr` (the probabilities as bfloat16 pairs): of the i-th
+// group of 4 columns thread t holds column 4 i + t % 4: w[2 i] of its first row, w[2 i + 1] of its second.
+__device__ __forceinline__ void tmem_st_16rows_16words(uint32_t addr, const uint32_t* w) {
+  asm volatile("tcgen05.st.sync.aligned.16x128b.x4.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -107,6 +143,203 @@ __device__ __forceinline__ uint32_t tc_pack(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&t);
 }
 
+// Softmax and epilogue of a tile's rows 0..15 by one warp (the warp of TMEM lanes 0..31), for tiles
+// that have no more rows: thread t has rows t / 4 and t / 4 + 8 and a quarter of their columns.
+__device__ __forceinline__ void attention_tc_few_rows(const AttnParams& p, uint32_t tmem, int lane, int n_work, int n_rounds,
+                                                      uint64_t* s_full, uint64_t* s_empty, uint64_t* p_full,
+                                                      uint64_t* pv_done, uint64_t* o_free, volatile int* abortp,
+                                                      int* abort_flag) {
+  const int G = p.G;
+  const float sl2 = p.scale * 1.4426950408889634f;
+  const int ra = lane >> 2, rb = ra + 8, cq = lane & 3;
+  auto fail = [&](int code) {
+    atomicCAS(&g_attn_status[0], 0, code);
+    *abort_flag = 1;
+  };
+  bool ok = true;
+  int g0 = 0;  // tiles of the pieces before this one
+  for (int i_round = 0; i_round < n_rounds && ok; ++i_round) {
+    const int w = i_round * (int)gridDim.x + ((i_round & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
+    if (w >= n_work) continue;
+    const Item it = load_item(p, p.n_items - 1 - w / p.Hkv);
+    const int kvh = w % p.Hkv;
+    const int n_tiles = it.ok ? (it.ke - it.kb + kTcKeys - 1) / kTcKeys : 0;
+    const int R = it.ok ? it.ntok * G : 0;
+    const int pos_base = it.kv_len - it.q_len + it.tok0;
+    // last key a row may read; rows that the tile does not have are never stored and need no mask
+    const int hi_a = ra < R ? min(it.ke - 1, pos_base + ra / G) : 0x7fffffff;
+    const int hi_b = rb < R ? min(it.ke - 1, pos_base + rb / G) : 0x7fffffff;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int g = g0 + j, sb = g & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb], (uint32_t)((g >> 1) & 1), abortp))) {
+        if (lane == 0) fail(206);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      float v[64];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) tmem_ld_16rows_32cols(tmem + (uint32_t)(sb * kTcKeys + 32 * k), v + 16 * k);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[sb]);  // the next product may overwrite this buffer
+      const int key0 = it.kb + j * kTcKeys;
+      const bool interior = __all_sync(0xffffffffu, key0 + kTcKeys - 1 <= min(hi_a, hi_b));
+      if (!interior) {
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+          const int c = key0 + 8 * q + 2 * cq;
+          if (c > hi_a) v[4 * q] = -INFINITY;
+          if (c + 1 > hi_a) v[4 * q + 1] = -INFINITY;
+          if (c > hi_b) v[4 * q + 2] = -INFINITY;
+          if (c + 1 > hi_b) v[4 * q + 3] = -INFINITY;
+        }
+      }
+      float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+      for (int q = 0; q < 16; ++q) {
+        mx_a = fmaxf(mx_a, fmaxf(v[4 * q], v[4 * q + 1]));
+        mx_b = fmaxf(mx_b, fmaxf(v[4 * q + 2], v[4 * q + 3]));
+      }
+      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2)) * sl2;  // the scale is positive
+      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2)) * sl2;
+      // move a row's running maximum only when it grew by more than 8 (or is not set yet)
+      float al_a = 1.f, al_b = 1.f;
+      if (mx_a > m_a + 8.f || (m_a == -INFINITY && mx_a > -INFINITY)) {
+        al_a = m_a == -INFINITY ? 0.f : tc_exp2(m_a - mx_a);
+        m_a = mx_a;
+      }
+      if (mx_b > m_b + 8.f || (m_b == -INFINITY && mx_b > -INFINITY)) {
+        al_b = m_b == -INFINITY ? 0.f : tc_exp2(m_b - mx_b);
+        m_b = mx_b;
+      }
+      l_a *= al_a;
+      l_b *= al_b;
+      const bool rescale = __any_sync(0xffffffffu, al_a != 1.f || al_b != 1.f) && j > 0;
+      if (g >= 2) {  // the product two tiles back has read the P buffer this tile writes
+        if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[sb], (uint32_t)(((g - 2) >> 1) & 1), abortp))) {
+          if (lane == 0) fail(207);
+          ok = false;
+          break;
+        }
+      }
+      if (rescale) {  // O must hold every product so far before it is scaled
+        if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[sb ^ 1], (uint32_t)(((g - 1) >> 1) & 1), abortp))) {
+          if (lane == 0) fail(209);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+#pragma unroll 1
+        for (int k = 0; k < 4; ++k) {
+          float o[16];
+          tmem_ld_16rows_32cols(tmem + (uint32_t)(2 * kTcKeys + 32 * k), o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            o[4 * i] *= al_a; o[4 * i + 1] *= al_a;
+            o[4 * i + 2] *= al_b; o[4 * i + 3] *= al_b;
+          }
+          tmem_st_16rows_32cols(tmem + (uint32_t)(2 * kTcKeys + 32 * k), o);
+        }
+        tmem_st_wait();
+      }
+      const float mb_a = m_a == -INFINITY ? 0.f : m_a, mb_b = m_b == -INFINITY ? 0.f : m_b;
+      float sum_a = 0.f, sum_b = 0.f;
+      // probabilities as bfloat16 pairs into rows 0..15 of the A operand in tensor memory
+      const uint32_t p_addr = tmem + (uint32_t)(kTcPCol + sb * (kTcKeys / 2));
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        uint32_t wds[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int x = 16 * k + 4 * i;
+          const float a0 = tc_exp2(fmaf(v[x], sl2, -mb_a)), a1 = tc_exp2(fmaf(v[x + 1], sl2, -mb_a));  // exp2(-inf) = 0
+          const float b0 = tc_exp2(fmaf(v[x + 2], sl2, -mb_b)), b1 = tc_exp2(fmaf(v[x + 3], sl2, -mb_b));
+          sum_a += a0 + a1;
+          sum_b += b0 + b1;
+          wds[2 * i] = tc_pack(a0, a1);
+          wds[2 * i + 1] = tc_pack(b0, b1);
+        }
+        tmem_st_16rows_16words(p_addr + (uint32_t)(16 * k), wds);
+      }
+      l_a += sum_a;
+      l_b += sum_b;
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[sb]);
+    }
+    if (!ok) break;
+    // ---- epilogue
+    if (n_tiles > 0) {
+      const int gl = g0 + n_tiles - 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[gl & 1], (uint32_t)((gl >> 1) & 1), abortp))) {
+        if (lane == 0) fail(208);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+    }
+    // a row's sum: over the four threads that share it
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    if (it.ok) {
+      const bool live = n_tiles > 0;
+      const float inv_a = live && l_a > 0.f ? 1.f / l_a : 0.f, inv_b = live && l_b > 0.f ? 1.f / l_b : 0.f;
+      const int tok_a = it.q_start + it.tok0 + ra / G, tok_b = it.q_start + it.tok0 + rb / G;
+      __nv_bfloat16* dst_a = (__nv_bfloat16*)p.out + ((size_t)tok_a * p.Hq + kvh * G + ra % G) * kTcD;
+      __nv_bfloat16* dst_b = (__nv_bfloat16*)p.out + ((size_t)tok_b * p.Hq + kvh * G + rb % G) * kTcD;
+      const size_t slot0 = ((size_t)(it.base + it.split) * p.Hkv + kvh) * p.tile_rows;
+#pragma unroll 1
+      for (int k = 0; k < 4; ++k) {
+        float o[16];
+        if (live) {
+          tmem_ld_16rows_32cols(tmem + (uint32_t)(2 * kTcKeys + 32 * k), o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) o[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int col = 32 * k + 8 * i + 2 * cq;
+          if (it.nsplit == 1) {
+            if (ra < R) *reinterpret_cast<uint32_t*>(dst_a + col) = tc_pack(o[4 * i] * inv_a, o[4 * i + 1] * inv_a);
+            if (rb < R) *reinterpret_cast<uint32_t*>(dst_b + col) = tc_pack(o[4 * i + 2] * inv_b, o[4 * i + 3] * inv_b);
+          } else {
+            if (ra < R) *reinterpret_cast<float2*>(p.part_o + (slot0 + ra) * kTcD + col) = make_float2(o[4 * i], o[4 * i + 1]);
+            if (rb < R) *reinterpret_cast<float2*>(p.part_o + (slot0 + rb) * kTcD + col) = make_float2(o[4 * i + 2], o[4 * i + 3]);
+          }
+        }
+      }
+      if (it.nsplit > 1 && cq == 0) {
+        if (ra < R) {
+          p.part_ml[(slot0 + ra) * 2] = m_a == -INFINITY ? -INFINITY : m_a * 0.6931471805599453f;
+          p.part_ml[(slot0 + ra) * 2 + 1] = live ? l_a : 0.f;
+        }
+        if (rb < R) {
+          p.part_ml[(slot0 + rb) * 2] = m_b == -INFINITY ? -INFINITY : m_b * 0.6931471805599453f;
+          p.part_ml[(slot0 + rb) * 2 + 1] = live ? l_b : 0.f;
+        }
+      }
+    }
+    if (n_tiles > 0) {  // the output accumulator has been read: the next piece's first product may overwrite it
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(o_free);
+    }
+    g0 += n_tiles;
+  }
+}
+
+template <bool FEW>
 __global__ void __launch_bounds__(kTcThreads)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, AttnParams p) {
@@ -135,17 +368,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
     mbar_init(&q_empty, 1);
-    mbar_init(&o_free, 4);
+    mbar_init(&o_free, FEW ? 1 : 4);
     for (int s = 0; s < kTcStages; ++s) {
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4);
-      mbar_init(&p_full[s], 4); mbar_init(&pv_done[s], 1);
+      mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], FEW ? 1 : 4);
+      mbar_init(&p_full[s], FEW ? 1 : 4); mbar_init(&pv_done[s], 1);
     }
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (FEW) {  // query rows that no load writes must not hold whatever the kernel before left there
+    for (int i = threadIdx.x; i < kTcTile / 16; i += kTcThreads) reinterpret_cast<uint4*>(tiles)[i] = make_uint4(0u, 0u, 0u, 0u);
+    fence_async_smem();
   }
   if (warp == 1) tmem_alloc(&tmem_slot, 512);
   tc_fence_before();
@@ -193,7 +430,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             break;
           }
           if (lane == 0) {
-            mbar_expect_tx(&q_full, (uint32_t)(2 * 128 * G * (kTcRows / G)));  // two boxes of (64, group, tokens per tile)
+            mbar_expect_tx(&q_full, (uint32_t)(2 * 128 * G * (p.tile_rows / G)));  // two boxes of (64, group, tokens per tile)
             for (int hh = 0; hh < 2; ++hh)  // (d, head, token): rows land as token-major, head-minor
               tma_load_3d(tiles + hh * kTcHalf, &map_q, &q_full, hh * 64, kvh * G, it.q_start + it.tok0);
           }
@@ -306,6 +543,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       g0 += n_tiles;
       ++qi;
     }
+  } else if (FEW) {
+    // ------------------------------------------------------------ softmax and epilogue of rows 0..15 by one warp
+    if ((warp & 3) == 0) attention_tc_few_rows(p, tmem, lane, n_work, n_rounds, s_full, s_empty, p_full, pv_done, &o_free, abortp,
+                                               &abort_flag);
   } else {
     // ------------------------------------------------------------ softmax and epilogue (warps 2..5), one row per thread
     const int quad = warp & 3;
@@ -494,19 +735,29 @@ inline bool attention_tc_fits(int head_dim, int page_size, int group) {
   return head_dim == kTcD && page_size >= 16 && page_size % 16 == 0 && group >= 1 && group <= kTcRows;
 }
 
+// Tiles of at most 16 rows (decode steps) on the same kernel with one softmax warp: the same sizes, at most
+// 16 query heads per KV head.
+constexpr int kTcFewRows = 16;
+inline bool attention_tc_few_fits(int head_dim, int page_size, int group) {
+  return attention_tc_fits(head_dim, page_size, group) && group <= kTcFewRows;
+}
+
+// `p.tile_rows` is 128, or 16 for the few-rows form.
 inline int launch_attention_tc(const AttnParams& p, int n_tokens, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem) != cudaSuccess)
+    if (cudaFuncSetAttribute(attention_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(attention_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem) != cudaSuccess)
       return 2;
     configured = true;
   }
+  if (p.tile_rows != kTcRows && p.tile_rows != kTcFewRows) return 5;
   CUtensorMap mq, mk, mv;
   {
     // queries [T, Hq, D] seen as (d, head, token); a box is (64, group, tokens per tile)
     const uint64_t dims[3] = {(uint64_t)kTcD, (uint64_t)p.Hq, (uint64_t)n_tokens};
     const uint64_t strides[2] = {(uint64_t)kTcD * 2, (uint64_t)p.Hq * kTcD * 2};
-    const uint32_t box[3] = {64, (uint32_t)p.G, (uint32_t)(kTcRows / p.G)};
+    const uint32_t box[3] = {64, (uint32_t)p.G, (uint32_t)(p.tile_rows / p.G)};
     if (!make_map(&mq, p.q, 3, dims, strides, box)) return 4;
   }
   {
@@ -524,7 +775,11 @@ inline int launch_attention_tc(const AttnParams& p, int n_tokens, cudaStream_t s
   }
   const long long n_work = (long long)p.n_items * p.Hkv;  // one CTA per SM, each takes every sms-th piece of work
   const int grid = (int)(n_work < sms ? n_work : sms);
-  FTK_LAUNCH(attention_tc_kernel, grid, kTcThreads, kTcSmem, s, mq, mk, mv, p);
+  if (p.tile_rows == kTcFewRows) {
+    FTK_LAUNCH(attention_tc_kernel<true>, grid, kTcThreads, kTcSmem, s, mq, mk, mv, p);
+  } else {
+    FTK_LAUNCH(attention_tc_kernel<false>, grid, kTcThreads, kTcSmem, s, mq, mk, mv, p);
+  }
   return 0;
 }
 

@@ -62,16 +62,22 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
                window: Optional[int], n_kv_heads: int, sm_count: int = 148,
                max_splits: int = 32, min_split_keys: int = 256,
                fixed_splits: Optional[int] = None,
-               sparse: Optional[Tuple[int, int]] = None) -> AttentionPlan:
+               sparse: Optional[Tuple[int, int]] = None, key_tile: Optional[int] = None) -> AttentionPlan:
     """``segments`` holds (q_len, kv_len) per segment, in step order.
 
     ``fixed_splits`` forces every tile to be planned with exactly that many item rows
     (unused ones get an empty key range); CUDA-graph replay uses it so that the item
     count of a step never changes.
 
+    ``key_tile`` is the number of keys the kernel walks at a time when it is one that runs one CTA per
+    SM through the whole list (128 for the tcgen05 kernels; None: 128 for tiles of 128 rows and more,
+    else 0): pieces are then multiples of it and the list is sorted by length.
+
     ``sparse = (block_size, topk)`` plans a block-sparse layer: one token per tile (every token has
     its own choice of key blocks) and key ranges that count chosen keys: ``min(topk, visible
     blocks) * block_size`` of them."""
+    if key_tile is None:
+        key_tile = 128 if tile_rows >= 128 else 0
     tpt = 1 if sparse else tokens_per_tile(tile_rows, group)
     tiles: List[Tuple[int, int, int, int, int]] = []  # seg, tok0, ntok, lo, hi
     for s, (q_len, kv_len) in enumerate(segments):
@@ -108,7 +114,7 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
         else:
             # splits that fill whole waves of resident CTAs, none shorter than min_split_keys
             want = wave_splits(n_tiles * n_kv_heads, target, most, span)
-        quantum = 128 if tile_rows >= 128 else SPLIT_QUANTUM  # a piece that ends inside a key tile pays for all of it
+        quantum = key_tile if key_tile else SPLIT_QUANTUM  # a piece that ends inside a key tile pays for all of it
         quanta = -(-span // quantum)
         n_real = max(1, min(want, quanta))
         per = -(-quanta // n_real) * quantum
@@ -121,7 +127,7 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
             rows.append([s, tok0, ntok, b, e, n_rows, i, base])
         if n_rows > 1:
             n_slots += n_rows
-    if tile_rows >= 128 and fixed_splits is None:
+    if key_tile and fixed_splits is None:
         # the tcgen05 kernels deal the list out from its end, to and fro over its CTAs: longest pieces last
         # here (their place in the list means nothing else: partial results are found by base + split)
         rows.sort(key=lambda r: r[4] - r[3])

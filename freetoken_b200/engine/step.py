@@ -115,13 +115,16 @@ class StepBuilder:
         return wave_splits(b * n_kv_heads, ctas_per_sm * self.sm_count, 16, self.longest_span())
 
     def attention_plan(self, group: int, tile_rows: int, window: Optional[int], n_kv_heads: int,
-                       head_dim: int) -> Any:
-        key = ("attention", group, tile_rows, window, n_kv_heads, head_dim)
+                       head_dim: int, few_rows: bool = False) -> Any:
+        """``few_rows``: the work list is for the tcgen05 kernel in its form for tiles of at most 16 rows (key tiles of 128)."""
+        key = ("attention", group, tile_rows, window, n_kv_heads, head_dim, few_rows)
         if key not in self.plans:
-            per_sm = 1 if tile_rows >= 128 else 2  # the tcgen05 kernels fill an SM with one CTA
+            tensor_core = tile_rows >= 128 or few_rows
+            per_sm = 1 if tensor_core else 2  # the tcgen05 kernels fill an SM with one CTA
             plan = build_plan(self.seg_lens, group, tile_rows, window, n_kv_heads,
                               sm_count=self.sm_count if per_sm == 2 else max(1, self.sm_count // 2),
-                              fixed_splits=self.fixed_splits(n_kv_heads, per_sm) if self.fixed else None)
+                              fixed_splits=self.fixed_splits(n_kv_heads, per_sm) if self.fixed else None,
+                              key_tile=128 if tensor_core else 0)
             self.plans[key] = plan
             self.plan_dims[key] = (n_kv_heads, tile_rows, head_dim)
             self.add(f"plan.{len(self.plans) - 1}", plan.items)

@@ -130,11 +130,13 @@ def bench_attention(a) -> dict:
     tile = 128 if (a.prefill >= 128 and not a.no_tc and ops.attention_tc_fits(D, P, G)) else 64
     if tile == 128 and a.pair:
         tile = 256  # two query tiles per CTA
+    few_rows = False
     if not a.prefill:
-        tc = a.tc and ops.attention_tc_fits(D, P, G)
-        fixed = wave_splits(len(segs) * Hkv, 148 if tc else 2 * 148, 16) if a.splits is None else a.splits
-        tile = 128 if tc else (16 if G <= 16 else 64)
-    plan = build_plan(segs, G, tile, None, Hkv, fixed_splits=fixed)
+        few_rows = a.few_rows and ops.attention_tc_few_fits(D, P, G)
+        tc = few_rows or (a.tc and ops.attention_tc_fits(D, P, G))
+        fixed = wave_splits(len(segs) * Hkv, 148 if tc else 2 * 148, 16, a.context) if a.splits is None else a.splits
+        tile = 16 if few_rows else 128 if tc else (16 if G <= 16 else 64)
+    plan = build_plan(segs, G, tile, None, Hkv, fixed_splits=fixed, key_tile=128 if (few_rows or tile >= 128) else 0)
     items = torch.from_numpy(plan.items).to(dev)
     po = pm = None
     if plan.n_slots:
@@ -142,7 +144,7 @@ def bench_attention(a) -> dict:
         pm = torch.empty(plan.n_slots, Hkv, tile, 2, dtype=torch.float32, device=dev)
     out = torch.empty_like(q)
     us = _time(lambda: ops.paged_attention(q, ks, vs, bt, seg, len(segs), items, plan.n_items, po, pm, out, tile,
-                                           D ** -0.5, None), a.iters, a.warmup, a.profile)
+                                           D ** -0.5, None, few_rows=few_rows), a.iters, a.warmup, a.profile)
     kv_bytes = sum(kv for _, kv in segs) * Hkv * D * 2 * 2
     flops = sum(4 * (ql * kv - ql * (ql - 1) // 2) * Hq * D for ql, kv in segs)
     return {"us": round(us, 2), "items": plan.n_items, "kv_bytes": kv_bytes, "gbs": round(kv_bytes / us / 1e3, 1),
@@ -287,7 +289,9 @@ def main(argv=None) -> int:
             p.add_argument("--page-size", type=int, default=16)
             p.add_argument("--splits", type=int, default=None)
             p.add_argument("--no-tc", action="store_true", help="prefill on the mma.sync kernel instead of tcgen05")
-            p.add_argument("--tc", action="store_true", help="decode on the tcgen05 kernel")
+            p.add_argument("--tc", action="store_true", help="decode on the tcgen05 kernel with 128-row query tiles")
+            p.add_argument("--few-rows", action="store_true",
+                           help="decode on the tcgen05 kernel in its form for tiles of at most 16 rows")
             p.add_argument("--pair", action="store_true", help="prefill on the tcgen05 kernel with two query tiles per CTA")
         elif name == "few":
             p.add_argument("--tokens", type=int, default=1)

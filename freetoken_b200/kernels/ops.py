@@ -71,6 +71,9 @@ _SIGNATURES = {
     "ftk_attention_tc_fits": [_i, _i, _i],
     "ftk_paged_attention_tc": [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
                                _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "ftk_attention_tc_few_fits": [_i, _i, _i],
+    "ftk_paged_attention_tc_few": [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
+                                      _i, _i, _i, _i, _i, _i, ctypes.c_float, _i, _vp],
     "ftk_paged_attention_tc_pair": [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
                                     _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "ftk_paged_attention_sparse": [_vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
@@ -359,7 +362,8 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
                     block_table: torch.Tensor, seg_info: torch.Tensor, n_segs: int,
                     items: torch.Tensor, n_items: int, part_o: Optional[torch.Tensor],
                     part_ml: Optional[torch.Tensor], out: torch.Tensor, tile_rows: int, scale: float,
-                    window: Optional[int], sel: Optional[torch.Tensor] = None, block_size: int = 0) -> None:
+                    window: Optional[int], sel: Optional[torch.Tensor] = None, block_size: int = 0,
+                    few_rows: bool = False) -> None:
     """Causal softmax attention of the step's queries over the paged keys and values.
 
     ``q, out [T, Hq, D]``; slabs ``[pages, Hkv, page_size, D]``; ``block_table [rows, width]``
@@ -373,6 +377,10 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
     per token and KV head, ascending, -1 padded, from :func:`sparse_select`); a query then reads only
     the keys of its chosen blocks, the work items hold one token each and their key ranges count
     chosen keys.
+
+    ``few_rows`` (with ``tile_rows = 16``, bfloat16) runs the tcgen05 kernel in its form for decode
+    steps (one warp takes the softmax of a tile's at most 16 rows); its work list has key pieces that
+    are multiples of 128 (``build_plan(..., key_tile=128)``).
     """
     T, Hq, D = q.shape
     pages, Hkv, P, D2 = k_slab.shape
@@ -384,10 +392,14 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
     if part_o is not None and (part_o.shape[1:] != (Hkv, tile_rows, D) or part_ml is None
                                or part_ml.shape != (n_slots, Hkv, tile_rows, 2)):
         raise KernelError("paged_attention: scratch shapes do not match tile_rows / heads")
-    if tile_rows in (128, 256):  # bfloat16 steps on the tcgen05 kernels: one query tile per CTA, or a pair of them
+    if few_rows and tile_rows != 16:
+        raise KernelError(f"paged_attention: few_rows goes with tiles of 16 rows, got {tile_rows}")
+    if tile_rows in (128, 256) or few_rows:
+        # bfloat16 steps on the tcgen05 kernels: one query tile per CTA, a pair of them, or tiles of a few rows
         if sel is not None or window or q.dtype != torch.bfloat16:
-            raise KernelError("paged_attention: 128-row tiles take bfloat16 without window or block selection")
-        fn = _lib().ftk_paged_attention_tc_pair if tile_rows == 256 else _lib().ftk_paged_attention_tc
+            raise KernelError("paged_attention: the tcgen05 kernels take bfloat16 without window or block selection")
+        fn = (_lib().ftk_paged_attention_tc_few if few_rows else
+              _lib().ftk_paged_attention_tc_pair if tile_rows == 256 else _lib().ftk_paged_attention_tc)
         _check(fn(
             _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"),
             _dev(block_table, "block_table", torch.int32), block_table.shape[1],
@@ -423,6 +435,11 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
 def attention_tc_fits(head_dim: int, page_size: int, group: int) -> bool:
     """Whether the tcgen05 attention kernel (tiles of 128 query rows) takes these sizes."""
     return bool(_lib().ftk_attention_tc_fits(head_dim, page_size, group))
+
+
+def attention_tc_few_fits(head_dim: int, page_size: int, group: int) -> bool:
+    """Whether the tcgen05 attention kernel takes these sizes in its form for tiles of at most 16 rows."""
+    return bool(_lib().ftk_attention_tc_few_fits(head_dim, page_size, group))
 
 
 def sparse_score_fits(n_heads: int, dim: int, block_size: int) -> bool:

@@ -12,7 +12,7 @@ library matrix products, as in the reference (python/freetoken/layers/linear.py:
 
 from __future__ import annotations
 
-from typing import Any, Dict, Optional
+from typing import Any, Dict, Optional, Tuple
 
 import torch
 
@@ -28,28 +28,41 @@ TC_PAIR_MIN_TOKENS = 1024  # from this many tokens on, a step goes to the kernel
 TC_MIN_DECODE_SPAN = 0   # decode steps go there from this length of the longest request (rounded up to 2^n) on
 
 
+def attention_kernel_form(dtype: torch.dtype, decode_only: bool = False, group: int = 1, n_tokens: int = 0,
+                          head_dim: int = 0, page_size: int = 0, window: Optional[int] = None,
+                          longest_span: int = 0) -> Tuple[int, bool]:
+    """``(query rows one attention CTA handles, the tcgen05 kernel's form for few rows)``.
+
+    16 rows in the 32-bit kernel.  bfloat16 steps whose sizes the tcgen05 kernels take: 128 rows for
+    long steps (``TC_MIN_TOKENS`` tokens and more; 256, two such tiles per CTA, from
+    ``TC_PAIR_MIN_TOKENS`` tokens on); decode steps go to the same kernel in its form for tiles of at
+    most 16 rows, where one warp takes the softmax (groups of up to 16 heads; ``longest_span`` is the longest
+    request's length rounded up to a power of two, from which on they go there:
+    ``TC_MIN_DECODE_SPAN``), larger groups to the 128-row kernel.  Otherwise 16 rows for decode steps
+    of small groups and 64 in the bfloat16 mma.sync kernels."""
+    if dtype != torch.bfloat16:
+        return 16, False
+    sized = bool(window is None and head_dim and page_size)
+    if decode_only:
+        if sized and longest_span >= TC_MIN_DECODE_SPAN:
+            if ops.attention_tc_few_fits(head_dim, page_size, group):
+                return 16, True
+            if ops.attention_tc_fits(head_dim, page_size, group):
+                return 128, False
+        return (16 if group <= 16 else 64), False
+    tc = sized and ops.attention_tc_fits(head_dim, page_size, group)
+    if tc and n_tokens >= TC_PAIR_MIN_TOKENS:
+        return 256, False
+    if tc and n_tokens >= TC_MIN_TOKENS:
+        return 128, False
+    return 64, False
+
+
 def attention_tile_rows(dtype: torch.dtype, decode_only: bool = False, group: int = 1, n_tokens: int = 0,
                         head_dim: int = 0, page_size: int = 0, window: Optional[int] = None,
                         longest_span: int = 0) -> int:
-    """Query rows (tokens x group heads) one attention CTA handles: 16 in the 32-bit kernel; 128 (the
-    tcgen05 kernel) for bfloat16 steps whose sizes it takes, long ones (``TC_MIN_TOKENS`` tokens and
-    more; 256, two such tiles per CTA, from ``TC_PAIR_MIN_TOKENS`` tokens on) and decode steps alike (measured at 2k tokens of context against the 16-row kernel: 11
-    against 13 microseconds at batch 1, 21 against 26 at batch 8, 105 against 133 at batch 64);
-    ``longest_span`` is the longest request's length rounded up to a power of two, from which on decode
-    steps go there (``TC_MIN_DECODE_SPAN``); otherwise 16 rows for decode steps of small groups and 64
-    in the bfloat16 mma.sync kernel."""
-    if dtype != torch.bfloat16:
-        return 16
-    tc = bool(window is None and head_dim and page_size and ops.attention_tc_fits(head_dim, page_size, group))
-    if decode_only:
-        if tc and longest_span >= TC_MIN_DECODE_SPAN:
-            return 128
-        return 16 if group <= 16 else 64
-    if tc and n_tokens >= TC_PAIR_MIN_TOKENS:
-        return 256
-    if tc and n_tokens >= TC_MIN_TOKENS:
-        return 128
-    return 64
+    """Query rows (tokens x group heads) one attention CTA handles (see :func:`attention_kernel_form`)."""
+    return attention_kernel_form(dtype, decode_only, group, n_tokens, head_dim, page_size, window, longest_span)[0]
 
 
 @MIXERS.register("gqa_attention")
@@ -112,21 +125,25 @@ class GQAttention(Mixer):
         return rows + 2 * 148 * 128 * (self.head_dim + 2) * 4 * 2
 
     # ------------------------------------------------------------------ step
+    def kernel_form(self, decode_only: bool, n_tokens: int = 0, page_size: int = 0, longest_span: int = 0):
+        return attention_kernel_form(self.env.dtype, decode_only, self.group, n_tokens, self.head_dim, page_size,
+                                     self.window, longest_span)
+
     def tile_rows(self, decode_only: bool, n_tokens: int = 0, page_size: int = 0, longest_span: int = 0) -> int:
-        return attention_tile_rows(self.env.dtype, decode_only, self.group, n_tokens, self.head_dim, page_size,
-                                   self.window, longest_span)
+        return self.kernel_form(decode_only, n_tokens, page_size, longest_span)[0]
 
     def plan_key(self, decode_only: bool = False, n_tokens: int = 0, page_size: int = 0, longest_span: int = 0):
-        return ("attention", self.group, self.tile_rows(decode_only, n_tokens, page_size, longest_span), self.window,
-                self.n_kv_heads, self.head_dim)
+        rows, few_rows = self.kernel_form(decode_only, n_tokens, page_size, longest_span)
+        return ("attention", self.group, rows, self.window, self.n_kv_heads, self.head_dim, few_rows)
 
     def prepare(self, builder) -> None:
         """Ask the step for the work list this mixer's attention kernel runs from."""
         n_tokens = sum(q for q, _ in builder.seg_lens)
         page_size = builder.engine.config.page_size if builder.engine is not None else 0
         # forward() of the same step runs the kernel this work list was made for
-        rows = self.tile_rows(builder.decode_only, n_tokens, page_size, builder.longest_span())
-        self._step_plan = builder.attention_plan(self.group, rows, self.window, self.n_kv_heads, self.head_dim)
+        rows, few_rows = self.kernel_form(builder.decode_only, n_tokens, page_size, builder.longest_span())
+        self._step_plan = builder.attention_plan(self.group, rows, self.window, self.n_kv_heads, self.head_dim,
+                                                 few_rows)
 
     def forward(self, h: torch.Tensor, step: StepState, cache: Any, writes_cache: bool) -> torch.Tensor:
         T = h.shape[0]
@@ -152,7 +169,7 @@ class GQAttention(Mixer):
         o = ws.get("attn.o", (T, self.n_heads, self.head_dim), dt, (cap, self.n_heads, self.head_dim))
         ops.paged_attention(q, cache.slabs["k"], cache.slabs["v"], cache.block_table, step.seg_info,
                             len(step.segments), plan.items_dev, plan.n_items, plan.part_o, plan.part_ml,
-                            o, self._step_plan[2], self.scale, self.window)
+                            o, self._step_plan[2], self.scale, self.window, few_rows=self._step_plan[6])
         out = ws.get("attn.out", (T, self.hidden), dt, (cap, self.hidden))
         ops.linear(o.view(T, self.q_dim), self.params["o_proj.weight"], out)
         return out

@@ -102,7 +102,7 @@ def norm_rope_store(x, head_dim, rotary_dim, positions, rope_table, eps, gemma, 
 
 
 def paged_attention(q, k_slab, v_slab, block_table, seg_info, n_segs, items, n_items, part_o, part_ml,
-                    out, tile_rows, scale, window, sel=None, block_size=0):
+                    out, tile_rows, scale, window, sel=None, block_size=0, few_rows=False):
     """Per query token, softmax over the visible keys gathered through the block table; the
     work list and the scratch are ignored (they only steer how the kernel splits the work).
     With ``sel`` a query reads only the keys of its chosen blocks."""
@@ -198,6 +198,10 @@ def attention_tc_fits(head_dim, page_size, group):
     return False  # the CPU tests plan for the other kernels
 
 
+def attention_tc_few_fits(head_dim, page_size, group):
+    return False
+
+
 def moe_small_fits(n_tokens, hidden, inter, top_k):
     return False  # the few-token kernels are a second route to the same result; the CPU stand-ins take the general one
 
@@ -276,7 +280,7 @@ def sample(logits, temperature, top_k, top_p, u, out):
 
 
 ALL = ["sparse_score_fits", "moe_small_fits", "copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "add_rmsnorm_routes", "act_and_mul", "cast", "table_update", "norm_rope_store",
-       "paged_attention", "router_topk", "moe_permute", "moe_route", "moe_route_fits", "linear", "attention_tc_fits", "moe_gather", "moe_gemm1_act", "moe_gemm2",
+       "paged_attention", "router_topk", "moe_permute", "moe_route", "moe_route_fits", "linear", "attention_tc_fits", "attention_tc_few_fits", "moe_gather", "moe_gemm1_act", "moe_gemm2",
        "moe_combine", "sample"]
 
 

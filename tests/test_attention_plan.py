@@ -81,15 +81,21 @@ def test_the_128_row_kernel_gets_pieces_on_tile_boundaries_sorted_by_length():
 
 
 def test_which_attention_kernel_a_step_gets():
-    """The rows per CTA name the kernel: 16 float32 / small bfloat16 tiles, 64 mma.sync, 128 tcgen05 with
-    one query tile, 256 with two (steps of a thousand tokens and more)."""
+    """The rows per CTA (and the few-rows flag) name the kernel: 16 float32 / small bfloat16 tiles, 64
+    mma.sync, 128 tcgen05 with one query tile, 256 with two (steps of a thousand tokens and more), 16
+    with the flag for decode steps on tcgen05."""
     import torch
 
-    from freetoken_b200.parts.attention import TC_MIN_TOKENS, TC_PAIR_MIN_TOKENS, attention_tile_rows as rows
+    from freetoken_b200.parts.attention import (TC_MIN_TOKENS, TC_PAIR_MIN_TOKENS, attention_kernel_form as form,
+                                                attention_tile_rows as rows)
 
     bf, f32 = torch.bfloat16, torch.float32
     assert rows(f32, False, 6, 4096, 128, 16) == 16 and rows(f32, True, 6, 8, 128, 16) == 16
-    assert rows(bf, True, 6, 8, 128, 16, None, 4096) == 128          # decode on the tcgen05 kernel
+    assert form(bf, True, 6, 8, 128, 16, None, 4096) == (16, True)   # decode on the tcgen05 kernel, few rows
+    assert form(bf, True, 16, 8, 128, 16, None, 4096) == (16, True)
+    assert form(bf, True, 24, 8, 128, 16, None, 4096) == (128, False)  # a group too large for its 16 columns
+    assert form(bf, True, 6, 8, 64, 16, None, 4096) == (16, False)
+    assert form(bf, False, 6, 4096, 128, 16) == (256, False)
     assert rows(bf, True, 6, 8, 64, 16, None, 4096) == 16            # head size it does not take
     assert rows(bf, True, 6, 8, 128, 16, 512, 4096) == 16            # a window
     assert rows(bf, True, 6, 8, 128, 8, None, 4096) == 16            # pages of 8 tokens

@@ -171,7 +171,7 @@ def test_norm_rope_store(dtype, Hq, Hkv, D, rd, P, gemma, norm, T):
 
 
 def run_attention(dtype, Hq, Hkv, D, P, segs, window, fixed_splits=None, force_split=False, seed=0, tile=None,
-                  spoil_reference=None):
+                  spoil_reference=None, few_rows=False):
     """segs: list of (q_len, kv_len).  Builds a shuffled page layout with NaN in every unwritten
     slot, runs kernel and reference, returns both outputs."""
     G = Hq // Hkv
@@ -201,6 +201,8 @@ def run_attention(dtype, Hq, Hkv, D, P, segs, window, fixed_splits=None, force_s
     kw = dict(sm_count=148)
     if force_split:
         kw = dict(sm_count=4096, min_split_keys=32)
+    if few_rows:
+        kw["key_tile"] = 128
     plan = build_plan(segs, G, tile, window, Hkv, fixed_splits=fixed_splits, **kw)
     items = torch.from_numpy(plan.items).to(DEV)
     part_o = part_ml = None
@@ -211,7 +213,7 @@ def run_attention(dtype, Hq, Hkv, D, P, segs, window, fixed_splits=None, force_s
     want = torch.empty_like(out)
     scale = D ** -0.5
     ops.paged_attention(q, ks, vs, bt, seg, len(segs), items, plan.n_items, part_o, part_ml, out, tile,
-                        scale, window)
+                        scale, window, few_rows=few_rows)
     if spoil_reference is not None:  # (segment, position): the reference is made blind to that key
         si, kpos = spoil_reference
         page = int(bt[rows[si], kpos // P])
@@ -313,6 +315,75 @@ def test_attention_decode_tiles(Hq, Hkv, D, P, fixed, window):
                                     force_split=fixed is None)
     assert not torch.isnan(out.float()).any()
     torch.testing.assert_close(out.float(), want.float(), **attn_tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("Hq,Hkv,P", [(12, 2, 16), (48, 8, 16), (5, 5, 32), (7, 1, 64), (16, 1, 16), (3, 1, 48), (10, 2, 16)])
+@pytest.mark.parametrize("fixed", [None, 1, 4, 16])
+def test_attention_tensor_core_decode_kernel(Hq, Hkv, P, fixed):
+    """The tcgen05 kernel in its form for tiles of at most 16 rows (one softmax warp, head size 128) on
+    single tokens and short portions: lengths on and off the edges of its 128-key tiles and 16-key
+    boxes, whole, in fixed numbers of pieces (some of them empty) and in forced pieces; every unwritten
+    cache slot holds NaN."""
+    G = Hq // Hkv
+    assert ops.attention_tc_few_fits(128, P, G)
+    assert not ops.attention_tc_few_fits(64, P, G) and not ops.attention_tc_few_fits(128, 8, 1)
+    assert not ops.attention_tc_few_fits(128, 16, 17)
+    segs = [(1, 1), (1, 130), (1, 17), (1, 700), (1, 128), (1, 129), (1, 1999), (1, 127), (1, 256), (1, 1024)]
+    if fixed is None:  # portions of a few tokens beside them: several tokens to a tile, or tiles of its own
+        segs += [(2, 64), (3, 300), (5, 5), (4, 1000)]
+    out, want, plan = run_attention(torch.bfloat16, Hq, Hkv, 128, P, segs, None, fixed_splits=fixed,
+                                    tile=16, force_split=fixed is None, few_rows=True)
+    assert fixed == 1 or plan.n_slots > 0
+    assert not torch.isnan(out.float()).any()
+    torch.testing.assert_close(out.float(), want.float(), **attn_tol(torch.bfloat16))
+    assert ops.read_status() == 0
+    names = list(ops.variant_counts())
+    assert any("at most 16 rows" in n for n in names), names
+
+
+def test_attention_tensor_core_decode_kernel_many_rounds():
+    """More pieces than SMs, so that every CTA works through several: the roles run on into the next
+    piece; twice in a row, so that the arrival counters of the first launch serve the second."""
+    segs = [(1, 300 + 37 * i) for i in range(48)]
+    for _ in range(2):
+        out, want, plan = run_attention(torch.bfloat16, 48, 8, 128, 16, segs, None, fixed_splits=2, tile=16,
+                                        few_rows=True)
+        assert plan.n_items * 8 > 2 * 148
+        assert not torch.isnan(out.float()).any()
+        torch.testing.assert_close(out.float(), want.float(), **attn_tol(torch.bfloat16))
+    assert ops.read_status() == 0
+
+
+def test_attention_tensor_core_decode_kernel_finds_a_far_key():
+    """One key among four thousand carries the whole weight, in a tile that is split along the keys: the
+    running maximum moves there, the accumulator is rescaled, and the merge weighs the pieces."""
+    torch.manual_seed(5)
+    Hq, Hkv, D, P, n = 12, 2, 128, 16, 4096
+    G = Hq // Hkv
+    pages = n // P + 1
+    for far in (37, 2100, 4095):
+        ks = torch.randn(pages, Hkv, P, D).mul(0.1)
+        vs = torch.randn(pages, Hkv, P, D)
+        q = torch.randn(1, Hq, D).mul(0.1)
+        direction = torch.randn(D)
+        direction = direction / direction.norm()
+        ks[1 + far // P, :, far % P] = direction * 30
+        q[0, :] = direction * 30
+        bt = torch.arange(1, pages, dtype=torch.int32).view(1, -1).to(DEV)
+        seg = torch.tensor([[0, 1, n, 0]], dtype=torch.int32, device=DEV)
+        rows = 16
+        plan = build_plan([(1, n)], G, rows, None, Hkv, fixed_splits=4, key_tile=128)
+        items = torch.from_numpy(plan.items).to(DEV)
+        qd, kd, vd = q.to(torch.bfloat16).to(DEV), ks.to(torch.bfloat16).to(DEV), vs.to(torch.bfloat16).to(DEV)
+        out = torch.empty_like(qd)
+        po = torch.empty(plan.n_slots, Hkv, rows, D, dtype=torch.float32, device=DEV)
+        pm = torch.empty(plan.n_slots, Hkv, rows, 2, dtype=torch.float32, device=DEV)
+        ops.paged_attention(qd, kd, vd, bt, seg, 1, items, plan.n_items, po, pm, out, rows, D ** -0.5, None,
+                            few_rows=True)
+        for h in range(Hq):
+            want = vd[1 + far // P, h // G, far % P].float()
+            torch.testing.assert_close(out[0, h].float(), want, rtol=2e-2, atol=2e-2)
+    assert ops.read_status() == 0
 
 
 def sparse_problem(dtype, Hq, Hkv, D, P, segs, block, seed=0):
