@@ -437,18 +437,26 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         ++qi;
         const int32_t* bt = p.block_table + (size_t)it.bt_row * p.bt_stride;
+        // this lane's page of tile j: looked up one tile ahead, so that the answer is there when the stage is free
+        auto page_of = [&](int j) {
+          const int key = it.kb + j * kTcKeys + 16 * box;
+          int page = 0;
+          if (j < n_tiles && key < it.ke) {
+            const int slot = key / p.P;
+            page = slot < p.bt_stride ? bt[slot] : 0;
+            if (page < 0 || page >= p.num_pages) page = 0;
+          }
+          return page;
+        };
+        int page_next = page_of(0);
         for (int j = 0; j < n_tiles && ok; ++j, ++g) {
           const int st = g % kTcStages;
           const uint32_t par = ((g / kTcStages) & 1) ^ 1;
           const int key0 = it.kb + j * kTcKeys;
           const int n_box = min(8, (it.ke - key0 + 15) >> 4);  // boxes of 16 keys that hold keys of the request
           const int key = key0 + 16 * box;
-          int page = 0;
-          if (box < n_box) {
-            const int slot = key / p.P;
-            page = slot < p.bt_stride ? bt[slot] : 0;
-            if (page < 0 || page >= p.num_pages) page = 0;
-          }
+          const int page = page_next;
+          page_next = page_of(j + 1);
           const int row = (page * p.Hkv + kvh) * p.P + key % p.P;
           if (!__all_sync(0x0000ffffu, mbar_wait(&empty[st], par, abortp))) {
             if (lane == 0) fail(201 + kv);
@@ -483,7 +491,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (j < n_tiles) {
           const int g = g0 + j, st = g & 1, ks = g % kTcStages;  // score buffer, key stage
           const uint32_t par = (g >> 1) & 1;
-          if (!mbar_wait(&k_full[ks], (uint32_t)(g / kTcStages) & 1u, abortp) || !mbar_wait(&s_empty[st], par ^ 1, abortp)) {
+          if (!mbar_wait2(&k_full[ks], (uint32_t)(g / kTcStages) & 1u, &s_empty[st], par ^ 1, abortp)) {
             if (lane == 0) fail(204);
             ok = false;
             break;
@@ -506,7 +514,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (j >= 1) {
           const int i = j - 1, g = g0 + i, st = g & 1, vs = g % kTcStages;  // probability buffer, value stage
           const uint32_t par = (g >> 1) & 1;
-          if (!mbar_wait(&p_full[st], par, abortp) || !mbar_wait(&v_full[vs], (uint32_t)(g / kTcStages) & 1u, abortp) ||
+          if (!mbar_wait2(&p_full[st], par, &v_full[vs], (uint32_t)(g / kTcStages) & 1u, abortp) ||
               (i == 0 && !mbar_wait(&o_free, (uint32_t)(qi & 1) ^ 1u, abortp))) {  // the piece before has read its output
             if (lane == 0) fail(205);
             ok = false;

@@ -40,6 +40,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
   return false;
 }
+// Two barriers at once: their tests go out back to back, so that waiting for both costs one test's
+// latency when both have flipped already.
+__device__ __forceinline__ bool mbar_wait2(uint64_t* bar_a, uint32_t parity_a, uint64_t* bar_b, uint32_t parity_b,
+                                           volatile int* abort_flag) {
+  bool a = false, b = false;
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    const bool ta = a || mbar_test(bar_a, parity_a), tb = b || mbar_test(bar_b, parity_b);
+    a = ta;
+    b = tb;
+    if (a && b) return true;
+    if ((i & 63) == 63) {
+      if (*abort_flag) return false;
+      __nanosleep(64);
+    }
+  }
+  return false;
+}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
