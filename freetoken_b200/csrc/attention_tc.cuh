@@ -388,10 +388,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  // barriers, TMEM and the work item (made on the host before the step) are set up while the kernel
-  // before this one still runs; what it wrote (queries, the new keys and values) is read from here on
-  pdl_wait();
-  pdl_trigger();
+  // Barriers and TMEM are set up while the kernel before this one still runs; what it wrote (queries,
+  // the new keys and values) is read after pdl_wait().  In the form for decode steps the loader warps do
+  // not wait there: the work list, the block tables and the keys and values of earlier steps were
+  // written by kernels that had ended before this one could start (every kernel of a step waits for the
+  // one before it before it lets the next one in, or ends), so they wait only before the queries and
+  // before a key tile that holds positions of this step.
+  if (!FEW || (warp != 0 && warp != 6)) pdl_wait();
+  if (!FEW || warp == 1) pdl_trigger();  // (after a wait: the kernel after this one may count on the one before being over)
   const uint32_t tmem = tmem_slot;
   volatile int* abortp = &abort_flag;
   const int G = p.G;
@@ -414,6 +418,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       uint64_t* empty = kv ? v_empty : k_empty;
       unsigned char* stage0 = tiles + (kv ? 1 + kTcStages : 1) * kTcTile + h * kTcHalf + box * 2048;
       bool ok = true;
+      bool waited = false;  // for the kernel before this one (decode steps)
       int g = 0;   // tiles of all pieces so far: stage g & 1
       int qi = 0;  // pieces with tiles so far
       for (int i_round = 0; i_round < n_rounds && ok; ++i_round) {
@@ -423,19 +428,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const int kvh = w % p.Hkv;
         const int n_tiles = tiles_of(it);
         if (n_tiles == 0) continue;
-        if (!kv) {  // the queries, once the products of the piece before have read theirs
+        // the queries go out once the products of the piece before have read theirs: before the first key
+        // tile, or (decode steps) after the key tiles that may go out before the kernel before this one is over
+        auto load_queries = [&]() -> bool {
           if (!__all_sync(0x0000ffffu, mbar_wait(&q_empty, (uint32_t)(qi & 1) ^ 1u, abortp))) {
             if (lane == 0) fail(210);
-            ok = false;
-            break;
+            return false;
           }
           if (lane == 0) {
             mbar_expect_tx(&q_full, (uint32_t)(2 * 128 * G * (p.tile_rows / G)));  // two boxes of (64, group, tokens per tile)
             for (int hh = 0; hh < 2; ++hh)  // (d, head, token): rows land as token-major, head-minor
               tma_load_3d(tiles + hh * kTcHalf, &map_q, &q_full, hh * 64, kvh * G, it.q_start + it.tok0);
           }
-        }
-        ++qi;
+          return true;
+        };
+        const int q_at = FEW ? min(n_tiles - 1, 1) : 0;
+        const int fresh_from = it.kv_len - it.q_len;  // first position that this step wrote
         const int32_t* bt = p.block_table + (size_t)it.bt_row * p.bt_stride;
         // this lane's page of tile j: looked up one tile ahead, so that the answer is there when the stage is free
         auto page_of = [&](int j) {
@@ -458,6 +466,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           const int page = page_next;
           page_next = page_of(j + 1);
           const int row = (page * p.Hkv + kvh) * p.P + key % p.P;
+          if (FEW && !waited && (key0 + kTcKeys > fresh_from || (!kv && j == q_at))) {
+            pdl_wait();
+            waited = true;
+          }
+          if (!kv && j == q_at && !load_queries()) {
+            ok = false;
+            break;
+          }
           if (!__all_sync(0x0000ffffu, mbar_wait(&empty[st], par, abortp))) {
             if (lane == 0) fail(201 + kv);
             ok = false;
@@ -467,6 +483,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           __syncwarp(0x0000ffffu);
           if (box < n_box) tma_load_2d(stage0 + st * kTcTile, map, &full[st], h * 64, row);
         }
+        ++qi;
       }
     }
   } else if (warp == 1) {
@@ -553,8 +570,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
   } else if (FEW) {
     // ------------------------------------------------------------ softmax and epilogue of rows 0..15 by one warp
-    if ((warp & 3) == 0) attention_tc_few_rows(p, tmem, lane, n_work, n_rounds, s_full, s_empty, p_full, pv_done, &o_free, abortp,
-                                               &abort_flag);
+    if ((warp & 3) == 0) {
+      attention_tc_few_rows(p, tmem, lane, n_work, n_rounds, s_full, s_empty, p_full, pv_done, &o_free, abortp, &abort_flag);
+    }
   } else {
     // ------------------------------------------------------------ softmax and epilogue (warps 2..5), one row per thread
     const int quad = warp & 3;

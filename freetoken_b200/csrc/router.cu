@@ -185,14 +185,43 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, const float
 
 // The whole routing of a small step in one launch: router logits (a float32 matrix-vector product
 // per token, python/freetoken/models/minimax_m3/moe.py:71-73), then, in the block that finishes
-// last, the choice of every token (route_token) and the counting sort of the routes by expert
-// (what moe_permute does).  A block holds kRouteExperts experts; its warps share their
-// weight rows and add their parts in a fixed order, so a token's logits never depend on the
-// batch.  Blocks count their arrival in g_route_arrivals; nobody waits for anybody.
-constexpr int kRouteWarps = 16;   // all of them share the block's weight rows, each a part of the width
-constexpr int kRouteExperts = 4;  // experts per block: a token's activations are loaded once for all of them
+// last, the choice of every token (route_one) and the sort of the routes by expert (what moe_permute
+// does).  A block holds kRouteExperts experts; its warps share their weight rows (a thread's piece of
+// them is on its way before the kernel waits for the one before it) and add their parts in a fixed
+// order, so a token's logits never depend on the batch.  Blocks count their arrival in
+// g_route_arrivals; nobody waits for anybody.
+constexpr int kRouteWarps = 24;   // all of them share the block's weight rows, each a part of the width
+constexpr int kRouteExperts = 2;  // experts per block: a token's activations are loaded once for all of them
 constexpr int kRouteTokens = 8;   // tokens per pass over the weight rows
+constexpr int kRouteVals = kRouteExperts * kRouteTokens;  // sums a thread carries
+static_assert(kRouteVals == 16, "warp_sum16 adds sixteen values per lane");
 __device__ unsigned int g_route_arrivals = 0;
+
+// Sixteen sums over the warp with sixteen shuffles: the lanes swap halves of what they carry and keep
+// the other half, four times; lanes 2 i and 2 i + 1 end up with the warp's sum of value i.
+__device__ __forceinline__ float warp_sum16(float (&v)[16], int lane) {
+  const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4, b1 = lane & 2;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float give = b4 ? v[i] : v[i + 8], keep = b4 ? v[i + 8] : v[i];
+    v[i] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float give = b3 ? v[i] : v[i + 4], keep = b3 ? v[i + 4] : v[i];
+    v[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const float give = b2 ? v[i] : v[i + 2], keep = b2 ? v[i + 2] : v[i];
+    v[i] = keep + __shfl_xor_sync(0xffffffffu, give, 4);
+  }
+  {
+    const float give = b1 ? v[0] : v[1], keep = b1 ? v[1] : v[0];
+    v[0] = keep + __shfl_xor_sync(0xffffffffu, give, 2);
+  }
+  return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
+}
 
 __global__ void __launch_bounds__(kRouteWarps * 32)
 moe_route_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
@@ -201,7 +230,7 @@ moe_route_kernel(const float* __restrict__ x, const float* __restrict__ w, const
                  int32_t* __restrict__ counts, int32_t* __restrict__ offsets, int32_t* __restrict__ routes,
                  int32_t* __restrict__ pos, int do_sort) {
   extern __shared__ float sm[];
-  __shared__ float part[kRouteExperts][kRouteTokens][kRouteWarps + 1];
+  __shared__ float part[kRouteVals][kRouteWarps + 1];
   __shared__ bool last;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int e0 = blockIdx.x * kRouteExperts;
@@ -222,11 +251,9 @@ moe_route_kernel(const float* __restrict__ x, const float* __restrict__ w, const
     for (int i = tid; i < n_experts; i += blockDim.x) sbias[i] = __ldg(bias + i);
   for (int t0 = 0; t0 < n_tokens; t0 += kRouteTokens) {
     const int nt = min(kRouteTokens, n_tokens - t0);
-    float acc[kRouteExperts][kRouteTokens];
+    float acc[kRouteVals];  // [expert][token]
 #pragma unroll
-    for (int j = 0; j < kRouteExperts; ++j)
-#pragma unroll
-      for (int u = 0; u < kRouteTokens; ++u) acc[j][u] = 0.f;
+    for (int i = 0; i < kRouteVals; ++i) acc[i] = 0.f;
 #pragma unroll 2
     for (int i = tid; i < h4; i += kRouteWarps * 32) {
       float4 wv[kRouteExperts], xv[kRouteTokens];
@@ -240,32 +267,29 @@ moe_route_kernel(const float* __restrict__ x, const float* __restrict__ w, const
       for (int j = 0; j < kRouteExperts; ++j)
 #pragma unroll
         for (int u = 0; u < kRouteTokens; ++u) {
-          acc[j][u] = fmaf(wv[j].x, xv[u].x, acc[j][u]);
-          acc[j][u] = fmaf(wv[j].y, xv[u].y, acc[j][u]);
-          acc[j][u] = fmaf(wv[j].z, xv[u].z, acc[j][u]);
-          acc[j][u] = fmaf(wv[j].w, xv[u].w, acc[j][u]);
+          float a = acc[j * kRouteTokens + u];
+          a = fmaf(wv[j].x, xv[u].x, a);
+          a = fmaf(wv[j].y, xv[u].y, a);
+          a = fmaf(wv[j].z, xv[u].z, a);
+          a = fmaf(wv[j].w, xv[u].w, a);
+          acc[j * kRouteTokens + u] = a;
         }
     }
-#pragma unroll
-    for (int j = 0; j < kRouteExperts; ++j)
-#pragma unroll
-      for (int u = 0; u < kRouteTokens; ++u) {
-        const float v = warp_sum(acc[j][u]);
-        if (lane == 0) part[j][u][warp] = v;
-      }
+    const float total = warp_sum16(acc, lane);
+    if (!(lane & 1)) part[lane >> 1][warp] = total;
     __syncthreads();
-    if (tid < kRouteExperts * kRouteTokens) {
+    if (tid < kRouteVals) {
       const int j = tid / kRouteTokens, u = tid % kRouteTokens;
       if (u < nt && e0 + j < n_experts) {
-        float v = part[j][u][0];
+        float v = part[tid][0];
 #pragma unroll
-        for (int q = 1; q < kRouteWarps; ++q) v += part[j][u][q];
+        for (int q = 1; q < kRouteWarps; ++q) v += part[tid][q];
         logits[(size_t)(t0 + u) * n_experts + e0 + j] = v;
       }
     }
     __syncthreads();
   }
-  if (tid < kRouteExperts * kRouteTokens) __threadfence();
+  if (tid < kRouteVals) __threadfence();
   __syncthreads();
   if (tid == 0) last = atomicAdd(&g_route_arrivals, 1u) == gridDim.x - 1;
   __syncthreads();
@@ -273,9 +297,7 @@ moe_route_kernel(const float* __restrict__ x, const float* __restrict__ w, const
   __threadfence();
   // ---- the last block: every token's choice
   const int n_routes = n_tokens * top_k;
-  int* cnt = reinterpret_cast<int*>(sbias + n_experts);
-  int* off = cnt + n_experts;          // n_experts + 1
-  int* sid = off + n_experts + 1;      // n_routes
+  int* sid = reinterpret_cast<int*>(sbias + n_experts);  // n_routes: the routes' experts
   float* s = sm + (size_t)warp * 2 * n_experts;
   for (int t = warp; t < n_tokens; t += kRouteWarps)
     route_one(logits + (size_t)t * n_experts, bias ? sbias : nullptr, n_experts, top_k, scoring, scale, s,
@@ -284,46 +306,31 @@ moe_route_kernel(const float* __restrict__ x, const float* __restrict__ w, const
     if (tid == 0) g_route_arrivals = 0;
     return;
   }
-  for (int i = tid; i < n_experts; i += blockDim.x) cnt[i] = 0;
   __syncthreads();
-  // ---- counting sort of the routes by expert; rows of one expert keep the order of the routes
-  for (int r = tid; r < n_routes; r += blockDim.x) atomicAdd(&cnt[sid[r]], 1);
-  __syncthreads();
-  if (warp == 0) {
-    const int per = (n_experts + 31) / 32;
-    const int lo = min(lane * per, n_experts), hi = min(lo + per, n_experts);
-    int mine = 0;
-    for (int i = lo; i < hi; ++i) mine += cnt[i];
-    int incl = mine;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int v = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += v;
+  // ---- the routes sorted by expert; rows of one expert keep the order of the routes.  A route's
+  // place is the number of routes that come before it, an expert's offset the number of routes to
+  // experts below it: every thread counts for itself, nothing is scanned or scattered.
+  for (int r = tid; r < n_routes; r += blockDim.x) {
+    const int e = sid[r];
+    int before = 0;
+    for (int q = 0; q < n_routes; ++q) {
+      const int eq = sid[q];
+      before += (eq < e || (eq == e && q < r)) ? 1 : 0;
     }
-    int run = incl - mine;
-    for (int i = lo; i < hi; ++i) {
-      off[i] = run;
-      run += cnt[i];
+    routes[before] = r;
+    pos[r] = before;
+  }
+  for (int i = tid; i <= n_experts; i += blockDim.x) {
+    int below = 0, same = 0;
+    for (int q = 0; q < n_routes; ++q) {
+      const int eq = sid[q];
+      below += eq < i ? 1 : 0;
+      same += eq == i ? 1 : 0;
     }
-    if (lane == 31) off[n_experts] = incl;
+    offsets[i] = below;
+    if (i < n_experts) counts[i] = same;
   }
-  __syncthreads();
-  for (int i = tid; i < n_experts; i += blockDim.x) {
-    counts[i] = cnt[i];
-    offsets[i] = off[i];
-    int run = off[i];
-    if (cnt[i])
-      for (int r = 0; r < n_routes; ++r)
-        if (sid[r] == i) {
-          routes[run] = r;
-          pos[r] = run;
-          ++run;
-        }
-  }
-  if (tid == 0) {
-    offsets[n_experts] = off[n_experts];
-    g_route_arrivals = 0;  // every block has arrived: ready for the next launch
-  }
+  if (tid == 0) g_route_arrivals = 0;  // every block has arrived: ready for the next launch
 }
 
 }  // namespace ftk
@@ -349,7 +356,7 @@ extern "C" int ftk_router_topk(const float* logits, const float* bias, int n_tok
 }
 
 static size_t route_smem(int n_tokens, int n_experts, int top_k) {
-  return (size_t)(kRouteWarps * 2 + 1) * n_experts * sizeof(float) + (size_t)(2 * n_experts + 1 + n_tokens * top_k) * sizeof(int);
+  return (size_t)(kRouteWarps * 2 + 1) * n_experts * sizeof(float) + (size_t)(n_tokens * top_k) * sizeof(int);
 }
 
 extern "C" int ftk_moe_route_fits(int n_tokens, int hidden, int n_experts, int top_k) {
