@@ -113,6 +113,13 @@ int ftk_moe_gather(const void* h, int dtype, const int32_t* sorted_routes, int n
 int ftk_moe_gemm1_act(const void* x_sorted, const void* w1, int dtype, const int32_t* expert_offsets,
                       int n_experts, int n_routes, int hidden, int inter, int act, float alpha,
                       float limit, void* out, void* stream);
+// The same from the tokens' rows x [n_tokens, hidden] in their own order (bfloat16, tensor cores): row r of
+// expert order is the row of token sorted_routes[r] / top_k, gathered by the kernel (steps whose token tiles have
+// at most 32 rows: ask ftk_moe_gemm1_gather_fits).
+int ftk_moe_gemm1_gather_fits(int hidden, int inter, int n_experts, int n_routes);
+int ftk_moe_gemm1_act_gather(const void* x, const void* w1, const int32_t* expert_offsets, const int32_t* sorted_routes,
+                             int top_k, int n_tokens, int n_experts, int n_routes, int hidden, int inter, int act,
+                             float alpha, float limit, void* out, void* stream);
 int ftk_moe_gemm2(const void* a, const void* w2, int dtype, const int32_t* expert_offsets,
                   const int32_t* sorted_routes, const float* topk_weights, int n_experts, int n_routes,
                   int hidden, int inter, void* out, void* stream);

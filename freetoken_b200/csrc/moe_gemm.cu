@@ -122,9 +122,9 @@ using namespace ftk;
 
 // Defined in moe_gemm_tc.cu: the tcgen05 kernels for bfloat16; return -1 when the sizes are not
 // theirs (the caller then uses the kernels above).
-int ftk_moe_gemm1_act_tc(const void* x_sorted, const void* w1, const int32_t* expert_offsets, int n_experts,
+int ftk_moe_gemm1_act_tc(const void* x, const void* w1, const int32_t* expert_offsets, int n_experts,
                          int n_routes, int hidden, int inter, int act, float alpha, float limit, void* out,
-                         cudaStream_t stream);
+                         const int32_t* sorted_routes, int top_k, int n_tokens, cudaStream_t stream);
 int ftk_moe_gemm2_tc(const void* a, const void* w2, const int32_t* expert_offsets, const int32_t* sorted_routes,
                      const float* topk_weights, int n_experts, int n_routes, int hidden, int inter, void* out,
                      cudaStream_t stream);
@@ -140,7 +140,7 @@ extern "C" int ftk_moe_gemm1_act(const void* x_sorted, const void* w1, int dtype
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == FTK_BF16) {
     const int rc = ftk_moe_gemm1_act_tc(x_sorted, w1, expert_offsets, n_experts, n_routes, hidden, inter, act, alpha,
-                                        limit, out, s);
+                                        limit, out, nullptr, 0, 0, s);
     if (rc >= 0) return rc;
   }
   const int tiles = (n_routes + kBM - 1) / kBM + n_experts;
@@ -157,6 +157,24 @@ extern "C" int ftk_moe_gemm1_act(const void* x_sorted, const void* w1, int dtype
                                                               nullptr, n_routes, act, alpha, limit, (__nv_bfloat16*)out);
   FTK_LAUNCH_CHECK("moe_gemm1_act");
   return 0;
+}
+
+// The same from the tokens' rows in their own order: the kernel gathers the rows of each expert itself
+// (bfloat16 on the tensor cores only; ftk_moe_gemm1_gather_fits says whether the sizes are taken).
+extern "C" int ftk_moe_gemm1_act_gather(const void* x, const void* w1, const int32_t* expert_offsets,
+                                        const int32_t* sorted_routes, int top_k, int n_tokens, int n_experts,
+                                        int n_routes, int hidden, int inter, int act, float alpha, float limit,
+                                        void* out, void* stream) {
+  FTK_REQUIRE(act == FTK_ACT_SILU || act == FTK_ACT_SWIGLUOAI, "moe_gemm1_act_gather: unknown activation %d", act);
+  FTK_REQUIRE(n_experts >= 1 && n_routes >= 0 && hidden >= 1 && inter >= 1 && top_k >= 1 && n_tokens >= 1,
+              "moe_gemm1_act_gather: bad sizes");
+  if (n_routes == 0) return 0;
+  FTK_REQUIRE(x && w1 && expert_offsets && sorted_routes && out, "moe_gemm1_act_gather: null pointer");
+  const int rc = ftk_moe_gemm1_act_tc(x, w1, expert_offsets, n_experts, n_routes, hidden, inter, act, alpha, limit, out,
+                                      sorted_routes, top_k, n_tokens, (cudaStream_t)stream);
+  FTK_REQUIRE(rc >= 0, "moe_gemm1_act_gather: width %d, expert width %d, %d experts are not taken by the tensor-core "
+              "kernel (ask ftk_moe_gemm1_gather_fits first; copy the rows with moe_gather otherwise)", hidden, inter, n_experts);
+  return rc;
 }
 
 extern "C" int ftk_moe_gemm2(const void* a, const void* w2, int dtype, const int32_t* expert_offsets,

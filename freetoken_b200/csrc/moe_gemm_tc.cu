@@ -13,12 +13,17 @@
 //                      holds both halves and a warp finds gate and up of a feature 16 lanes apart; the
 //                      interleave is done by the tensor map itself (a 5-D view [E, I/16, 2, 16, K] of the
 //                      weights), so it is still one TMA instruction per stage.
-//   B (activations)  : TMA tile [BN rows x 64 k] from a 2-D map over the expert-sorted rows [R, K].
+//   B (activations)  : TMA tile [BN rows x 64 k] from a 2-D map over the expert-sorted rows [R, K]; or,
+//                      for gemm1 given the tokens in their own order and the sorted routes, gathered by
+//                      two more warps with 16-byte cp.async copies straight into the swizzled tile (a
+//                      token's row is read where the norm wrote it: no copy of the rows into expert
+//                      order, no launch for it).
 //   D (accumulator)  : TMEM, 128 lanes x BN float32 columns, two buffers so the epilogue of one tile
 //                      overlaps the main loop of the next.
 //
-// One CTA = 6 warps: warp 0 issues TMA loads, warp 1 allocates TMEM and issues tcgen05.mma, warps 2-5
-// read the accumulator (tcgen05.ld, one TMEM lane quadrant each), apply the epilogue and store.
+// One CTA = 8 warps: warp 0 issues TMA loads, warp 1 allocates TMEM and issues tcgen05.mma, warps 2-5
+// read the accumulator (tcgen05.ld, one TMEM lane quadrant each), apply the epilogue and store, warps
+// 6-7 gather token rows (gemm1 from unsorted tokens only; otherwise they leave at once).
 //   gemm1 epilogue: gate and up are rounded to bfloat16 (where the reference stores them), the up
 //                   half reaches the gate half's lanes by a warp shuffle, act(g, u) is stored.
 //   gemm2 epilogue: accumulator x route weight (float32), stored as bfloat16.
@@ -40,7 +45,8 @@ namespace ftk {
 
 __device__ int g_status[4];  // [0] first error code, [1] block, [2] detail; 0 = fine
 
-constexpr int kThreads = 192;
+constexpr int kThreads = 256;
+constexpr int kGatherThreads = 64;  // warps 6 and 7
 constexpr int kBK = 64;          // k elements per stage (128 bytes: one swizzle row)
 constexpr int kTileM = 128;      // accumulator rows (TMEM lanes)
 constexpr int kABytes = kTileM * kBK * 2;
@@ -53,8 +59,13 @@ struct TcParams {
   int n_out;                     // output features per row (I for gemm1, H for gemm2)
   int m_tiles;                   // feature tiles per expert
   int up_row_offset;             // gemm1: I (row of the up half that matches gate row 0)
-  const int32_t* sorted_routes;  // gemm2
+  const int32_t* sorted_routes;  // gemm2; gemm1 when it gathers
   const float* route_weights;    // gemm2
+  // gemm1 gathering its rows: the tokens' rows [gather_rows, K] in their own order; sorted row r is the row
+  // of token sorted_routes[r] / gather_div
+  const __nv_bfloat16* gather_src;
+  int gather_div;
+  int gather_rows;
   int n_routes;
   int act;
   float alpha, limit;
@@ -102,9 +113,10 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
   const uint32_t tiles_base = (smem_addr(dyn_smem) + 1023u) & ~1023u;
   unsigned char* tiles = dyn_smem + (tiles_base - smem_addr(dyn_smem));
 
+  const bool gathers = GATED && p.gather_src != nullptr;
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::kStages; ++s) {
-      mbar_init(&full_bar[s], 1);
+      mbar_init(&full_bar[s], gathers ? 1 + kGatherThreads : 1);  // the TMA thread, and every gathering thread
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -190,7 +202,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
       const bool thin_tail = 2 * (total_tiles - full_waves) <= G;
       const int depth_main = S::kDepth;
       auto stage_bytes = [&](int rows) {
-        const int nb = (rows + S::kBBoxRows - 1) / S::kBBoxRows;
+        const int nb = gathers ? 0 : (rows + S::kBBoxRows - 1) / S::kBBoxRows;
         return (uint32_t)(S::kAtoms * (kABytes + nb * S::kBBoxRows * kBK * 2));
       };
       auto load_a = [&](int s, int kb, int m0, int e) {
@@ -207,6 +219,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
         }
       };
       auto load_b = [&](int s, int kb, int row0, int rows) {
+        if (gathers) return;  // warps 6 and 7 bring the rows
         unsigned char* b = tiles + s * S::kStageBytes + S::kAtoms * kABytes;
         const int nb = (rows + S::kBBoxRows - 1) / S::kBBoxRows;
 #pragma unroll
@@ -277,6 +290,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
             abort_flag = 1;
             break;
           }
+          if (gathers) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // rows written by cp.async
           tc_fence_after();
           const uint32_t a_addr = tiles_base + s * S::kStageBytes;
 #pragma unroll
@@ -298,6 +312,61 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
         acc_phase ^= 1u << acc;
         acc ^= 1;
       }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------ gather (warps 6 and 7, gemm1 from unsorted tokens)
+    // Thread g copies 16-byte chunk g % 8 of the 128-byte row pieces of rows g / 8, g / 8 + 8, ... of the
+    // token tile, into the place the 128-byte swizzle gives it; a row without a token is filled with zeros.
+    if (gathers) {
+      const int g = (warp - 6) * 32 + lane, c = g & 7, rbase = g >> 3;
+      constexpr int kPer = BN / 8;  // rows of a tile per thread
+      pdl_wait();
+      int i = 0;
+      bool ok = true;
+      for (int t = t_first; t < total_tiles && ok; t += G) {
+        int e, row0, rows, m0;
+        locate(t, e, row0, rows, m0);
+        const int r_end = min(BN, (rows + 15) & ~15);  // the columns the MMAs compute
+        int tok[kPer];
+#pragma unroll
+        for (int q = 0; q < kPer; ++q) {
+          const int r = rbase + 8 * q;
+          int tk = -1;
+          if (r < rows) {
+            const int route = p.sorted_routes[row0 + r];
+            tk = route >= 0 ? route / p.gather_div : -1;
+            if (tk >= p.gather_rows) tk = -1;
+          }
+          tok[q] = tk;
+        }
+        for (int kb = 0; kb < k_blocks && ok; ++kb, ++i) {
+          const int s = i % S::kStages;
+          if (i >= S::kStages && !mbar_wait(&empty_bar[s], (uint32_t)(i / S::kStages - 1) & 1u, abortp)) {
+            ok = false;
+            atomicCAS(&g_status[0], 0, 105);
+            abort_flag = 1;
+            break;
+          }
+          const uint32_t b_addr = tiles_base + s * S::kStageBytes + S::kAtoms * kABytes;
+#pragma unroll
+          for (int h = 0; h < S::kAtoms; ++h) {
+            const int k0 = (kb * S::kAtoms + h) * kBK + c * 8;
+#pragma unroll
+            for (int q = 0; q < kPer; ++q) {
+              const int r = rbase + 8 * q;
+              if (r < r_end) {
+                const bool there = tok[q] >= 0 && k0 < p.K;  // (K is a multiple of 8: a chunk is inside or outside)
+                const __nv_bfloat16* src = p.gather_src + (there ? (size_t)tok[q] * p.K + k0 : 0);
+                const uint32_t dst = b_addr + h * S::kBBytes + r * 128 + ((c ^ (r & 7)) << 4);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(there ? 16 : 0) : "memory");
+              }
+            }
+          }
+          // this thread's arrival at the stage's barrier happens when its copies have landed
+          asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(&full_bar[s])) : "memory");
+        }
+      }
+      asm volatile("cp.async.wait_all;" ::: "memory");
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
@@ -503,7 +572,7 @@ static int run_tc(const void* x, int x_cols, const void* w, int w_rows, const Tc
     }
   }
   {
-    const uint64_t dims[2] = {K, (uint64_t)p.n_routes};
+    const uint64_t dims[2] = {K, (uint64_t)(p.gather_src ? p.gather_rows : p.n_routes)};  // (not read when the kernel gathers)
     const uint64_t strides[1] = {K * 2};
     const uint32_t box[2] = {kBK, (uint32_t)(bn < 32 ? bn : 32)};  // Smem::kBBoxRows
     if (!make_map(&mb, x, 2, dims, strides, box)) {
@@ -544,15 +613,35 @@ extern "C" int ftk_set_moe_tensor_cores(int enabled) {
   return 0;
 }
 
-int ftk_moe_gemm1_act_tc(const void* x_sorted, const void* w1, const int32_t* expert_offsets, int n_experts,
+// `sorted_routes` given: x holds the tokens' rows [n_tokens, hidden] in their own order and the kernel
+// gathers (row r of expert order is the row of token sorted_routes[r] / top_k); nullptr: x holds the
+// n_routes rows in expert order.
+int ftk_moe_gemm1_act_tc(const void* x, const void* w1, const int32_t* expert_offsets, int n_experts,
                          int n_routes, int hidden, int inter, int act, float alpha, float limit, void* out,
-                         cudaStream_t stream) {
+                         const int32_t* sorted_routes, int top_k, int n_tokens, cudaStream_t stream) {
   if (!g_tc_enabled) return -1;
   TcParams p{};
   p.offsets = expert_offsets; p.n_experts = n_experts; p.K = hidden; p.n_out = inter;
   p.m_tiles = (inter + 63) / 64; p.up_row_offset = inter; p.n_routes = n_routes;
   p.act = act; p.alpha = alpha; p.limit = limit; p.out = (__nv_bfloat16*)out;
-  return run_tc<true>(x_sorted, hidden, w1, 2 * inter, p, stream, "moe_gemm1_act (tcgen05)");
+  if (sorted_routes) {
+    if (top_k < 1 || n_tokens < 1 || pick_bn(n_routes, n_experts) > 32) return -1;
+    p.sorted_routes = sorted_routes;
+    p.gather_src = (const __nv_bfloat16*)x;
+    p.gather_div = top_k;
+    p.gather_rows = n_tokens;
+  }
+  return run_tc<true>(x, hidden, w1, 2 * inter, p, stream,
+                      sorted_routes ? "moe_gemm1_act (tcgen05, gathering)" : "moe_gemm1_act (tcgen05)");
+}
+
+// Whether ftk_moe_gemm1_act_gather will take these sizes on the tensor cores (bfloat16 only).  Token tiles of
+// up to 32 rows only: the two gathering warps keep up with those (measured at 256 experts of 3072 x 1536:
+// as fast as from copied rows up to 512 tokens x 8 routes; with 64-row tiles, 1,024 tokens, 0.82 ms against
+// 0.72, with 128-row tiles, 2,048 tokens, 1.67 against 0.77), so longer steps copy their rows first.
+extern "C" int ftk_moe_gemm1_gather_fits(int hidden, int inter, int n_experts, int n_routes) {
+  return g_tc_enabled && hidden % 8 == 0 && inter % 16 == 0 && n_experts <= kMaxExperts && n_routes >= 1 &&
+         pick_bn(n_routes, n_experts) <= 32;
 }
 
 int ftk_moe_gemm2_tc(const void* a, const void* w2, const int32_t* expert_offsets, const int32_t* sorted_routes,

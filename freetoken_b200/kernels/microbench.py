@@ -90,8 +90,11 @@ def bench_moe(a) -> dict:
     for name, fn, wbytes, flops in (
             ("gemm1", lambda: ops.moe_gemm1_act(x, w1, off, "silu", 1.702, 7.0, act), distinct * 2 * I * H * 2,
              2 * T * k * 2 * I * H),
+            ("gemm1_gather", (lambda: ops.moe_gemm1_act_gather(h, routes, k, w1, off, "silu", 1.702, 7.0, act))
+             if ops.moe_gemm1_gather_fits(torch.bfloat16, H, I, E, T * k) else None,
+             distinct * 2 * I * H * 2, 2 * T * k * 2 * I * H),
             ("gemm2", lambda: ops.moe_gemm2(act, w2, off, routes, wts, y), distinct * H * I * 2, 2 * T * k * H * I)):
-        if a.only and a.only != name:
+        if (a.only and a.only != name) or fn is None:
             continue
         us = _time(fn, a.iters, a.warmup, a.profile)
         out[name] = {"us": round(us, 2), "weight_bytes": wbytes, "gbs": round(wbytes / us / 1e3, 1),

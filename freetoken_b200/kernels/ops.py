@@ -91,6 +91,8 @@ _SIGNATURES = {
     "ftk_moe_small_down": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ftk_moe_gather": [_vp, _i, _vp, _i, _i, _i, _vp, _vp],
     "ftk_moe_gemm1_act": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _f, _f, _vp, _vp],
+    "ftk_moe_gemm1_gather_fits": [_i, _i, _i, _i],
+    "ftk_moe_gemm1_act_gather": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _vp],
     "ftk_moe_gemm2": [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "ftk_moe_combine": [_vp, _i, _vp, _i, _i, _i, _vp, _vp, _vp],
     "ftk_act_and_mul": [_vp, _i, _i, _i, _i, _f, _f, _vp, _vp],
@@ -663,6 +665,29 @@ def moe_gemm1_act(x_sorted: torch.Tensor, w1: torch.Tensor, expert_offsets: torc
                                     _dev(expert_offsets, "expert_offsets", torch.int32), E, R, H,
                                     two_i // 2, ACT_CODES[act], float(alpha), float(limit),
                                     _dev(out, "out"), _stream()), "moe_gemm1_act")
+
+
+def moe_gemm1_gather_fits(dtype: torch.dtype, hidden: int, inter: int, n_experts: int, n_routes: int) -> bool:
+    """Whether :func:`moe_gemm1_act_gather` takes these sizes (bfloat16 on the tensor cores, few enough routes
+    per expert for token tiles of at most 32 rows)."""
+    return dtype == torch.bfloat16 and bool(_lib().ftk_moe_gemm1_gather_fits(hidden, inter, n_experts, n_routes))
+
+
+def moe_gemm1_act_gather(h: torch.Tensor, sorted_routes: torch.Tensor, top_k: int, w1: torch.Tensor,
+                         expert_offsets: torch.Tensor, act: str, alpha: float, limit: float, out: torch.Tensor) -> None:
+    """:func:`moe_gather` and :func:`moe_gemm1_act` in one kernel: ``out[r] = act(h[sorted_routes[r] // top_k]
+    W1[e]^T)`` for the rows ``r`` of each expert; ``h [T, H]`` holds the tokens in their own order."""
+    T, H = h.shape
+    E, two_i, H2 = w1.shape
+    R = sorted_routes.numel()
+    if H2 != H or two_i % 2 or out.shape != (R, two_i // 2) or w1.dtype != h.dtype or out.dtype != h.dtype \
+            or h.dtype != torch.bfloat16 or R != T * top_k or not h.is_contiguous():
+        raise KernelError("moe_gemm1_act_gather: shapes or dtypes do not agree")
+    _check(_lib().ftk_moe_gemm1_act_gather(_dev(h, "h"), _dev(w1, "w1"),
+                                           _dev(expert_offsets, "expert_offsets", torch.int32),
+                                           _dev(sorted_routes, "sorted_routes", torch.int32), int(top_k), T, E, R, H,
+                                           two_i // 2, ACT_CODES[act], float(alpha), float(limit),
+                                           _dev(out, "out"), _stream()), "moe_gemm1_act_gather")
 
 
 def moe_gemm2(a: torch.Tensor, w2: torch.Tensor, expert_offsets: torch.Tensor,

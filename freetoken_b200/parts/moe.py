@@ -134,11 +134,16 @@ class MoE(FeedForward):
         record = self.env.shared.get("record_expert_counts")
         if record is not None:  # measurement hook: which experts a step touched, layer by layer
             record.append(counts.clone())
-        x = ws.get("moe.x", (R, self.hidden), dt, (cap * k, self.hidden))
-        ops.moe_gather(h, routes, k, x)
         a = ws.get("moe.act", (R, self.inter), dt, (cap * k, self.inter))
-        ops.moe_gemm1_act(x, self.params["experts.gate_up_proj"], offsets, self.act, self.alpha,
-                          self.limit, a)
+        if ops.moe_gemm1_gather_fits(dt, self.hidden, self.inter, E, R) and h.is_contiguous():
+            # the gate/up kernel reads each expert's rows where they lie: no copy into expert order
+            ops.moe_gemm1_act_gather(h, routes, k, self.params["experts.gate_up_proj"], offsets, self.act,
+                                     self.alpha, self.limit, a)
+        else:
+            x = ws.get("moe.x", (R, self.hidden), dt, (cap * k, self.hidden))
+            ops.moe_gather(h, routes, k, x)
+            ops.moe_gemm1_act(x, self.params["experts.gate_up_proj"], offsets, self.act, self.alpha,
+                              self.limit, a)
         y = ws.get("moe.y", (R, self.hidden), dt, (cap * k, self.hidden))
         ops.moe_gemm2(a, self.params["experts.down_proj"], offsets, routes, wts.view(-1), y)
         shared = self.shared.forward(h, step) if self.shared is not None else None

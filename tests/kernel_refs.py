@@ -194,6 +194,10 @@ def linear(x, w, out):
     out.copy_((x.float() @ w.float().T).to(out.dtype))
 
 
+def moe_gemm1_gather_fits(dtype, hidden, inter, n_experts, n_routes):
+    return False  # the CPU tests copy the rows first
+
+
 def attention_tc_fits(head_dim, page_size, group):
     return False  # the CPU tests plan for the other kernels
 
@@ -280,7 +284,7 @@ def sample(logits, temperature, top_k, top_p, u, out):
 
 
 ALL = ["sparse_score_fits", "moe_small_fits", "copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "add_rmsnorm_routes", "act_and_mul", "cast", "table_update", "norm_rope_store",
-       "paged_attention", "router_topk", "moe_permute", "moe_route", "moe_route_fits", "linear", "attention_tc_fits", "attention_tc_few_fits", "moe_gather", "moe_gemm1_act", "moe_gemm2",
+       "paged_attention", "router_topk", "moe_permute", "moe_route", "moe_route_fits", "linear", "attention_tc_fits", "attention_tc_few_fits", "moe_gemm1_gather_fits", "moe_gather", "moe_gemm1_act", "moe_gemm2",
        "moe_combine", "sample"]
 
 

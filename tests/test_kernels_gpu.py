@@ -827,6 +827,45 @@ def test_moe_tensor_core_gemms_match_cuda_core_gemms(E, H, I, R, k):
         assert ((got.float() - exact).abs() <= bound).all()
 
 
+@pytest.mark.parametrize("E,H,I,T,k", [(256, 3072, 1536, 8, 8), (256, 3072, 1536, 500, 8), (32, 512, 256, 120, 4),
+                                       (8, 64, 32, 5, 2), (6, 200, 48, 30, 3), (16, 1000, 112, 120, 2), (4, 128, 64, 1, 4)])
+def test_moe_gate_up_product_gathers_its_rows(E, H, I, T, k):
+    """The gate/up kernel reading each expert's rows from the tokens in their own order (two warps copy
+    them into the swizzled tile) against the same kernel on rows copied into expert order first: the
+    same products in the same order, so the results are equal bit for bit (the other tests hold that kernel
+    to the references).  Decode-like and prefill-like
+    row counts (token tiles of 16 and 32 rows), a crowded expert, widths that end inside a 64-element piece of k."""
+    assert ops.moe_gemm1_gather_fits(torch.bfloat16, H, I, E, T * k)
+    assert not ops.moe_gemm1_gather_fits(torch.float32, H, I, E, T * k)
+    assert not ops.moe_gemm1_gather_fits(torch.bfloat16, H + 4, I, E, T * k)
+    assert not ops.moe_gemm1_gather_fits(torch.bfloat16, H, I, E, 100 * E)  # token tiles of more than 32 rows
+    g = torch.Generator().manual_seed(T + k)
+    ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32)
+    if T > 100:
+        ids[: T // 2, 0] = 3  # one crowded expert: several token tiles
+        ids[: T // 2, 1:] = torch.stack([torch.randperm(E - 4, generator=g)[: k - 1] + 4 for _ in range(T // 2)]).to(torch.int32)
+    ids = ids.to(DEV)
+    counts = torch.empty(E, dtype=torch.int32, device=DEV)
+    off = torch.empty(E + 1, dtype=torch.int32, device=DEV)
+    routes = torch.empty(T * k, dtype=torch.int32, device=DEV)
+    pos = torch.empty(T * k, dtype=torch.int32, device=DEV)
+    ops.moe_permute(ids, E, counts, off, routes, pos)
+    h = rnd(T, H, dtype=torch.bfloat16)
+    w1 = rnd(E, 2 * I, H, dtype=torch.bfloat16, scale=0.05)
+    x = torch.empty(T * k, H, dtype=torch.bfloat16, device=DEV)
+    ops.moe_gather(h, routes, k, x)
+    want = torch.full((T * k, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    got = torch.full((T * k, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.moe_gemm1_act(x, w1, off, "swigluoai", 1.702, 7.0, want)
+    for _ in range(2):  # twice: the stages' barriers start from where the launch before left nothing
+        got.fill_(float("nan"))
+        ops.moe_gemm1_act_gather(h, routes, k, w1, off, "swigluoai", 1.702, 7.0, got)
+        assert not torch.isnan(got).any()
+        assert torch.equal(got, want)
+    assert ops.read_status() == 0
+    assert any("gate/up" in n for n in ops.variant_counts())
+
+
 @pytest.mark.parametrize("V", [256, 331, 50000, 200064, 16390])
 def test_sample(V):
     R = 9
