@@ -88,7 +88,7 @@ int ftk_sparse_select(const void* iq, const void* ik_slab, int dtype, const int3
 // Whether bfloat16 block scores of these sizes can be taken on the tensor cores (`scores [T, n_heads, max_blocks]`
 // float32 scratch must then be given to ftk_sparse_select).
 int ftk_sparse_score_fits(int n_heads, int dim, int block_size);
-int ftk_router_topk(const float* logits, const float* bias, int n_tokens, int n_experts, int top_k,
+int ftk_router_topk(const float* logits, int n_parts, const float* bias, int n_tokens, int n_experts, int top_k,
                     int scoring, float scale, int32_t* ids, float* weights, void* stream);
 // Router logits (float32 x [T, hidden] times gate_w [E, hidden]), choice and sort of the routes in one
 // launch, for steps of at most 32 tokens (beyond that the

@@ -13,21 +13,30 @@ namespace ftk {
 
 constexpr int kRouterWarps = 4;
 
+// A token's logit of expert e: the row holds n_parts blocks of n_experts values that are added in their
+// order (one block: the logits themselves; three: the products of the activations with the three
+// bfloat16 pieces of the float32 router weights, largest first).
+__device__ __forceinline__ float logit_of(const float* __restrict__ row, int e, int n_experts, int n_parts) {
+  float v = __ldcg(row + e);
+  for (int q = 1; q < n_parts; ++q) v += __ldcg(row + (size_t)q * n_experts + e);
+  return v;
+}
+
 // Scores, choice and weights of one token, by one warp.  `s` and `c` hold n_experts floats each.
-__device__ __forceinline__ void route_token(const float* __restrict__ row, const float* __restrict__ bias,
+__device__ __forceinline__ void route_token(const float* __restrict__ row, int n_parts, const float* __restrict__ bias,
                                             int n_experts, int top_k, int scoring, float scale, float* s, float* c,
                                             int32_t* __restrict__ ids, float* __restrict__ weights,
                                             int32_t* ids_copy) {
   const int lane = threadIdx.x & 31;
   if (scoring == FTK_SCORE_SIGMOID) {
-    for (int e = lane; e < n_experts; e += 32) s[e] = 1.f / (1.f + expf(-__ldcg(row + e)));
+    for (int e = lane; e < n_experts; e += 32) s[e] = 1.f / (1.f + expf(-logit_of(row, e, n_experts, n_parts)));
   } else {
     float mx = -INFINITY;
-    for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, __ldcg(row + e));
+    for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, logit_of(row, e, n_experts, n_parts));
     mx = warp_max(mx);
     float sum = 0.f;
     for (int e = lane; e < n_experts; e += 32) {
-      const float v = expf(__ldcg(row + e) - mx);
+      const float v = expf(logit_of(row, e, n_experts, n_parts) - mx);
       s[e] = v;
       sum += v;
     }
@@ -81,7 +90,7 @@ __device__ __forceinline__ unsigned int order_key(float v) {
 }
 
 template <int PER>
-__device__ __forceinline__ void route_token_regs(const float* __restrict__ row, const float* __restrict__ bias,
+__device__ __forceinline__ void route_token_regs(const float* __restrict__ row, int n_parts, const float* __restrict__ bias,
                                                  int n_experts, int top_k, int scoring, float scale, float* wbuf,
                                                  int32_t* __restrict__ ids, float* __restrict__ weights,
                                                  int32_t* ids_copy) {
@@ -91,7 +100,7 @@ __device__ __forceinline__ void route_token_regs(const float* __restrict__ row, 
 #pragma unroll
   for (int q = 0; q < PER; ++q) {
     const int e = q * 32 + lane;
-    sv[q] = e < n_experts ? __ldcg(row + e) : -INFINITY;
+    sv[q] = e < n_experts ? logit_of(row, e, n_experts, n_parts) : -INFINITY;
   }
   if (scoring == FTK_SCORE_SIGMOID) {
 #pragma unroll
@@ -156,20 +165,20 @@ __device__ __forceinline__ void route_token_regs(const float* __restrict__ row, 
 }
 
 // One token by one warp, in registers where the experts fit; `s` holds 2 * n_experts floats.
-__device__ __forceinline__ void route_one(const float* __restrict__ row, const float* __restrict__ bias, int n_experts,
+__device__ __forceinline__ void route_one(const float* __restrict__ row, int n_parts, const float* __restrict__ bias, int n_experts,
                                           int top_k, int scoring, float scale, float* s, int32_t* __restrict__ ids,
                                           float* __restrict__ weights, int32_t* ids_copy) {
   if (n_experts <= 128)
-    route_token_regs<4>(row, bias, n_experts, top_k, scoring, scale, s, ids, weights, ids_copy);
+    route_token_regs<4>(row, n_parts, bias, n_experts, top_k, scoring, scale, s, ids, weights, ids_copy);
   else if (n_experts <= 256)
-    route_token_regs<8>(row, bias, n_experts, top_k, scoring, scale, s, ids, weights, ids_copy);
+    route_token_regs<8>(row, n_parts, bias, n_experts, top_k, scoring, scale, s, ids, weights, ids_copy);
   else if (n_experts <= 512)
-    route_token_regs<16>(row, bias, n_experts, top_k, scoring, scale, s, ids, weights, ids_copy);
+    route_token_regs<16>(row, n_parts, bias, n_experts, top_k, scoring, scale, s, ids, weights, ids_copy);
   else
-    route_token(row, bias, n_experts, top_k, scoring, scale, s, s + n_experts, ids, weights, ids_copy);
+    route_token(row, n_parts, bias, n_experts, top_k, scoring, scale, s, s + n_experts, ids, weights, ids_copy);
 }
 
-__global__ void router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+__global__ void router_topk_kernel(const float* __restrict__ logits, int n_parts, const float* __restrict__ bias,
                                    int n_tokens, int n_experts, int top_k, int scoring, float scale,
                                    int32_t* __restrict__ ids, float* __restrict__ weights) {
   pdl_wait();
@@ -179,7 +188,7 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, const float
   const int t = blockIdx.x * kRouterWarps + warp;
   if (t >= n_tokens) return;
   float* s = sm + (size_t)warp * 2 * n_experts;  // unbiased scores
-  route_one(logits + (size_t)t * n_experts, bias, n_experts, top_k, scoring, scale, s,
+  route_one(logits + (size_t)t * n_parts * n_experts, n_parts, bias, n_experts, top_k, scoring, scale, s,
             ids + (size_t)t * top_k, weights + (size_t)t * top_k, nullptr);
 }
 
@@ -300,7 +309,7 @@ moe_route_kernel(const float* __restrict__ x, const float* __restrict__ w, const
   int* sid = reinterpret_cast<int*>(sbias + n_experts);  // n_routes: the routes' experts
   float* s = sm + (size_t)warp * 2 * n_experts;
   for (int t = warp; t < n_tokens; t += kRouteWarps)
-    route_one(logits + (size_t)t * n_experts, bias ? sbias : nullptr, n_experts, top_k, scoring, scale, s,
+    route_one(logits + (size_t)t * n_experts, 1, bias ? sbias : nullptr, n_experts, top_k, scoring, scale, s,
               ids + (size_t)t * top_k, weights + (size_t)t * top_k, do_sort ? sid + (size_t)t * top_k : nullptr);
   if (!do_sort) {  // the caller's kernels take the routes in token order
     if (tid == 0) g_route_arrivals = 0;
@@ -337,8 +346,9 @@ moe_route_kernel(const float* __restrict__ x, const float* __restrict__ w, const
 
 using namespace ftk;
 
-extern "C" int ftk_router_topk(const float* logits, const float* bias, int n_tokens, int n_experts, int top_k,
+extern "C" int ftk_router_topk(const float* logits, int n_parts, const float* bias, int n_tokens, int n_experts, int top_k,
                                int scoring, float scale, int32_t* ids, float* weights, void* stream) {
+  FTK_REQUIRE(n_parts >= 1 && n_parts <= 4, "router_topk: %d blocks of logits per token (1 to 4)", n_parts);
   FTK_REQUIRE(scoring == FTK_SCORE_SIGMOID || scoring == FTK_SCORE_SOFTMAX, "router_topk: unknown scoring %d", scoring);
   FTK_REQUIRE(n_experts >= 1 && top_k >= 1 && top_k <= n_experts, "router_topk: top_k=%d of %d experts", top_k, n_experts);
   FTK_REQUIRE(n_tokens >= 0, "router_topk: bad token count");
@@ -348,8 +358,8 @@ extern "C" int ftk_router_topk(const float* logits, const float* bias, int n_tok
   FTK_REQUIRE(smem <= 200 * 1024, "router_topk: %d experts exceed what one block can hold (6400)", n_experts);
   if (smem > 48 * 1024) cudaFuncSetAttribute(router_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   const int blocks = (n_tokens + kRouterWarps - 1) / kRouterWarps;
-  note_variant("routing: expert choice from given logits");
-  FTK_LAUNCH(router_topk_kernel, blocks, kRouterWarps * 32, smem, (cudaStream_t)stream, logits, bias, n_tokens, n_experts, top_k,
+  note_variant(n_parts > 1 ? "routing: expert choice from logits given in pieces" : "routing: expert choice from given logits");
+  FTK_LAUNCH(router_topk_kernel, blocks, kRouterWarps * 32, smem, (cudaStream_t)stream, logits, n_parts, bias, n_tokens, n_experts, top_k,
                                                                                scoring, scale, ids, weights);
   FTK_LAUNCH_CHECK("router_topk");
   return 0;

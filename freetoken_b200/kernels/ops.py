@@ -80,7 +80,7 @@ _SIGNATURES = {
                                    _i, _i, _i, _i, _i, _i, _f, _vp, _i, _i, _vp],
     "ftk_sparse_select": [_vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
     "ftk_sparse_score_fits": [_i, _i, _i],
-    "ftk_router_topk": [_vp, _vp, _i, _i, _i, _i, _f, _vp, _vp, _vp],
+    "ftk_router_topk": [_vp, _i, _vp, _i, _i, _i, _i, _f, _vp, _vp, _vp],
     "ftk_moe_permute": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp],
     "ftk_moe_route_fits": [_i, _i, _i, _i],
     "ftk_moe_route": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp],
@@ -482,19 +482,25 @@ def sparse_select(iq: torch.Tensor, ik_slab: torch.Tensor, block_table: torch.Te
 
 # --------------------------------------------------------------------------- experts
 def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, scoring: str,
-                scale: float, ids: torch.Tensor, weights: torch.Tensor) -> None:
+                scale: float, ids: torch.Tensor, weights: torch.Tensor, n_parts: int = 1) -> None:
     """Expert choice from float32 router logits ``[T, E]``.
 
     sigmoid: ``s = sigmoid(l)``; choice by ``s + bias``; ``w = s[ids] / (sum + 1e-20) * scale``.
     softmax: ``s = softmax(l)``; choice by ``s (+ bias)``; ``w = s[ids] / sum * scale``.
     The largest goes first; the lower expert index wins a tie.
+
+    With ``n_parts > 1`` the logits come as ``[T, n_parts * E]``: a token's logit of expert ``e`` is the
+    32-bit sum of ``logits[t, q * E + e]`` over the parts ``q`` in their order.
     """
-    T, E = logits.shape
+    T, PE = logits.shape
+    if n_parts < 1 or PE % n_parts or not logits.is_contiguous():
+        raise KernelError("router_topk: logits must be contiguous [T, n_parts * E]")
+    E = PE // n_parts
     if ids.shape != (T, top_k) or weights.shape != (T, top_k):
         raise KernelError("router_topk: ids / weights must be [T, top_k]")
     if bias is not None and bias.shape != (E,):
         raise KernelError("router_topk: bias must be [E]")
-    _check(_lib().ftk_router_topk(_dev(logits, "logits", torch.float32), _dev(bias, "bias", torch.float32),
+    _check(_lib().ftk_router_topk(_dev(logits, "logits", torch.float32), int(n_parts), _dev(bias, "bias", torch.float32),
                                   T, E, top_k, SCORE_CODES[scoring], float(scale),
                                   _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32),
                                   _stream()), "router_topk")

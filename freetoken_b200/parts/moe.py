@@ -27,11 +27,36 @@ from .base import FEED_FORWARDS, BuildEnv, FeedForward, Part, RouteSum, StepStat
 from .mlp import GatedMLP
 
 
+SPLIT_ROUTER_PRODUCT = True  # long bfloat16 steps: router logits as three tensor-core products (see split_in_three)
+
+
+def split_in_three(w: torch.Tensor) -> Optional[torch.Tensor]:
+    """The float32 matrix ``w [E, H]`` as three bfloat16 matrices stacked to ``[3 E, H]`` whose sum is ``w``
+    exactly (8 + 8 + 8 bits of its 24-bit mantissas), largest first; None where that is not so (values near
+    the end of the exponent range).
+
+    The router's input in a bfloat16 step is the norm's bfloat16 output, so a product of it with a
+    bfloat16 piece is exact in 32 bits and ``x W^T`` is the 32-bit sum of three bfloat16 matrix products
+    with 32-bit accumulators: the tensor cores take what the float32 product of the reference
+    (python/freetoken/models/minimax_m3/moe.py:71-73) does on the CUDA cores, with the same products and
+    other rounding of the partial sums only."""
+    w = w.float()
+    hi = w.to(torch.bfloat16)
+    r1 = w - hi.float()
+    mid = r1.to(torch.bfloat16)
+    r2 = r1 - mid.float()
+    lo = r2.to(torch.bfloat16)
+    if not torch.equal((hi.float() + mid.float()) + lo.float(), w) or not torch.isfinite(w).all():
+        return None
+    return torch.cat([hi, mid, lo], dim=0).contiguous()
+
+
 @FEED_FORWARDS.register("moe")
 class MoE(FeedForward):
     """params: ``hidden``, ``inter``, ``n_experts``, ``top_k``, ``scoring`` ("sigmoid" |
     "softmax"), ``bias`` (bool), ``scale``, ``act``, ``alpha``, ``limit``,
-    ``shared_inter`` (0 = no shared expert)."""
+    ``shared_inter`` (0 = no shared expert).  ``h_f32`` given to the forward calls of a bfloat16 model
+    is ``float32(h)``, as a norm's ``out_f32`` is."""
 
     wants_f32_input = True
 
@@ -71,11 +96,17 @@ class MoE(FeedForward):
     def children(self) -> Dict[str, Part]:
         return {"shared_experts": self.shared} if self.shared is not None else {}
 
+    def bind(self, tensors) -> None:
+        super().bind(tensors)
+        self._gate_pieces = None
+        if self.env.dtype == torch.bfloat16 and SPLIT_ROUTER_PRODUCT:
+            self._gate_pieces = split_in_three(self.params["gate.weight"])
+
     def workspace_bytes(self, n_tokens: int) -> int:
         item = 4 if self.env.dtype == torch.float32 else 2
         T, k, H, I, E = n_tokens, self.top_k, self.hidden, self.inter, self.n_experts
         routed = T * k * ((2 * H + I) * item + 4 * 4)  # expert-ordered input, activation, output; ids, weights, sort
-        return routed + T * (H * (4 + item) + E * 4) + (2 * E + 1) * 4
+        return routed + T * (H * (4 + item) + E * 4 * 4) + (2 * E + 1) * 4  # (logits, and their three pieces)
 
     def forward(self, h: torch.Tensor, step: StepState, h_f32: Optional[torch.Tensor] = None) -> torch.Tensor:
         return self.forward_lazy(h, step, h_f32).rows()
@@ -127,6 +158,12 @@ class MoE(FeedForward):
         if ops.moe_route_fits(T, self.hidden, E, k):  # small steps: logits, choice and sort in one launch
             ops.moe_route(h_f32, self.params["gate.weight"], bias, k, self.scoring, self.scale, logits, ids, wts,
                           counts, offsets, routes, pos)
+        elif self._gate_pieces is not None and h.dtype == torch.bfloat16:
+            # h_f32 is float32(h): the three products below are exact, their 32-bit sums are the logits
+            pieces = ws.get("moe.logit_pieces", (T, 3 * E), torch.float32, (cap, 3 * E))
+            torch.mm(h, self._gate_pieces.t(), out_dtype=torch.float32, out=pieces)
+            ops.router_topk(pieces, bias, k, self.scoring, self.scale, ids, wts, n_parts=3)
+            ops.moe_permute(ids, E, counts, offsets, routes, pos)
         else:
             torch.matmul(h_f32, self.params["gate.weight"].t(), out=logits)
             ops.router_topk(logits, bias, k, self.scoring, self.scale, ids, wts)

@@ -168,8 +168,13 @@ def sparse_select(iq, ik_slab, block_table, seg_info, n_segs, block_size, local_
             sel[q_start + t, :, : chosen.shape[1]] = chosen.to(torch.int32)
 
 
-def router_topk(logits, bias, top_k, scoring, scale, ids, weights):
+def router_topk(logits, bias, top_k, scoring, scale, ids, weights, n_parts=1):
     l = logits.float()
+    if n_parts > 1:
+        parts = l.view(l.shape[0], n_parts, -1)
+        l = parts[:, 0]
+        for q in range(1, n_parts):
+            l = l + parts[:, q]
     s = torch.sigmoid(l) if scoring == "sigmoid" else torch.softmax(l, dim=-1)
     c = s + bias.float() if bias is not None else s
     idx = torch.argsort(c, dim=-1, descending=True, stable=True)[:, :top_k]

@@ -827,6 +827,43 @@ def test_moe_tensor_core_gemms_match_cuda_core_gemms(E, H, I, R, k):
         assert ((got.float() - exact).abs() <= bound).all()
 
 
+@pytest.mark.parametrize("scoring,bias", [("sigmoid", True), ("softmax", False)])
+@pytest.mark.parametrize("T,H,E,k", [(300, 3072, 256, 8), (70, 520, 33, 5), (40, 96, 301, 2)])
+def test_router_logits_from_three_bfloat16_products(scoring, bias, T, H, E, k):
+    """Long bfloat16 steps: the float32 router weights split into three bfloat16 pieces whose sum is the
+    weight exactly, three tensor-core products with 32-bit accumulators, and the choice kernel adding the
+    pieces.  The products are the exact ones; what differs from the float32 matrix product is the rounding
+    of the partial sums (the tensor cores' 32-bit accumulators cut off where the CUDA cores round), so the
+    distance to the float64 product is held to 1.5e-6 of sum |x||w| (measured: 6.4e-7 at a width of 3,072
+    against 1.2e-7 for the library's float32 product; 1.8e-4 is the bound of a 32-bit sum of that length).
+    The choice is the one the reference statement makes from the summed logits."""
+    from freetoken_b200.parts.moe import split_in_three
+
+    w = rnd(E, H, scale=H ** -0.5, seed=5)
+    w[0, 0] = 1.0 + 2.0 ** -23   # needs all three pieces
+    w[1, 1] = -3.0e-30           # tiny
+    pieces = split_in_three(w)
+    assert pieces is not None and pieces.shape == (3 * E, H) and pieces.dtype == torch.bfloat16
+    assert torch.equal((pieces[:E].float() + pieces[E:2 * E].float()) + pieces[2 * E:].float(), w)
+    assert split_in_three(torch.full((2, 8), float("inf"), device=DEV)) is None
+    x = rnd(T, H, dtype=torch.bfloat16, scale=1.0)
+    got3 = torch.mm(x, pieces.t(), out_dtype=torch.float32)
+    logits = (got3[:, :E] + got3[:, E:2 * E]) + got3[:, 2 * E:]
+    exact = x.double() @ w.double().T
+    plain = x.float() @ w.t()
+    scale_ = (x.double().abs() @ w.double().abs().T)  # what the rounding errors are relative to
+    err_split = ((logits.double() - exact).abs() / scale_).max().item()
+    err_plain = ((plain.double() - exact).abs() / scale_).max().item()
+    assert err_split < 1.5e-6 and err_split < 16 * err_plain + 1e-7, (err_split, err_plain)
+    b = rnd(E, scale=0.01, seed=7) if bias else None
+    ids, wts = torch.empty(T, k, dtype=torch.int32, device=DEV), torch.empty(T, k, device=DEV)
+    ids2, w2 = torch.empty_like(ids), torch.empty_like(wts)
+    ops.router_topk(got3.contiguous(), b, k, scoring, 2.5, ids, wts, n_parts=3)
+    ref.router_topk(logits, b, k, scoring, 2.5, ids2, w2)
+    assert torch.equal(ids, ids2)
+    torch.testing.assert_close(wts, w2, rtol=1e-5, atol=1e-7)
+
+
 @pytest.mark.parametrize("E,H,I,T,k", [(256, 3072, 1536, 8, 8), (256, 3072, 1536, 500, 8), (32, 512, 256, 120, 4),
                                        (8, 64, 32, 5, 2), (6, 200, 48, 30, 3), (16, 1000, 112, 120, 2), (4, 128, 64, 1, 4)])
 def test_moe_gate_up_product_gathers_its_rows(E, H, I, T, k):

@@ -149,7 +149,7 @@ def test_cuts_agree_at_real_sizes(dtype, real):
         assert any(k.startswith("expert gate/up product: tcgen05") and "deep pipeline" in k and
                    any(f"{n} tokens a tile" in k for n in (64, 128, 256)) for k in ran_whole), ran_whole
         assert ran_whole.get("route sort: three passes over 128-route segments")
-        assert ran_whole.get("routing: expert choice from given logits")
+        assert ran_whole.get("routing: expert choice from logits given in pieces")
         assert ran_cut.get("attention: tcgen05, 128-row query tiles") and ran_cut.get("attention: bfloat16 mma.sync, 64-row tiles")
         assert ran_mixed.get("attention: tcgen05, 128-row query tiles")
     for name, ran in (("whole", ran_whole), ("portions", ran_cut), ("mixed", ran_mixed)):
