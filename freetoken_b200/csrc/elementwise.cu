@@ -3,7 +3,6 @@
 //
 // All of them are memory-bound; each row is read once, in 8- or 16-byte pieces where the row
 // length allows it (a scalar path takes every other length), and all arithmetic is float32.
-#include <cstdlib>
 #include "common.cuh"
 
 namespace ftk {
@@ -295,7 +294,6 @@ static int launch_norm(const void* x, float* residual, const float* weight, void
   int threads = hidden >= 2048 ? 256 : 128;
   // few rows: a thread per four elements, so that every load of a row is in flight at once
   if (n_rows <= 64 && vec) threads = hidden / 4 >= 1024 ? 1024 : (hidden / 4 + 31) / 32 * 32 > threads ? (hidden / 4 + 31) / 32 * 32 : threads;
-  if (const char* e = getenv("FTK_NORM_THREADS")) threads = atoi(e);
   const size_t smem = (size_t)hidden * sizeof(float);
   auto kv = add_rmsnorm_kernel<XT, OT, true>;
   auto ks = add_rmsnorm_kernel<XT, OT, false>;

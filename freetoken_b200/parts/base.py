@@ -243,6 +243,10 @@ class FeedForward(Part):
 
     wants_f32_input: bool = False  # ask the preceding norm for a 32-bit copy of its output
 
+    def f32_input_needed(self, n_tokens: int) -> bool:
+        """Whether a step of ``n_tokens`` tokens will read that copy (``h_f32`` may be None otherwise)."""
+        return self.wants_f32_input
+
 
 class Embedding(Part):
     """Token ids to rows of the 32-bit residual stream."""

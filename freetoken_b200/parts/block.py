@@ -48,7 +48,7 @@ class PreNormResidualBlock(Block):
             a = self.mixer.forward(h, step, cache, writes_cache)
         h2 = ws.get("block.h2", (T, self.hidden), dt, (cap, self.hidden))
         h32 = None
-        if self.ffn.wants_f32_input and dt != torch.float32:
+        if self.ffn.f32_input_needed(T) and dt != torch.float32:
             h32 = ws.get("block.h2_f32", (T, self.hidden), torch.float32, (cap, self.hidden))
         self.post_norm.add_forward(a, residual, h2, out_f32=h32)
         lazy = getattr(self.ffn, "forward_lazy", None)

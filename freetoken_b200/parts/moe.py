@@ -77,6 +77,7 @@ class MoE(FeedForward):
         self.alpha = float(spec.get("alpha", 1.702))
         self.limit = float(spec.get("limit", 7.0))
         self.shared_inter = int(spec.get("shared_inter", 0) or 0)
+        self._gate_pieces: Optional[torch.Tensor] = None
         self.shared: Optional[GatedMLP] = None
         if self.shared_inter:
             self.shared = GatedMLP(PartSpec("gated_mlp", dict(
@@ -95,6 +96,11 @@ class MoE(FeedForward):
 
     def children(self) -> Dict[str, Part]:
         return {"shared_experts": self.shared} if self.shared is not None else {}
+
+    def f32_input_needed(self, n_tokens: int) -> bool:
+        # long bfloat16 steps take the router product from the bfloat16 rows themselves
+        return not (self._gate_pieces is not None and self.env.dtype == torch.bfloat16
+                    and not ops.moe_route_fits(n_tokens, self.hidden, self.n_experts, self.top_k))
 
     def bind(self, tensors) -> None:
         super().bind(tensors)
@@ -138,7 +144,7 @@ class MoE(FeedForward):
         T = h.shape[0]
         ws, dt, cap = self.env.workspace, self.env.dtype, self.env.max_step_tokens
         k, E, R = self.top_k, self.n_experts, T * self.top_k
-        if h_f32 is None:
+        if h_f32 is None and self.f32_input_needed(T):
             if h.dtype == torch.float32:
                 h_f32 = h
             else:
@@ -159,7 +165,7 @@ class MoE(FeedForward):
             ops.moe_route(h_f32, self.params["gate.weight"], bias, k, self.scoring, self.scale, logits, ids, wts,
                           counts, offsets, routes, pos)
         elif self._gate_pieces is not None and h.dtype == torch.bfloat16:
-            # h_f32 is float32(h): the three products below are exact, their 32-bit sums are the logits
+            # the router reads float32(h): the three products below are exact, their 32-bit sums are the logits
             pieces = ws.get("moe.logit_pieces", (T, 3 * E), torch.float32, (cap, 3 * E))
             torch.mm(h, self._gate_pieces.t(), out_dtype=torch.float32, out=pieces)
             ops.router_topk(pieces, bias, k, self.scoring, self.scale, ids, wts, n_parts=3)
