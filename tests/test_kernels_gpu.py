@@ -652,7 +652,9 @@ def test_linear_pads_few_rows_inside_its_buffers(T, N, K, dtype):
 
 
 @pytest.mark.parametrize("scoring,bias", [("sigmoid", True), ("softmax", False)])
-@pytest.mark.parametrize("T,H,E,k", [(1, 64, 8, 2), (8, 3072, 256, 8), (13, 100, 7, 3), (32, 520, 33, 5), (9, 36, 301, 1)])
+@pytest.mark.parametrize("T,H,E,k", [(1, 64, 8, 2), (8, 3072, 256, 8), (13, 100, 7, 3), (32, 520, 33, 5), (9, 36, 301, 1),
+                                     (1, 3072, 256, 8), (3, 64, 256, 8), (5, 128, 200, 6), (6, 96, 64, 64), (12, 256, 100, 4),
+                                     (7, 64, 40, 40)])
 def test_moe_route_in_one_launch(scoring, bias, T, H, E, k):
     """Logits, choice and sort in one launch against the three separate statements; run several
     times so that the arrival counter is seen to come back to zero."""
