@@ -189,11 +189,16 @@ norm_rope_store_vec_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, in
     // rotation partners: the lane half a rotary span away, on either side
     const int hop = half >> 3;  // lanes per half span
     float partner[8];
+    if (hop > 0 && (hop & (hop - 1)) == 0) {  // a power of two: the partner is the lane with that bit flipped
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float up = __shfl_down_sync(0xffffffffu, v[j], hop & 31);
-      const float dn = __shfl_up_sync(0xffffffffu, v[j], hop & 31);
-      partner[j] = low ? up : dn;
+      for (int j = 0; j < 8; ++j) partner[j] = __shfl_xor_sync(0xffffffffu, v[j], hop & 31);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float up = __shfl_down_sync(0xffffffffu, v[j], hop & 31);
+        const float dn = __shfl_up_sync(0xffffffffu, v[j], hop & 31);
+        partner[j] = low ? up : dn;
+      }
     }
     if (rot && in) {
 #pragma unroll
@@ -203,7 +208,9 @@ norm_rope_store_vec_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, in
   if (!store) return;
   __nv_bfloat16* dst;
   if (S.slab) {
-    const long long page = slot / S.page_size, off = slot % S.page_size;
+    // (slots are 32-bit numbers: the 64-bit division costs several times the 32-bit one)
+    const unsigned int us = (unsigned int)slot, ps = (unsigned int)S.page_size;
+    const unsigned int page = us / ps, off = us % ps;
     dst = (__nv_bfloat16*)S.slab + (((size_t)page * S.n_heads + hl) * S.page_size + off) * kHeadDim;
   } else {
     dst = (__nv_bfloat16*)S.dense_out + ((size_t)t * S.n_heads + hl) * kHeadDim;
