@@ -52,6 +52,30 @@ def wave_splits(base_ctas: int, slots: int, limit: int, span: int = 2048) -> int
     return best
 
 
+def deal_rows(spans: Sequence[int], total: int, cap: int) -> List[int]:
+    """``total`` item rows dealt to tiles in proportion to their key spans: every tile at least one, none
+    more than ``cap`` (as far as ``total`` allows), the sum exactly ``total``.  Equal spans get equal shares."""
+    n = len(spans)
+    if n == 0:
+        return []
+    total = max(total, n)
+    weight = [max(1, int(sp)) for sp in spans]
+    whole = sum(weight)
+    want = [w * total / whole for w in weight]
+    got = [max(1, min(cap, int(x))) for x in want]
+    # hand out what is left by largest remainder, take back what is too much from the largest shares
+    while sum(got) < total:
+        open_ = [i for i in range(n) if got[i] < cap]
+        if not open_:
+            open_ = list(range(n))  # every tile is at the cap: the rest are empty rows on the longest tiles
+        i = max(open_, key=lambda j: (want[j] - got[j], weight[j], -j))
+        got[i] += 1
+    while sum(got) > total:
+        i = max((j for j in range(n) if got[j] > 1), key=lambda j: (got[j] - want[j], -weight[j], j))
+        got[i] -= 1
+    return got
+
+
 def tokens_per_tile(tile_rows: int, group: int) -> int:
     if tile_rows == 256:  # two tiles of 128 rows, each with whole tokens
         return 2 * max(1, 128 // group)
@@ -65,9 +89,11 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
                sparse: Optional[Tuple[int, int]] = None, key_tile: Optional[int] = None) -> AttentionPlan:
     """``segments`` holds (q_len, kv_len) per segment, in step order.
 
-    ``fixed_splits`` forces every tile to be planned with exactly that many item rows
-    (unused ones get an empty key range); CUDA-graph replay uses it so that the item
-    count of a step never changes.
+    ``fixed_splits`` fixes the number of item rows at that many per tile on average: the rows are dealt
+    to the tiles in proportion to their key spans (:func:`deal_rows`; a request of 20,000 tokens beside one
+    of 1,000 gets twenty times the pieces, so that the pieces are about equally long; rows a tile cannot
+    use get an empty key range).  CUDA-graph replay uses it so that the item count and the number of
+    scratch slots of a step never change.
 
     ``key_tile`` is the number of keys the kernel walks at a time when it is one that runs one CTA per
     SM through the whole list (128 for the tcgen05 kernels; None: 128 for tiles of 128 rows and more,
@@ -102,11 +128,14 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
     mean_span = all_keys / max(1, n_tiles)
     rows: List[List[int]] = []
     n_slots = 0
-    for (s, tok0, ntok, lo, hi) in tiles:
+    dealt = None
+    if fixed_splits is not None and fixed_splits > 1:
+        dealt = deal_rows([hi - lo for _, _, _, lo, hi in tiles], n_tiles * fixed_splits, max(fixed_splits, max_splits))
+    for ti, (s, tok0, ntok, lo, hi) in enumerate(tiles):
         span = hi - lo
         most = min(max_splits, max(1, span // min_split_keys))
         if fixed_splits is not None:
-            want = fixed_splits
+            want = dealt[ti] if dealt is not None else fixed_splits
         elif n_tiles * n_kv_heads >= target:
             want = 1
             if span > piece and span > 2 * mean_span:
@@ -119,15 +148,15 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
         n_real = max(1, min(want, quanta))
         per = -(-quanta // n_real) * quantum
         n_real = max(1, -(-span // per)) if span > 0 else 1
-        n_rows = fixed_splits if fixed_splits is not None else n_real
+        n_rows = want if fixed_splits is not None else n_real
         base = n_slots if n_rows > 1 else 0
         for i in range(n_rows):
             b = min(hi, lo + i * per)
             e = min(hi, lo + (i + 1) * per)
             rows.append([s, tok0, ntok, b, e, n_rows, i, base])
-        if n_rows > 1:
+        if n_rows > 1 or dealt is not None:  # (fixed plans: the slots are numbered the same whatever the shares)
             n_slots += n_rows
-    if key_tile and fixed_splits is None:
+    if key_tile:
         # the tcgen05 kernels deal the list out from its end, to and fro over its CTAs: longest pieces last
         # here (their place in the list means nothing else: partial results are found by base + split)
         rows.sort(key=lambda r: r[4] - r[3])

@@ -75,9 +75,49 @@ def test_the_128_row_kernel_gets_pieces_on_tile_boundaries_sorted_by_length():
         lo = parts[0][1]
         for (_, _, e0, _, _) in parts[:-1]:
             assert (e0 - lo) % 128 == 0, "a piece ends where a 128-key tile ends"
-    # with a fixed number of splits (graph replay) the list keeps its order: tile after tile
+    # a fixed number of rows (graph replay): as many rows and slots whatever the lengths, dealt by length
     fixed = build_plan([(1, 3000), (1, 500)], 6, 128, None, n_kv_heads=8, fixed_splits=3)
-    assert [r[0] for r in fixed.items.tolist()] == [0, 0, 0, 1, 1, 1]
+    assert sorted(r[0] for r in fixed.items.tolist()) == [0, 0, 0, 0, 0, 1] and fixed.n_slots == 6
+    spans = [r[4] - r[3] for r in fixed.items.tolist()]
+    assert spans == sorted(spans)
+
+
+def test_fixed_plans_deal_their_rows_by_length():
+    """Graph-replayed decode steps: the number of item rows and of scratch slots depends on the batch size
+    and the split count only, the rows go to the requests in proportion to their lengths, every key is in
+    exactly one piece, and equal lengths give the plan they always gave."""
+    from freetoken_b200.engine.attention_plan import deal_rows
+
+    assert deal_rows([2048] * 8, 16, 32) == [2] * 8
+    assert deal_rows([1000, 20000, 5000, 100], 16, 32) == [1, 12, 2, 1]
+    assert deal_rows([10, 10], 6, 2) == [3, 3]          # more rows than the cap allows: still all dealt
+    assert deal_rows([5], 4, 32) == [4] and deal_rows([], 4, 32) == []
+    rng = np.random.default_rng(0)
+    for _ in range(50):
+        b, s = int(rng.integers(1, 20)), int(rng.integers(1, 9))
+        segs = [(1, int(rng.integers(1, 30000))) for _ in range(b)]
+        for key_tile in (0, 128):
+            plan = build_plan(segs, 6, 16, None, n_kv_heads=8, fixed_splits=s, key_tile=key_tile)
+            assert plan.n_items == b * s
+            assert plan.n_slots == (b * s if s > 1 else 0)
+            covered = {i: [] for i in range(b)}
+            for seg, tok0, ntok, kb, ke, nsplit, split, base in plan.items.tolist():
+                assert 1 <= nsplit <= 64 and 0 <= split < nsplit and 0 <= kb <= ke <= segs[seg][1]
+                assert nsplit == 1 or base + nsplit <= plan.n_slots
+                covered[seg].append((kb, ke, nsplit, base))
+            for i, parts in covered.items():
+                parts.sort()
+                assert len(parts) == parts[0][2] and len({p[3] for p in parts}) == 1
+                real = [(a, e) for a, e, _, _ in parts if e > a]
+                assert real[0][0] == 0 and real[-1][1] == segs[i][1]
+                assert all(real[j][1] == real[j + 1][0] for j in range(len(real) - 1))
+            longest = max(ke - kb for _, _, _, kb, ke, _, _, _ in plan.items.tolist())
+            fair = sum(kv for _, kv in segs) / (b * s)
+            if s > 1 and max(kv for _, kv in segs) / s > 2048:
+                assert longest <= 2.2 * fair + 2 * 128 + 256, (segs, s, longest, fair)
+    same = build_plan([(1, 2100)] * 8, 6, 16, None, n_kv_heads=8, fixed_splits=2, key_tile=128)
+    assert sorted((r[0], r[3], r[4], r[5], r[6]) for r in same.items.tolist()) == sorted(
+        (i, kb, ke, 2, j) for i in range(8) for j, (kb, ke) in enumerate([(0, 1152), (1152, 2100)]))
 
 
 def test_which_attention_kernel_a_step_gets():
