@@ -230,24 +230,26 @@ __global__ void __launch_bounds__(kGemvThreads) routed_down_kernel(
   const int c_begin = ks * (k8 / n_ks), c_end = ks == n_ks - 1 ? k8 : c_begin + k8 / n_ks;
   const int route = blockIdx.y;
   const int row0 = (blockIdx.x * groups + rg) * R;
-  // (the expert ids come from the routing kernel, two launches back, which has ended: every kernel
-  // waits for the one before it before it lets the next one in)
+  // The expert ids come from the routing kernel, at least two launches back, which has ended (every kernel
+  // waits for the one before it before it lets the next one in, or ends): the id is read and the first
+  // weights are on their way while the gate/up kernel before this one still runs.
+  const int e = ids[route];
+  const bool routed = e >= 0 && e < n_experts;
+  const __nv_bfloat16* we = w2 + (size_t)(routed ? e : 0) * H * I;
+  const uint4* wr[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) wr[r] = reinterpret_cast<const uint4*>(we + (size_t)min(row0 + r, H - 1) * I);
+  uint4 wv[R][U];
+  if (routed) load_turn<R, U>(wr, c_begin, c_end, lane, wv);
   pdl_wait();
   pdl_trigger();
-  const int e = ids[route];
-  if (e < 0 || e >= n_experts) {
+  if (!routed) {  // a route to no expert contributes nothing
     for (int i = threadIdx.x; i < groups * R; i += kGemvThreads) {
       const int n = blockIdx.x * groups * R + i;
       if (n < H) y[(size_t)route * H + n] = __float2bfloat16_rn(0.f);
     }
     return;
   }
-  const __nv_bfloat16* we = w2 + (size_t)e * H * I;
-  const uint4* wr[R];
-#pragma unroll
-  for (int r = 0; r < R; ++r) wr[r] = reinterpret_cast<const uint4*>(we + (size_t)min(row0 + r, H - 1) * I);
-  uint4 wv[R][U];
-  load_turn<R, U>(wr, c_begin, c_end, lane, wv);
   const uint4* x4 = reinterpret_cast<const uint4*>(a + (size_t)route * I);
   for (int i = threadIdx.x; i < k8; i += kGemvThreads) sx[i] = x4[i];
   __syncthreads();

@@ -638,7 +638,10 @@ def moe_small_gate_up(h: torch.Tensor, ids: torch.Tensor, w1: torch.Tensor, act:
 
 def moe_small_down(a: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w2: torch.Tensor,
                    out: torch.Tensor) -> None:
-    """``out[r] = (a[r] W2[ids.flat[r]]^T) * weights.flat[r]`` for the routes of up to four tokens."""
+    """``out[r] = (a[r] W2[ids.flat[r]]^T) * weights.flat[r]`` for the routes of up to four tokens.
+    ``ids`` are read while the launch before this one may still run (they are the routing kernel's, which
+    ended before :func:`moe_small_gate_up` began): a caller that writes them just before must do so with an
+    ordinary launch."""
     R, I = a.shape
     E, H, I2 = w2.shape
     T, k = ids.shape
