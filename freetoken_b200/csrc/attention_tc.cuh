@@ -60,6 +60,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t addr, float (&v)[32]) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// 32 consecutive columns of this thread's row in one load; completed by tmem_ld_wait()
+__device__ __forceinline__ void tmem_ld32_start(uint32_t addr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(addr) : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
 __device__ __forceinline__ void tmem_st32(uint32_t addr, const float (&v)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -605,10 +615,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const int key0 = it.kb + j * kTcKeys;
       // the row's 128 scores, in registers for both passes
       float v0[32], v1[32], v2[32], v3[32];
-      tmem_ld32(s_addr, v0);
-      tmem_ld32(s_addr + 32, v1);
-      tmem_ld32(s_addr + 64, v2);
-      tmem_ld32(s_addr + 96, v3);
+      tmem_ld32_start(s_addr, v0);
+      tmem_ld32_start(s_addr + 32, v1);
+      tmem_ld32_start(s_addr + 64, v2);
+      tmem_ld32_start(s_addr + 96, v3);
+      tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[sb]);  // the next product may overwrite this buffer

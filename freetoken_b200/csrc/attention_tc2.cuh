@@ -20,20 +20,14 @@
 
 namespace ftk {
 
-// 64 consecutive columns of this thread's row in one load
-__device__ __forceinline__ void tmem_ld64(uint32_t addr, float (&v)[64]) {
-  uint32_t r[64];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];\n\t"
-      "tcgen05.wait::ld.sync.aligned;"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
-      : "r"(addr) : "memory");
-#pragma unroll
-  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
-}
+// The softmax warps take the registers that the loading and issuing warps do not need (a warpgroup = four
+// consecutive warps changes its share together).
+template <int N> __device__ __forceinline__ void regs_give() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void regs_take() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 
 constexpr int kTc2Stages = 2;                                    // key and value tiles in flight
-constexpr int kTc2Threads = 352;                                  // 2 loaders + 1 MMA + 2 x 4 softmax warps
+constexpr int kTc2Threads = 384;                                  // a warpgroup of 2 loaders + 1 MMA (+ 1 idle), 2 x 4 softmax warps
+constexpr int kTc2RegsFew = 72, kTc2RegsMany = 216;                // of 384 x 168: what 128 threads give, 256 take
 constexpr int kTc2Smem = (2 + 2 * kTc2Stages) * kTcTile + 1024;    // Q_A, Q_B, K and V stages
 
 __global__ void __launch_bounds__(kTc2Threads, 1)
@@ -85,10 +79,12 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     abort_flag = 1;
   };
 
-  if (warp == 0 || warp == 6) {
-    // ------------------------------------------------------------ TMA producers: warp 0 keys (and queries), warp 6 values
+  if (warp < 4) {
+  regs_give<kTc2RegsFew>();  // (warp 3 only fills the warpgroup)
+  if (warp == 0 || warp == 2) {
+    // ------------------------------------------------------------ TMA producers: warp 0 keys (and queries), warp 2 values
     if (lane < 16) {
-      const int kv = warp == 6, box = lane >> 1, h = lane & 1;
+      const int kv = warp == 2, box = lane >> 1, h = lane & 1;
       const CUtensorMap* map = kv ? &map_v : &map_k;
       uint64_t* full = kv ? v_full : k_full;
       uint64_t* empty = kv ? v_empty : k_empty;
@@ -240,9 +236,11 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         ++px[x];
       }
     }
+  }
   } else {
-    // ------------------------------------------------------------ softmax and epilogue: warps 2..5 tile A, warps 7..10 tile B
-    const int X = warp <= 5 ? 0 : 1;
+    regs_take<kTc2RegsMany>();
+    // ------------------------------------------------------------ softmax and epilogue: warps 4..7 tile A, warps 8..11 tile B
+    const int X = warp < 8 ? 0 : 1;
     const int quad = warp & 3;
     const int r = quad * 32 + lane;           // row of the tile = TMEM lane
     const float sl2 = p.scale * 1.4426950408889634f;
@@ -274,23 +272,29 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
         tc_fence_after();
         const int key0 = it.kb + j * kTcKeys;
-        // Two passes over the row's 128 scores, 64 at a time from TMEM (352 threads leave no room to keep
-        // all of them in registers): the largest, then the probabilities.
+        // the row's 128 scores, in registers for both passes (the largest, then the probabilities)
+        float v[128];
+        tmem_ld32_start(s_addr, v);
+        tmem_ld32_start(s_addr + 32, v + 32);
+        tmem_ld32_start(s_addr + 64, v + 64);
+        tmem_ld32_start(s_addr + 96, v + 96);
+        tmem_ld_wait();
         // a tile that every row of the warp reads in full needs no mask (most tiles of a long prompt)
         const bool interior = __all_sync(0xffffffffu, key0 + kTcKeys - 1 <= hi);
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          float v[64];
-          tmem_ld64(s_addr + c * 64, v);
-          if (!interior) {
+        if (!interior) {
 #pragma unroll
-            for (int i = 0; i < 64; ++i)
-              if (key0 + c * 64 + i > hi) v[i] = -INFINITY;
-          }
-#pragma unroll
-          for (int i = 0; i < 64; ++i) mx = fmaxf(mx, v[i]);
+          for (int i = 0; i < 128; ++i)
+            if (key0 + i > hi) v[i] = -INFINITY;
         }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int i = 0; i < 128; i += 4) {
+          mx4[0] = fmaxf(mx4[0], v[i]);
+          mx4[1] = fmaxf(mx4[1], v[i + 1]);
+          mx4[2] = fmaxf(mx4[2], v[i + 2]);
+          mx4[3] = fmaxf(mx4[3], v[i + 3]);
+        }
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         mx *= sl2;  // the scale is positive: the largest score stays the largest
         // move the running maximum only when it grew by more than 8 (or is not set yet)
         float alpha = 1.f;
@@ -317,26 +321,18 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
         const float mb = m_used == -INFINITY ? 0.f : m_used;
         float sum = 0.f;
-        // probabilities as bfloat16 over the first 64 columns of the scores: the 16 columns that chunk c
-        // writes hold scores that have been read by then
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          float v[64];
-          tmem_ld64(s_addr + c * 64, v);
+        // probabilities as bfloat16 over the first 64 columns of the scores (which are all in registers by now)
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            uint32_t pk[16];
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const int k = c * 64 + h * 32 + i;
-              const bool m0 = !interior && key0 + k > hi, m1 = !interior && key0 + k + 1 > hi;
-              const float p0 = m0 ? 0.f : tc_exp2(fmaf(v[h * 32 + i], sl2, -mb));
-              const float p1 = m1 ? 0.f : tc_exp2(fmaf(v[h * 32 + i + 1], sl2, -mb));
-              sum += p0 + p1;
-              pk[i >> 1] = tc_pack(p0, p1);
-            }
-            tmem_st16u(s_addr + (uint32_t)((2 * c + h) * 16), pk);
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = tc_exp2(fmaf(v[c * 32 + i], sl2, -mb));  // exp2(-inf) = 0 for masked keys
+            const float p1 = tc_exp2(fmaf(v[c * 32 + i + 1], sl2, -mb));
+            sum += p0 + p1;
+            pk[i >> 1] = tc_pack(p0, p1);
           }
+          tmem_st16u(s_addr + (uint32_t)(c * 16), pk);
         }
         l += sum;
         tmem_st_wait();
