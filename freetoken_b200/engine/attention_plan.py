@@ -52,6 +52,26 @@ def wave_splits(base_ctas: int, slots: int, limit: int, span: int = 2048) -> int
     return best
 
 
+SPLIT_COST_KEYS = 100  # what writing a piece's partial result and merging it costs on top, in keys' worth of time
+DEAL_MOST_CUTS = 16    # the longest tile is tried in up to this many pieces
+DEAL_SEARCH_LIMIT = 8  # lists of more than this many pieces per CTA are dealt evenly enough as they are
+DEAL_MOST_PIECES = 4   # pieces of cut tiles per CTA that partial results are set aside for
+
+
+def dealt_makespan(costs: Sequence[float], n_kv_heads: int, ctas: int, key_tile: int) -> float:
+    """The busiest CTA's load when the tcgen05 kernels deal a list out: the pieces sorted by length, each
+    once per KV head, the longest first, round after round to and fro over ``min(ctas, pieces)`` CTAs.
+    ``costs`` are in keys; a piece pays for whole key tiles."""
+    c = np.sort(np.asarray(costs, dtype=np.float64))[::-1]
+    c = np.ceil(c / key_tile) * key_tile
+    c = np.repeat(c, n_kv_heads)
+    g = max(1, min(ctas, c.shape[0]))
+    rounds = -(-c.shape[0] // g)
+    c = np.concatenate([c, np.zeros(rounds * g - c.shape[0])]).reshape(rounds, g)
+    c[1::2] = c[1::2, ::-1]
+    return float(c.sum(axis=0).max())
+
+
 def deal_rows(spans: Sequence[int], total: int, cap: int) -> List[int]:
     """``total`` item rows dealt to tiles in proportion to their key spans: every tile at least one, none
     more than ``cap`` (as far as ``total`` allows), the sum exactly ``total``.  Equal spans get equal shares."""
@@ -97,7 +117,9 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
 
     ``key_tile`` is the number of keys the kernel walks at a time when it is one that runs one CTA per
     SM through the whole list (128 for the tcgen05 kernels; None: 128 for tiles of 128 rows and more,
-    else 0): pieces are then multiples of it and the list is sorted by length.
+    else 0): pieces are then multiples of it, the list is sorted by length, and for lists of a few pieces
+    per CTA the number of pieces per tile is the one with which the kernel's dealing ends soonest
+    (:func:`dealt_makespan`).
 
     ``sparse = (block_size, topk)`` plans a block-sparse layer: one token per tile (every token has
     its own choice of key blocks) and key ranges that count chosen keys: ``min(topk, visible
@@ -131,6 +153,9 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
     dealt = None
     if fixed_splits is not None and fixed_splits > 1:
         dealt = deal_rows([hi - lo for _, _, _, lo, hi in tiles], n_tiles * fixed_splits, max(fixed_splits, max_splits))
+    quantum = key_tile if key_tile else SPLIT_QUANTUM  # a piece that ends inside a key tile pays for all of it
+    wants: List[int] = []
+    mosts: List[int] = []
     for ti, (s, tok0, ntok, lo, hi) in enumerate(tiles):
         span = hi - lo
         most = min(max_splits, max(1, span // min_split_keys))
@@ -142,12 +167,63 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
                 want = max(1, min(most, int(-(-span // piece))))
         else:
             # splits that fill whole waves of resident CTAs, none shorter than min_split_keys
+            if key_tile:  # (no more pieces than the mixers set partial results aside for)
+                most = max(1, min(most, DEAL_MOST_PIECES * target // (n_tiles * n_kv_heads)))
             want = wave_splits(n_tiles * n_kv_heads, target, most, span)
-        quantum = key_tile if key_tile else SPLIT_QUANTUM  # a piece that ends inside a key tile pays for all of it
+        wants.append(want)
+        mosts.append(most)
+
+    def cut(span: int, want: int) -> Tuple[int, int]:
+        """(keys per piece, pieces) of a tile cut into at most ``want`` pieces of whole quanta."""
         quanta = -(-span // quantum)
         n_real = max(1, min(want, quanta))
         per = -(-quanta // n_real) * quantum
-        n_real = max(1, -(-span // per)) if span > 0 else 1
+        return per, (max(1, -(-span // per)) if span > 0 else 1)
+
+    if key_tile and fixed_splits is None and n_tiles * n_kv_heads <= DEAL_SEARCH_LIMIT * target:
+        # The tcgen05 kernels run one CTA per SM through the sorted list, to and fro; with a few pieces per
+        # CTA the last round decides (200 equal pieces on 148 CTAs take two rounds, 400 halves three half
+        # rounds).  So: the counts from above against pieces of at most L keys for a few L (a k-th of the
+        # longest tile; shorter tiles get fewer pieces), the kernel's dealing played through for each.
+        spans = np.asarray([hi - lo for _, _, _, lo, hi in tiles], dtype=np.int64)
+        quanta = -(-spans // quantum)
+        cap = np.asarray(mosts, dtype=np.int64)
+
+        def played(counts: np.ndarray) -> Optional[float]:
+            n = np.maximum(1, np.minimum(counts, quanta))
+            per = -(-quanta // n) * quantum          # keys per piece, as cut() has them
+            n = np.where(spans > 0, np.maximum(1, -(-spans // per)), 1)
+            if int(n[n > 1].sum()) * n_kv_heads > DEAL_MOST_PIECES * target:
+                return None  # (the partial results of so many pieces would not fit what the mixers set aside)
+            costs = np.repeat(per, n).astype(np.float64)
+            last = np.cumsum(n) - 1
+            costs[last] = spans - (n - 1) * per      # a tile's last piece is what is left
+            costs += FIXED_COST_KEYS + np.repeat(np.where(n > 1, SPLIT_COST_KEYS, 0), n)
+            return dealt_makespan(costs, n_kv_heads, target, key_tile)
+
+        best = np.asarray(wants, dtype=np.int64)
+        best_t = played(best)
+        longest = int(spans.max()) if n_tiles else 0
+        seen = None
+        for k in range(1, DEAL_MOST_CUTS + 1):
+            limit = -(-longest // (k * quantum)) * quantum  # keys per piece
+            if limit < min_split_keys:
+                break
+            counts = np.maximum(1, np.minimum(cap, -(-spans // limit)))
+            if seen is not None and np.array_equal(counts, seen):
+                continue
+            seen = counts
+            t = played(counts)
+            if t is None:
+                break  # (more cuts need more room still)
+            if best_t is None or t < best_t * 0.97:
+                best, best_t = counts, t
+        wants = [int(x) for x in best]
+
+    for ti, (s, tok0, ntok, lo, hi) in enumerate(tiles):
+        span = hi - lo
+        want = wants[ti]
+        per, n_real = cut(span, want)
         n_rows = want if fixed_splits is not None else n_real
         base = n_slots if n_rows > 1 else 0
         for i in range(n_rows):

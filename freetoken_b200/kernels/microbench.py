@@ -110,7 +110,7 @@ def bench_attention(a) -> dict:
     Hq, Hkv, D, P = a.q_heads, a.kv_heads, a.head_dim, a.page_size
     G = Hq // Hkv
     if a.prefill:
-        segs = [(a.prefill, a.prefill)]
+        segs = [(a.prefill, a.past + a.prefill)]  # a portion of a prompt after --past earlier tokens
     else:
         segs = [(1, a.context)] * a.batch
     n_pages = sum(-(-kv // P) for _, kv in segs) + 1
@@ -139,7 +139,9 @@ def bench_attention(a) -> dict:
         tc = few_rows or (a.tc and ops.attention_tc_fits(D, P, G))
         fixed = wave_splits(len(segs) * Hkv, 148 if tc else 2 * 148, 16, a.context) if a.splits is None else a.splits
         tile = 16 if few_rows else 128 if tc else (16 if G <= 16 else 64)
-    plan = build_plan(segs, G, tile, None, Hkv, fixed_splits=fixed, key_tile=128 if (few_rows or tile >= 128) else 0)
+    tensor_core = few_rows or tile >= 128  # (one CTA per SM: the engine plans these for half as many CTA slots)
+    plan = build_plan(segs, G, tile, None, Hkv, sm_count=74 if tensor_core else 148, fixed_splits=fixed,
+                      key_tile=128 if tensor_core else 0)
     items = torch.from_numpy(plan.items).to(dev)
     po = pm = None
     if plan.n_slots:
@@ -286,6 +288,7 @@ def main(argv=None) -> int:
             p.add_argument("--batch", type=int, default=8)
             p.add_argument("--context", type=int, default=2048)
             p.add_argument("--prefill", type=int, default=0)
+            p.add_argument("--past", type=int, default=0, help="tokens of the request before the --prefill portion")
             p.add_argument("--q-heads", type=int, default=48)
             p.add_argument("--kv-heads", type=int, default=8)
             p.add_argument("--head-dim", type=int, default=128)

@@ -17,6 +17,7 @@ from typing import Any, Dict, Optional, Tuple
 import torch
 
 from ..config.spec import PagedKVNeed, ParamSpec, PartSpec
+from ..engine.attention_plan import DEAL_MOST_PIECES
 from ..errors import ConfigError
 from ..kernels import ops
 from .base import MIXERS, BuildEnv, Mixer, StepState
@@ -25,6 +26,8 @@ from .rope import shared_position
 
 TC_MIN_TOKENS = 128      # shortest step that goes to the tcgen05 attention kernel
 TC_PAIR_MIN_TOKENS = 1024  # from this many tokens on, a step goes to the kernel with two query tiles per CTA
+TC_PAIR_MIN_TOKENS_LONG = 256  # ... and from this many on when its longest request has TC_PAIR_MIN_SPAN keys and more
+TC_PAIR_MIN_SPAN = 16384       # (rounded up to 2^n): such tiles are cut along the keys into enough pieces for every SM
 TC_MIN_DECODE_SPAN = 0   # decode steps go there from this length of the longest request (rounded up to 2^n) on
 
 
@@ -35,7 +38,8 @@ def attention_kernel_form(dtype: torch.dtype, decode_only: bool = False, group: 
 
     16 rows in the 32-bit kernel.  bfloat16 steps whose sizes the tcgen05 kernels take: 128 rows for
     long steps (``TC_MIN_TOKENS`` tokens and more; 256, two such tiles per CTA, from
-    ``TC_PAIR_MIN_TOKENS`` tokens on); decode steps go to the same kernel in its form for tiles of at
+    ``TC_PAIR_MIN_TOKENS`` tokens on, or from ``TC_PAIR_MIN_TOKENS_LONG`` for portions of long prompts);
+    decode steps go to the same kernel in its form for tiles of at
     most 16 rows, where one warp takes the softmax (groups of up to 16 heads; ``longest_span`` is the longest
     request's length rounded up to a power of two, from which on they go there:
     ``TC_MIN_DECODE_SPAN``), larger groups to the 128-row kernel.  Otherwise 16 rows for decode steps
@@ -51,7 +55,8 @@ def attention_kernel_form(dtype: torch.dtype, decode_only: bool = False, group: 
                 return 128, False
         return (16 if group <= 16 else 64), False
     tc = sized and ops.attention_tc_fits(head_dim, page_size, group)
-    if tc and n_tokens >= TC_PAIR_MIN_TOKENS:
+    if tc and (n_tokens >= TC_PAIR_MIN_TOKENS or
+               (n_tokens >= TC_PAIR_MIN_TOKENS_LONG and longest_span >= TC_PAIR_MIN_SPAN)):
         return 256, False
     if tc and n_tokens >= TC_MIN_TOKENS:
         return 128, False
@@ -119,10 +124,10 @@ class GQAttention(Mixer):
 
     def workspace_bytes(self, n_tokens: int) -> int:
         item = 4 if self.env.dtype == torch.float32 else 2
-        # qkv, q, o, out; and the 32-bit partial results of tiles split along the keys (two CTAs'
-        # worth of slots per SM, 128 rows each at most)
+        # qkv, q, o, out; and the 32-bit partial results of tiles split along the keys (at most
+        # attention_plan.DEAL_MOST_PIECES pieces per SM, 256 rows each at most)
         rows = n_tokens * (3 * self.q_dim + 2 * self.kv_dim + self.hidden) * item
-        return rows + 2 * 148 * 128 * (self.head_dim + 2) * 4 * 2
+        return rows + DEAL_MOST_PIECES * 148 * 256 * (self.head_dim + 2) * 4
 
     # ------------------------------------------------------------------ step
     def kernel_form(self, decode_only: bool, n_tokens: int = 0, page_size: int = 0, longest_span: int = 0):

@@ -4,7 +4,8 @@ splits, long tiles beside many short ones are cut, even steps are not."""
 import numpy as np
 import pytest
 
-from freetoken_b200.engine.attention_plan import SPLIT_QUANTUM, build_plan, wave_splits
+from freetoken_b200.engine.attention_plan import (DEAL_MOST_PIECES, FIXED_COST_KEYS, SPLIT_QUANTUM, build_plan,
+                                                  dealt_makespan, wave_splits)
 
 
 def ranges_by_tile(plan):
@@ -120,6 +121,42 @@ def test_fixed_plans_deal_their_rows_by_length():
         (i, kb, ke, 2, j) for i in range(8) for j, (kb, ke) in enumerate([(0, 1152), (1152, 2100)]))
 
 
+def test_lists_of_a_few_pieces_per_cta_are_cut_so_that_the_dealing_ends_soonest():
+    """The tcgen05 kernels run 148 CTAs through the sorted list, to and fro.  A 512-token portion after
+    65,024 tokens is 25 tiles x 8 KV heads = 200 equally long pieces: whole they take two rounds, as halves
+    three half rounds.  With two query tiles per piece (104 pieces) quarters take three quarter rounds."""
+    # the model itself: 200 equal pieces on 148 CTAs, then 400 halves
+    assert dealt_makespan([1280.0] * 25, 8, 148, 128) == 2 * 1280
+    assert dealt_makespan([640.0] * 50, 8, 148, 128) == 3 * 640
+    # sorted, the longest first, to and fro: the CTA with the longest piece gets the shortest of the next round
+    assert dealt_makespan([128.0, 256.0, 384.0, 512.0], 1, 2, 128) == 640
+
+    segs = [(512, 65536)]
+    one = build_plan(segs, 6, 128, None, 8, sm_count=74, key_tile=128)
+    assert set(one.items[:, 5].tolist()) == {2} and one.n_items == 50
+    pair = build_plan(segs, 6, 256, None, 8, sm_count=74, key_tile=128)
+    assert set(pair.items[:, 5].tolist()) == {4} and pair.n_items == 52
+    for plan in (one, pair):  # never more pieces than partial results are set aside for
+        assert plan.n_slots * 8 <= DEAL_MOST_PIECES * 148
+        for parts in ranges_by_tile(plan).values():
+            parts.sort()
+            assert parts[0][1] == 0 and all(a[2] == b[1] for a, b in zip(parts, parts[1:]))
+            assert all((b - 0) % 128 == 0 for _, b, _, _, _ in parts)
+    # what the choice rests on: the busiest CTA's keys, whole against cut
+    def busiest(plan):
+        return dealt_makespan([FIXED_COST_KEYS + ke - kb for _, _, _, kb, ke, _, _, _ in plan.items.tolist()], 8, 148, 128)
+    whole = build_plan(segs, 6, 128, None, 8, sm_count=74, key_tile=128, max_splits=1)
+    assert set(whole.items[:, 5].tolist()) == {1}
+    assert busiest(one) < 0.8 * busiest(whole)
+
+    # a whole prompt of 2,048 tokens has pieces of every length: dealt to and fro they end together, no cut
+    fresh = build_plan([(2048, 2048)], 6, 256, None, 8, sm_count=74, key_tile=128)
+    assert set(fresh.items[:, 5].tolist()) == {1}
+    # graph-replayed plans keep their fixed number of rows
+    fixed = build_plan([(1, 4096)] * 8, 6, 16, None, 8, sm_count=74, key_tile=128, fixed_splits=2)
+    assert fixed.n_items == 16
+
+
 def test_which_attention_kernel_a_step_gets():
     """The rows per CTA (and the few-rows flag) name the kernel: 16 float32 / small bfloat16 tiles, 64
     mma.sync, 128 tcgen05 with one query tile, 256 with two (steps of a thousand tokens and more), 16
@@ -142,4 +179,7 @@ def test_which_attention_kernel_a_step_gets():
     assert rows(bf, False, 6, TC_MIN_TOKENS - 1, 128, 16) == 64
     assert rows(bf, False, 6, TC_MIN_TOKENS, 128, 16) == 128
     assert rows(bf, False, 6, TC_PAIR_MIN_TOKENS, 128, 16) == 256
+    # a portion of a long prompt is cut along the keys into enough pieces for two tiles per CTA
+    assert rows(bf, False, 6, 512, 128, 16, None, 65536) == 256 and rows(bf, False, 6, 512, 128, 16, None, 8192) == 128
+    assert rows(bf, False, 6, 200, 128, 16, None, 65536) == 128
     assert rows(bf, False, 6, 4096, 80, 16) == 64

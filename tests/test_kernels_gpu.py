@@ -171,7 +171,7 @@ def test_norm_rope_store(dtype, Hq, Hkv, D, rd, P, gemma, norm, T):
 
 
 def run_attention(dtype, Hq, Hkv, D, P, segs, window, fixed_splits=None, force_split=False, seed=0, tile=None,
-                  spoil_reference=None, few_rows=False):
+                  spoil_reference=None, few_rows=False, plan_kw=None):
     """segs: list of (q_len, kv_len).  Builds a shuffled page layout with NaN in every unwritten
     slot, runs kernel and reference, returns both outputs."""
     G = Hq // Hkv
@@ -203,6 +203,7 @@ def run_attention(dtype, Hq, Hkv, D, P, segs, window, fixed_splits=None, force_s
         kw = dict(sm_count=4096, min_split_keys=32)
     if few_rows:
         kw["key_tile"] = 128
+    kw.update(plan_kw or {})
     plan = build_plan(segs, G, tile, window, Hkv, fixed_splits=fixed_splits, **kw)
     items = torch.from_numpy(plan.items).to(DEV)
     part_o = part_ml = None
@@ -257,6 +258,23 @@ def test_attention_tensor_core_kernel_split_keys(tile):
     segs = [(140, 3000)]
     out, want, plan = run_attention(torch.bfloat16, 12, 2, 128, 16, segs, None, force_split=True, tile=tile)
     assert plan.n_slots > 0
+    assert not torch.isnan(out).any()
+    torch.testing.assert_close(out.float(), want.float(), **attn_tol(torch.bfloat16))
+    assert ops.read_status() == 0
+
+
+@pytest.mark.parametrize("tile", [128, 256])
+def test_attention_tensor_core_kernel_portion_of_a_long_prompt_beside_single_tokens(tile):
+    """A 300-token portion after 19,700 earlier tokens beside decoding requests, with the work list as the
+    engine makes it for these kernels (one CTA per SM, pieces on key-tile edges): the long tiles are cut along
+    the keys into the number of pieces with which the kernel's dealing ends soonest, the short ones are not."""
+    segs = [(300, 20000), (1, 700), (1, 128), (1, 1999), (1, 1)]
+    G = 6
+    plan = build_plan(segs, G, tile, None, 2, sm_count=74, key_tile=128)
+    cut = {tuple(r[:3]): r[5] for r in plan.items.tolist()}
+    assert all(n > 1 for (seg, _, _), n in cut.items() if seg == 0) and all(n == 1 for (seg, _, _), n in cut.items() if seg > 0)
+    out, want, used = run_attention(torch.bfloat16, 12, 2, 128, 16, segs, None, tile=tile, plan_kw=dict(sm_count=74, key_tile=128))
+    assert used.n_items == plan.n_items and used.n_slots == plan.n_slots > 0
     assert not torch.isnan(out).any()
     torch.testing.assert_close(out.float(), want.float(), **attn_tol(torch.bfloat16))
     assert ops.read_status() == 0
