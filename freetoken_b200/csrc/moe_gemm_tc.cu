@@ -108,6 +108,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
   __shared__ int abort_flag;
   __shared__ int tile_prefix[kMaxExperts + 1];  // token tiles of experts 0..e-1
   __shared__ float turn[4][16][33];             // per epilogue warp: a 16-token chunk turned round
+  __shared__ float tile_w[GATED ? 1 : 4][GATED ? 1 : BN];  // per epilogue warp: the route weights of a tile's tokens
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t tiles_base = (smem_addr(dyn_smem) + 1023u) & ~1023u;
@@ -377,6 +378,19 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
     for (int t = t_first; t < total_tiles; t += G) {
       int e, row0, rows, m0;
       locate(t, e, row0, rows, m0);
+      if (!GATED) {
+        // the route weights of the tile's tokens, fetched while the products still run
+        __syncwarp();
+        for (int n = lane; n < BN; n += 32) {
+          float wl = 0.f;
+          if (n < rows) {
+            const int route = p.sorted_routes[row0 + n];
+            wl = (route >= 0 && route < p.n_routes) ? p.route_weights[route] : 0.f;
+          }
+          tile_w[quad][n] = wl;
+        }
+        __syncwarp();
+      }
       // the whole warp takes one decision: the loads below need all 32 lanes
       if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[acc], (acc_phase >> acc) & 1u, abortp))) {
         if (lane == 0) atomicCAS(&g_status[0], 0, 104);
@@ -386,26 +400,22 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
       tc_fence_after();
       const int c_end = min(BN, (rows + 15) & ~15);
       const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * S::kAccCols);
-#pragma unroll 1
-      for (int c = 0; c < c_end; c += 16) {
-        float v[16];
-        tmem_ld16(t_addr + c, v);
-        if (c + 16 >= c_end) {  // last read of this accumulator buffer: hand it back to the MMA warp
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&acc_empty[acc]);
-        }
-        float (*tb)[33] = turn[quad];
+      float (*tb)[33] = turn[quad];
+      // One chunk of 16 tokens (columns c..c+15 of this warp's 32 accumulator rows), turned round through
+      // shared memory so that a thread stores 8 consecutive features of one token.
+      auto chunk = [&](const uint32_t (&r)[16], int c) {
         if (GATED) {
-          // lanes 0-15 of a quadrant hold gate, lanes 16-31 the up values of the same 16 features
+          // lanes 0-15 of a quadrant hold gate, lanes 16-31 the up values of the same 16 features.  Both halves
+          // work: a lane of the first takes tokens 0-7 of its feature (and gets their up values from its
+          // partner), a lane of the second tokens 8-15 (and gets their gate values).
+          const bool first = lane < 16;
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float up = __shfl_down_sync(0xffffffffu, v[i], 16);
-            if (lane < 16) {
-              const float g = to_float(__float2bfloat16_rn(v[i]));
-              const float u = to_float(__float2bfloat16_rn(up));
-              tb[i][lane] = gated_act(g, u, p.act, p.alpha, p.limit);
-            }
+          for (int i = 0; i < 8; ++i) {
+            const float mine = __uint_as_float(first ? r[i] : r[8 + i]);
+            const float theirs = __shfl_xor_sync(0xffffffffu, __uint_as_float(first ? r[8 + i] : r[i]), 16);
+            const float g = to_float(__float2bfloat16_rn(first ? mine : theirs));
+            const float u = to_float(__float2bfloat16_rn(first ? theirs : mine));
+            tb[first ? i : 8 + i][lane & 15] = gated_act_fast(g, u, p.act, p.alpha, p.limit);
           }
           __syncwarp();
           // 16 tokens x 16 features: one 16-byte store (8 features of one token) per thread
@@ -424,14 +434,8 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
           }
           __syncwarp();
         } else {
-          // route weights of this chunk's 16 tokens: lanes 0-15 fetch one each
-          float wl = 0.f;
-          if (lane < 16 && c + lane < rows) {
-            const int route = p.sorted_routes[row0 + c + lane];
-            wl = (route >= 0 && route < p.n_routes) ? p.route_weights[route] : 0.f;
-          }
 #pragma unroll
-          for (int i = 0; i < 16; ++i) tb[i][lane] = v[i] * __shfl_sync(0xffffffffu, wl, i);
+          for (int i = 0; i < 16; ++i) tb[i][lane] = __uint_as_float(r[i]) * tile_w[quad][c + i];
           __syncwarp();
           // 16 tokens x 32 features: two 16-byte stores per thread
 #pragma unroll
@@ -452,6 +456,27 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
             }
           }
           __syncwarp();
+        }
+      };
+      // after the last read of this accumulator buffer it goes back to the MMA warp
+      auto release = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      };
+      // the next chunk's load runs under this chunk's arithmetic and stores
+      uint32_t ra[16], rb[16];
+      tmem_ld16_start(t_addr, ra);
+#pragma unroll 1
+      for (int c = 0; c < c_end; c += 32) {
+        tmem_ld16_finish(ra);
+        const bool more = c + 16 < c_end;
+        if (more) tmem_ld16_start(t_addr + c + 16, rb); else release();
+        chunk(ra, c);
+        if (more) {
+          tmem_ld16_finish(rb);
+          if (c + 32 < c_end) tmem_ld16_start(t_addr + c + 32, ra); else release();
+          chunk(rb, c + 16);
         }
       }
       acc_phase ^= 1u << acc;

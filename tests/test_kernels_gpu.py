@@ -794,11 +794,15 @@ def test_moe_grouped_gemms(dtype, E, H, I, counts, act):
 
 
 @pytest.mark.parametrize("E,H,I,R,k", [(256, 3072, 1536, 64, 8), (256, 3072, 1536, 2048, 8), (32, 512, 256, 700, 4),
-                                       (8, 64, 32, 9, 2), (16, 1024, 1000, 300, 2)])
+                                       (8, 64, 32, 9, 2), (16, 1024, 1000, 300, 2),
+                                       (12, 1664, 1536, 4000, 2), (24, 640, 1600, 2500, 2), (40, 1152, 1088, 1900, 2)])
 def test_moe_tensor_core_gemms_match_cuda_core_gemms(E, H, I, R, k):
     """The tcgen05 kernels against the CUDA-core kernels on the same inputs (and, for the small
     cases, against the plain reference), at decode-like and prefill-like row counts, including
-    experts without rows and experts with more rows than one token tile."""
+    experts without rows and experts with more rows than one token tile.  The last three have hundreds
+    of rows per expert and hundreds of tiles: token tiles of 256 and 128 rows in the deep-pipeline form,
+    where a CTA multiplies two feature tiles with each token tile (widths of 13 x 128, 25 x 64, 17 x 64
+    and 9 x 128 features: an odd number of feature tiles, so the last pair has one)."""
     g = torch.Generator().manual_seed(R)
     ids = torch.randint(0, E, (R,), generator=g)
     if R > 100:
