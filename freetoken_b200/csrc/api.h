@@ -135,6 +135,7 @@ int ftk_read_status(int* out);
 int ftk_debug_set_status(int unit, int code);
 // 0 sends bfloat16 grouped expert products to the CUDA-core kernels; default 1 (tcgen05).
 int ftk_set_moe_tensor_cores(int enabled);
+int ftk_set_moe_pairs(int enabled);
 int ftk_sample(const float* logits, int n_rows, int vocab, const float* temperature,
                const int32_t* top_k, const float* top_p, const float* u, int32_t* out, void* stream);
 

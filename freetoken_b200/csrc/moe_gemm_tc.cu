@@ -74,17 +74,24 @@ struct TcParams {
 
 // DEEP: one CTA per SM (many tiles: each SM streams on its own, with a longer pipeline for the large
 // token tiles); otherwise two CTAs per SM (few tiles: more of them run at once).
-template <int BN, bool DEEP>
+// PAIR: two CTAs (a cluster) work on one tile of 256 weight rows x BN tokens with cta_group::2: each CTA
+// loads and multiplies its own 128 weight rows (its own feature tile) and half of the tile's tokens, the
+// tensor cores read the other half from the partner's shared memory.  A token tile then enters an SM once per
+// 256 weight rows instead of once per 128, which is what binds these sizes (measured: 9.0-9.4 TB/s from L2
+// into the SMs at 4,096, 8,192 and 16,384 tokens, whatever the pipeline's depth and the boxes' size).
+template <int BN, bool DEEP, bool PAIR = false>
 struct Smem {
   // 64-element pieces of k per stage.  Two of them make every row of a weight tile a 256-byte read,
   // which the memory serves faster than twice 128 bytes (measured: 6.7 against 6.1 TB/s).
   static constexpr int kAtoms = DEEP ? 2 : 1;
-  static constexpr int kStages = DEEP ? (BN <= 16 ? 5 : (BN <= 32 ? 4 : (BN <= 64 ? 4 : (BN <= 128 ? 3 : 2))))
-                                      : (BN <= 16 ? 5 : (BN <= 128 ? 4 : 3));
+  static constexpr int kStages = PAIR ? 3
+                                 : DEEP ? (BN <= 16 ? 5 : (BN <= 32 ? 4 : (BN <= 64 ? 4 : (BN <= 128 ? 3 : 2))))
+                                        : (BN <= 16 ? 5 : (BN <= 128 ? 4 : 3));
   // loads kept in flight while every CTA streams (measured for the small token tiles: 144 KB per SM
   // is the best; more of them from all SMs at once slow the memory down)
   static constexpr int kDepth = (DEEP && BN <= 16) ? 4 : kStages;
-  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kBRows = PAIR ? BN / 2 : BN;  // token rows of a tile in this CTA's shared memory
+  static constexpr int kBBytes = kBRows * kBK * 2;
   static constexpr int kBBoxRows = BN < 32 ? BN : 32;  // token rows per TMA box: only boxes with rows are loaded
   static constexpr int kStageBytes = kAtoms * (kABytes + kBBytes);
   static constexpr int kAccCols = BN;                  // TMEM columns of one accumulator buffer
@@ -92,7 +99,7 @@ struct Smem {
   static constexpr int kDynamic = kStages * kStageBytes + 1024;
 };
 
-template <int BN, bool GATED, bool DEEP>
+template <int BN, bool GATED, bool DEEP, bool PAIR = false>
 __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_b,
                                                                TcParams p) {
@@ -101,9 +108,10 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
   // tiles of the first loads go out before the wait too; what the kernel before wrote (the activations)
   // is read after it, and nothing is stored before it.
   pdl_trigger();
-  using S = Smem<BN, DEEP>;
+  using S = Smem<BN, DEEP, PAIR>;
   extern __shared__ unsigned char dyn_smem[];
   __shared__ uint64_t full_bar[S::kStages], empty_bar[S::kStages], acc_full[2], acc_empty[2];
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;  // CTA 0 of a pair leads: it issues the products
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   __shared__ int tile_prefix[kMaxExperts + 1];  // token tiles of experts 0..e-1
@@ -122,12 +130,14 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 4);
+      mbar_init(&acc_empty[a], PAIR ? 8 : 4);  // the epilogue warps (of both CTAs)
     }
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(&tmem_slot, S::kTmemCols);
+  if (warp == 1) {
+    if (PAIR) tmem_alloc_pair(&tmem_slot, S::kTmemCols); else tmem_alloc(&tmem_slot, S::kTmemCols);
+  }
   // token tiles per expert, prefix-summed by warp 0
   if (warp == 0) {
     const int E = p.n_experts;
@@ -155,30 +165,33 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // the partner's barriers are set up before anything arrives at them
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
-  const int total_tiles = tile_prefix[p.n_experts] * p.m_tiles;
+  const int m_units = PAIR ? (p.m_tiles + 1) / 2 : p.m_tiles;  // feature tiles, or pairs of them
+  const int total_tiles = tile_prefix[p.n_experts] * m_units;
   // Tiles are dealt out in turns.  A last turn with a tile for only a few CTAs costs about two thirds of
   // a whole turn (a lone SM streams a tile at about 70 GB/s, not much faster than its share when all
   // SMs stream).  Where that costs more than it, only as many CTAs take part as fill every turn: with
   // 1,344 tiles on 148 SMs, 135 CTAs take ten tiles each instead of 148 taking nine and twelve of them
   // a tenth.  The others leave at once.  Costs are counted in tile times of a full turn.
-  const int all = (int)gridDim.x;
+  const int all = PAIR ? (int)gridDim.x / 2 : (int)gridDim.x;           // CTAs, or pairs of them
+  const int me = PAIR ? (int)blockIdx.x / 2 : (int)blockIdx.x;
   const int turns = (total_tiles + all - 1) / all;
   const int even = turns > 0 ? (total_tiles + turns - 1) / turns : 1;
   const int rest = total_tiles % all;
   const int cost_all = total_tiles - rest + (rest ? max(rest, 2 * all / 3) : 0);
   // (one CTA per SM and the small token tiles only: that is where it was measured)
   const int G = (DEEP && BN <= 32 && turns * even < cost_all) ? even : all;
-  const int t_first = (int)blockIdx.x < G ? (int)blockIdx.x : total_tiles;
+  const int t_first = me < G ? me : total_tiles;
   const int k_blocks = (p.K + S::kAtoms * kBK - 1) / (S::kAtoms * kBK);  // k past the end reads as zero
   volatile int* abortp = &abort_flag;
 
   constexpr int kFeat = GATED ? 64 : 128;  // output features of one feature tile
   // tile -> expert, token tile, first feature
   auto locate = [&](int t, int& e, int& row0, int& rows, int& m0) {
-    const int g = t / p.m_tiles;
-    m0 = (t % p.m_tiles) * kFeat;
+    const int g = t / m_units;
+    m0 = PAIR ? ((t % m_units) * 2 + (int)rank) * kFeat : (t % m_units) * kFeat;
     int lo = 0, hi = p.n_experts - 1;  // last e with tile_prefix[e] <= g
     while (lo < hi) {
       const int mid = (lo + hi + 1) >> 1;
@@ -188,6 +201,18 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
     const int start = p.offsets[e], end = p.offsets[e + 1];
     row0 = start + (g - tile_prefix[e]) * BN;
     rows = min(BN, end - row0);
+  };
+  // the token rows this CTA loads for a tile: first row and number of boxes.  A pair computes a multiple of 64
+  // columns, half of them from each CTA's shared memory.
+  auto token_part = [&](int row0, int rows, int& b0, int& nb) {
+    if (PAIR) {
+      const int half = min(BN, (rows + 63) & ~63) / 2;
+      b0 = row0 + (int)rank * half;
+      nb = half / S::kBBoxRows;
+    } else {
+      b0 = row0;
+      nb = (rows + S::kBBoxRows - 1) / S::kBBoxRows;
+    }
   };
 
   if (warp == 0) {
@@ -203,9 +228,14 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
       const bool thin_tail = 2 * (total_tiles - full_waves) <= G;
       const int depth_main = S::kDepth;
       auto stage_bytes = [&](int rows) {
-        const int nb = gathers ? 0 : (rows + S::kBBoxRows - 1) / S::kBBoxRows;
-        return (uint32_t)(S::kAtoms * (kABytes + nb * S::kBBoxRows * kBK * 2));
+        int b0, nb;
+        token_part(0, rows, b0, nb);
+        if (gathers) nb = 0;
+        // (the leading CTA of a pair counts the partner's bytes too: both load the same amount)
+        return (uint32_t)((PAIR ? 2 : 1) * S::kAtoms * (kABytes + nb * S::kBBoxRows * kBK * 2));
       };
+      // the barrier a stage's loads are counted at: this CTA's, of a pair the leading CTA's
+      auto full_of = [&](int s) { return PAIR ? cluster_address_of(&full_bar[s], 0) : smem_addr(&full_bar[s]); };
       auto load_a = [&](int s, int kb, int m0, int e) {
         unsigned char* a = tiles + s * S::kStageBytes;
 #pragma unroll
@@ -213,21 +243,26 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
           const int k0 = (kb * S::kAtoms + h) * kBK;
           unsigned char* dst = a + h * kABytes;  // weight rows past the expert's last read as zero
           if (GATED) {  // (k, row in group, gate|up, group of 16 features, expert)
-            tma_load_5d(dst, &map_a, &full_bar[s], k0, 0, 0, m0 >> 4, e);
+            if (PAIR) tma_load_5d_pair(dst, &map_a, full_of(s), k0, 0, 0, m0 >> 4, e);
+            else tma_load_5d(dst, &map_a, &full_bar[s], k0, 0, 0, m0 >> 4, e);
           } else {
-            tma_load_3d(dst, &map_a, &full_bar[s], k0, m0, e);
+            if (PAIR) tma_load_3d_pair(dst, &map_a, full_of(s), k0, m0, e);
+            else tma_load_3d(dst, &map_a, &full_bar[s], k0, m0, e);
           }
         }
       };
       auto load_b = [&](int s, int kb, int row0, int rows) {
         if (gathers) return;  // warps 6 and 7 bring the rows
         unsigned char* b = tiles + s * S::kStageBytes + S::kAtoms * kABytes;
-        const int nb = (rows + S::kBBoxRows - 1) / S::kBBoxRows;
+        int b0, nb;
+        token_part(row0, rows, b0, nb);
 #pragma unroll
         for (int h = 0; h < S::kAtoms; ++h)
-          for (int jb = 0; jb < nb; ++jb)
-            tma_load_2d(b + h * S::kBBytes + jb * S::kBBoxRows * kBK * 2, &map_b, &full_bar[s],
-                        (kb * S::kAtoms + h) * kBK, row0 + jb * S::kBBoxRows);
+          for (int jb = 0; jb < nb; ++jb) {
+            unsigned char* dst = b + h * S::kBBytes + jb * S::kBBoxRows * kBK * 2;
+            if (PAIR) tma_load_2d_pair(dst, &map_b, full_of(s), (kb * S::kAtoms + h) * kBK, b0 + jb * S::kBBoxRows);
+            else tma_load_2d(dst, &map_b, &full_bar[s], (kb * S::kAtoms + h) * kBK, b0 + jb * S::kBBoxRows);
+          }
       };
       // the weights of the first loads, while the kernel before this one may still be running
       int ahead = 0;
@@ -236,7 +271,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
         locate(t_first, e, row0, rows, m0);
         ahead = min(depth_main, k_blocks);
         for (int kb = 0; kb < ahead; ++kb) {
-          mbar_expect_tx(&full_bar[kb], stage_bytes(rows));
+          if (rank == 0) mbar_expect_tx(&full_bar[kb], stage_bytes(rows));
           load_a(kb, kb, m0, e);
         }
         pdl_wait();
@@ -258,22 +293,23 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
             break;
           }
           const int s = i % S::kStages;
-          mbar_expect_tx(&full_bar[s], stage_bytes(rows));
+          if (rank == 0) mbar_expect_tx(&full_bar[s], stage_bytes(rows));
           load_a(s, kb, m0, e);
           load_b(s, kb, row0, rows);
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------ MMA issuer (of a pair: the leading CTA's)
+    if (lane == 0 && rank == 0) {
       int s = 0;
       uint32_t phase = 0;
       uint32_t acc_phase = 0;  // bit a: phase of accumulator buffer a
       int acc = 0;
       bool ok = true;
       for (int t = t_first; t < total_tiles && ok; t += G) {
-        if (!mbar_wait(&acc_empty[acc], ((acc_phase >> acc) & 1u) ^ 1u, abortp)) {
+        if (!(PAIR ? mbar_wait_cluster(&acc_empty[acc], ((acc_phase >> acc) & 1u) ^ 1u, abortp)
+                   : mbar_wait(&acc_empty[acc], ((acc_phase >> acc) & 1u) ^ 1u, abortp))) {
           atomicCAS(&g_status[0], 0, 102);
           abort_flag = 1;
           break;
@@ -282,10 +318,10 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
         int e, row0, rows, m0;
         locate(t, e, row0, rows, m0);
         // only the columns of tokens that exist are computed (and only their boxes were loaded)
-        const uint32_t idesc = instr_desc(min(BN, (rows + 15) & ~15));
+        const uint32_t idesc = PAIR ? instr_desc_pair(min(BN, (rows + 63) & ~63)) : instr_desc(min(BN, (rows + 15) & ~15));
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * S::kAccCols);
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(&full_bar[s], phase, abortp)) {
+          if (!mbar_wait(&full_bar[s], phase, abortp)) {  // (of a pair: both CTAs' loads are counted here)
             ok = false;
             atomicCAS(&g_status[0], 0, 103);
             abort_flag = 1;
@@ -299,17 +335,20 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
             const uint64_t b_desc = smem_desc(a_addr + S::kAtoms * kABytes + h * S::kBBytes);
             const uint64_t a_desc = smem_desc(a_addr + h * kABytes);
 #pragma unroll
-            for (int k = 0; k < kBK / 16; ++k)  // 16 k elements = 32 bytes = 2 descriptor units
-              tc_mma(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | h | k) != 0);
+            for (int k = 0; k < kBK / 16; ++k) {  // 16 k elements = 32 bytes = 2 descriptor units
+              if (PAIR) tc_mma_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | h | k) != 0);
+              else tc_mma(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | h | k) != 0);
+            }
           }
-          tc_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
+          // frees the stage (in both CTAs of a pair) when these MMAs have read it
+          if (PAIR) tc_commit_pair(&empty_bar[s]); else tc_commit(&empty_bar[s]);
           if (++s == S::kStages) {
             s = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        tc_commit(&acc_full[acc]);
+        if (PAIR) tc_commit_pair(&acc_full[acc]); else tc_commit(&acc_full[acc]);
         acc_phase ^= 1u << acc;
         acc ^= 1;
       }
@@ -462,7 +501,9 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
       auto release = [&]() {
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        if (lane == 0) {
+          if (PAIR && rank == 1) mbar_arrive_remote(&acc_empty[acc], 0); else mbar_arrive(&acc_empty[acc]);
+        }
       };
       // the next chunk's load runs under this chunk's arithmetic and stores
       uint32_t ra[16], rb[16];
@@ -490,9 +531,10 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // nothing of the partner's is still on its way to this CTA
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, S::kTmemCols);
+    if (PAIR) tmem_dealloc_pair(tmem_base, S::kTmemCols); else tmem_dealloc(tmem_base, S::kTmemCols);
   }
 }
 
@@ -550,6 +592,46 @@ static int launch_tc_impl(const CUtensorMap& ma, const CUtensorMap& mb, const Tc
   if (grid > max_tiles) grid = max_tiles;
   if (grid < 1) grid = 1;
   FTK_LAUNCH(kern, grid, kThreads, S::kDynamic, s, ma, mb, p);
+  return 0;
+}
+
+static int g_pairs_enabled = 1;
+
+// Token tiles of 256 rows, many tiles: pairs of CTAs on tiles of 256 weight rows.  -1 when the device
+// cannot hold a cluster of two such CTAs (the caller then launches the one-CTA form).
+template <bool GATED>
+static int launch_tc_pairs(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int max_token_tiles, cudaStream_t s) {
+  using S = Smem<256, true, true>;
+  auto kern = moe_gemm_tc_kernel<256, GATED, true, true>;
+  static int clusters = -1;
+  if (clusters < 0) {
+    clusters = 0;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic) != cudaSuccess) return -1;
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(sms / 2 * 2));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = S::kDynamic;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) clusters = n < sms / 2 ? n : sms / 2;
+    cudaGetLastError();
+  }
+  if (clusters < 1) return -1;
+  note_variant(GATED ? "expert gate/up product: tcgen05, 256 tokens a tile, pairs of CTAs"
+                     : "expert down product: tcgen05, 256 tokens a tile, pairs of CTAs");
+  const long long pair_tiles = (long long)max_token_tiles * ((p.m_tiles + 1) / 2);
+  const int pairs = (int)(pair_tiles < clusters ? (pair_tiles < 1 ? 1 : pair_tiles) : clusters);
+  launch_kernel_clusters(kern, 2, dim3((unsigned)(2 * pairs)), dim3(kThreads), (size_t)S::kDynamic, s, ma, mb, p);
   return 0;
 }
 
@@ -616,7 +698,18 @@ static int run_tc(const void* x, int x_cols, const void* w, int w_rows, const Tc
     case 32: rc = launch_tc<32, GATED>(ma, mb, p, max_tiles, likely_tiles, s); break;
     case 64: rc = launch_tc<64, GATED>(ma, mb, p, max_tiles, likely_tiles, s); break;
     case 128: rc = launch_tc<128, GATED>(ma, mb, p, max_tiles, likely_tiles, s); break;
-    default: rc = launch_tc<256, GATED>(ma, mb, p, max_tiles, likely_tiles, s); break;
+    default: {
+      int dev = 0, sms = 148;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      rc = -1;
+      // (the gate/up product only: with the down product's shorter sums the pairs were measured 8 % slower than
+      // single CTAs, 1.19 against 1.10 ms at 8,192 tokens; gate/up 1.50 against 1.86)
+      if (GATED && g_pairs_enabled && likely_tiles > 2 * sms && p.m_tiles >= 2 && !p.gather_src)
+        rc = launch_tc_pairs<GATED>(ma, mb, p, (p.n_routes + bn - 1) / bn + p.n_experts, s);
+      if (rc < 0) rc = launch_tc<256, GATED>(ma, mb, p, max_tiles, likely_tiles, s);
+      break;
+    }
   }
   if (rc) {
     set_error("%s: cannot configure the tensor-core kernel", name);
@@ -635,6 +728,12 @@ static int g_tc_enabled = 1;
 // 0 sends bfloat16 grouped products to the CUDA-core kernels (for comparisons); default 1.
 extern "C" int ftk_set_moe_tensor_cores(int enabled) {
   g_tc_enabled = enabled ? 1 : 0;
+  return 0;
+}
+
+// 0 keeps token tiles of 256 rows on the one-CTA form (for comparisons); default 1: pairs of CTAs where they fit.
+extern "C" int ftk_set_moe_pairs(int enabled) {
+  g_pairs_enabled = enabled ? 1 : 0;
   return 0;
 }
 

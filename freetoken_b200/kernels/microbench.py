@@ -69,6 +69,7 @@ def _time(fn, iters: int, warmup: int, profile: bool) -> float:
 
 def bench_moe(a) -> dict:
     dev = "cuda"
+    ops.set_moe_pairs(not getattr(a, "no_pairs", False))
     E, H, I, k, T = a.experts, a.hidden, a.inter, a.top_k, a.tokens
     g = torch.Generator(device=dev).manual_seed(0)
     w1 = torch.empty(E, 2 * I, H, dtype=torch.bfloat16, device=dev).normal_(0, 0.02, generator=g)
@@ -284,6 +285,8 @@ def main(argv=None) -> int:
             p.add_argument("--inter", type=int, default=1536)
             p.add_argument("--top-k", type=int, default=8)
             p.add_argument("--only", choices=["gemm1", "gemm2"], default=None)
+            p.add_argument("--no-pairs", action="store_true",
+                           help="256-token tiles on the one-CTA form of the tcgen05 kernel instead of pairs of CTAs")
         elif name == "attention":
             p.add_argument("--batch", type=int, default=8)
             p.add_argument("--context", type=int, default=2048)

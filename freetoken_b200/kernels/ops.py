@@ -102,6 +102,7 @@ _SIGNATURES = {
     "ftk_copy_tokens": [_vp, _i, _vp, _vp, _i, _i, _i, _vp],
     "ftk_read_status": [ctypes.POINTER(ctypes.c_int)],
     "ftk_set_moe_tensor_cores": [_i],
+    "ftk_set_moe_pairs": [_i],
     "ftk_debug_set_status": [_i, _i],
     "ftk_variant_counts": [ctypes.c_char_p, _i, _i],
 }
@@ -205,6 +206,12 @@ def debug_set_status(unit: int, code: int) -> None:
 def set_moe_tensor_cores(enabled: bool) -> None:
     """False sends bfloat16 grouped expert products to the CUDA-core kernels (comparisons only)."""
     _lib().ftk_set_moe_tensor_cores(1 if enabled else 0)
+
+
+def set_moe_pairs(enabled: bool) -> None:
+    """False keeps expert products with 256-token tiles on the one-CTA form of the tcgen05 kernel instead of
+    pairs of CTAs (comparisons only)."""
+    _lib().ftk_set_moe_pairs(1 if enabled else 0)
 
 
 # --------------------------------------------------------------------------- elementwise

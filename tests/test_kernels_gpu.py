@@ -669,6 +669,38 @@ def test_linear_pads_few_rows_inside_its_buffers(T, N, K, dtype):
     torch.testing.assert_close(tight_o.float(), want, **tol(dtype))
 
 
+@pytest.mark.parametrize("E,H,I,R", [(12, 1664, 1536, 4000), (24, 640, 1600, 2500), (100, 256, 128, 40000)])
+def test_moe_gate_up_product_by_pairs_of_ctas_equals_single_ctas(E, H, I, R):
+    """Token tiles of 256 rows, hundreds of tiles: the gate/up product runs on pairs of CTAs (cta_group::2:
+    256 weight rows a tile, each CTA loads half of the tokens).  Every output element is the same sum in the
+    same order as in the one-CTA form, so the results are equal bit for bit; experts with a few rows, with
+    exactly 256, with 257 and with none are among them, and widths of an odd number of feature tiles."""
+    g = torch.Generator().manual_seed(E)
+    ids = torch.randint(0, E, (R,), generator=g)
+    ids[: R // 3] = 3        # a crowded expert: several token tiles
+    ids[ids == 5] = 6        # an expert without rows
+    ids[R // 3: R // 3 + 256] = 7
+    ids[ids == 8] = 9
+    ids[R // 3 + 256: R // 3 + 256 + 257] = 8
+    counts = torch.bincount(ids, minlength=E)
+    off = torch.tensor([0] + counts.cumsum(0).tolist(), dtype=torch.int32, device=DEV)
+    x = rnd(R, H, dtype=torch.bfloat16)
+    w1 = rnd(E, 2 * I, H, dtype=torch.bfloat16, scale=0.05)
+    outs = []
+    for pairs in (True, False):
+        ops.set_moe_pairs(pairs)
+        ops.variant_counts(reset=True)
+        a = torch.full((R, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.moe_gemm1_act(x, w1, off, "swigluoai", 1.702, 7.0, a)
+        ran = ops.variant_counts()
+        assert bool(ran.get("expert gate/up product: tcgen05, 256 tokens a tile, pairs of CTAs")) == pairs, ran
+        outs.append(a)
+    ops.set_moe_pairs(True)
+    assert ops.read_status() == 0
+    assert not torch.isnan(outs[0]).any()
+    assert torch.equal(outs[0], outs[1])
+
+
 @pytest.mark.parametrize("scoring,bias", [("sigmoid", True), ("softmax", False)])
 @pytest.mark.parametrize("T,H,E,k", [(1, 64, 8, 2), (8, 3072, 256, 8), (13, 100, 7, 3), (32, 520, 33, 5), (9, 36, 301, 1),
                                      (1, 3072, 256, 8), (3, 64, 256, 8), (5, 128, 200, 6), (6, 96, 64, 64), (12, 256, 100, 4),
