@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
   __shared__ int abort_flag;
   __shared__ int tile_prefix[kMaxExperts + 1];  // token tiles of experts 0..e-1
   __shared__ float turn[4][16][33];             // per epilogue warp: a 16-token chunk turned round
-  __shared__ float tile_w[GATED ? 1 : 4][GATED ? 1 : BN];  // per epilogue warp: the route weights of a tile's tokens
+  __shared__ float tile_w[GATED ? 1 : 2][GATED ? 1 : 4][GATED ? 1 : BN];  // per epilogue warp: the route weights of this tile's tokens and the next's
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t tiles_base = (smem_addr(dyn_smem) + 1023u) & ~1023u;
@@ -414,22 +414,39 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
     uint32_t acc_phase = 0;
     int acc = 0;
     pdl_wait();  // nothing is stored while the kernel before this one runs; a block without tiles waits too
+    // The route weights of a tile's tokens (down product) are two loads, one after the other: token -> route ->
+    // weight.  They are fetched a tile ahead, the routes before this tile's accumulator is waited for, the
+    // weights in the middle of its chunks, so that neither holds the epilogue up.
+    constexpr int kWPer = (BN + 31) / 32;
+    int wbuf = 0;
+    int next_route[kWPer];
+    auto fetch_routes = [&](int t2) {
+      int e2, row02, rows2, m02;
+      if (t2 < total_tiles) locate(t2, e2, row02, rows2, m02); else rows2 = 0;
+#pragma unroll
+      for (int j = 0; j < kWPer; ++j) {
+        const int n = lane + 32 * j;
+        next_route[j] = (n < rows2) ? p.sorted_routes[row02 + n] : -1;
+      }
+    };
+    auto fetch_weights = [&](int buf) {
+      float wv[kWPer];
+#pragma unroll
+      for (int j = 0; j < kWPer; ++j)
+        wv[j] = (next_route[j] >= 0 && next_route[j] < p.n_routes) ? p.route_weights[next_route[j]] : 0.f;
+#pragma unroll
+      for (int j = 0; j < kWPer; ++j)
+        if (lane + 32 * j < BN) tile_w[buf][quad][lane + 32 * j] = wv[j];
+      __syncwarp();
+    };
+    if (!GATED) {
+      fetch_routes(t_first);
+      fetch_weights(0);
+    }
     for (int t = t_first; t < total_tiles; t += G) {
       int e, row0, rows, m0;
       locate(t, e, row0, rows, m0);
-      if (!GATED) {
-        // the route weights of the tile's tokens, fetched while the products still run
-        __syncwarp();
-        for (int n = lane; n < BN; n += 32) {
-          float wl = 0.f;
-          if (n < rows) {
-            const int route = p.sorted_routes[row0 + n];
-            wl = (route >= 0 && route < p.n_routes) ? p.route_weights[route] : 0.f;
-          }
-          tile_w[quad][n] = wl;
-        }
-        __syncwarp();
-      }
+      if (!GATED) fetch_routes(t + G);
       // the whole warp takes one decision: the loads below need all 32 lanes
       if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[acc], (acc_phase >> acc) & 1u, abortp))) {
         if (lane == 0) atomicCAS(&g_status[0], 0, 104);
@@ -474,7 +491,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
           __syncwarp();
         } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) tb[i][lane] = __uint_as_float(r[i]) * tile_w[quad][c + i];
+          for (int i = 0; i < 16; ++i) tb[i][lane] = __uint_as_float(r[i]) * tile_w[wbuf][quad][c + i];
           __syncwarp();
           // 16 tokens x 32 features: two 16-byte stores per thread
 #pragma unroll
@@ -508,8 +525,13 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
       // the next chunk's load runs under this chunk's arithmetic and stores
       uint32_t ra[16], rb[16];
       tmem_ld16_start(t_addr, ra);
+      bool weights_fetched = GATED;
 #pragma unroll 1
       for (int c = 0; c < c_end; c += 32) {
+        if (!weights_fetched && 2 * c >= c_end) {  // (the other buffer: this tile still reads its own)
+          fetch_weights(wbuf ^ 1);
+          weights_fetched = true;
+        }
         tmem_ld16_finish(ra);
         const bool more = c + 16 < c_end;
         if (more) tmem_ld16_start(t_addr + c + 16, rb); else release();
@@ -520,6 +542,8 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_tc_kernel(const __grid_cons
           chunk(rb, c + 16);
         }
       }
+      if (!weights_fetched) fetch_weights(wbuf ^ 1);
+      wbuf ^= 1;
       acc_phase ^= 1u << acc;
       acc ^= 1;
     }
@@ -703,9 +727,7 @@ static int run_tc(const void* x, int x_cols, const void* w, int w_rows, const Tc
       cudaGetDevice(&dev);
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
       rc = -1;
-      // (the gate/up product only: with the down product's shorter sums the pairs were measured 8 % slower than
-      // single CTAs, 1.19 against 1.10 ms at 8,192 tokens; gate/up 1.50 against 1.86)
-      if (GATED && g_pairs_enabled && likely_tiles > 2 * sms && p.m_tiles >= 2 && !p.gather_src)
+      if (g_pairs_enabled && likely_tiles > 2 * sms && p.m_tiles >= 2 && !p.gather_src)
         rc = launch_tc_pairs<GATED>(ma, mb, p, (p.n_routes + bn - 1) / bn + p.n_experts, s);
       if (rc < 0) rc = launch_tc<256, GATED>(ma, mb, p, max_tiles, likely_tiles, s);
       break;

@@ -670,8 +670,8 @@ def test_linear_pads_few_rows_inside_its_buffers(T, N, K, dtype):
 
 
 @pytest.mark.parametrize("E,H,I,R", [(12, 1664, 1536, 4000), (24, 640, 1600, 2500), (100, 256, 128, 40000)])
-def test_moe_gate_up_product_by_pairs_of_ctas_equals_single_ctas(E, H, I, R):
-    """Token tiles of 256 rows, hundreds of tiles: the gate/up product runs on pairs of CTAs (cta_group::2:
+def test_moe_products_by_pairs_of_ctas_equal_single_ctas(E, H, I, R):
+    """Token tiles of 256 rows, hundreds of tiles: the expert products run on pairs of CTAs (cta_group::2:
     256 weight rows a tile, each CTA loads half of the tokens).  Every output element is the same sum in the
     same order as in the one-CTA form, so the results are equal bit for bit; experts with a few rows, with
     exactly 256, with 257 and with none are among them, and widths of an odd number of feature tiles."""
@@ -686,19 +686,27 @@ def test_moe_gate_up_product_by_pairs_of_ctas_equals_single_ctas(E, H, I, R):
     off = torch.tensor([0] + counts.cumsum(0).tolist(), dtype=torch.int32, device=DEV)
     x = rnd(R, H, dtype=torch.bfloat16)
     w1 = rnd(E, 2 * I, H, dtype=torch.bfloat16, scale=0.05)
+    w2 = rnd(E, H, I, dtype=torch.bfloat16, scale=0.05)
+    a_in = rnd(R, I, dtype=torch.bfloat16, seed=9)
+    routes = torch.randperm(R).to(torch.int32).to(DEV)
+    wts = torch.rand(R, device=DEV) + 0.5
     outs = []
     for pairs in (True, False):
         ops.set_moe_pairs(pairs)
         ops.variant_counts(reset=True)
         a = torch.full((R, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+        y = torch.full((R, H), float("nan"), dtype=torch.bfloat16, device=DEV)
         ops.moe_gemm1_act(x, w1, off, "swigluoai", 1.702, 7.0, a)
+        ops.moe_gemm2(a_in, w2, off, routes, wts, y)
         ran = ops.variant_counts()
         assert bool(ran.get("expert gate/up product: tcgen05, 256 tokens a tile, pairs of CTAs")) == pairs, ran
-        outs.append(a)
+        if (H + 127) // 128 * E * 2 > 296:  # (enough tiles of the down product for the deep form)
+            assert bool(ran.get("expert down product: tcgen05, 256 tokens a tile, pairs of CTAs")) == pairs, ran
+        outs.append((a, y))
     ops.set_moe_pairs(True)
     assert ops.read_status() == 0
-    assert not torch.isnan(outs[0]).any()
-    assert torch.equal(outs[0], outs[1])
+    assert not torch.isnan(outs[0][0]).any() and not torch.isnan(outs[0][1]).any()
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
 
 
 @pytest.mark.parametrize("scoring,bias", [("sigmoid", True), ("softmax", False)])
