@@ -84,7 +84,7 @@ struct Smem {
   // 64-element pieces of k per stage.  Two of them make every row of a weight tile a 256-byte read,
   // which the memory serves faster than twice 128 bytes (measured: 6.7 against 6.1 TB/s).
   static constexpr int kAtoms = DEEP ? 2 : 1;
-  static constexpr int kStages = PAIR ? 3
+  static constexpr int kStages = PAIR ? (BN <= 128 ? 4 : 3)
                                  : DEEP ? (BN <= 16 ? 5 : (BN <= 32 ? 4 : (BN <= 64 ? 4 : (BN <= 128 ? 3 : 2))))
                                         : (BN <= 16 ? 5 : (BN <= 128 ? 4 : 3));
   // loads kept in flight while every CTA streams (measured for the small token tiles: 144 KB per SM
@@ -623,10 +623,10 @@ static int g_pairs_enabled = 1;
 
 // Token tiles of 256 rows, many tiles: pairs of CTAs on tiles of 256 weight rows.  -1 when the device
 // cannot hold a cluster of two such CTAs (the caller then launches the one-CTA form).
-template <bool GATED>
+template <int BN, bool GATED>
 static int launch_tc_pairs(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int max_token_tiles, cudaStream_t s) {
-  using S = Smem<256, true, true>;
-  auto kern = moe_gemm_tc_kernel<256, GATED, true, true>;
+  using S = Smem<BN, true, true>;
+  auto kern = moe_gemm_tc_kernel<BN, GATED, true, true>;
   static int clusters = -1;
   if (clusters < 0) {
     clusters = 0;
@@ -651,8 +651,10 @@ static int launch_tc_pairs(const CUtensorMap& ma, const CUtensorMap& mb, const T
     cudaGetLastError();
   }
   if (clusters < 1) return -1;
-  note_variant(GATED ? "expert gate/up product: tcgen05, 256 tokens a tile, pairs of CTAs"
-                     : "expert down product: tcgen05, 256 tokens a tile, pairs of CTAs");
+  note_variant(BN == 256 ? (GATED ? "expert gate/up product: tcgen05, 256 tokens a tile, pairs of CTAs"
+                                  : "expert down product: tcgen05, 256 tokens a tile, pairs of CTAs")
+                         : (GATED ? "expert gate/up product: tcgen05, 128 tokens a tile, pairs of CTAs"
+                                  : "expert down product: tcgen05, 128 tokens a tile, pairs of CTAs"));
   const long long pair_tiles = (long long)max_token_tiles * ((p.m_tiles + 1) / 2);
   const int pairs = (int)(pair_tiles < clusters ? (pair_tiles < 1 ? 1 : pair_tiles) : clusters);
   launch_kernel_clusters(kern, 2, dim3((unsigned)(2 * pairs)), dim3(kThreads), (size_t)S::kDynamic, s, ma, mb, p);
@@ -721,14 +723,23 @@ static int run_tc(const void* x, int x_cols, const void* w, int w_rows, const Tc
     case 16: rc = launch_tc<16, GATED>(ma, mb, p, max_tiles, likely_tiles, s); break;
     case 32: rc = launch_tc<32, GATED>(ma, mb, p, max_tiles, likely_tiles, s); break;
     case 64: rc = launch_tc<64, GATED>(ma, mb, p, max_tiles, likely_tiles, s); break;
-    case 128: rc = launch_tc<128, GATED>(ma, mb, p, max_tiles, likely_tiles, s); break;
+    case 128: {
+      int dev = 0, sms = 148;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      rc = -1;
+      if (g_pairs_enabled && likely_tiles > 2 * sms && p.m_tiles >= 2 && !p.gather_src)
+        rc = launch_tc_pairs<128, GATED>(ma, mb, p, (p.n_routes + bn - 1) / bn + p.n_experts, s);
+      if (rc < 0) rc = launch_tc<128, GATED>(ma, mb, p, max_tiles, likely_tiles, s);
+      break;
+    }
     default: {
       int dev = 0, sms = 148;
       cudaGetDevice(&dev);
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
       rc = -1;
       if (g_pairs_enabled && likely_tiles > 2 * sms && p.m_tiles >= 2 && !p.gather_src)
-        rc = launch_tc_pairs<GATED>(ma, mb, p, (p.n_routes + bn - 1) / bn + p.n_experts, s);
+        rc = launch_tc_pairs<256, GATED>(ma, mb, p, (p.n_routes + bn - 1) / bn + p.n_experts, s);
       if (rc < 0) rc = launch_tc<256, GATED>(ma, mb, p, max_tiles, likely_tiles, s);
       break;
     }
@@ -753,7 +764,7 @@ extern "C" int ftk_set_moe_tensor_cores(int enabled) {
   return 0;
 }
 
-// 0 keeps token tiles of 256 rows on the one-CTA form (for comparisons); default 1: pairs of CTAs where they fit.
+// 0 keeps token tiles of 128 and 256 rows on the one-CTA form (for comparisons); default 1: pairs of CTAs where they fit.
 extern "C" int ftk_set_moe_pairs(int enabled) {
   g_pairs_enabled = enabled ? 1 : 0;
   return 0;

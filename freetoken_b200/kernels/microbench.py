@@ -286,7 +286,7 @@ def main(argv=None) -> int:
             p.add_argument("--top-k", type=int, default=8)
             p.add_argument("--only", choices=["gemm1", "gemm2"], default=None)
             p.add_argument("--no-pairs", action="store_true",
-                           help="256-token tiles on the one-CTA form of the tcgen05 kernel instead of pairs of CTAs")
+                           help="128- and 256-token tiles on the one-CTA form of the tcgen05 kernel instead of pairs of CTAs")
         elif name == "attention":
             p.add_argument("--batch", type=int, default=8)
             p.add_argument("--context", type=int, default=2048)

@@ -209,8 +209,8 @@ def set_moe_tensor_cores(enabled: bool) -> None:
 
 
 def set_moe_pairs(enabled: bool) -> None:
-    """False keeps expert products with 256-token tiles on the one-CTA form of the tcgen05 kernel instead of
-    pairs of CTAs (comparisons only)."""
+    """False keeps expert products with 128- and 256-token tiles on the one-CTA form of the tcgen05 kernel instead
+    of pairs of CTAs (comparisons only)."""
     _lib().ftk_set_moe_pairs(1 if enabled else 0)
 
 

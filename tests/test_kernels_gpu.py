@@ -669,10 +669,11 @@ def test_linear_pads_few_rows_inside_its_buffers(T, N, K, dtype):
     torch.testing.assert_close(tight_o.float(), want, **tol(dtype))
 
 
-@pytest.mark.parametrize("E,H,I,R", [(12, 1664, 1536, 4000), (24, 640, 1600, 2500), (100, 256, 128, 40000)])
+@pytest.mark.parametrize("E,H,I,R", [(12, 1664, 1536, 4000), (24, 640, 1600, 2500), (100, 256, 128, 40000),
+                                     (40, 1152, 1088, 1900)])
 def test_moe_products_by_pairs_of_ctas_equal_single_ctas(E, H, I, R):
-    """Token tiles of 256 rows, hundreds of tiles: the expert products run on pairs of CTAs (cta_group::2:
-    256 weight rows a tile, each CTA loads half of the tokens).  Every output element is the same sum in the
+    """Token tiles of 256 (in the last case 128) rows, hundreds of tiles: the expert products run on pairs of CTAs
+    (cta_group::2: 256 weight rows a tile, each CTA loads half of the tokens).  Every output element is the same sum in the
     same order as in the one-CTA form, so the results are equal bit for bit; experts with a few rows, with
     exactly 256, with 257 and with none are among them, and widths of an odd number of feature tiles."""
     g = torch.Generator().manual_seed(E)
@@ -699,9 +700,10 @@ def test_moe_products_by_pairs_of_ctas_equal_single_ctas(E, H, I, R):
         ops.moe_gemm1_act(x, w1, off, "swigluoai", 1.702, 7.0, a)
         ops.moe_gemm2(a_in, w2, off, routes, wts, y)
         ran = ops.variant_counts()
-        assert bool(ran.get("expert gate/up product: tcgen05, 256 tokens a tile, pairs of CTAs")) == pairs, ran
-        if (H + 127) // 128 * E * 2 > 296:  # (enough tiles of the down product for the deep form)
-            assert bool(ran.get("expert down product: tcgen05, 256 tokens a tile, pairs of CTAs")) == pairs, ran
+        tile = 128 if R // E < 80 else 256  # (the last case has 128-token tiles)
+        assert bool(ran.get(f"expert gate/up product: tcgen05, {tile} tokens a tile, pairs of CTAs")) == pairs, ran
+        if (H + 127) // 128 * E * (256 // tile) > 296:  # (enough tiles of the down product for the deep form)
+            assert bool(ran.get(f"expert down product: tcgen05, {tile} tokens a tile, pairs of CTAs")) == pairs, ran
         outs.append((a, y))
     ops.set_moe_pairs(True)
     assert ops.read_status() == 0

@@ -1,7 +1,7 @@
 """The engine at MiniMax-M3's real layer sizes (one layer of hidden 3072, 48 query / 8 KV heads of
 128, rotary 64, 256 experts top-8 of width 1536, sigmoid router with bias): sizes at which steps take
 kernel forms that the tiny configurations never reach (the two-tile tcgen05 attention, tensor-core
-expert products with wide token tiles and deep pipelines, the three-pass route sort, the expert choice
+expert products with wide token tiles, deep pipelines and pairs of CTAs, the three-pass route sort, the expert choice
 after a library product, library products over thousands of columns).  The vocabulary is cut to
 20,008 rows (the real 200,064 would only lengthen the head product, which is the library's).
 
@@ -146,7 +146,7 @@ def test_cuts_agree_at_real_sizes(dtype, real):
 
     if dtype == "bfloat16":  # the forms these sizes were meant to reach
         assert ran_whole.get("attention: tcgen05, two 128-row query tiles per CTA")
-        assert any(k.startswith("expert gate/up product: tcgen05") and "deep pipeline" in k and
+        assert any(k.startswith("expert gate/up product: tcgen05") and ("deep pipeline" in k or "pairs of CTAs" in k) and
                    any(f"{n} tokens a tile" in k for n in (64, 128, 256)) for k in ran_whole), ran_whole
         assert ran_whole.get("route sort: three passes over 128-route segments")
         assert ran_whole.get("routing: expert choice from logits given in pieces")
