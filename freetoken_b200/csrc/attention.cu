@@ -951,7 +951,10 @@ static int paged_attention_tc_impl(const void* q, const void* k_slab, const void
   FTK_LAUNCH_CHECK("paged_attention_tc");
   if (n_slots > 0) {
     dim3 grid(n_items, n_kv_heads);
-    FTK_LAUNCH(attention_merge_kernel<__nv_bfloat16>, grid, 128, 0, s, p);
+    // a CTA merges its share of a tile's rows, a warp a row at a time (three trips to memory one after the
+    // other): tiles of 128 and 256 rows get as many warps as a tile cut in two has rows per CTA / 4
+    const int threads = p.tile_rows >= 256 ? 768 : (p.tile_rows >= 128 ? 512 : 128);  // (71 registers a thread)
+    FTK_LAUNCH(attention_merge_kernel<__nv_bfloat16>, grid, threads, 0, s, p);
     FTK_LAUNCH_CHECK("paged_attention_tc merge");
   }
   return 0;

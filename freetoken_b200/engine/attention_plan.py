@@ -32,6 +32,7 @@ class AttentionPlan:
     n_slots: int  # partial slots used (0 when nothing is split)
     tokens_per_tile: int
     max_splits: int
+    est_us: Optional[float] = None  # the launch's estimated time, where the kernel's costs per piece were given
 
 
 FIXED_COST_KEYS = 100  # what a CTA's start-up, write-out and merge cost, in keys' worth of time
@@ -102,11 +103,29 @@ def tokens_per_tile(tile_rows: int, group: int) -> int:
     return max(1, tile_rows // group)
 
 
+@dataclass(frozen=True)
+class PieceCosts:
+    """What a piece of work costs a tcgen05 attention kernel, fitted to timings on a B200 (21 portions of 256
+    to 4,096 tokens after 0 to 65,536 earlier ones, both forms; the estimates built on these are within 10 % of
+    every one of them and name the faster form in every case): microseconds per 128-key tile of a piece, per
+    piece, and on top per piece of a tile that is cut along the keys (its partial result is written in 32-bit
+    and merged)."""
+    us_per_key_tile: float
+    fixed_us: float
+    split_us: float
+
+
+TC_ONE_TILE_COSTS = PieceCosts(1.35, 4.0, 3.0)  # 128 query rows a piece
+TC_TWO_TILE_COSTS = PieceCosts(2.1, 6.0, 9.0)   # 256 query rows a piece (two tiles on the same keys)
+LAUNCH_US = 4.0
+
+
 def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
                window: Optional[int], n_kv_heads: int, sm_count: int = 148,
                max_splits: int = 32, min_split_keys: int = 256,
                fixed_splits: Optional[int] = None,
-               sparse: Optional[Tuple[int, int]] = None, key_tile: Optional[int] = None) -> AttentionPlan:
+               sparse: Optional[Tuple[int, int]] = None, key_tile: Optional[int] = None,
+               costs: Optional[PieceCosts] = None) -> AttentionPlan:
     """``segments`` holds (q_len, kv_len) per segment, in step order.
 
     ``fixed_splits`` fixes the number of item rows at that many per tile on average: the rows are dealt
@@ -119,7 +138,8 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
     SM through the whole list (128 for the tcgen05 kernels; None: 128 for tiles of 128 rows and more,
     else 0): pieces are then multiples of it, the list is sorted by length, and for lists of a few pieces
     per CTA the number of pieces per tile is the one with which the kernel's dealing ends soonest
-    (:func:`dealt_makespan`).
+    (:func:`dealt_makespan`).  ``costs`` gives that search the kernel's measured costs per piece and the
+    plan an estimate of the launch's time (``est_us``), by which a step chooses between kernel forms.
 
     ``sparse = (block_size, topk)`` plans a block-sparse layer: one token per tile (every token has
     its own choice of key blocks) and key ranges that count chosen keys: ``min(topk, visible
@@ -127,89 +147,91 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
     if key_tile is None:
         key_tile = 128 if tile_rows >= 128 else 0
     tpt = 1 if sparse else tokens_per_tile(tile_rows, group)
-    tiles: List[Tuple[int, int, int, int, int]] = []  # seg, tok0, ntok, lo, hi
-    for s, (q_len, kv_len) in enumerate(segments):
-        pos0 = kv_len - q_len
-        for tok0 in range(0, q_len, tpt):
-            ntok = min(tpt, q_len - tok0)
-            hi = pos0 + tok0 + ntok  # last query's position + 1
-            lo = 0
-            if window is not None:
-                lo = max(0, pos0 + tok0 - window + 1)
-            if sparse:
-                block, topk = sparse
-                lo, hi = 0, min(topk, (pos0 + tok0) // block + 1) * block
-            tiles.append((s, tok0, ntok, lo, hi))
-    n_tiles = len(tiles)
+    # tiles: segment, first token, tokens, first key, one past the last key
+    seg_q = np.asarray([q for q, _ in segments], dtype=np.int64).reshape(-1)
+    seg_kv = np.asarray([kv for _, kv in segments], dtype=np.int64).reshape(-1)
+    per_seg = -(-np.maximum(seg_q, 0) // tpt)
+    seg = np.repeat(np.arange(seg_q.shape[0], dtype=np.int64), per_seg)
+    tok0 = (np.arange(int(per_seg.sum()), dtype=np.int64) - (np.cumsum(per_seg) - per_seg)[seg]) * tpt
+    ntok = np.minimum(tpt, seg_q[seg] - tok0)
+    pos0 = (seg_kv - seg_q)[seg]
+    hi = pos0 + tok0 + ntok  # last query's position + 1
+    lo = np.zeros_like(hi)
+    if window is not None:
+        lo = np.maximum(0, pos0 + tok0 - window + 1)
+    if sparse:
+        block, topk = sparse
+        lo = np.zeros_like(hi)
+        hi = np.minimum(topk, (pos0 + tok0) // block + 1) * block
+    spans = hi - lo
+    n_tiles = int(spans.shape[0])
     target = 2 * sm_count
-    # keys of all tiles together, per resident CTA: a tile that is long against that and against the
-    # other tiles would keep one SM busy long after the rest is done (a long portion beside many
-    # single tokens), so it is cut into pieces of half that share
-    all_keys = sum(hi - lo for _, _, _, lo, hi in tiles)
-    piece = max(all_keys * n_kv_heads / max(1, target) / 2, float(min_split_keys))
-    mean_span = all_keys / max(1, n_tiles)
-    rows: List[List[int]] = []
-    n_slots = 0
-    dealt = None
-    if fixed_splits is not None and fixed_splits > 1:
-        dealt = deal_rows([hi - lo for _, _, _, lo, hi in tiles], n_tiles * fixed_splits, max(fixed_splits, max_splits))
     quantum = key_tile if key_tile else SPLIT_QUANTUM  # a piece that ends inside a key tile pays for all of it
-    wants: List[int] = []
-    mosts: List[int] = []
-    for ti, (s, tok0, ntok, lo, hi) in enumerate(tiles):
-        span = hi - lo
-        most = min(max_splits, max(1, span // min_split_keys))
-        if fixed_splits is not None:
-            want = dealt[ti] if dealt is not None else fixed_splits
-        elif n_tiles * n_kv_heads >= target:
-            want = 1
-            if span > piece and span > 2 * mean_span:
-                want = max(1, min(most, int(-(-span // piece))))
+    quanta = -(-spans // quantum)
+    mosts = np.minimum(max_splits, np.maximum(1, spans // min_split_keys))
+    dealt = None
+    if fixed_splits is not None:
+        if fixed_splits > 1:
+            dealt = deal_rows(spans.tolist(), n_tiles * fixed_splits, max(fixed_splits, max_splits))
+            wants = np.asarray(dealt, dtype=np.int64)
         else:
-            # splits that fill whole waves of resident CTAs, none shorter than min_split_keys
-            if key_tile:  # (no more pieces than the mixers set partial results aside for)
-                most = max(1, min(most, DEAL_MOST_PIECES * target // (n_tiles * n_kv_heads)))
-            want = wave_splits(n_tiles * n_kv_heads, target, most, span)
-        wants.append(want)
-        mosts.append(most)
+            wants = np.full(n_tiles, fixed_splits, dtype=np.int64)
+    elif n_tiles * n_kv_heads >= target:
+        # keys of all tiles together, per resident CTA: a tile that is long against that and against the
+        # other tiles would keep one SM busy long after the rest is done (a long portion beside many
+        # single tokens), so it is cut into pieces of half that share
+        all_keys = int(spans.sum())
+        piece = max(all_keys * n_kv_heads / max(1, target) / 2, float(min_split_keys))
+        mean_span = all_keys / max(1, n_tiles)
+        cut_it = (spans > piece) & (spans > 2 * mean_span)
+        wants = np.where(cut_it, np.maximum(1, np.minimum(mosts, np.ceil(spans / piece).astype(np.int64))), 1)
+    else:
+        # splits that fill whole waves of resident CTAs, none shorter than min_split_keys
+        if key_tile and n_tiles:  # (no more pieces than the mixers set partial results aside for)
+            mosts = np.maximum(1, np.minimum(mosts, DEAL_MOST_PIECES * target // (n_tiles * n_kv_heads)))
+        known = {}
+        wants = np.ones(n_tiles, dtype=np.int64)
+        for i in range(n_tiles):
+            k = (int(mosts[i]), int(spans[i]))
+            if k not in known:
+                known[k] = wave_splits(n_tiles * n_kv_heads, target, k[0], k[1])
+            wants[i] = known[k]
 
-    def cut(span: int, want: int) -> Tuple[int, int]:
-        """(keys per piece, pieces) of a tile cut into at most ``want`` pieces of whole quanta."""
-        quanta = -(-span // quantum)
-        n_real = max(1, min(want, quanta))
-        per = -(-quanta // n_real) * quantum
-        return per, (max(1, -(-span // per)) if span > 0 else 1)
+    fixed_keys, split_keys = float(FIXED_COST_KEYS), float(SPLIT_COST_KEYS)
+    if costs is not None and key_tile:
+        fixed_keys = costs.fixed_us / costs.us_per_key_tile * key_tile
+        split_keys = costs.split_us / costs.us_per_key_tile * key_tile
 
-    if key_tile and fixed_splits is None and n_tiles * n_kv_heads <= DEAL_SEARCH_LIMIT * target:
+    def pieces_of(counts: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
+        """(keys per piece, pieces) of every tile cut into at most ``counts`` pieces of whole quanta."""
+        n = np.maximum(1, np.minimum(counts, quanta))
+        per = -(-np.maximum(quanta, 1) // n) * quantum
+        return per, np.where(spans > 0, np.maximum(1, -(-spans // per)), 1)
+
+    def played(counts: np.ndarray) -> Optional[float]:
+        per, n = pieces_of(counts)
+        if int(n[n > 1].sum()) * n_kv_heads > DEAL_MOST_PIECES * target:
+            return None  # (the partial results of so many pieces would not fit what the mixers set aside)
+        piece_keys = np.repeat(per, n).astype(np.float64)
+        last = np.cumsum(n) - 1
+        piece_keys[last] = spans - (n - 1) * per      # a tile's last piece is what is left
+        piece_keys += fixed_keys + np.repeat(np.where(n > 1, split_keys, 0.0), n)
+        return dealt_makespan(piece_keys, n_kv_heads, target, key_tile)
+
+    best_t = None
+    if key_tile and fixed_splits is None and n_tiles and n_tiles * n_kv_heads <= DEAL_SEARCH_LIMIT * target:
         # The tcgen05 kernels run one CTA per SM through the sorted list, to and fro; with a few pieces per
         # CTA the last round decides (200 equal pieces on 148 CTAs take two rounds, 400 halves three half
         # rounds).  So: the counts from above against pieces of at most L keys for a few L (a k-th of the
         # longest tile; shorter tiles get fewer pieces), the kernel's dealing played through for each.
-        spans = np.asarray([hi - lo for _, _, _, lo, hi in tiles], dtype=np.int64)
-        quanta = -(-spans // quantum)
-        cap = np.asarray(mosts, dtype=np.int64)
-
-        def played(counts: np.ndarray) -> Optional[float]:
-            n = np.maximum(1, np.minimum(counts, quanta))
-            per = -(-quanta // n) * quantum          # keys per piece, as cut() has them
-            n = np.where(spans > 0, np.maximum(1, -(-spans // per)), 1)
-            if int(n[n > 1].sum()) * n_kv_heads > DEAL_MOST_PIECES * target:
-                return None  # (the partial results of so many pieces would not fit what the mixers set aside)
-            costs = np.repeat(per, n).astype(np.float64)
-            last = np.cumsum(n) - 1
-            costs[last] = spans - (n - 1) * per      # a tile's last piece is what is left
-            costs += FIXED_COST_KEYS + np.repeat(np.where(n > 1, SPLIT_COST_KEYS, 0), n)
-            return dealt_makespan(costs, n_kv_heads, target, key_tile)
-
-        best = np.asarray(wants, dtype=np.int64)
-        best_t = played(best)
-        longest = int(spans.max()) if n_tiles else 0
+        best, best_t = wants, played(wants)
+        longest = int(spans.max())
         seen = None
         for k in range(1, DEAL_MOST_CUTS + 1):
             limit = -(-longest // (k * quantum)) * quantum  # keys per piece
             if limit < min_split_keys:
                 break
-            counts = np.maximum(1, np.minimum(cap, -(-spans // limit)))
+            counts = np.maximum(1, np.minimum(mosts, -(-spans // limit)))
             if seen is not None and np.array_equal(counts, seen):
                 continue
             seen = counts
@@ -218,24 +240,33 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
                 break  # (more cuts need more room still)
             if best_t is None or t < best_t * 0.97:
                 best, best_t = counts, t
-        wants = [int(x) for x in best]
+        wants = best
 
-    for ti, (s, tok0, ntok, lo, hi) in enumerate(tiles):
-        span = hi - lo
-        want = wants[ti]
-        per, n_real = cut(span, want)
-        n_rows = want if fixed_splits is not None else n_real
-        base = n_slots if n_rows > 1 else 0
-        for i in range(n_rows):
-            b = min(hi, lo + i * per)
-            e = min(hi, lo + (i + 1) * per)
-            rows.append([s, tok0, ntok, b, e, n_rows, i, base])
-        if n_rows > 1 or dealt is not None:  # (fixed plans: the slots are numbered the same whatever the shares)
-            n_slots += n_rows
-    if key_tile:
+    per, n_real = pieces_of(wants)
+    n_rows = wants if fixed_splits is not None else n_real
+    n_rows = np.maximum(1, n_rows)
+    slotted = (n_rows > 1) | (dealt is not None)  # (fixed plans: the slots are numbered the same whatever the shares)
+    slot_start = np.cumsum(np.where(slotted, n_rows, 0)) - np.where(slotted, n_rows, 0)
+    n_slots = int(np.where(slotted, n_rows, 0).sum())
+    tile_of = np.repeat(np.arange(n_tiles), n_rows)
+    first = np.cumsum(n_rows) - n_rows
+    i = np.arange(int(n_rows.sum())) - first[tile_of]
+    b = np.minimum(hi[tile_of], lo[tile_of] + i * per[tile_of])
+    e = np.minimum(hi[tile_of], lo[tile_of] + (i + 1) * per[tile_of])
+    base = np.where(n_rows[tile_of] > 1, slot_start[tile_of], 0)
+    items = np.stack([seg[tile_of], tok0[tile_of], ntok[tile_of], b, e, n_rows[tile_of], i, base], axis=1)
+    if key_tile and items.shape[0]:
         # the tcgen05 kernels deal the list out from its end, to and fro over its CTAs: longest pieces last
         # here (their place in the list means nothing else: partial results are found by base + split)
-        rows.sort(key=lambda r: r[4] - r[3])
-    items = np.asarray(rows, dtype=np.int32).reshape(-1, ITEM_INTS)
+        items = items[np.argsort(e - b, kind="stable")]
+    items = np.ascontiguousarray(items, dtype=np.int32).reshape(-1, ITEM_INTS)
+    est_us = None
+    if costs is not None and key_tile and n_tiles and fixed_splits is None:
+        if best_t is None:
+            best_t = played(wants)
+        if best_t is not None:
+            est_us = best_t / key_tile * costs.us_per_key_tile + LAUNCH_US
+            if n_slots:  # partial results written and read again in 32-bit (heads of 128), and the merge's launch
+                est_us += 4.0 + n_slots * n_kv_heads * min(tile_rows, 256) * 130 * 4 / 4e6
     return AttentionPlan(items=items, n_items=items.shape[0], n_slots=n_slots,
-                         tokens_per_tile=tpt, max_splits=max_splits)
+                         tokens_per_tile=tpt, max_splits=max_splits, est_us=est_us)

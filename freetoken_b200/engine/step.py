@@ -21,7 +21,7 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from .attention_plan import AttentionPlan, build_plan, wave_splits
+from .attention_plan import TC_ONE_TILE_COSTS, TC_TWO_TILE_COSTS, AttentionPlan, build_plan, wave_splits
 
 ALIGN = 4  # int32 elements = 16 bytes
 
@@ -96,6 +96,7 @@ class StepBuilder:
         self.sections: List[Tuple[str, np.ndarray]] = []
         self.decode_only = all(q == 1 for q, _ in self.seg_lens)
         self.plans: Dict[Any, AttentionPlan] = {}
+        self._drafts: Dict[Any, AttentionPlan] = {}  # work lists made to compare kernel forms, not (yet) part of the step
         self.plan_dims: Dict[Any, Tuple[int, int, int]] = {}
 
     def add(self, name: str, arr: np.ndarray) -> None:
@@ -119,16 +120,37 @@ class StepBuilder:
         """``few_rows``: the work list is for the tcgen05 kernel in its form for tiles of at most 16 rows (key tiles of 128)."""
         key = ("attention", group, tile_rows, window, n_kv_heads, head_dim, few_rows)
         if key not in self.plans:
-            tensor_core = tile_rows >= 128 or few_rows
-            per_sm = 1 if tensor_core else 2  # the tcgen05 kernels fill an SM with one CTA
-            plan = build_plan(self.seg_lens, group, tile_rows, window, n_kv_heads,
-                              sm_count=self.sm_count if per_sm == 2 else max(1, self.sm_count // 2),
-                              fixed_splits=self.fixed_splits(n_kv_heads, per_sm) if self.fixed else None,
-                              key_tile=128 if tensor_core else 0)
+            plan = self._drafts.pop(key, None) or self._draft(group, tile_rows, window, n_kv_heads, few_rows)
             self.plans[key] = plan
             self.plan_dims[key] = (n_kv_heads, tile_rows, head_dim)
             self.add(f"plan.{len(self.plans) - 1}", plan.items)
         return key
+
+    def _draft(self, group: int, tile_rows: int, window: Optional[int], n_kv_heads: int, few_rows: bool) -> AttentionPlan:
+        tensor_core = tile_rows >= 128 or few_rows
+        per_sm = 1 if tensor_core else 2  # the tcgen05 kernels fill an SM with one CTA
+        costs = None
+        if tile_rows >= 128 and not self.fixed:  # what a piece costs these kernels: for the cuts and for est_us
+            costs = TC_TWO_TILE_COSTS if tile_rows == 256 else TC_ONE_TILE_COSTS
+        return build_plan(self.seg_lens, group, tile_rows, window, n_kv_heads,
+                          sm_count=self.sm_count if per_sm == 2 else max(1, self.sm_count // 2),
+                          fixed_splits=self.fixed_splits(n_kv_heads, per_sm) if self.fixed else None,
+                          key_tile=128 if tensor_core else 0, costs=costs)
+
+    def cheaper_attention_rows(self, group: int, window: Optional[int], n_kv_heads: int, head_dim: int) -> int:
+        """128 or 256: the tcgen05 attention kernel (one or two query tiles a piece) whose work list for this step
+        is estimated to end sooner; the two-tile form has to be ahead by 3 %.  The list of the form chosen is
+        kept for :meth:`attention_plan`."""
+        est = {}
+        for rows in (128, 256):
+            key = ("attention", group, rows, window, n_kv_heads, head_dim, False)
+            plan = self.plans.get(key) or self._drafts.get(key)
+            if plan is None:
+                plan = self._drafts[key] = self._draft(group, rows, window, n_kv_heads, False)
+            est[rows] = plan.est_us
+        if est[128] is None or est[256] is None:
+            return 128
+        return 256 if est[256] < 0.97 * est[128] else 128
 
     def sparse_attention_plan(self, group: int, tile_rows: int, n_kv_heads: int, head_dim: int,
                               block_size: int, topk: int) -> Any:

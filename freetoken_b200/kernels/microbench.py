@@ -24,7 +24,7 @@ import sys
 
 import torch
 
-from ..engine.attention_plan import build_plan, wave_splits
+from ..engine.attention_plan import TC_ONE_TILE_COSTS, TC_TWO_TILE_COSTS, build_plan, wave_splits
 from . import ops
 
 HBM_GBS = 6650.0  # used when no measured peaks are on file
@@ -141,8 +141,11 @@ def bench_attention(a) -> dict:
         fixed = wave_splits(len(segs) * Hkv, 148 if tc else 2 * 148, 16, a.context) if a.splits is None else a.splits
         tile = 16 if few_rows else 128 if tc else (16 if G <= 16 else 64)
     tensor_core = few_rows or tile >= 128  # (one CTA per SM: the engine plans these for half as many CTA slots)
+    costs = None
+    if tile >= 128 and fixed is None:  # as the engine plans these kernels' work lists
+        costs = TC_TWO_TILE_COSTS if tile == 256 else TC_ONE_TILE_COSTS
     plan = build_plan(segs, G, tile, None, Hkv, sm_count=74 if tensor_core else 148, fixed_splits=fixed,
-                      key_tile=128 if tensor_core else 0)
+                      key_tile=128 if tensor_core else 0, costs=costs)
     items = torch.from_numpy(plan.items).to(dev)
     po = pm = None
     if plan.n_slots:
@@ -153,7 +156,8 @@ def bench_attention(a) -> dict:
                                            D ** -0.5, None, few_rows=few_rows), a.iters, a.warmup, a.profile)
     kv_bytes = sum(kv for _, kv in segs) * Hkv * D * 2 * 2
     flops = sum(4 * (ql * kv - ql * (ql - 1) // 2) * Hq * D for ql, kv in segs)
-    return {"us": round(us, 2), "items": plan.n_items, "kv_bytes": kv_bytes, "gbs": round(kv_bytes / us / 1e3, 1),
+    return {"us": round(us, 2), "items": plan.n_items, "est_us": None if plan.est_us is None else round(plan.est_us, 1),
+            "kv_bytes": kv_bytes, "gbs": round(kv_bytes / us / 1e3, 1),
             "hbm_frac": round(kv_bytes / us / 1e3 / HBM_GBS, 3), "tflops": round(flops / us / 1e6, 1),
             "tensor_frac": round(flops / us / 1e6 / BF16_TFLOPS, 3)}
 

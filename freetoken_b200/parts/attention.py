@@ -147,6 +147,10 @@ class GQAttention(Mixer):
         page_size = builder.engine.config.page_size if builder.engine is not None else 0
         # forward() of the same step runs the kernel this work list was made for
         rows, few_rows = self.kernel_form(builder.decode_only, n_tokens, page_size, builder.longest_span())
+        if rows >= 128 and not few_rows and not builder.decode_only and n_tokens >= TC_PAIR_MIN_TOKENS_LONG \
+                and hasattr(builder, "cheaper_attention_rows"):
+            # one or two query tiles a piece: whichever work list the kernel is estimated to get through sooner
+            rows = builder.cheaper_attention_rows(self.group, self.window, self.n_kv_heads, self.head_dim)
         self._step_plan = builder.attention_plan(self.group, rows, self.window, self.n_kv_heads, self.head_dim,
                                                  few_rows)
 

@@ -157,6 +157,31 @@ def test_lists_of_a_few_pieces_per_cta_are_cut_so_that_the_dealing_ends_soonest(
     assert fixed.n_items == 16
 
 
+def test_a_step_takes_the_tcgen05_attention_form_whose_work_list_ends_sooner():
+    """Long steps choose between one and two query tiles a piece by the estimated time of each form's work list
+    (the kernel's measured costs per piece, the dealing played through).  The cases are timings on a B200:
+    (tokens of the portion, tokens before it) -> microseconds with one tile a piece, with two."""
+    from freetoken_b200.engine.step import StepBuilder
+
+    measured = {(256, 0): (10.8, 14.0), (768, 0): (23.5, 24.7), (1024, 0): (34.2, 32.3), (4096, 0): (291.6, 243.9),
+                (256, 4096): (53.8, 62.6), (256, 65536): (538.8, 488.5), (512, 4096): (109.1, 91.7),
+                (512, 65024): (1050.8, 895.9), (768, 8192): (190.1, 264.2), (1024, 8192): (281.9, 297.7),
+                (1024, 32768): (1044.7, 938.5), (2048, 8192): (592.6, 503.5)}
+    for (tokens, past), (one, two) in measured.items():
+        builder = StepBuilder(None, [(tokens, past + tokens)], False, 148)
+        rows = builder.cheaper_attention_rows(6, None, 8, 128)
+        assert rows == (256 if two < one else 128), (tokens, past)
+        for form, us in ((128, one), (256, two)):
+            plan = builder._drafts[("attention", 6, form, None, 8, 128, False)]
+            assert abs(plan.est_us / us - 1) < 0.12, (tokens, past, form, plan.est_us, us)
+        # the list of the chosen form is the one the step then uses
+        key = builder.attention_plan(6, rows, None, 8, 128)
+        assert builder.plans[key].est_us is not None and len(builder.sections) == 1
+    # graph-replayed decode steps keep their fixed lists: no estimate, no choice
+    fixed = StepBuilder(None, [(1, 4096)] * 8, True, 148)
+    assert fixed.plans[fixed.attention_plan(6, 16, None, 8, 128, few_rows=True)].est_us is None
+
+
 def test_which_attention_kernel_a_step_gets():
     """The rows per CTA (and the few-rows flag) name the kernel: 16 float32 / small bfloat16 tiles, 64
     mma.sync, 128 tcgen05 with one query tile, 256 with two (steps of a thousand tokens and more), 16
