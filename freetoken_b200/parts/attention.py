@@ -38,7 +38,9 @@ def attention_kernel_form(dtype: torch.dtype, decode_only: bool = False, group: 
 
     16 rows in the 32-bit kernel.  bfloat16 steps whose sizes the tcgen05 kernels take: 128 rows for
     long steps (``TC_MIN_TOKENS`` tokens and more; 256, two such tiles per CTA, from
-    ``TC_PAIR_MIN_TOKENS`` tokens on, or from ``TC_PAIR_MIN_TOKENS_LONG`` for portions of long prompts);
+    ``TC_PAIR_MIN_TOKENS`` tokens on, or from ``TC_PAIR_MIN_TOKENS_LONG`` for portions of long prompts: the
+    rule for callers without a step's work lists; a step itself takes, from ``TC_PAIR_MIN_TOKENS_LONG`` tokens
+    on, the form whose work list is estimated to end sooner, see ``GQAttention.prepare``);
     decode steps go to the same kernel in its form for tiles of at
     most 16 rows, where one warp takes the softmax (groups of up to 16 heads; ``longest_span`` is the longest
     request's length rounded up to a power of two, from which on they go there:
