@@ -224,7 +224,7 @@ __global__ void __launch_bounds__(kF32Rows * 32) attention_f32_kernel(AttnParams
 // splits' values are fetched eight at a time, so a row costs a few memory round trips however many
 // splits there are.
 template <typename T>
-__global__ void attention_merge_kernel(AttnParams p) {
+__global__ void __launch_bounds__(512) attention_merge_kernel(AttnParams p) {
   const Item it = load_item(p, blockIdx.x);  // the work list was made on the host before the step
   pdl_wait();
   pdl_trigger();
@@ -239,6 +239,18 @@ __global__ void attention_merge_kernel(AttnParams p) {
   const int warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
   for (int r = it.split + warp * it.nsplit; r < R; r += it.nsplit * n_warps) {
     const size_t slot0 = ((size_t)it.base * p.Hkv + kvh) * p.tile_rows + r;
+    // the first eight splits' values of the row's first 128 columns: asked for together with the weights
+    // (they do not depend on them), so that a row is two trips to memory one after the other, not three.  A
+    // piece without keys has weight 0 and a slot that nobody wrote: its values are dropped below.
+    auto fetch = [&](int d, int i0, float4 (&x)[8]) {
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        x[u] = (i0 + u < it.nsplit && d < D)
+                   ? *reinterpret_cast<const float4*>(p.part_o + (slot0 + (i0 + u) * slot_step) * D + d)
+                   : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    float4 first[8];
+    fetch(4 * lane, 0, first);
     // weights of the splits, spread over the lanes
     float wgt[kMaxMergeSplits / 32];
     float lsum[kMaxMergeSplits / 32];
@@ -270,17 +282,18 @@ __global__ void attention_merge_kernel(AttnParams p) {
       for (int i0 = 0; i0 < it.nsplit; i0 += 8) {  // eight loads in flight before the first use
         float4 x[8];
         float w[8];
+        if (d0 == 0 && i0 == 0) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u) x[u] = first[u];
+        } else {
+          fetch(d, i0, x);
+        }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
           const int i = i0 + u;
           const float wsrc = (i >> 5) ? wgt[1] : wgt[0];
           w[u] = __shfl_sync(0xffffffffu, wsrc, i & 31);
-          x[u] = (i < it.nsplit && d < D && w[u] != 0.f)
-                     ? *reinterpret_cast<const float4*>(p.part_o + (slot0 + i * slot_step) * D + d)
-                     : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
+          if (w[u] == 0.f) x[u] = make_float4(0.f, 0.f, 0.f, 0.f);
           acc.x += x[u].x * w[u];
           acc.y += x[u].y * w[u];
           acc.z += x[u].z * w[u];
@@ -953,7 +966,7 @@ static int paged_attention_tc_impl(const void* q, const void* k_slab, const void
     dim3 grid(n_items, n_kv_heads);
     // a CTA merges its share of a tile's rows, a warp a row at a time (three trips to memory one after the
     // other): tiles of 128 and 256 rows get as many warps as a tile cut in two has rows per CTA / 4
-    const int threads = p.tile_rows >= 256 ? 768 : (p.tile_rows >= 128 ? 512 : 128);  // (71 registers a thread)
+    const int threads = p.tile_rows >= 128 ? 512 : 128;  // (96 registers a thread)
     FTK_LAUNCH(attention_merge_kernel<__nv_bfloat16>, grid, threads, 0, s, p);
     FTK_LAUNCH_CHECK("paged_attention_tc merge");
   }
