@@ -24,15 +24,22 @@
 // One CTA = 8 warps: warp 0 issues TMA loads, warp 1 allocates TMEM and issues tcgen05.mma, warps 2-5
 // read the accumulator (tcgen05.ld, one TMEM lane quadrant each), apply the epilogue and store, warps
 // 6-7 gather token rows (gemm1 from unsorted tokens only; otherwise they leave at once).
-//   gemm1 epilogue: gate and up are rounded to bfloat16 (where the reference stores them), the up
-//                   half reaches the gate half's lanes by a warp shuffle, act(g, u) is stored.
-//   gemm2 epilogue: accumulator x route weight (float32), stored as bfloat16.
-//   Both epilogues turn the (feature x token) accumulator chunk round in a warp-private piece of
-//   shared memory and store 16 bytes per thread.
+//   gemm1 epilogue: gate and up are rounded to bfloat16 (where the reference stores them), the two
+//                   half-warps swap what the other needs by a warp shuffle (one takes tokens 0-7 of a
+//                   chunk, the other tokens 8-15), act(g, u) is stored.
+//   gemm2 epilogue: accumulator x route weight (float32), stored as bfloat16; a tile's route weights
+//                   (token -> route -> weight, two loads one after the other) are fetched a tile ahead.
+//   Both epilogues read the accumulator 16 columns at a time, the next chunk's load under this chunk's
+//   arithmetic, turn the (feature x token) chunk round in a warp-private piece of shared memory and
+//   store 16 bytes per thread.
 // CTAs are persistent: tile t -> (expert, token tile, feature tile) is derived from the device-side
 // expert offsets, so ragged row counts need no padding and no host round trip.
 //
-// No cluster launch and no multicast: every CTA loads its own tiles.  Every wait on an mbarrier is
+// Token tiles of 128 and 256 rows with many tiles (long steps) run on PAIRS of CTAs, clusters of two
+// (template argument PAIR, see Smem): one tile of 256 weight rows per pair, tcgen05.mma.cta_group::2 issued
+// by the leading CTA, each CTA loading its own weight rows and half of the tokens; the partner's TMA loads
+// are counted at the leading CTA's barrier, tcgen05.commit with cluster multicast arrives at both CTAs'
+// barriers.  No TMA load is multicast: every CTA loads its own tiles.  Every wait on an mbarrier is
 // bounded; on a timeout the CTA records a status code, lets copies in flight land, frees its TMEM and
 // returns, and the host reports the code (ftk_read_status).
 //
