@@ -3,9 +3,10 @@ splits, long tiles beside many short ones are cut, even steps are not."""
 
 import numpy as np
 import pytest
+from hypothesis import given, settings, strategies as st
 
-from freetoken_b200.engine.attention_plan import (DEAL_MOST_PIECES, FIXED_COST_KEYS, SPLIT_QUANTUM, build_plan,
-                                                  dealt_makespan, wave_splits)
+from freetoken_b200.engine.attention_plan import (DEAL_MOST_PIECES, FIXED_COST_KEYS, SPLIT_QUANTUM, TC_ONE_TILE_COSTS,
+                                                  TC_TWO_TILE_COSTS, build_plan, dealt_makespan, wave_splits)
 
 
 def ranges_by_tile(plan):
@@ -38,6 +39,54 @@ def test_splits_cover_each_tile_once(segs, group, tile, window):
         if len(parts) > 1:
             slots += list(range(parts[0][4], parts[0][4] + len(parts)))
     assert sorted(slots) == list(range(plan.n_slots)), "partial slots are used once each"
+
+
+SEGMENT = st.tuples(st.sampled_from([1, 1, 1, 2, 5, 17, 64, 300, 512, 1300, 2048]),
+                    st.sampled_from([0, 0, 3, 64, 500, 3000, 20000, 70000])).map(lambda qp: (qp[0], qp[0] + qp[1]))
+
+
+@settings(max_examples=150, deadline=None)
+@given(segs=st.lists(SEGMENT, min_size=1, max_size=12), group=st.sampled_from([1, 3, 6, 8]),
+       tile=st.sampled_from([16, 64, 128, 256]), window=st.sampled_from([None, None, 32, 500]),
+       n_kv=st.sampled_from([1, 2, 8]), sm=st.sampled_from([74, 148]), fixed=st.sampled_from([None, None, 1, 2, 5]),
+       key_tile=st.sampled_from([None, 0, 128]), priced=st.booleans())
+def test_any_step_is_covered_once_by_its_work_list(segs, group, tile, window, n_kv, sm, fixed, key_tile, priced):
+    """Whatever the step, the kernel form, the window and the way the pieces are chosen (fixed counts for graph
+    replay, the wave rule, the dealing search with or without the kernels' costs): every tile of whole tokens is
+    there once, its pieces follow each other from its first visible key to its last without a gap, cuts lie on
+    the kernel's quantum, every cut tile has partial slots of its own, and a list for the kernels that deal it
+    out themselves is sorted by length."""
+    if tile < group:
+        tile = 64 if group > 16 else 16
+    costs = (TC_TWO_TILE_COSTS if tile == 256 else TC_ONE_TILE_COSTS) if (priced and tile >= 128) else None
+    plan = build_plan(segs, group, tile, window, n_kv, sm_count=sm, fixed_splits=fixed, key_tile=key_tile, costs=costs)
+    quantum = 128 if (key_tile == 128 or (key_tile is None and tile >= 128)) else SPLIT_QUANTUM
+    tpt = 2 * max(1, 128 // group) if tile == 256 else max(1, tile // group)
+    want_tiles = {(s, t0, min(tpt, q - t0)) for s, (q, _) in enumerate(segs) for t0 in range(0, q, tpt)}
+    by_tile = ranges_by_tile(plan)
+    assert set(by_tile) == want_tiles
+    used_slots = []
+    for (seg, tok0, ntok), parts in by_tile.items():
+        q_len, kv_len = segs[seg]
+        pos0 = kv_len - q_len
+        hi = pos0 + tok0 + ntok
+        lo = max(0, pos0 + tok0 - window + 1) if window else 0
+        parts.sort()
+        assert [p[0] for p in parts] == list(range(len(parts))) and all(p[3] == len(parts) for p in parts)
+        assert parts[0][1] == lo and parts[-1][2] == hi
+        for (_, kb, ke, _, _), (_, kb2, _, _, _) in zip(parts, parts[1:]):
+            assert kb <= ke == kb2 and ((ke - lo) % quantum == 0 or ke == hi)
+        if len(parts) > 1:
+            assert len({p[4] for p in parts}) == 1
+            used_slots += list(range(parts[0][4], parts[0][4] + len(parts)))
+    assert len(set(used_slots)) == len(used_slots) and all(0 <= x < plan.n_slots for x in used_slots)
+    if quantum == 128:
+        lengths = (plan.items[:, 4] - plan.items[:, 3]).tolist()
+        assert lengths == sorted(lengths)
+    if fixed is not None and fixed > 1:
+        assert plan.n_items == fixed * len(want_tiles) and plan.n_slots == plan.n_items  # what a graph was recorded with
+    if costs is not None and fixed is None:
+        assert plan.est_us is None or plan.est_us > 0
 
 
 def test_a_long_portion_beside_many_single_tokens_is_cut():
